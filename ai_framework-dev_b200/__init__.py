@@ -1,0 +1,13 @@
+"""B200-native dense-layer path: fused GEMM + bias + activation forward, its backward and the
+strided-batched form, behind the reference's operator interface.
+
+`ops_gemm` mirrors graph_executor_v2/python/graph_executor_v2/ops/gemm.py (forward, backward, forward_into,
+backward_into) and `Dense` mirrors layers/dense_gemm.py; both call the CUDA library through its C ABI.
+There is no CPU fallback: importing works anywhere, computing needs the built library and a CUDA device.
+"""
+from . import _lib  # noqa: F401
+from . import ops_gemm  # noqa: F401
+from .dense import Dense  # noqa: F401
+from ._lib import load_library, library_path  # noqa: F401
+
+__all__ = ["ops_gemm", "Dense", "load_library", "library_path"]

@@ -1,0 +1,111 @@
+"""ctypes binding of libge2_b200.so (declarations follow include/ge2_b200.h)."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+_LIB = None
+
+
+def library_path() -> Path:
+    return _PKG / "lib" / "libge2_b200.so"
+
+
+class ParamsLegacy(C.Structure):
+    _fields_ = [("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("has_bias", C.c_int), ("act", C.c_int)]
+
+
+class ParamsEx(C.Structure):
+    _fields_ = [("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
+                ("lda", C.c_int), ("ldb", C.c_int), ("ldc", C.c_int), ("ldd", C.c_int),
+                ("alpha", C.c_float), ("beta", C.c_float),
+                ("use_C", C.c_int), ("has_bias", C.c_int),
+                ("bias_kind", C.c_int), ("act_kind", C.c_int),
+                ("leaky_slope", C.c_float),
+                ("save_preact", C.c_int), ("ldZ", C.c_int)]
+
+
+class ParamsBwd(C.Structure):
+    _fields_ = [("M", C.c_int), ("N", C.c_int), ("K", C.c_int),
+                ("lda", C.c_int), ("ldb", C.c_int), ("ldc", C.c_int),
+                ("ldgY", C.c_int), ("ldZ", C.c_int),
+                ("ldgA", C.c_int), ("ldgB", C.c_int), ("ldgC", C.c_int),
+                ("alpha", C.c_float), ("beta", C.c_float),
+                ("bias_kind", C.c_int), ("act_kind", C.c_int),
+                ("leaky_slope", C.c_float)]
+
+
+class ParamsTyped(C.Structure):
+    _fields_ = [("base", ParamsEx),
+                ("dtype", C.c_int), ("z_dtype", C.c_int), ("math", C.c_int),
+                ("trans_b", C.c_int), ("batch", C.c_int),
+                ("strideA", C.c_longlong), ("strideB", C.c_longlong), ("strideC", C.c_longlong),
+                ("strideD", C.c_longlong), ("strideZ", C.c_longlong)]
+
+
+class ParamsBwdTyped(C.Structure):
+    _fields_ = [("base", ParamsBwd),
+                ("dtype", C.c_int), ("z_dtype", C.c_int), ("math", C.c_int),
+                ("scratch_bytes", C.c_size_t)]
+
+
+# numbering of the C ABI
+BIAS_SCALAR, BIAS_PER_M, BIAS_PER_N = 0, 1, 2
+ACT = {"none": 0, "relu": 1, "leaky_relu": 2, "leakyrelu": 2, "lrelu": 2, "gelu": 3, "sigmoid": 4, "tanh": 5}
+DT_F32, DT_F16, DT_BF16 = 0, 1, 2
+MATH_FP32, MATH_TENSOR = 0, 1
+
+# every symbol include/ge2_b200.h declares
+EXPORTS = [
+    "ge2_launch", "ge2_launch_gemm_bias_act_f32", "ge2_launch_gemm_bias_act_tc_f16",
+    "ge2_launch_gemm_bias_act_f32_ex", "ge2_launch_gemm_bias_act_bwd_f32_ex",
+    "ge2_launch_gemm_bias_act_typed", "ge2_launch_gemm_bias_act_bwd_typed",
+    "ge2b_backward_scratch_bytes", "ge2b_device_status", "ge2b_sm_count", "ge2b_version",
+    "ge2b_last_route", "ge2b_launches_total",
+]
+
+
+def load_library() -> C.CDLL:
+    """Loads the CUDA launch layer.  Raises if it has not been built: there is nothing to fall back to."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = library_path()
+    if not path.exists():
+        raise RuntimeError(
+            f"{path} is missing: build it with `python __graft_entry__.py` (nvcc, sm_100a). "
+            "This package has no CPU or eager fallback.")
+    lib = C.CDLL(str(path))
+    launch_sig = [C.POINTER(C.c_size_t), C.c_int, C.c_void_p]
+    for name in ("ge2_launch_gemm_bias_act_f32", "ge2_launch_gemm_bias_act_tc_f16",
+                 "ge2_launch_gemm_bias_act_f32_ex", "ge2_launch_gemm_bias_act_bwd_f32_ex",
+                 "ge2_launch_gemm_bias_act_typed", "ge2_launch_gemm_bias_act_bwd_typed"):
+        fn = getattr(lib, name)
+        fn.argtypes = launch_sig
+        fn.restype = C.c_int
+    lib.ge2_launch.argtypes = [C.c_char_p] + launch_sig
+    lib.ge2_launch.restype = C.c_int
+    lib.ge2b_backward_scratch_bytes.argtypes = [C.c_longlong, C.c_longlong]
+    lib.ge2b_backward_scratch_bytes.restype = C.c_size_t
+    lib.ge2b_device_status.argtypes = [C.c_int]
+    lib.ge2b_device_status.restype = C.c_int
+    lib.ge2b_sm_count.restype = C.c_int
+    lib.ge2b_version.restype = C.c_char_p
+    lib.ge2b_last_route.restype = C.c_int
+    lib.ge2b_launches_total.restype = C.c_longlong
+    _LIB = lib
+    return lib
+
+
+def make_bufs(ptrs, params) -> "C.Array":
+    """bufs[] of the C ABI: device pointers as uintptr_t, then the HOST address of the parameter struct."""
+    vals = [int(p) for p in ptrs] + [C.addressof(params)]
+    return (C.c_size_t * len(vals))(*vals)
+
+
+def check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    msg = {-1: "bad arguments", -2: "CUDA error", -99: "not implemented"}.get(rc, "error")
+    raise RuntimeError(f"[ge2_b200::{what}] {msg} (code {rc})")

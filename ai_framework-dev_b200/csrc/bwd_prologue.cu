@@ -1,0 +1,180 @@
+// Backward prologue of the dense layer:  gZ = gY * act'(Z), optional gC = beta * gZ, and the bias
+// gradient as a reduction of gZ over rows (per-column bias), over columns (per-row bias) or over
+// everything (scalar bias).
+//
+// Replaces the reference's bwd_epilogue_kernel (backends/cuda/ops/gemm/kernels/regemm_backward.cu:92-130),
+// which issues one atomicAdd per element for the bias gradient.  Here each thread owns 8 consecutive
+// columns (one or two 16-byte accesses), a CTA covers 256 columns x 64 rows, sums in registers and shared
+// memory, and issues one fp32 atomic per column (or row) per CTA.  The bias gradient is always formed
+// from the fp32 value of gZ, before gZ is rounded to its storage type.  The buffer gZ is scratch memory
+// that the two backward GEMMs read afterwards.
+#include <cuda_runtime.h>
+
+#include "epilogue_math.cuh"
+#include "ge2_internal.hpp"
+
+namespace ge2b {
+namespace {
+
+constexpr int kColsPerThread = 8;
+constexpr int kTX = 32, kTY = 8;
+constexpr int kTileCols = kTX * kColsPerThread;   // 256
+constexpr int kTileRows = 64;
+
+struct ProParams {
+  BwdPrologueArgs a;
+  int gy_vec, z_vec, gz_vec, gc_vec;
+};
+
+__device__ __forceinline__ void load8(const void* base, long long off, int dt, bool vec, int n, float (&v)[8]) {
+  if (vec && n == 8) {
+    if (dt == kF32) {
+      const float4 x = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off);
+      const float4 y = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + off + 4);
+      v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w; v[4] = y.x; v[5] = y.y; v[6] = y.z; v[7] = y.w;
+    } else {
+      const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(base) + off);
+      const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        if (dt == kBF16) {
+          v[2 * t]     = __uint_as_float(w[t] << 16);
+          v[2 * t + 1] = __uint_as_float(w[t] & 0xffff0000u);
+        } else {
+          const __half2 h = *reinterpret_cast<const __half2*>(&w[t]);
+          v[2 * t] = __low2float(h); v[2 * t + 1] = __high2float(h);
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = (j < n) ? load_as_f32(base, off + j, dt) : 0.f;
+  }
+}
+
+__device__ __forceinline__ void store8(void* base, long long off, int dt, bool vec, int n, const float (&v)[8]) {
+  if (vec && n == 8) {
+    if (dt == kF32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + off)     = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + off + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+      unsigned w[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        if (dt == kBF16) {
+          w[t] = static_cast<unsigned>(f32_to_bf16_bits(v[2 * t])) | (static_cast<unsigned>(f32_to_bf16_bits(v[2 * t + 1])) << 16);
+        } else {
+          const __half2 h = __floats2half2_rn(v[2 * t], v[2 * t + 1]);
+          w[t] = *reinterpret_cast<const unsigned*>(&h);
+        }
+      }
+      *reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(base) + off) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (j < n) store_from_f32(base, off + j, dt, v[j]);
+  }
+}
+
+template <int ACT>
+__global__ void __launch_bounds__(kTX * kTY)
+bwd_prologue_kernel(const ProParams pp) {
+  const BwdPrologueArgs& a = pp.a;
+  __shared__ float red[kTY][kTileCols + 1];
+
+  const int col0 = blockIdx.x * kTileCols + threadIdx.x * kColsPerThread;
+  const int row_base = blockIdx.y * kTileRows;
+  const int ncols = min(kColsPerThread, a.N - col0);   // <= 0 when this thread is past the edge
+  const bool want_bias = a.gBias != nullptr && a.bias_kind != kBiasNone;
+
+  float colsum[kColsPerThread];
+#pragma unroll
+  for (int j = 0; j < kColsPerThread; ++j) colsum[j] = 0.f;
+  float total = 0.f;
+
+  for (int r = threadIdx.y; r < kTileRows; r += kTY) {
+    const int m = row_base + r;
+    float rowsum = 0.f;
+    if (m < a.M && ncols > 0) {
+      float gy[8], z[8], gz[8];
+      load8(a.gY, static_cast<long long>(m) * a.ldgY + col0, a.gy_dtype, pp.gy_vec != 0, ncols, gy);
+      load8(a.Z, static_cast<long long>(m) * a.ldZ + col0, a.z_dtype, pp.z_vec != 0, ncols, z);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        gz[j] = (j < ncols) ? gy[j] * act_bwd<ACT>(z[j], a.leaky) : 0.f;
+        colsum[j] += gz[j];
+        rowsum += gz[j];
+      }
+      store8(a.gZ, static_cast<long long>(m) * a.ldgZ + col0, a.gz_dtype, pp.gz_vec != 0, ncols, gz);
+      if (a.gC != nullptr) {
+        float gc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) gc[j] = a.beta * gz[j];
+        store8(a.gC, static_cast<long long>(m) * a.ldgC + col0, a.gc_dtype, pp.gc_vec != 0, ncols, gc);
+      }
+    }
+    if (want_bias && a.bias_kind == kBiasPerM) {
+      // all 32 lanes of a warp share the row: one atomic per (row, CTA)
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) rowsum += __shfl_xor_sync(0xffffffffu, rowsum, o);
+      if (threadIdx.x == 0 && m < a.M) atomicAdd(a.gBias + m, rowsum);
+    }
+    total += rowsum;
+  }
+
+  if (!want_bias || a.bias_kind == kBiasPerM) return;
+
+  if (a.bias_kind == kBiasPerN) {
+#pragma unroll
+    for (int j = 0; j < kColsPerThread; ++j) red[threadIdx.y][threadIdx.x * kColsPerThread + j] = colsum[j];
+    __syncthreads();
+    const int c = threadIdx.y * kTX + threadIdx.x;     // 0..255: one column each
+    float s = 0.f;
+#pragma unroll
+    for (int y = 0; y < kTY; ++y) s += red[y][c];
+    const int gc = blockIdx.x * kTileCols + c;
+    if (gc < a.N) atomicAdd(a.gBias + gc, s);
+  } else {  // scalar: everything
+    // `total` here is the per-lane partial (rowsum before the per-row shuffle is only taken for PerM)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    if (threadIdx.x == 0) red[threadIdx.y][0] = total;
+    __syncthreads();
+    if (threadIdx.x == 0 && threadIdx.y == 0) {
+      float s = 0.f;
+#pragma unroll
+      for (int y = 0; y < kTY; ++y) s += red[y][0];
+      atomicAdd(a.gBias, s);
+    }
+  }
+}
+
+bool vec_ok(const void* p, long long ld, int dt) {
+  if (!p) return false;
+  return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && (ld * dtype_bytes(dt)) % 16 == 0;
+}
+
+}  // namespace
+
+cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s) {
+  if (a.M < 1 || a.N < 1 || !a.gY || !a.Z || !a.gZ) return cudaErrorInvalidValue;
+  ProParams pp{};
+  pp.a = a;
+  pp.gy_vec = vec_ok(a.gY, a.ldgY, a.gy_dtype);
+  pp.z_vec  = vec_ok(a.Z, a.ldZ, a.z_dtype);
+  pp.gz_vec = vec_ok(a.gZ, a.ldgZ, a.gz_dtype);
+  pp.gc_vec = vec_ok(a.gC, a.ldgC, a.gc_dtype);
+  dim3 block(kTX, kTY), grid((a.N + kTileCols - 1) / kTileCols, (a.M + kTileRows - 1) / kTileRows);
+  switch (a.act) {
+    case kActReLU:    bwd_prologue_kernel<kActReLU><<<grid, block, 0, s>>>(pp); break;
+    case kActLeaky:   bwd_prologue_kernel<kActLeaky><<<grid, block, 0, s>>>(pp); break;
+    case kActGELU:    bwd_prologue_kernel<kActGELU><<<grid, block, 0, s>>>(pp); break;
+    case kActSigmoid: bwd_prologue_kernel<kActSigmoid><<<grid, block, 0, s>>>(pp); break;
+    case kActTanh:    bwd_prologue_kernel<kActTanh><<<grid, block, 0, s>>>(pp); break;
+    default:          bwd_prologue_kernel<kActNone><<<grid, block, 0, s>>>(pp); break;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace ge2b

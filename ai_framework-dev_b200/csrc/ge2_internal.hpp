@@ -1,0 +1,79 @@
+// Internal parameter blocks shared by the host launch layer and the CUDA kernels of the
+// dense-layer path  D = act(alpha * A.B + beta * C + bias)  and its backward.
+//
+// Numbering of ActKind / BiasKind / DType follows the reference's ABI-anchored enums
+// (backends/cuda/ops/_common/shim/enums.hpp:10-24, ai_device.hpp:14-16) so that values
+// can be passed through unchanged from the operator API.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+namespace ge2b {
+
+enum : int { kActNone = 0, kActReLU = 1, kActLeaky = 2, kActGELU = 3, kActSigmoid = 4, kActTanh = 5 };
+enum : int { kBiasNone = 0, kBiasScalar = 1, kBiasPerM = 2, kBiasPerN = 3 };
+enum : int { kF32 = 0, kF16 = 1, kBF16 = 2 };
+
+// Error bits written by device code into the per-device status word (never cleared by kernels).
+enum : int {
+  kErrWaitTimeout = 1,   // a bounded mbarrier wait ran out
+  kErrAborted     = 2    // a role left its loop because another role timed out
+};
+
+__host__ __device__ inline int dtype_bytes(int dt) { return dt == kF32 ? 4 : 2; }
+
+// Everything the fused epilogue needs.  Pointers may be null where stated.
+struct EpilogueArgs {
+  void*        D;    long long ldd, strideD;      // output, row-major [M,N] per batch slice
+  void*        Z;    long long ldz, strideZ;      // pre-activation stash (null = not saved)
+  const void*  C;    long long ldc, strideC;      // addend scaled by beta (null = none)
+  const float* bias;                              // always fp32 (null = none)
+  int   bias_kind;                                // kBias*
+  int   act;                                      // kAct*
+  float leaky;
+  float alpha, beta;
+  int   d_dtype;                                  // dtype of D and C
+  int   z_dtype;                                  // dtype of Z
+};
+
+// One (optionally strided-batched) GEMM  D[b] = epi(A[b] (M x K) . B[b] (K x N)).
+//   a_mn == false : A is stored with the reduction index contiguous  (memory rows = M,  row length K)
+//   a_mn == true  : A is stored with the M index contiguous          (memory rows = K,  row length M)
+//   b_mn == false : B is stored with the reduction index contiguous  (memory rows = N,  row length K)
+//   b_mn == true  : B is stored with the N index contiguous          (memory rows = K,  row length N)
+// Strides are in elements; a batch stride of 0 broadcasts the operand to every slice.
+struct GemmProblem {
+  int M, N, K, batch;
+  int in_dtype;                                   // kBF16 / kF16 / kF32
+  int math;                                       // for kF32: 0 = exact fp32 FMA, 1 = TF32 tensor cores
+  bool a_mn, b_mn;
+  const void* A; long long lda, strideA;
+  const void* B; long long ldb, strideB;
+  EpilogueArgs epi;
+};
+
+// gZ = gY * act'(Z) with the column/row/total reduction into gBias.
+struct BwdPrologueArgs {
+  int M, N;
+  const void* gY; long long ldgY; int gy_dtype;
+  const void* Z;  long long ldZ;  int z_dtype;
+  void* gZ; long long ldgZ; int gz_dtype;         // scratch that the two backward GEMMs read
+  void* gC; long long ldgC; int gc_dtype; float beta;   // optional gC = beta * gZ
+  float* gBias; int bias_kind;                    // fp32, zeroed by the launcher before the kernel
+  int act; float leaky;
+};
+
+// ---- launchers (each returns cudaSuccess or the launch error) ----
+cudaError_t launch_gemm_simt(const GemmProblem& g, cudaStream_t s);      // exact fp32-accumulate FMA path (any dtype, any ld)
+bool        gemm_tc_supported(const GemmProblem& g, const char** why);   // alignment / dtype rules of the TMA + tcgen05 path
+cudaError_t launch_gemm_tc(const GemmProblem& g, cudaStream_t s);        // TMA + tcgen05 + TMEM path
+cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s);
+
+// Reads (and optionally clears) the device status word of the current device. Synchronises.
+int  device_status_word(bool clear);
+int* device_status_ptr();   // device address of the status word for the current device
+
+int  sm_count();            // cached multiprocessor count of the current device
+
+}  // namespace ge2b

@@ -1,0 +1,513 @@
+// Tensor-core GEMM with fused epilogue for sm_100a:  D[b] = act(alpha * A[b].B[b] + beta * C[b] + bias).
+//
+// This is the B200 replacement for the reference's fp32 SIMT forward kernel
+// (backends/cuda/ops/gemm/kernels/regemm_gemm_bias_act.cu:254-395) and for the two cublasSgemm
+// calls of its backward (regemm_backward.cu:265-291).  One persistent CTA per SM, 192 threads:
+//   warp 0      TMA producer: 128-byte-swizzled operand tiles into a shared-memory ring
+//   warp 1      MMA issuer:   tcgen05.mma (kind::f16 for bf16/f16, kind::tf32 for fp32) into TMEM;
+//               also owns TMEM allocation
+//   warps 2..5  epilogue:     tcgen05.ld of the finished accumulator, alpha/beta.C/bias/activation,
+//               optional pre-activation stash, one store of D
+// The accumulator is double-buffered in TMEM (2 x BLOCK_N columns) so the epilogue of tile i overlaps
+// the main loop of tile i+1.  Operands may be stored with either the reduction index or the M/N index
+// contiguous, which lets forward (X.W), dX (gZ.W^T) and dW (X^T.gZ) all read the caller's row-major
+// tensors directly, and a third tensor-map dimension carries the batch of the strided-batched form.
+// No TMA load uses cluster multicast.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <mutex>
+
+#include "epilogue_math.cuh"
+#include "ge2_internal.hpp"
+#include "sm100_ptx.cuh"
+
+namespace ge2b {
+namespace {
+
+constexpr int kBlockM        = 128;   // UMMA M (one TMEM lane per output row)
+constexpr int kNumThreads    = 192;
+constexpr int kEpilogueWarp0 = 2;
+constexpr int kGroupM        = 8;     // tile rasterisation: groups of 8 row-blocks sweep the columns
+
+struct TcParams {
+  int M, N, K, batch;
+  int m_blocks, n_blocks, k_blocks;
+  int a_bcast, b_bcast;     // operand has batch stride 0: always read slice 0
+  uint32_t idesc;
+  EpilogueArgs epi;
+  int d_vec, z_vec, c_vec, bias_vec;   // 16-byte vector access allowed for that tensor
+  int* status;
+};
+
+template <int kElemBytes, int kBlockN, int kStages>
+struct TcCfg {
+  static constexpr int kBlockK     = 128 / kElemBytes;    // one 128-byte swizzle row of the reduction index
+  static constexpr int kUmmaK      = 32 / kElemBytes;     // reduction depth of one tcgen05.mma
+  static constexpr int kAStage     = kBlockM * 128;
+  static constexpr int kBStage     = kBlockN * 128;
+  static constexpr int kStageBytes = kAStage + kBStage;
+  static constexpr int kTmemCols   = 2 * kBlockN;
+  static constexpr int kBarBytes   = 256;
+  static constexpr int kSmemBytes  = kStages * kStageBytes + kBarBytes + 1024;   // +1024: manual alignment
+  static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
+};
+
+// ---- row-fragment stores: one thread owns `n` (<= 32) consecutive columns of one output row ----
+__device__ __forceinline__ void store_row_frag(void* base, long long off, int dt, const float (&v)[32], int n,
+                                               bool vec) {
+  if (dt == kF32) {
+    float* p = reinterpret_cast<float*>(base) + off;
+    if (vec && n == 32) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        reinterpret_cast<float4*>(p)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < n) p[j] = v[j];
+    }
+  } else {
+    unsigned short* p = reinterpret_cast<unsigned short*>(base) + off;
+    if (vec && n == 32) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float lo = v[8 * j + 2 * t], hi = v[8 * j + 2 * t + 1];
+          if (dt == kBF16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+            w[t] = *reinterpret_cast<uint32_t*>(&h);
+          } else {
+            __half2 h = __floats2half2_rn(lo, hi);
+            w[t] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        reinterpret_cast<uint4*>(p)[j] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < n) {
+          if (dt == kBF16) p[j] = f32_to_bf16_bits(v[j]);
+          else             reinterpret_cast<__half*>(p)[j] = __float2half_rn(v[j]);
+        }
+    }
+  }
+}
+
+__device__ __forceinline__ void load_row_frag(const void* base, long long off, int dt, float (&v)[32], int n,
+                                              bool vec) {
+  if (dt == kF32) {
+    const float* p = reinterpret_cast<const float*>(base) + off;
+    if (vec && n == 32) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 f = reinterpret_cast<const float4*>(p)[j];
+        v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = (j < n) ? p[j] : 0.f;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = (j < n) ? load_as_f32(base, off + j, dt) : 0.f;
+  }
+}
+
+template <int ACT>
+__device__ __forceinline__ void apply_act32(float (&v)[32], float leaky) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = act_fwd<ACT>(v[j], leaky);
+}
+
+// Epilogue math for one 32-column fragment of one row (order of operations follows the reference's
+// Epilogue::apply, backends/cuda/ops/_common/shim/traits.hpp:30-73): alpha, + beta*C, + bias, stash Z, act.
+__device__ __forceinline__ void epilogue_frag(const TcParams& p, float (&v)[32], int b, int row, int col0, int ncols,
+                                              bool row_ok) {
+  const EpilogueArgs& e = p.epi;
+  if (e.alpha != 1.f) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= e.alpha;
+  }
+  if (e.C != nullptr && e.beta != 0.f && row_ok) {
+    float c[32];
+    load_row_frag(e.C, static_cast<long long>(b) * e.strideC + static_cast<long long>(row) * e.ldc + col0, e.d_dtype,
+                  c, ncols, p.c_vec != 0);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = fmaf(e.beta, c[j], v[j]);
+  }
+  if (e.bias != nullptr) {
+    if (e.bias_kind == kBiasPerN) {
+      if (p.bias_vec && ncols == 32) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float4 f = __ldg(reinterpret_cast<const float4*>(e.bias + col0) + j);
+          v[4 * j] += f.x; v[4 * j + 1] += f.y; v[4 * j + 2] += f.z; v[4 * j + 3] += f.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncols) v[j] += __ldg(e.bias + col0 + j);
+      }
+    } else if (e.bias_kind == kBiasPerM) {
+      const float bm = row_ok ? __ldg(e.bias + row) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] += bm;
+    } else if (e.bias_kind == kBiasScalar) {
+      const float bs = __ldg(e.bias);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] += bs;
+    }
+  }
+  if (e.Z != nullptr && row_ok)
+    store_row_frag(e.Z, static_cast<long long>(b) * e.strideZ + static_cast<long long>(row) * e.ldz + col0, e.z_dtype,
+                   v, ncols, p.z_vec != 0);
+  switch (e.act) {
+    case kActReLU:    apply_act32<kActReLU>(v, e.leaky); break;
+    case kActLeaky:   apply_act32<kActLeaky>(v, e.leaky); break;
+    case kActGELU:    apply_act32<kActGELU>(v, e.leaky); break;
+    case kActSigmoid: apply_act32<kActSigmoid>(v, e.leaky); break;
+    case kActTanh:    apply_act32<kActTanh>(v, e.leaky); break;
+    default: break;
+  }
+  if (row_ok)
+    store_row_frag(e.D, static_cast<long long>(b) * e.strideD + static_cast<long long>(row) * e.ldd + col0, e.d_dtype,
+                   v, ncols, p.d_vec != 0);
+}
+
+// Persistent tile order: within a batch slice, groups of kGroupM row-blocks sweep all column-blocks,
+// so CTAs that run together share operand tiles through L2.
+__device__ __forceinline__ void decode_tile(const TcParams& p, long long tile, int& b, int& mb, int& nb) {
+  const int per_batch = p.m_blocks * p.n_blocks;
+  b = static_cast<int>(tile / per_batch);
+  const int t = static_cast<int>(tile - static_cast<long long>(b) * per_batch);
+  const int group_sz = kGroupM * p.n_blocks;
+  const int g = t / group_sz;
+  const int first_m = g * kGroupM;
+  const int rows_in_group = min(kGroupM, p.m_blocks - first_m);
+  const int r = t - g * group_sz;
+  mb = first_m + r % rows_in_group;
+  nb = r / rows_in_group;
+}
+
+template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages>
+__global__ void __launch_bounds__(kNumThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+  using Cfg = TcCfg<kElemBytes, kBlockN, kStages>;
+  constexpr bool kTf32 = (kElemBytes == 4);
+
+  extern __shared__ uint8_t smem_raw[];
+  // 128-byte swizzle needs 1024-byte aligned tile bases.
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t smem_base = raw_addr + pad;
+
+  // Barrier block lives after the operand ring.
+  uint8_t* bar_blk = smem + kStages * Cfg::kStageBytes;
+  const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes;
+  auto full_bar   = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar  = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tfull_bar  = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(bar_blk + 8 * (2 * kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_blk + 8 * (2 * kStages + 4) + 8);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), 4); }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+    ptx::prefetch_tensormap(&tmA);
+    ptx::prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), Cfg::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const long long total_tiles = static_cast<long long>(p.batch) * p.m_blocks * p.n_blocks;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        int b, mb, nb;
+        decode_tile(p, tile, b, mb, nb);
+        const int m0 = mb * kBlockM, n0 = nb * kBlockN;
+        const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t fb = full_bar(stage);
+          ptx::mbar_arrive_expect_tx(fb, Cfg::kStageBytes);
+          const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
+          const uint32_t b_dst = a_dst + Cfg::kAStage;
+          const int k0 = kb * Cfg::kBlockK;
+          if constexpr (!kAMN) {
+            ptx::tma_load_3d(a_dst, &tmA, fb, k0, m0, ba);                       // box {kBlockK, 128}
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBlockM / Cfg::kBlockK; ++j)                      // boxes {kBlockK(m), kBlockK(k)}
+              ptx::tma_load_3d(a_dst + j * (Cfg::kBlockK * 128), &tmA, fb, m0 + j * Cfg::kBlockK, k0, ba);
+          }
+          if constexpr (!kBMN) {
+            ptx::tma_load_3d(b_dst, &tmB, fb, k0, n0, bb);                       // box {kBlockK, kBlockN}
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBlockN / Cfg::kBlockK; ++j)
+              ptx::tma_load_3d(b_dst + j * (Cfg::kBlockK * 128), &tmB, fb, n0 + j * Cfg::kBlockK, k0, bb);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      // Descriptor geometry.  Reduction-contiguous tiles: rows of 128 bytes, 8-row groups 1024 bytes apart,
+      // a k-step of one MMA is 32 bytes inside the swizzled row.  M/N-contiguous tiles: each 128-byte row holds
+      // one reduction index, 8 reduction rows form a 1024-byte group, and the next block of 128 bytes along M/N
+      // starts kBlockK rows later; a k-step is kUmmaK rows.
+      // 32-bit operands with M/N contiguous use the 32-byte-unit swizzle, whose pattern repeats every 4 rows.
+      constexpr uint32_t kLboMN = Cfg::kBlockK * 128, kSbo = 1024;
+      constexpr uint32_t kSboMN = kTf32 ? 512 : 1024;
+      constexpr uint32_t kTypeMN = kTf32 ? 1u : 2u;
+      constexpr uint32_t kAStep = kAMN ? Cfg::kUmmaK * 128 : 32;
+      constexpr uint32_t kBStep = kBMN ? Cfg::kUmmaK * 128 : 32;
+      int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
+      for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * kBlockN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_src = smem_base + stage * Cfg::kStageBytes;
+          const uint32_t b_src = a_src + Cfg::kAStage;
+#pragma unroll
+          for (int ks = 0; ks < Cfg::kBlockK / Cfg::kUmmaK; ++ks) {
+            const uint64_t ad = kAMN ? ptx::make_smem_desc_sw128(a_src + ks * kAStep, kLboMN, kSboMN, kTypeMN)
+                                     : ptx::make_smem_desc_sw128(a_src + ks * kAStep, 0u, kSbo);
+            const uint64_t bd = kBMN ? ptx::make_smem_desc_sw128(b_src + ks * kBStep, kLboMN, kSboMN, kTypeMN)
+                                     : ptx::make_smem_desc_sw128(b_src + ks * kBStep, 0u, kSbo);
+            ptx::umma<kTf32>(d_tmem, ad, bd, p.idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+          }
+          ptx::umma_commit(empty_bar(stage));          // frees this ring slot when the MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::umma_commit(tfull_bar(acc));              // accumulator complete
+        acc ^= 1; if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ===================== epilogue (4 warps, one TMEM lane quarter each) =====================
+    const int q = warp & 3;                            // hardware rule: a warp reads lanes 32*(warp%4)..+31
+    int acc = 0; uint32_t acc_phase = 0; bool ok = true;
+    for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      int b, mb, nb;
+      decode_tile(p, tile, b, mb, nb);
+      const int row = mb * kBlockM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const int n0 = nb * kBlockN;
+      if (!ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + acc * kBlockN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < kBlockN; c += 32) {
+        const int col0 = n0 + c;
+        if (col0 >= p.N) break;                        // uniform over the warp
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(t_row + c, r);
+        ptx::tmem_wait_ld();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        epilogue_frag(p, v, b, row, col0, min(32, p.N - col0), row_ok);
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+      acc ^= 1; if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  __syncthreads();
+  if (*abort_flag != 0) {
+    // A wait ran out: give copies still in flight time to land before shared memory is released.
+    if (threadIdx.x == 0) atomicOr(p.status, kErrWaitTimeout);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) { __nanosleep(1000); }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side: tensor maps, configuration choice, launch.
+// ------------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// 3-D map {inner, rows, batch} over a row-major operand; box {box_inner, box_rows, 1}, 128-byte swizzle,
+// out-of-range elements read as zero (which makes ragged K, M and N tiles correct without special code).
+bool make_operand_map(CUtensorMap* map, int dtype, const void* base, long long inner, long long rows, long long ld,
+                      long long batch, long long batch_stride, int box_inner, int box_rows, bool swizzle_32b_units) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (!enc) return false;
+  const int esz = dtype_bytes(dtype);
+  const CUtensorMapDataType dt = dtype == kF32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  if (batch_stride <= 0 || batch <= 1) { batch = 1; batch_stride = rows * ld; }
+  cuuint64_t dims[3]    = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * esz, static_cast<cuuint64_t>(batch_stride) * esz};
+  cuuint32_t box[3]     = {static_cast<cuuint32_t>(box_inner), static_cast<cuuint32_t>(box_rows), 1u};
+  cuuint32_t estr[3]    = {1u, 1u, 1u};
+  const CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         swizzle_32b_units ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+bool tensor_vec_ok(const void* p, long long ld, long long batch_stride, int dt) {
+  if (!p) return false;
+  const int esz = dtype_bytes(dt);
+  return aligned16(p) && (ld * esz) % 16 == 0 && (batch_stride * esz) % 16 == 0;
+}
+
+template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages>
+cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
+  using Cfg = TcCfg<kElemBytes, kBlockN, kStages>;
+  auto kernel = gemm_tc_kernel<kElemBytes, kAMN, kBMN, kBlockN, kStages>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+
+  p.m_blocks = (g.M + kBlockM - 1) / kBlockM;
+  p.n_blocks = (g.N + kBlockN - 1) / kBlockN;
+  p.k_blocks = (g.K + Cfg::kBlockK - 1) / Cfg::kBlockK;
+  const int ab_format = g.in_dtype == kF32 ? 2 : (g.in_dtype == kBF16 ? 1 : 0);
+  p.idesc = ptx::make_idesc(ab_format, kAMN, kBMN, kBlockM, kBlockN);
+
+  CUtensorMap tmA, tmB;
+  bool ok;
+  constexpr bool kWide = (kElemBytes == 4);   // M/N-contiguous 32-bit tiles are swizzled in 32-byte units
+  if (!kAMN) ok = make_operand_map(&tmA, g.in_dtype, g.A, g.K, g.M, g.lda, g.batch, g.strideA, Cfg::kBlockK, kBlockM, false);
+  else       ok = make_operand_map(&tmA, g.in_dtype, g.A, g.M, g.K, g.lda, g.batch, g.strideA, Cfg::kBlockK, Cfg::kBlockK, kWide);
+  if (!ok) return cudaErrorInvalidValue;
+  if (!kBMN) ok = make_operand_map(&tmB, g.in_dtype, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, Cfg::kBlockK, kBlockN, false);
+  else       ok = make_operand_map(&tmB, g.in_dtype, g.B, g.N, g.K, g.ldb, g.batch, g.strideB, Cfg::kBlockK, Cfg::kBlockK, kWide);
+  if (!ok) return cudaErrorInvalidValue;
+
+  const long long tiles = static_cast<long long>(g.batch) * p.m_blocks * p.n_blocks;
+  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  kernel<<<grid, kNumThreads, Cfg::kSmemBytes, s>>>(tmA, tmB, p);
+  return cudaGetLastError();
+}
+
+template <int kElemBytes, bool kAMN, bool kBMN>
+cudaError_t launch_bn(const GemmProblem& g, TcParams& p, int block_n, cudaStream_t s) {
+  if (block_n == 128) return launch_cfg<kElemBytes, kAMN, kBMN, 128, 6>(g, p, s);
+  return launch_cfg<kElemBytes, kAMN, kBMN, 256, 4>(g, p, s);
+}
+
+template <int kElemBytes>
+cudaError_t launch_major(const GemmProblem& g, TcParams& p, int block_n, cudaStream_t s) {
+  if (g.a_mn) return g.b_mn ? launch_bn<kElemBytes, true, true>(g, p, block_n, s)
+                            : launch_bn<kElemBytes, true, false>(g, p, block_n, s);
+  return g.b_mn ? launch_bn<kElemBytes, false, true>(g, p, block_n, s)
+                : launch_bn<kElemBytes, false, false>(g, p, block_n, s);
+}
+
+// 256-wide tiles run the tensor pipe at full rate; 128-wide tiles are limited by shared-memory operand
+// bandwidth but quantise better onto the SMs.  Pick the better estimate.
+int choose_block_n(const GemmProblem& g) {
+  if (const char* e = getenv("GE2B_BLOCK_N")) {
+    const int v = atoi(e);
+    if (v == 128 || v == 256) return v;
+  }
+  if (g.N <= 128) return 128;
+  const double sms = sm_count();
+  const long long mb = (g.M + kBlockM - 1) / kBlockM;
+  auto cost = [&](int bn, double rate) {
+    const long long tiles = static_cast<long long>(g.batch) * mb * ((g.N + bn - 1) / bn);
+    const double waves = static_cast<double>((tiles + static_cast<long long>(sms) - 1) / static_cast<long long>(sms));
+    return waves * bn / rate;      // time units: one 128-wide tile at full rate = 128
+  };
+  return cost(256, 1.0) <= cost(128, 0.85) ? 256 : 128;
+}
+
+}  // namespace
+
+bool gemm_tc_supported(const GemmProblem& g, const char** why) {
+  auto fail = [&](const char* m) { if (why) *why = m; return false; };
+  if (g.M < 1 || g.N < 1 || g.K < 1 || g.batch < 1) return fail("empty problem");
+  if (g.in_dtype == kF32 && g.math != 1) return fail("fp32 operands without TF32 opt-in");
+  const int esz = dtype_bytes(g.in_dtype);
+  if (!aligned16(g.A) || !aligned16(g.B)) return fail("operand base not 16-byte aligned");
+  if ((g.lda * esz) % 16 || (g.ldb * esz) % 16) return fail("operand row pitch not a multiple of 16 bytes");
+  if ((g.strideA * esz) % 16 || (g.strideB * esz) % 16) return fail("batch stride not a multiple of 16 bytes");
+  if (g.strideA < 0 || g.strideB < 0) return fail("negative batch stride");
+  if (!encode_tiled_fn()) return fail("driver lacks cuTensorMapEncodeTiled");
+  if (!g.epi.D) return fail("no output");
+  return true;
+}
+
+cudaError_t launch_gemm_tc(const GemmProblem& g, cudaStream_t s) {
+  TcParams p{};
+  p.M = g.M; p.N = g.N; p.K = g.K; p.batch = g.batch;
+  p.a_bcast = (g.batch > 1 && g.strideA == 0) ? 1 : 0;
+  p.b_bcast = (g.batch > 1 && g.strideB == 0) ? 1 : 0;
+  p.epi = g.epi;
+  p.d_vec = tensor_vec_ok(g.epi.D, g.epi.ldd, g.epi.strideD, g.epi.d_dtype);
+  p.z_vec = tensor_vec_ok(g.epi.Z, g.epi.ldz, g.epi.strideZ, g.epi.z_dtype);
+  p.c_vec = tensor_vec_ok(g.epi.C, g.epi.ldc, g.epi.strideC, g.epi.d_dtype);
+  p.bias_vec = g.epi.bias && aligned16(g.epi.bias);
+  p.status = device_status_ptr();
+  if (!p.status) return cudaErrorInvalidDevice;
+  const int bn = choose_block_n(g);
+  return g.in_dtype == kF32 ? launch_major<4>(g, p, bn, s) : launch_major<2>(g, p, bn, s);
+}
+
+}  // namespace ge2b

@@ -1,0 +1,145 @@
+/*
+ * C ABI of the B200 dense-layer launch layer (libge2_b200.so).
+ *
+ * The first five entry points are the reference's own C ABI for this path, unchanged: same names,
+ * same `bufs[]` conventions (device pointers as uintptr_t, LAST entry a HOST pointer to the parameter
+ * struct, read during the call), same return codes (0 ok, -1 bad arguments, -2 CUDA error,
+ * -99 not implemented).  The remaining entry points are additions behind the same convention for the
+ * 16-bit / TF32 tensor-core paths, the strided-batched form and host-buffer calls.
+ *
+ * All launches are asynchronous on `stream` (a cudaStream_t cast to void*; NULL = default stream).
+ * Nothing is retained after a call returns.  There is no CPU fallback: without a CUDA device every
+ * launch returns -2.
+ */
+#ifndef GE2_B200_H_
+#define GE2_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef uintptr_t ge2_uintptr;
+
+/* ---- enums: numbering of the reference's C ABI (dev/backend/graph_executor_v2/include/ge_v2_api_ex.h:15-28).
+ *      Note GE2_BIAS_* differs from the C++ BiasKind numbering (None=0, Scalar=1, PerM=2, PerN=3). ---- */
+typedef enum { GE2_BIAS_SCALAR = 0, GE2_BIAS_PER_M = 1, GE2_BIAS_PER_N = 2 } ge2_bias_kind_t;
+typedef enum {
+  GE2_ACT_NONE = 0, GE2_ACT_RELU = 1, GE2_ACT_LEAKY_RELU = 2, GE2_ACT_GELU = 3, GE2_ACT_SIGMOID = 4, GE2_ACT_TANH = 5
+} ge2_act_kind_t;
+
+/* dtype numbering of the reference's DType (backends/cuda/ops/_common/shim/ai_device.hpp:15) */
+typedef enum { GE2_DT_F32 = 0, GE2_DT_F16 = 1, GE2_DT_BF16 = 2 } ge2_dtype_t;
+/* arithmetic for fp32 tensors: exact fp32 FMA (parity with the reference's fp32 path) or TF32 tensor cores */
+typedef enum { GE2_MATH_FP32 = 0, GE2_MATH_TENSOR = 1 } ge2_math_t;
+
+/* ---- replaces dev/backend/graph_executor_v2/include/ge_v2_api.h:12-18 ---- */
+typedef struct {
+  int M, N, K;
+  int has_bias; /* 0/1 */
+  int act;      /* 0 none, 1 ReLU */
+} ge2_gemm_bias_act_params_t;
+
+/* ---- replaces dev/backend/graph_executor_v2/include/ge_v2_api_ex.h:37-62 ---- */
+typedef struct {
+  int M, N, K;
+  int lda, ldb, ldc, ldd;     /* <= 0: row-major default (K, N, N, N) */
+  float alpha;                /* 0 is read as 1 */
+  float beta;
+  int use_C, has_bias;        /* 0/1: whether bufs[] carries C / bias */
+  ge2_bias_kind_t bias_kind;
+  ge2_act_kind_t act_kind;
+  float leaky_slope;
+  int save_preact;            /* 1: bufs[] carries Z and the pre-activation is written there */
+  int ldZ;                    /* <= 0: ldd */
+} ge2_gemm_bias_act_params_ex_t;
+
+/* ---- replaces dev/backend/graph_executor_v2/include/ge_v2_api_ex.h:94-113 ---- */
+typedef struct {
+  int M, N, K;
+  int lda, ldb, ldc;
+  int ldgY, ldZ;
+  int ldgA, ldgB, ldgC;       /* <= 0: row-major default */
+  float alpha, beta;
+  ge2_bias_kind_t bias_kind;
+  ge2_act_kind_t act_kind;
+  float leaky_slope;
+} ge2_gemm_bias_act_bwd_params_t;
+
+/* Name-keyed dispatcher.  Replaces dev/backend/graph_executor_v2/src/launch_table.cpp:31-96 (declared again
+ * in graph_executor_v2/include/ai/legacy_ge2_api.h:7-13).  Names: "gemm_bias_act_f32", "gemm_bias_act_tc_f16",
+ * "gemm_bias_act_f32_ex" | "gemm_bias_act_ex", "gemm_bias_act_bwd_f32_ex" | "gemm_bias_act_bwd", and the
+ * additions "gemm_bias_act_typed" | "gemm_strided_batched", "gemm_bias_act_bwd_typed".  Unknown name: -1. */
+int ge2_launch(const char* name, const ge2_uintptr* bufs, int n, void* stream);
+
+/* fp32, D = act(A.B + bias).  bufs = [A, B, (bias), D, &ge2_gemm_bias_act_params_t].
+ * Replaces dev/backend/graph_executor_v2/src/my_kernels.cu:36-73. */
+int ge2_launch_gemm_bias_act_f32(const ge2_uintptr* bufs, int n, void* stream);
+
+/* fp16 tensor-core form of the call above: A, B, D are IEEE half, bias fp32, fp32 accumulation.
+ * The reference ships this slot as a stub returning -99 (my_kernels.cu:76-80); here it runs on tcgen05. */
+int ge2_launch_gemm_bias_act_tc_f16(const ge2_uintptr* bufs, int n, void* stream);
+
+/* fp32, D = act(alpha*A.B + beta*C + bias) with optional pre-activation stash.
+ * bufs = [A, B, (C), D, (bias), (Z), &ge2_gemm_bias_act_params_ex_t].
+ * Replaces dev/backend/graph_executor_v2/src/my_kernels.cu:117-195. */
+int ge2_launch_gemm_bias_act_f32_ex(const ge2_uintptr* bufs, int n, void* stream);
+
+/* fp32 backward.  bufs = [A, B, C|0, gY, Z, gA|0, gB|0, gC|0, gBias|0, &ge2_gemm_bias_act_bwd_params_t]
+ * (fixed 10 slots).  The gZ scratch is taken from the stream-ordered allocator, as the reference does
+ * when it is given no workspace.  Replaces dev/backend/graph_executor_v2/src/my_kernels.cu:199-254. */
+int ge2_launch_gemm_bias_act_bwd_f32_ex(const ge2_uintptr* bufs, int n, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Additions: typed + strided-batched forward, typed backward.
+ * ------------------------------------------------------------------------------------------------ */
+typedef struct {
+  ge2_gemm_bias_act_params_ex_t base;
+  ge2_dtype_t dtype;          /* of A, B, C and D */
+  ge2_dtype_t z_dtype;        /* of Z */
+  ge2_math_t math;            /* fp32 tensors only */
+  int trans_b;                /* 1: B is given as [N,K] row-major (the Q.K^T form); ldb default becomes K */
+  int batch;                  /* <= 1: a single GEMM */
+  long long strideA, strideB, strideC, strideD, strideZ; /* elements between slices; 0 broadcasts an input */
+} ge2_gemm_typed_params_t;
+
+/* Same bufs layout as ge2_launch_gemm_bias_act_f32_ex with &ge2_gemm_typed_params_t last.  Stands in for the
+ * per-(batch, head) loops of 2-D GEMM calls in backends/cuda/ops/sdpa/launcher.cu:185-222,236-270, the per-image
+ * loop of backends/cuda/ops/conv2d/launcher.cu:180-227 and dev/backend/graph_executor/ge/gemm_rm.cuh:38-66. */
+int ge2_launch_gemm_bias_act_typed(const ge2_uintptr* bufs, int n, void* stream);
+
+typedef struct {
+  ge2_gemm_bias_act_bwd_params_t base;
+  ge2_dtype_t dtype;          /* of A, B, C, gY, gA, gB, gC */
+  ge2_dtype_t z_dtype;        /* of Z */
+  ge2_math_t math;
+  size_t scratch_bytes;       /* size of the scratch in slot 9 (0 = not stated) */
+} ge2_gemm_bwd_typed_params_t;
+
+/* bufs = [A, B, C|0, gY, Z, gA|0, gB|0, gC|0, gBias|0, scratch|0, &ge2_gemm_bwd_typed_params_t] (fixed 11 slots).
+ * `scratch` holds gZ (M*N elements of `dtype`); with scratch == 0 it is taken from the stream-ordered allocator.
+ * Typed form of backends/cuda/ops/gemm/kernels/regemm_backward.cu:151-301. */
+int ge2_launch_gemm_bias_act_bwd_typed(const ge2_uintptr* bufs, int n, void* stream);
+
+/* Bytes of gZ scratch the backward needs (mirrors GemmRequiredBackwardScratchBytes,
+ * backends/cuda/ops/gemm/api.hpp:107-112, which always counts fp32). */
+size_t ge2b_backward_scratch_bytes(long long M, long long N);
+
+/* Device status word of the current device: 0, or a bit set when a bounded wait inside a kernel ran out.
+ * Synchronises the device.  clear != 0 resets it. */
+int ge2b_device_status(int clear);
+int ge2b_sm_count(void);
+const char* ge2b_version(void);
+
+/* Introspection for tests and benchmarks: which kernel family the calling thread's most recent GEMM went to
+ * (0 none, 1 exact-fp32 CUDA-core kernel, 2 tcgen05 tensor-core kernel) and how many kernels this library
+ * has launched in the process. */
+int ge2b_last_route(void);
+long long ge2b_launches_total(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GE2_B200_H_ */

@@ -1,0 +1,55 @@
+"""The C-ABI library loads and exports every symbol include/ge2_b200.h declares; struct layouts used by the
+Python binding match the header; argument errors are reported with the reference's codes.  No compute."""
+import ctypes as C
+import re
+import subprocess
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_exports_every_declared_symbol(pkg, lib):
+    header = (ROOT / "include" / "ge2_b200.h").read_text()
+    declared = set(re.findall(r"\b(ge2b?_[a-z0-9_]+)\s*\(", header))
+    declared -= {n for n in declared if n.endswith("_t")}
+    assert declared, "no declarations found"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+    assert set(pkg._lib.EXPORTS) == declared
+
+
+def test_struct_sizes_match_the_header(pkg, tmp_path):
+    src = tmp_path / "sz.c"
+    src.write_text('#include <stdio.h>\n#include "ge2_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu\\n",'
+                   "sizeof(ge2_gemm_bias_act_params_t),sizeof(ge2_gemm_bias_act_params_ex_t),"
+                   "sizeof(ge2_gemm_bias_act_bwd_params_t),sizeof(ge2_gemm_typed_params_t),"
+                   "sizeof(ge2_gemm_bwd_typed_params_t));return 0;}\n")
+    exe = tmp_path / "sz"
+    subprocess.run(["gcc", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
+    sizes = list(map(int, subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()))
+    L = pkg._lib
+    assert sizes == [C.sizeof(L.ParamsLegacy), C.sizeof(L.ParamsEx), C.sizeof(L.ParamsBwd), C.sizeof(L.ParamsTyped),
+                     C.sizeof(L.ParamsBwdTyped)]
+
+
+def test_argument_errors_use_reference_codes(pkg, lib):
+    L = pkg._lib
+    assert lib.ge2_launch(None, None, 0, None) == -1
+    p = L.ParamsEx()
+    bufs = L.make_bufs([0, 0, 0], p)
+    assert lib.ge2_launch(b"no_such_kernel", bufs, len(bufs), None) == -1
+    assert lib.ge2_launch(b"gemm_bias_act_f32_ex", bufs, 2, None) == -1          # too few buffers
+    assert lib.ge2_launch(b"gemm_bias_act_bwd_f32_ex", bufs, 4, None) == -1      # backward wants 10 slots
+    assert lib.ge2_launch(b"gemm_bias_act_f32_ex", bufs, len(bufs), None) == -1  # null pointers, zero sizes
+    assert lib.ge2b_backward_scratch_bytes(8, 16) == 8 * 16 * 4
+    assert lib.ge2b_backward_scratch_bytes(0, 16) == 0
+    assert b"sm_100a" in lib.ge2b_version()
+
+
+def test_missing_library_is_a_loud_error(pkg, monkeypatch, tmp_path):
+    import pytest
+    L = pkg._lib
+    monkeypatch.setattr(L, "_LIB", None)
+    monkeypatch.setattr(L, "library_path", lambda: tmp_path / "nope.so")
+    with pytest.raises(RuntimeError, match="no CPU or eager fallback"):
+        L.load_library()

@@ -1,0 +1,378 @@
+"""GPU parity tests of the dense-layer path: every call goes through the C ABI of libge2_b200.so and is
+compared with the CPU oracle, the golden vectors made from the reference's own epilogue code, and (where it
+was built) the reference's own GPU kernels.
+
+Tolerances (from the contract of this path):
+  fp32 tensors, exact path      pre-activation Z bit-identical to the oracle / golden; Y, gA, gB, gBias within
+                                the reference tests' own bounds (atol 1e-5 / rtol 1e-4 forward, 3e-4 backward)
+  bf16 / f16 / TF32 tensor cores  relative Frobenius error <= 2e-2 against float64 on the rounded inputs
+"""
+import ctypes as C
+import itertools
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+from cases import CASES  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+ROOT = Path(__file__).resolve().parent.parent
+FRO_TOL = 2e-2
+
+ACT_CODE = {"none": 0, "relu": 1, "leaky_relu": 2, "gelu": 3, "sigmoid": 4, "tanh": 5}
+ABI_BIAS = {1: 0, 2: 1, 3: 2}   # oracle numbering (scalar 1, per-row 2, per-column 3) -> C-ABI numbering
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def host(t):
+    return t.detach().float().cpu().numpy()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(lib):
+    yield
+    torch.cuda.synchronize()
+    assert lib.ge2b_device_status(1) == 0, "a bounded wait inside a kernel timed out"
+
+
+# --------------------------------------------------------------------------- fp32 exact, legacy C ABI
+def legacy_forward_ex(pkg, lib, c, by_name=False):
+    L = pkg._lib
+    A, B = dev(c["A"]), dev(c["B"])
+    M, K = c["A"].shape
+    N = c["B"].shape[1]
+    D = torch.full((M, N), float("nan"), device="cuda")
+    Z = torch.full((M, N), float("nan"), device="cuda")
+    Cin = dev(c["C"]) if c["C"] is not None else None
+    bias = dev(c["bias"].reshape(-1)) if c["bias"] is not None else None
+    p = L.ParamsEx()
+    p.M, p.N, p.K = M, N, K
+    p.lda = p.ldb = p.ldc = p.ldd = 0
+    p.alpha, p.beta = c["alpha"], c["beta"]
+    p.use_C, p.has_bias = int(Cin is not None), int(bias is not None)
+    p.bias_kind = ABI_BIAS.get(c["bias_kind"], 0)
+    p.act_kind = ACT_CODE[c["act"]]
+    p.leaky_slope = c["leaky"]
+    p.save_preact, p.ldZ = 1, 0
+    ptrs = [A.data_ptr(), B.data_ptr()] + ([Cin.data_ptr()] if Cin is not None else []) + [D.data_ptr()] + \
+           ([bias.data_ptr()] if bias is not None else []) + [Z.data_ptr()]
+    bufs = L.make_bufs(ptrs, p)
+    s = torch.cuda.current_stream().cuda_stream
+    rc = lib.ge2_launch(b"gemm_bias_act_f32_ex", bufs, len(bufs), s) if by_name else \
+        lib.ge2_launch_gemm_bias_act_f32_ex(bufs, len(bufs), s)
+    assert rc == 0
+    torch.cuda.synchronize()
+    return D, Z
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_fp32_forward_matches_golden_and_oracle(pkg, lib, oracle, name):
+    c = CASES[name]()
+    g = np.load(GOLD / f"{name}.npz")
+    D, Z = legacy_forward_ex(pkg, lib, c, by_name=(name.startswith("legacy")))
+    assert lib.ge2b_last_route() == 1
+    assert np.array_equal(host(Z), g["Z"]), "pre-activation must be bit-identical to the reference's"
+    np.testing.assert_allclose(host(D), g["Y"], rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_fp32_backward_matches_oracle(pkg, lib, oracle, name):
+    L = pkg._lib
+    c = CASES[name]()
+    g = np.load(GOLD / f"{name}.npz")
+    M, K = c["A"].shape
+    N = c["B"].shape[1]
+    kind = c["bias_kind"] or 3
+    A, B, gY, Z = dev(c["A"]), dev(c["B"]), dev(c["gY"]), dev(g["Z"])
+    Cin = dev(c["C"]) if c["C"] is not None else None
+    gA = torch.full((M, K), float("nan"), device="cuda")
+    gB = torch.full((K, N), float("nan"), device="cuda")
+    gC = torch.full((M, N), float("nan"), device="cuda") if Cin is not None else None
+    nb = {1: 1, 2: M, 3: N}[kind]
+    gBias = torch.full((nb,), float("nan"), device="cuda")
+    p = L.ParamsBwd()
+    p.M, p.N, p.K = M, N, K
+    p.alpha, p.beta = c["alpha"], c["beta"]
+    p.bias_kind, p.act_kind, p.leaky_slope = ABI_BIAS[kind], ACT_CODE[c["act"]], c["leaky"]
+    ptr = lambda t: t.data_ptr() if t is not None else 0   # noqa: E731
+    bufs = L.make_bufs([ptr(A), ptr(B), ptr(Cin), ptr(gY), ptr(Z), ptr(gA), ptr(gB), ptr(gC), ptr(gBias)], p)
+    assert lib.ge2_launch(b"gemm_bias_act_bwd_f32_ex", bufs, len(bufs), torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    o = oracle.backward_f32(c["A"], c["B"], c["gY"], g["Z"], act=c["act"], leaky=c["leaky"], alpha=c["alpha"],
+                            beta=c["beta"], bias_kind=kind, want_gC=Cin is not None)
+    np.testing.assert_allclose(host(gA), o["gA"], rtol=1e-4, atol=3e-4)
+    np.testing.assert_allclose(host(gB), o["gB"], rtol=1e-4, atol=3e-4)
+    np.testing.assert_allclose(host(gBias), o["gBias"], rtol=1e-4, atol=3e-4)
+    if Cin is not None:
+        np.testing.assert_allclose(host(gC), o["gC"], rtol=1e-5, atol=1e-5)
+
+
+def test_legacy_relu_entry_and_name_table(pkg, lib, oracle):
+    L = pkg._lib
+    c = CASES["relu128"]()
+    A, B, bias = dev(c["A"]), dev(c["B"]), dev(c["bias"])
+    D = torch.empty((128, 128), device="cuda")
+    p = L.ParamsLegacy(128, 128, 128, 1, 1)
+    bufs = L.make_bufs([A.data_ptr(), B.data_ptr(), bias.data_ptr(), D.data_ptr()], p)
+    assert lib.ge2_launch(b"gemm_bias_act_f32", bufs, len(bufs), None) == 0
+    torch.cuda.synchronize()
+    g = np.load(GOLD / "relu128.npz")
+    np.testing.assert_array_equal(host(D), g["Y"])     # ReLU has no transcendental: exact
+    # the fp16 slot: same call shape with half tensors, on tensor cores
+    Ah, Bh = A.half(), B.half()
+    Dh = torch.empty((128, 128), device="cuda", dtype=torch.float16)
+    bufs = L.make_bufs([Ah.data_ptr(), Bh.data_ptr(), bias.data_ptr(), Dh.data_ptr()], p)
+    assert lib.ge2_launch(b"gemm_bias_act_tc_f16", bufs, len(bufs), None) == 0
+    torch.cuda.synchronize()
+    assert lib.ge2b_last_route() == 2
+    y64, _ = oracle.forward_f64(host(Ah), host(Bh), c["bias"], act="relu")
+    assert oracle.rel_fro(host(Dh), y64) <= FRO_TOL
+
+
+SMALL = [1, 7, 16, 33, 127, 128, 129, 255, 257]
+
+
+@pytest.mark.parametrize("act", ["none", "gelu"])
+def test_fp32_small_shape_sweep_bit_exact(pkg, lib, oracle, act):
+    rng = np.random.default_rng(11)
+    combos = list(itertools.product(SMALL, SMALL, SMALL))
+    picks = [combos[i] for i in rng.choice(len(combos), 40, replace=False)] + [(1, 1, 1), (257, 257, 257)]
+    for (M, N, K) in picks:
+        A = rng.standard_normal((M, K), dtype=np.float32)
+        B = rng.standard_normal((K, N), dtype=np.float32)
+        b = rng.standard_normal(N, dtype=np.float32)
+        Y, Z = pkg.ops_gemm.forward(dev(A), dev(B), dev(b), act=act, return_z=True)
+        Yo, Zo = oracle.forward_f32(A, B, b, act=act)
+        assert np.array_equal(host(Z), Zo), (M, N, K)
+        np.testing.assert_allclose(host(Y), Yo, rtol=1e-4, atol=1e-5)
+
+
+def test_padded_rows_and_canaries_fp32_and_bf16(pkg, lib, oracle):
+    """ld > cols on every tensor; the padding must not be written."""
+    rng = np.random.default_rng(5)
+    M, K, N = 200, 136, 304
+    for dtype, math in ((torch.float32, "fp32"), (torch.bfloat16, "fp32"), (torch.float32, "tf32")):
+        Af = oracle.bf16_round(rng.standard_normal((M, K), dtype=np.float32))
+        Bf = oracle.bf16_round(rng.standard_normal((K, N), dtype=np.float32))
+        b = rng.standard_normal(N, dtype=np.float32)
+        Abuf = torch.zeros((M, K + 8), device="cuda", dtype=dtype)
+        Bbuf = torch.zeros((K, N + 16), device="cuda", dtype=dtype)
+        Abuf[:, :K] = dev(Af, dtype)
+        Bbuf[:, :N] = dev(Bf, dtype)
+        out = torch.full((M, N + 24), 777.0, device="cuda", dtype=dtype)
+        zout = torch.full((M, N + 8), 555.0, device="cuda", dtype=dtype)
+        pkg.ops_gemm.forward_into(Abuf[:, :K], Bbuf[:, :N], out=out[:, :N], bias=dev(b), with_bias=True, act="relu",
+                                  save_z=True, z_out=zout[:, :N], math=math)
+        torch.cuda.synchronize()
+        assert torch.all(out[:, N:] == 777.0) and torch.all(zout[:, N:] == 555.0)
+        y64, z64 = oracle.forward_f64(Af, Bf, b, act="relu")
+        tol = 1e-5 if (dtype == torch.float32 and math == "fp32") else FRO_TOL
+        assert oracle.rel_fro(host(out[:, :N]), y64) <= tol
+        assert oracle.rel_fro(host(zout[:, :N]), z64) <= tol
+
+
+# --------------------------------------------------------------------------- tensor-core paths
+def tc_case(pkg, lib, oracle, M, K, N, dtype, math, act, seed=0, z_dtype=None, expect_route=2):
+    X, W, b, dY = oracle.dense_inputs(M, K, N, seed=seed)
+    if dtype != torch.float32:
+        X, W, dY = (oracle.bf16_round(a) if dtype == torch.bfloat16 else a.astype(np.float16).astype(np.float32)
+                    for a in (X, W, dY))
+    tX, tW, tdY, tb = dev(X, dtype), dev(W, dtype), dev(dY, dtype), dev(b)
+    Y, Z = pkg.ops_gemm.forward(tX, tW, tb, act=act, return_z=True, math=math, z_dtype=z_dtype)
+    if expect_route:
+        assert lib.ge2b_last_route() == expect_route
+    g = pkg.ops_gemm.backward(tX, tW, tdY, Z, act=act, want_gBias=True, math=math)
+    torch.cuda.synchronize()
+    Y64, Z64 = oracle.forward_f64(X, W, b, act=act)
+    g64 = oracle.backward_f64(X, W, dY, host(Z), act=act)
+    errs = {"Y": oracle.rel_fro(host(Y), Y64), "Z": oracle.rel_fro(host(Z), Z64),
+            "dX": oracle.rel_fro(host(g["gA"]), g64["gA"]), "dW": oracle.rel_fro(host(g["gB"]), g64["gB"]),
+            "db": oracle.rel_fro(host(g["gBias"]).ravel(), g64["gBias"])}
+    return errs
+
+
+@pytest.mark.parametrize("act", ["none", "relu", "gelu", "sigmoid", "tanh", "leaky_relu"])
+@pytest.mark.parametrize("dtype,math", [(torch.bfloat16, "fp32"), (torch.float16, "fp32"), (torch.float32, "tf32")])
+def test_tensor_core_forward_backward_vs_float64(pkg, lib, oracle, dtype, math, act):
+    errs = tc_case(pkg, lib, oracle, 384, 320, 512, dtype, math, act)
+    assert all(e <= FRO_TOL for e in errs.values()), errs
+
+
+@pytest.mark.parametrize("shape", [(128, 64, 128), (129, 72, 136), (1, 8, 8), (333, 1000, 264), (1024, 1024, 1024),
+                                   (16, 1024, 2048), (2048, 136, 24)])
+def test_bf16_ragged_shapes(pkg, lib, oracle, shape):
+    M, K, N = shape
+    errs = tc_case(pkg, lib, oracle, M, K, N, torch.bfloat16, "fp32", "gelu", seed=3, z_dtype=torch.float32)
+    assert all(e <= FRO_TOL for e in errs.values()), errs
+
+
+def test_bf16_unaligned_pitch_uses_the_cuda_core_kernel(pkg, lib, oracle):
+    """K and N not multiples of 8 elements: TMA cannot address the rows, the exact kernel takes over."""
+    errs = tc_case(pkg, lib, oracle, 65, 37, 51, torch.bfloat16, "fp32", "gelu", expect_route=1)
+    assert all(e <= FRO_TOL for e in errs.values()), errs
+
+
+def test_config2_full_size_row_sampled(pkg, lib, oracle):
+    """M=N=K=4096 bf16 GELU forward + backward; float64 reference on sampled rows / columns only."""
+    M = N = K = 4096
+    X, W, b, dY = oracle.dense_inputs(M, K, N, seed=0)
+    X, W, dY = (oracle.bf16_round(a) for a in (X, W, dY))
+    tX, tW, tdY, tb = dev(X, torch.bfloat16), dev(W, torch.bfloat16), dev(dY, torch.bfloat16), dev(b)
+    Y, Z = pkg.ops_gemm.forward(tX, tW, tb, act="gelu", return_z=True)
+    g = pkg.ops_gemm.backward(tX, tW, tdY, Z, act="gelu", want_gBias=True)
+    torch.cuda.synchronize()
+    rng = np.random.default_rng(1)
+    rows = np.sort(rng.choice(M, 96, replace=False))
+    Y64, Z64 = oracle.forward_f64(X[rows], W, b, act="gelu")
+    assert oracle.rel_fro(host(Y[rows]), Y64) <= FRO_TOL
+    assert oracle.rel_fro(host(Z[rows]), Z64) <= FRO_TOL
+    Zh = host(Z)
+    gZ = dY.astype(np.float64) * oracle.act_deriv_f64("gelu", Zh)
+    assert oracle.rel_fro(host(g["gA"][rows]), gZ[rows] @ W.astype(np.float64).T) <= FRO_TOL
+    cols = np.sort(rng.choice(K, 96, replace=False))
+    assert oracle.rel_fro(host(g["gB"][cols]), X[:, cols].astype(np.float64).T @ gZ) <= FRO_TOL
+    assert oracle.rel_fro(host(g["gBias"]).ravel(), gZ.sum(axis=0)) <= FRO_TOL
+
+
+def test_linearity_at_full_size(pkg, lib):
+    """act = none: f(X1 + X2) == f(X1) + f(X2) up to bf16 output rounding, at 4096^3."""
+    torch.manual_seed(0)
+    n = 4096
+    X1 = torch.randn(n, n, device="cuda").bfloat16()
+    X2 = (torch.randn(n, n, device="cuda") * 0.5).bfloat16()
+    W = (torch.randn(n, n, device="cuda") / 64).bfloat16()
+    Xs = (X1.float() + X2.float()).bfloat16()
+    exact = (Xs.float() == X1.float() + X2.float())
+    y1 = pkg.ops_gemm.forward(X1, W).float()
+    y2 = pkg.ops_gemm.forward(X2, W).float()
+    ys = pkg.ops_gemm.forward(Xs, W).float()
+    rows = exact.all(dim=1)                       # rows where the bf16 sum is exact
+    assert rows.sum() >= 0
+    num = (ys - (y1 + y2))[rows].norm() if rows.any() else torch.tensor(0.0)
+    den = ys[rows].norm() if rows.any() else torch.tensor(1.0)
+    assert float(num / den) <= 1e-2
+
+
+def test_run_to_run_determinism(pkg, lib):
+    torch.manual_seed(1)
+    X = torch.randn(1024, 768, device="cuda").bfloat16()
+    W = torch.randn(768, 1280, device="cuda").bfloat16()
+    gY = torch.randn(1024, 1280, device="cuda").bfloat16()
+    b = torch.randn(1280, device="cuda")
+    outs = []
+    for _ in range(2):
+        Y, Z = pkg.ops_gemm.forward(X, W, b, act="gelu", return_z=True)
+        g = pkg.ops_gemm.backward(X, W, gY, Z, act="gelu")
+        outs.append((Y.clone(), Z.clone(), g["gA"].clone(), g["gB"].clone()))
+    for a, c in zip(*outs):
+        assert torch.equal(a, c)
+
+
+# --------------------------------------------------------------------------- strided-batched form
+@pytest.mark.parametrize("dtype,math", [(torch.bfloat16, "fp32"), (torch.float32, "tf32"), (torch.float32, "fp32")])
+def test_batched_attention_gemms(pkg, lib, oracle, dtype, math):
+    """S = (Q.K^T)/sqrt(d) and O = P.V per (batch, head) in one launch each (reduced B, H, L of config 4)."""
+    Bn, H, L, d = 2, 3, 256, 128
+    rng = np.random.default_rng(0)
+    Q = oracle.bf16_round(rng.standard_normal((Bn, H, L, d), dtype=np.float32))
+    Kx = oracle.bf16_round(rng.standard_normal((Bn, H, L, d), dtype=np.float32))
+    V = oracle.bf16_round(rng.standard_normal((Bn, H, L, d), dtype=np.float32))
+    raw = rng.standard_normal((Bn, H, L, L)).astype(np.float64)
+    P = np.exp(raw - raw.max(-1, keepdims=True))
+    P = oracle.bf16_round((P / P.sum(-1, keepdims=True)).astype(np.float32))
+    tQ, tK, tV, tP = (dev(a, dtype) for a in (Q, Kx, V, P))
+    S = torch.empty((Bn, H, L, L), device="cuda", dtype=dtype)
+    O = torch.empty((Bn, H, L, d), device="cuda", dtype=dtype)
+    scale = 1.0 / np.sqrt(d)
+    pkg.ops_gemm.forward_batched(tQ, tK, out=S, trans_b=True, alpha=scale, math=math)
+    pkg.ops_gemm.forward_batched(tP, tV, out=O, math=math)
+    torch.cuda.synchronize()
+    S64 = scale * np.einsum("bhld,bhmd->bhlm", Q.astype(np.float64), Kx.astype(np.float64))
+    O64 = np.einsum("bhlm,bhmd->bhld", P.astype(np.float64), V.astype(np.float64))
+    tol = 1e-5 if (dtype == torch.float32 and math == "fp32") else FRO_TOL
+    assert oracle.rel_fro(host(S), S64) <= tol
+    assert oracle.rel_fro(host(O), O64) <= tol
+
+
+def test_batched_shared_weight_broadcast(pkg, lib, oracle):
+    """Batch stride 0 on B: every slice multiplies the same weight (the per-image conv2d / v1 executor form)."""
+    rng = np.random.default_rng(2)
+    A = oracle.bf16_round(rng.standard_normal((5, 96, 72), dtype=np.float32))
+    W = oracle.bf16_round(rng.standard_normal((1, 72, 40), dtype=np.float32))
+    b = rng.standard_normal(40, dtype=np.float32)
+    out = torch.empty((5, 96, 40), device="cuda", dtype=torch.bfloat16)
+    pkg.ops_gemm.forward_batched(dev(A, torch.bfloat16), dev(W, torch.bfloat16), out=out, bias=dev(b), act="relu")
+    torch.cuda.synchronize()
+    ref = np.maximum(A.astype(np.float64) @ W[0].astype(np.float64) + b, 0)
+    assert oracle.rel_fro(host(out), ref) <= FRO_TOL
+
+
+# --------------------------------------------------------------------------- Dense layer
+def test_dense_layer_eager_and_into(pkg, lib, oracle):
+    layer = pkg.Dense(256, activation="gelu", dtype=torch.bfloat16, seed=0)
+    x = torch.randn(128, 192, device="cuda").bfloat16()
+    y = layer(x)
+    gy = torch.randn_like(y)
+    gx = layer.backward(gy)
+    y2 = torch.empty_like(y)
+    z2 = torch.empty_like(y)
+    layer.forward_into(x, out=y2, z_out=z2)
+    gA, gW = torch.empty_like(x), torch.empty_like(layer.W)
+    gb = torch.empty((1, 256), device="cuda")
+    work = torch.empty((128, 256), device="cuda")
+    layer.backward_into(gy, gA_out=gA, gW_out=gW, gB_out=gb, work_dZ=work)
+    torch.cuda.synchronize()
+    assert torch.equal(y, y2) and torch.equal(gx, gA)
+    Y64, Z64 = oracle.forward_f64(host(x), host(layer.W), host(layer.b), act="gelu")
+    assert oracle.rel_fro(host(y), Y64) <= FRO_TOL
+
+
+# --------------------------------------------------------------------------- the reference's own GPU kernels
+def _ref_gpu():
+    so = ROOT / "oracle" / "_ref" / "libref_gemm.so"
+    if not so.exists():
+        pytest.skip("oracle/_ref/libref_gemm.so was not built (needs the reference tree at build time)")
+    lib = C.CDLL(str(so))
+    lib.ref_gpu_forward.restype = C.c_int
+    lib.ref_gpu_forward.argtypes = [C.c_void_p] * 3 + [C.c_longlong] + [C.c_void_p] * 2 + [C.c_int] * 4 + \
+                                   [C.c_float, C.c_void_p]
+    lib.ref_gpu_backward.restype = C.c_int
+    lib.ref_gpu_backward.argtypes = [C.c_void_p] * 7 + [C.c_longlong, C.c_void_p] + [C.c_int] * 4 + \
+                                    [C.c_float, C.c_void_p]
+    return lib
+
+
+@pytest.mark.parametrize("act", ["relu", "gelu", "sigmoid", "tanh"])
+def test_fp32_path_against_reference_gpu_kernels(pkg, lib, oracle, act):
+    """Config 1 (256x512 . 512x512 + b, seed 0) through the reference's GemmCudaLaunch / GemmCudaBackward built
+    for sm_100a, and through this library, on the same device buffers."""
+    ref = _ref_gpu()
+    X, W, b, dY = oracle.dense_inputs(256, 512, 512, seed=0)
+    tX, tW, tb, tdY = dev(X), dev(W), dev(b), dev(dY)
+    Yr, Zr = torch.empty((256, 512), device="cuda"), torch.empty((256, 512), device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    assert ref.ref_gpu_forward(tX.data_ptr(), tW.data_ptr(), tb.data_ptr(), 512, Yr.data_ptr(), Zr.data_ptr(),
+                               256, 512, 512, ACT_CODE[act], 0.01, s) == 0
+    Y, Z = pkg.ops_gemm.forward(tX, tW, tb, act=act, return_z=True)
+    torch.cuda.synchronize()
+    assert torch.equal(Z, Zr), "pre-activation differs from the reference kernel's"
+    rel = ((Y - Yr).abs() / Yr.abs().clamp_min(1e-5)).max().item()
+    assert rel <= 1e-5, rel
+    gAr, gBr = torch.empty_like(tX), torch.empty_like(tW)
+    gbr = torch.empty(512, device="cuda")
+    scratch = torch.empty((256, 512), device="cuda")
+    assert ref.ref_gpu_backward(tX.data_ptr(), tW.data_ptr(), tdY.data_ptr(), Zr.data_ptr(), gAr.data_ptr(),
+                                gBr.data_ptr(), gbr.data_ptr(), 512, scratch.data_ptr(), 256, 512, 512,
+                                ACT_CODE[act], 0.01, s) == 0
+    g = pkg.ops_gemm.backward(tX, tW, tdY, Z, act=act, want_gBias=True)
+    torch.cuda.synchronize()
+    for got, want in ((g["gA"], gAr), (g["gB"], gBr), (g["gBias"].ravel(), gbr)):
+        err = ((got - want).abs() / want.abs().clamp_min(1.0)).max().item()
+        assert err <= 1e-5 * 30, err   # different summation orders over 256..512 terms of O(1) products
