@@ -47,7 +47,7 @@ class ParamsTyped(C.Structure):
 class ParamsBwdTyped(C.Structure):
     _fields_ = [("base", ParamsBwd),
                 ("dtype", C.c_int), ("z_dtype", C.c_int), ("math", C.c_int),
-                ("scratch_bytes", C.c_size_t)]
+                ("scratch_bytes", C.c_size_t), ("reuse_gz", C.c_int)]
 
 
 # numbering of the C ABI
@@ -63,6 +63,7 @@ EXPORTS = [
     "ge2_launch_gemm_bias_act_typed", "ge2_launch_gemm_bias_act_bwd_typed",
     "ge2b_backward_scratch_bytes", "ge2b_device_status", "ge2b_sm_count", "ge2b_version",
     "ge2b_last_route", "ge2b_launches_total",
+    "ge2b_dense_plan_create", "ge2b_dense_plan_step", "ge2b_dense_plan_destroy",
 ]
 
 
@@ -94,6 +95,13 @@ def load_library() -> C.CDLL:
     lib.ge2b_version.restype = C.c_char_p
     lib.ge2b_last_route.restype = C.c_int
     lib.ge2b_launches_total.restype = C.c_longlong
+    lib.ge2b_dense_plan_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                           C.c_float, C.c_int, C.c_int]
+    lib.ge2b_dense_plan_create.restype = C.c_int
+    lib.ge2b_dense_plan_step.argtypes = [C.c_void_p] * 9
+    lib.ge2b_dense_plan_step.restype = C.c_int
+    lib.ge2b_dense_plan_destroy.argtypes = [C.c_void_p]
+    lib.ge2b_dense_plan_destroy.restype = None
     _LIB = lib
     return lib
 

@@ -120,7 +120,7 @@ int ge2_launch_gemm_bias_act_typed(const ge2_uintptr* bufs, int n, void* stream)
 }
 
 static int backward_common(const ge2_uintptr* bufs, const ge2_gemm_bias_act_bwd_params_t& pb, int dtype, int z_dtype,
-                           int math, void* scratch, size_t scratch_bytes, void* stream) {
+                           int math, void* scratch, size_t scratch_bytes, bool reuse_gz, void* stream) {
   DenseBackward b;
   b.M = pb.M; b.N = pb.N; b.K = pb.K;
   b.dtype = dtype; b.z_dtype = z_dtype; b.math = math;
@@ -140,7 +140,7 @@ static int backward_common(const ge2_uintptr* bufs, const ge2_gemm_bias_act_bwd_
   b.bias_kind = b.gBias ? map_bias(pb.bias_kind) : kBiasNone;
   b.act = map_act(pb.act_kind);
   b.leaky = pb.leaky_slope;
-  b.scratch = scratch; b.scratch_bytes = scratch_bytes;
+  b.scratch = scratch; b.scratch_bytes = scratch_bytes; b.reuse_gz = reuse_gz;
   return dense_backward(b, reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -148,7 +148,7 @@ int ge2_launch_gemm_bias_act_bwd_f32_ex(const ge2_uintptr* bufs, int n, void* st
   if (!bufs || n < 10) return kBadArgs;
   const auto* pb = reinterpret_cast<const ge2_gemm_bias_act_bwd_params_t*>(bufs[n - 1]);
   if (!pb) return kBadArgs;
-  return backward_common(bufs, *pb, kF32, kF32, 0, nullptr, 0, stream);
+  return backward_common(bufs, *pb, kF32, kF32, 0, nullptr, 0, false, stream);
 }
 
 int ge2_launch_gemm_bias_act_bwd_typed(const ge2_uintptr* bufs, int n, void* stream) {
@@ -158,7 +158,7 @@ int ge2_launch_gemm_bias_act_bwd_typed(const ge2_uintptr* bufs, int n, void* str
   if (!dtype_ok(pt->dtype) || !dtype_ok(pt->z_dtype)) return kBadArgs;
   const int math = (pt->dtype == GE2_DT_F32) ? (pt->math == GE2_MATH_TENSOR ? 1 : 0) : 1;
   return backward_common(bufs, pt->base, pt->dtype, pt->z_dtype, math, reinterpret_cast<void*>(bufs[9]),
-                         pt->scratch_bytes, stream);
+                         pt->scratch_bytes, pt->reuse_gz != 0, stream);
 }
 
 int ge2_launch(const char* name, const ge2_uintptr* bufs, int n, void* stream) {

@@ -74,6 +74,7 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
   const int esz = dtype_bytes(b.dtype);
   const size_t need = static_cast<size_t>(b.M) * static_cast<size_t>(b.N) * esz;
 
+  if (b.reuse_gz && !b.scratch) return kBadArgs;
   void* gZ = b.scratch;
   bool owned = false;
   if (gZ) {
@@ -87,6 +88,7 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
     return rc;
   };
 
+  if (!b.reuse_gz) {
   // gC is zero when there is no C or beta == 0 (regemm_backward.cu:184-189); gBias accumulates from zero.
   const bool fuse_gc = b.gC && b.C && b.beta != 0.f;
   if (b.gC && !fuse_gc) {
@@ -113,6 +115,7 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
   pa.act = b.act; pa.leaky = b.leaky;
   if (launch_bwd_prologue(pa, s) != cudaSuccess) return finish(kCudaError);
   g_launches.fetch_add(1, std::memory_order_relaxed);
+  }
 
   auto plain_epilogue = [&](void* D, long long ldd) {
     EpilogueArgs e{};

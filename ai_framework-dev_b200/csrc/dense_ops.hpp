@@ -38,6 +38,7 @@ struct DenseBackward {
   int act = kActNone; float leaky = 0.01f;
   float alpha = 1.f, beta = 0.f;
   void* scratch = nullptr; size_t scratch_bytes = 0;   // gZ; null: stream-ordered allocation
+  bool reuse_gz = false;   // scratch already holds gZ of this (gY, Z): skip the prologue (and leave gC / gBias alone)
 };
 
 enum : int { kOk = 0, kBadArgs = -1, kCudaError = -2, kUnimplemented = -99 };

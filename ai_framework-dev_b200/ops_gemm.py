@@ -166,10 +166,12 @@ def forward(A, B, bias=None, *, act="none", with_bias=False, leaky_slope=0.01, s
 
 
 def backward_into(A, B, gY, Z, *, act="none", with_bias=False, leaky_slope=0.01, C=None, gA_out=None, gB_out=None,
-                  gC_out=None, gBias_out=None, stream=None, work_dZ=None, lt_workspace=None, math="fp32") -> None:
+                  gC_out=None, gBias_out=None, stream=None, work_dZ=None, lt_workspace=None, math="fp32",
+                  reuse_dZ=False) -> None:
     """(A, B, gY, Z) -> gA_out, gB_out, gBias_out.  `work_dZ` is the gZ scratch (at least M*N elements of the
     tensors' dtype); without it the scratch comes from the stream-ordered allocator, which a graph capture
-    does not allow.  `lt_workspace` is accepted for signature compatibility and not used."""
+    does not allow.  `lt_workspace` is accepted for signature compatibility and not used.  With reuse_dZ the
+    scratch is taken to hold gZ already (from an earlier call with the same gY and Z) and only the GEMMs run."""
     M, K = _check_2d(A, "A")
     K2, N = _check_2d(B, "B")
     if K != K2:
@@ -216,6 +218,9 @@ def backward_into(A, B, gY, Z, *, act="none", with_bias=False, leaky_slope=0.01,
     b.leaky_slope = float(leaky_slope)
     p.dtype, p.z_dtype, p.math = dt, _dt(Z, "Z"), _math_code(math)
     p.scratch_bytes = work_dZ.numel() * work_dZ.element_size() if work_dZ is not None else 0
+    if reuse_dZ and work_dZ is None:
+        raise ValueError("reuse_dZ needs work_dZ")
+    p.reuse_gz = 1 if reuse_dZ else 0
     ptr = lambda t: t.data_ptr() if t is not None else 0   # noqa: E731
     bufs = _lib.make_bufs([ptr(A), ptr(B), ptr(C), ptr(gY), ptr(Z), ptr(gA_out), ptr(gB_out), ptr(gC_out),
                            ptr(gBias_out), ptr(work_dZ)], p)

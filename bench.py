@@ -1,0 +1,346 @@
+#!/usr/bin/env python
+"""Benchmark of the dense-layer hot path on B200.
+
+Workload (BASELINE.json configs[1]): dense layer forward + backward, M = N = K = 4096, bf16 tensors with fp32
+accumulation, fp32 bias, tanh-GELU epilogue; outputs Y, Z (pre-activation), dX, dW, db.  One step = one forward
+and one backward over one batch.  Work counted per step: 6*M*N*K flop (2 forward + 4 backward); epilogue,
+bias and reduction arithmetic is not counted.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N > 1 (under torch.distributed.run): every rank runs its own M = 4096 rows against the same W (batch sharded
+along M, weak scaling); dW and db are combined by ONE NCCL all-reduce per step, launched after the dW GEMM so
+that it overlaps the dX GEMM.  `value` counts the flop of all ranks over the slowest rank's device time.
+
+Prints ONE JSON line on rank 0.  `--impl reference` times the CPU restatement of the reference's path (the
+oracle) on this host's cores on a bounded row-slab of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M = N = K = 4096
+ACT = "gelu"
+FLOP_PER_STEP = 6.0 * M * N * K
+FLOP_FWD_LAUNCH = 2.0 * M * N * K
+METRIC = "dense_gemm_bias_gelu_fwd_bwd_throughput"
+UNIT = "TFLOP/s"
+CONFIG = {
+    "workload": "dense layer fwd+bwd, M=N=K=4096, bf16 in / fp32 accumulate, fp32 bias, GELU(tanh), outputs Y,Z,dX,dW,db",
+    "l2": "no flush: a step touches 8 tensors x 32 MiB = 256 MiB, twice the 126 MB L2",
+}
+FALLBACK_PEAK_TFLOPS = 1590.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one forward launch at this workload (see profiles/); None until captured
+FWD_LAUNCH_DRAM_BYTES = None
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"]), "measured (burst)"
+        except Exception:
+            pass
+    return FALLBACK_PEAK_TFLOPS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.004):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._loop, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr is not None:
+            self._thr.join(timeout=1.0)
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------ CPU legs
+def cpu_fwd_bwd(oracle, rows, X, W, b, dY):
+    """One forward + backward of the oracle on a slab of `rows` rows; returns seconds."""
+    t0 = time.perf_counter()
+    Y, Z = oracle.forward_f32(X[:rows], W, b, act=ACT)
+    oracle.backward_f32(X[:rows], W, dY[:rows], Z, act=ACT)
+    return time.perf_counter() - t0
+
+
+def cpu_inputs(oracle):
+    X, W, b, dY = oracle.dense_inputs(512, K, N, seed=0)        # at most 512 rows are ever sampled
+    return tuple(oracle.bf16_round(a) for a in (X, W)) + (b, oracle.bf16_round(dY))
+
+
+def cpu_rows_for(oracle, data, seconds_per_step):
+    t = cpu_fwd_bwd(oracle, 4, *data)
+    rows = int(max(1, min(512, 4 * seconds_per_step / max(t, 1e-6))))
+    return rows
+
+
+def run_cpu_baseline(target_seconds=12.0):
+    oracle = importlib.import_module("oracle.dense_oracle")
+    data = cpu_inputs(oracle)
+    rows = cpu_rows_for(oracle, data, target_seconds)
+    t = cpu_fwd_bwd(oracle, rows, *data)
+    return {"value": 6.0 * rows * N * K / t / 1e12, "unit": UNIT, "cores": oracle.n_threads(), "kind": "port",
+            "sample": f"rows 0..{rows - 1} of the M=4096 batch (all of N and K), forward + backward once, {t:.1f} s; "
+                      "fp32 fmaf chains of oracle/dense_oracle.c over bf16-rounded inputs, rows split over host threads"}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    oracle = importlib.import_module("oracle.dense_oracle")
+    data = cpu_inputs(oracle)
+    budget = 150.0 / max(1, args.steps + args.warmup)
+    rows = cpu_rows_for(oracle, data, min(budget, 10.0))
+    for _ in range(args.warmup):
+        cpu_fwd_bwd(oracle, rows, *data)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_fwd_bwd(oracle, rows, *data)
+    dt = time.perf_counter() - t0
+    value = 6.0 * rows * N * K * args.steps / dt / 1e12
+    sample = (f"each step = forward + backward of rows 0..{rows - 1} of the M=4096 batch (all of N and K) through "
+              "oracle/dense_oracle.c, the CPU restatement of the reference path (the reference has no CPU GEMM of its "
+              "own), rows split over all host threads")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": CONFIG,
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": oracle.n_threads(), "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the dense-layer path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    pkg = importlib.import_module("ai_framework-dev_b200")
+    lib = pkg.load_library()
+    og = pkg.ops_gemm
+    dev = torch.device("cuda", local)
+
+    # seeded synthetic inputs: X, dY ~ N(0,1); W ~ U(+-sqrt(6/K)); b ~ U(-0.1, 0.1); each rank its own rows
+    gen = torch.Generator(device="cpu").manual_seed(0)
+    lim = (6.0 / K) ** 0.5
+    W_h = ((torch.rand((K, N), generator=gen) * 2 - 1) * lim).bfloat16().pin_memory()
+    b_h = (torch.rand((N,), generator=gen) * 0.2 - 0.1).pin_memory()
+    gen.manual_seed(1 + rank)
+    X_h = torch.randn((M, K), generator=gen).bfloat16().pin_memory()
+    dY_h = torch.randn((M, N), generator=gen).bfloat16().pin_memory()
+    X, W, b, dY = X_h.to(dev), W_h.to(dev), b_h.to(dev), dY_h.to(dev)
+    Y = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
+    Z = torch.empty_like(Y)
+    work = torch.empty_like(Y)
+    dX = torch.empty((M, K), device=dev, dtype=torch.bfloat16)
+    dW = torch.empty((K, N), device=dev, dtype=torch.bfloat16)
+    db = torch.empty((1, N), device=dev, dtype=torch.float32)
+    comm = torch.cuda.Stream(device=dev) if world > 1 else None
+    fwd_events = []
+
+    def step(timed):
+        if timed:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        og.forward_into(X, W, out=Y, bias=b, with_bias=True, act=ACT, save_z=True, z_out=Z)
+        if timed:
+            e1.record()
+            fwd_events.append((e0, e1))
+        # dW and db first, so that their all-reduce runs under the dX GEMM
+        og.backward_into(X, W, dY, Z, act=ACT, with_bias=True, gB_out=dW, gBias_out=db, work_dZ=work)
+        handles = []
+        if world > 1:
+            comm.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(comm):
+                handles.append(dist.all_reduce(dW, async_op=True))
+                handles.append(dist.all_reduce(db, async_op=True))
+        og.backward_into(X, W, dY, Z, act=ACT, gA_out=dX, work_dZ=work, reuse_dZ=True)
+        for h in handles:
+            h.wait()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    if args.profile:
+        # a short, fixed launch sequence for a profiler capture: 2 warm-up steps, then 2 more
+        for _ in range(4):
+            if args.profile == "fwd":
+                og.forward_into(X, W, out=Y, bias=b, with_bias=True, act=ACT, save_z=True, z_out=Z)
+            else:
+                step(False)
+        barrier()
+        print(json.dumps({"profile": args.profile, "status": lib.ge2b_device_status(0)}), flush=True)
+        return
+
+    for _ in range(max(3, args.warmup)):
+        step(False)
+    barrier()
+    launches0 = lib.ge2b_launches_total()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        t0.record()
+        for _ in range(args.steps):
+            step(True)
+        t1.record()
+        barrier()
+    launches = lib.ge2b_launches_total() - launches0
+    ms = torch.tensor([t0.elapsed_time(t1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    total_ms = float(ms.item())
+    value = world * FLOP_PER_STEP * args.steps / (total_ms * 1e-3) / 1e12
+    fwd_ms = statistics.mean(a.elapsed_time(c) for a, c in fwd_events)
+    assert lib.ge2b_device_status(0) == 0, "a bounded wait inside a kernel timed out"
+
+    # ---- end to end through the host-buffer plan of the C ABI: pinned host inputs up, results down, every step
+    import ctypes as C
+    plan = C.c_void_p()
+    L = pkg._lib
+    rc = lib.ge2b_dense_plan_create(C.byref(plan), M, K, N, L.DT_BF16, L.ACT[ACT], 0.01, 1, L.MATH_TENSOR)
+    assert rc == 0, rc
+    Y_o = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    dX_o = torch.empty((M, K), dtype=torch.bfloat16).pin_memory()
+    dW_o = torch.empty((K, N), dtype=torch.bfloat16).pin_memory()
+    db_o = torch.empty((N,), dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        r = lib.ge2b_dense_plan_step(plan, X_h.data_ptr(), W_h.data_ptr(), b_h.data_ptr(), dY_h.data_ptr(),
+                                     Y_o.data_ptr(), dX_o.data_ptr(), dW_o.data_ptr(), db_o.data_ptr())
+        assert r == 0, r
+
+    e2e_steps = max(1, min(args.steps, 50))
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    with ClockSampler(local) as clk2:
+        w0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        torch.cuda.synchronize()
+        w1 = time.perf_counter()
+    e2e_ms = torch.tensor([(w1 - w0) * 1e3], device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    lib.ge2b_dense_plan_destroy(plan)
+    h2d = X_h.numel() * 2 + W_h.numel() * 2 + dY_h.numel() * 2 + b_h.numel() * 4
+    d2h = Y_o.numel() * 2 + dX_o.numel() * 2 + dW_o.numel() * 2 + db_o.numel() * 4
+    e2e_value = world * FLOP_PER_STEP * e2e_steps / (float(e2e_ms.item()) * 1e-3) / 1e12
+    # plausibility of the plan's results against the device-resident run
+    assert torch.equal(Y_o, Y.cpu()), "host-plan Y differs from the device-resident forward"
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        achieved = FLOP_FWD_LAUNCH / (fwd_ms * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(CONFIG, parallelism=f"dp{world} (rows of the batch; one all-reduce of dW+db per step)"
+                           if world > 1 else "single GPU"),
+            "clocks": clk.summary(),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "timer": "host clock around synchronous plan steps, max over ranks",
+                    "api": "ge2b_dense_plan_step (C ABI, pinned host buffers)", "clocks": clk2.summary()},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": FWD_LAUNCH_DRAM_BYTES,
+                         "kernel": "gemm_tc_kernel (forward launch: 2*M*N*K flop, CUDA events around each launch "
+                                   "inside the timed region)",
+                         "peak_source": f"MEASURED_PEAKS.json bf16_tflops, {peak_kind}",
+                         "frac_of_nominal_2250": achieved / 2250.0},
+        }
+        if world == 1 and not args.skip_cpu_baseline:
+            line["cpu_baseline"] = run_cpu_baseline()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile", default="", choices=["", "fwd", "step"],
+                    help="run a short fixed launch sequence (for ncu) instead of the benchmark")
+    ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU-oracle leg (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

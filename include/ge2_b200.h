@@ -116,12 +116,29 @@ typedef struct {
   ge2_dtype_t z_dtype;        /* of Z */
   ge2_math_t math;
   size_t scratch_bytes;       /* size of the scratch in slot 9 (0 = not stated) */
+  int reuse_gz;               /* 1: the scratch already holds gZ from an earlier call on the same gY and Z: only the
+                                 requested GEMMs run (lets a caller launch dW, start its all-reduce, then launch dX) */
 } ge2_gemm_bwd_typed_params_t;
 
 /* bufs = [A, B, C|0, gY, Z, gA|0, gB|0, gC|0, gBias|0, scratch|0, &ge2_gemm_bwd_typed_params_t] (fixed 11 slots).
  * `scratch` holds gZ (M*N elements of `dtype`); with scratch == 0 it is taken from the stream-ordered allocator.
  * Typed form of backends/cuda/ops/gemm/kernels/regemm_backward.cu:151-301. */
 int ge2_launch_gemm_bias_act_bwd_typed(const ge2_uintptr* bufs, int n, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Host-buffer plan: forward + backward of one dense layer with inputs and results in HOST memory.
+ * Counterpart of the reference's GemmPlan (graph_executor_v2/src/bindings/py_api.cpp:403-523): device buffers
+ * are allocated at creation; a step copies inputs up, runs Y = act(X.W + b) and (dX, dW, db) from dY, and copies
+ * the results down, pipelined over internal streams.  A step returns when the results are in host memory.
+ * Null result pointers are skipped.  Use page-locked host memory for full PCIe speed.  One plan serves one
+ * thread at a time.
+ * ------------------------------------------------------------------------------------------------ */
+typedef struct ge2b_dense_plan ge2b_dense_plan;
+int ge2b_dense_plan_create(ge2b_dense_plan** out, int M, int K, int N, ge2_dtype_t dtype, ge2_act_kind_t act,
+                           float leaky_slope, int has_bias, ge2_math_t math);
+int ge2b_dense_plan_step(ge2b_dense_plan* plan, const void* X, const void* W, const float* bias, const void* dY,
+                         void* Y, void* dX, void* dW, float* db);
+void ge2b_dense_plan_destroy(ge2b_dense_plan* plan);
 
 /* Bytes of gZ scratch the backward needs (mirrors GemmRequiredBackwardScratchBytes,
  * backends/cuda/ops/gemm/api.hpp:107-112, which always counts fp32). */
