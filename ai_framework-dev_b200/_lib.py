@@ -55,6 +55,7 @@ BIAS_SCALAR, BIAS_PER_M, BIAS_PER_N = 0, 1, 2
 ACT = {"none": 0, "relu": 1, "leaky_relu": 2, "leakyrelu": 2, "lrelu": 2, "gelu": 3, "sigmoid": 4, "tanh": 5}
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2
 MATH_FP32, MATH_TENSOR = 0, 1
+NOALLOC_SCRATCH_BYTES = 16 << 20
 
 # every symbol include/ge2_b200.h declares
 EXPORTS = [
@@ -64,6 +65,7 @@ EXPORTS = [
     "ge2b_backward_scratch_bytes", "ge2b_device_status", "ge2b_sm_count", "ge2b_version",
     "ge2b_last_route", "ge2b_launches_total",
     "ge2b_dense_plan_create", "ge2b_dense_plan_step", "ge2b_dense_plan_destroy",
+    "ge2_launch_gemm_bias_act_bwd_noalloc",
 ]
 
 
@@ -81,7 +83,8 @@ def load_library() -> C.CDLL:
     launch_sig = [C.POINTER(C.c_size_t), C.c_int, C.c_void_p]
     for name in ("ge2_launch_gemm_bias_act_f32", "ge2_launch_gemm_bias_act_tc_f16",
                  "ge2_launch_gemm_bias_act_f32_ex", "ge2_launch_gemm_bias_act_bwd_f32_ex",
-                 "ge2_launch_gemm_bias_act_typed", "ge2_launch_gemm_bias_act_bwd_typed"):
+                 "ge2_launch_gemm_bias_act_typed", "ge2_launch_gemm_bias_act_bwd_typed",
+                 "ge2_launch_gemm_bias_act_bwd_noalloc"):
         fn = getattr(lib, name)
         fn.argtypes = launch_sig
         fn.restype = C.c_int

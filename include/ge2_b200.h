@@ -140,6 +140,17 @@ int ge2b_dense_plan_step(ge2b_dense_plan* plan, const void* X, const void* W, co
                          void* Y, void* dX, void* dW, float* db);
 void ge2b_dense_plan_destroy(ge2b_dense_plan* plan);
 
+/* Backward for callers that may not allocate device memory and have no scratch of their own to pass: the gZ
+ * scratch is a fixed GE2B_NOALLOC_SCRATCH_BYTES array inside the library's device image (held by every GPU that
+ * loads the library, until the process exits).  This entry point has no counterpart in the reference, whose
+ * backward either receives a workspace or calls cudaMallocAsync.
+ * bufs = [A, B, C|0, gY, Z, gA|0, gB|0, gC|0, gBias|0, &ge2_gemm_bwd_typed_params_t]  (10 slots; scratch_bytes and
+ * reuse_gz of the struct are ignored).  Returns -1 when M*N*sizeof(element) > GE2B_NOALLOC_SCRATCH_BYTES.
+ * All calls on one GPU share the array: calls whose kernels may overlap on the GPU must be ordered by the caller.
+ * The first call on a device performs a one-time address lookup; make it before any stream capture begins. */
+#define GE2B_NOALLOC_SCRATCH_BYTES (16u << 20)
+int ge2_launch_gemm_bias_act_bwd_noalloc(const ge2_uintptr* bufs, int n, void* stream);
+
 /* Bytes of gZ scratch the backward needs (mirrors GemmRequiredBackwardScratchBytes,
  * backends/cuda/ops/gemm/api.hpp:107-112, which always counts fp32). */
 size_t ge2b_backward_scratch_bytes(long long M, long long N);
