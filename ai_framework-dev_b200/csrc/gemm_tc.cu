@@ -43,17 +43,19 @@ struct TcParams {
   int* status;
 };
 
-template <int kElemBytes, int kBlockN, int kStages>
+template <int kElemBytes, int kBlockN, int kStages, int kCG>
 struct TcCfg {
   static constexpr int kBlockK     = 128 / kElemBytes;    // one 128-byte swizzle row of the reduction index
   static constexpr int kUmmaK      = 32 / kElemBytes;     // reduction depth of one tcgen05.mma
-  static constexpr int kAStage     = kBlockM * 128;
-  static constexpr int kBStage     = kBlockN * 128;
+  static constexpr int kAStage     = kBlockM * 128;             // this CTA's 128 rows of A
+  static constexpr int kBStage     = (kBlockN / kCG) * 128;     // this CTA's share of B
   static constexpr int kStageBytes = kAStage + kBStage;
-  static constexpr int kTmemCols   = 2 * kBlockN;
+  static constexpr int kTmemCols   = (kCG == 2) ? 512 : 2 * kBlockN;   // pairs take all columns so both CTAs get base 0
   static constexpr int kBarBytes   = 256;
   static constexpr int kSmemBytes  = kStages * kStageBytes + kBarBytes + 1024;   // +1024: manual alignment
   static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
+  static_assert(kSmemBytes <= 232448, "operand ring exceeds the shared memory of one SM");
+  static_assert(8 * (2 * kStages + 4) + 16 <= kBarBytes, "barrier block too small");
 };
 
 // ---- row-fragment stores: one thread owns `n` (<= 32) consecutive columns of one output row ----
@@ -196,11 +198,17 @@ __device__ __forceinline__ void decode_tile(const TcParams& p, long long tile, i
   nb = r / rows_in_group;
 }
 
-template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages>
+// kCG = 1: one CTA per tile (128 x kBlockN).  kCG = 2: a pair of CTAs on neighbouring SMs shares one
+// 256 x kBlockN tile: each CTA stages its own 128 rows of A and its own half of B, the MMAs are issued by the
+// pair's first CTA and write 128 accumulator rows into each CTA's TMEM, and each CTA runs the epilogue of its
+// own rows.  Halving B's shared-memory footprint per CTA buys a deeper operand ring.
+template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
-  using Cfg = TcCfg<kElemBytes, kBlockN, kStages>;
+  using Cfg = TcCfg<kElemBytes, kBlockN, kStages, kCG>;
   constexpr bool kTf32 = (kElemBytes == 4);
+  constexpr int kTileM = kBlockM * kCG;          // rows of one scheduled tile
+  constexpr int kLocalN = kBlockN / kCG;         // B rows/columns staged by one CTA
 
   extern __shared__ uint8_t smem_raw[];
   // 128-byte swizzle needs 1024-byte aligned tile bases.
@@ -221,10 +229,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = (kCG == 2) ? ptx::cluster_ctarank() : 0u;
+  const bool leader = (cta_rank == 0);
+  const int unit = (kCG == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);   // tile walker id
+  const int n_units = (kCG == 2) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), 4); }
+    for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), 4 * kCG); }
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
@@ -232,45 +244,57 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     ptx::prefetch_tensormap(&tmB);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), Cfg::kTmemCols);
-    ptx::tmem_relinquish();
+    if constexpr (kCG == 2) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), Cfg::kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), Cfg::kTmemCols);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if constexpr (kCG == 2) ptx::cluster_sync_all();   // the peer's barriers exist before anything signals them
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
 
   const long long total_tiles = static_cast<long long>(p.batch) * p.m_blocks * p.n_blocks;
 
   if (warp == 0) {
-    // ===================== TMA producer =====================
+    // ===================== TMA producer (every CTA stages its own share) =====================
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0; bool ok = true;
-      for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (long long tile = unit; ok && tile < total_tiles; tile += n_units) {
         int b, mb, nb;
         decode_tile(p, tile, b, mb, nb);
-        const int m0 = mb * kBlockM, n0 = nb * kBlockN;
+        const int m0 = mb * kTileM + static_cast<int>(cta_rank) * kBlockM;
+        const int n0 = nb * kBlockN + static_cast<int>(cta_rank) * kLocalN;
         const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
-          const uint32_t fb = full_bar(stage);
-          ptx::mbar_arrive_expect_tx(fb, Cfg::kStageBytes);
+          // The pair's first CTA owns the "full" barrier and announces the bytes of both CTAs.
+          if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes * kCG);
+          const uint32_t fb = (kCG == 2) ? ptx::map_to_cta(full_bar(stage), 0u) : full_bar(stage);
           const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
           const uint32_t b_dst = a_dst + Cfg::kAStage;
           const int k0 = kb * Cfg::kBlockK;
+          auto load = [&](uint32_t dst, const void* tm, int c0, int c1, int c2) {
+            if constexpr (kCG == 2) ptx::tma_load_3d_pair(dst, tm, fb, c0, c1, c2);
+            else                    ptx::tma_load_3d(dst, tm, fb, c0, c1, c2);
+          };
           if constexpr (!kAMN) {
-            ptx::tma_load_3d(a_dst, &tmA, fb, k0, m0, ba);                       // box {kBlockK, 128}
+            load(a_dst, &tmA, k0, m0, ba);                                      // box {kBlockK, 128}
           } else {
 #pragma unroll
-            for (int j = 0; j < kBlockM / Cfg::kBlockK; ++j)                      // boxes {kBlockK(m), kBlockK(k)}
-              ptx::tma_load_3d(a_dst + j * (Cfg::kBlockK * 128), &tmA, fb, m0 + j * Cfg::kBlockK, k0, ba);
+            for (int j = 0; j < kBlockM / Cfg::kBlockK; ++j)                    // boxes {kBlockK(m), kBlockK(k)}
+              load(a_dst + j * (Cfg::kBlockK * 128), &tmA, m0 + j * Cfg::kBlockK, k0, ba);
           }
           if constexpr (!kBMN) {
-            ptx::tma_load_3d(b_dst, &tmB, fb, k0, n0, bb);                       // box {kBlockK, kBlockN}
+            load(b_dst, &tmB, k0, n0, bb);                                      // box {kBlockK, kLocalN}
           } else {
 #pragma unroll
-            for (int j = 0; j < kBlockN / Cfg::kBlockK; ++j)
-              ptx::tma_load_3d(b_dst + j * (Cfg::kBlockK * 128), &tmB, fb, n0 + j * Cfg::kBlockK, k0, bb);
+            for (int j = 0; j < kLocalN / Cfg::kBlockK; ++j)
+              load(b_dst + j * (Cfg::kBlockK * 128), &tmB, n0 + j * Cfg::kBlockK, k0, bb);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -278,8 +302,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ===================== MMA issuer =====================
-    if (lane == 0) {
+    // ===================== MMA issuer (first CTA of the pair only) =====================
+    if (lane == 0 && leader) {
       // Descriptor geometry.  Reduction-contiguous tiles: rows of 128 bytes, 8-row groups 1024 bytes apart,
       // a k-step of one MMA is 32 bytes inside the swizzled row.  M/N-contiguous tiles: each 128-byte row holds
       // one reduction index, 8 reduction rows form a 1024-byte group, and the next block of 128 bytes along M/N
@@ -290,8 +314,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       constexpr uint32_t kTypeMN = kTf32 ? 1u : 2u;
       constexpr uint32_t kAStep = kAMN ? Cfg::kUmmaK * 128 : 32;
       constexpr uint32_t kBStep = kBMN ? Cfg::kUmmaK * 128 : 32;
+      auto commit_both = [&](uint32_t local_bar) {
+        if constexpr (kCG == 2) {
+          ptx::umma_commit_pair(ptx::map_to_cta(local_bar, 0u));
+          ptx::umma_commit_pair(ptx::map_to_cta(local_bar, 1u));
+        } else {
+          ptx::umma_commit(local_bar);
+        }
+      };
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
-      for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+      for (long long tile = unit; ok && tile < total_tiles; tile += n_units) {
         if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kBlockN;
@@ -306,13 +338,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                      : ptx::make_smem_desc_sw128(a_src + ks * kAStep, 0u, kSbo);
             const uint64_t bd = kBMN ? ptx::make_smem_desc_sw128(b_src + ks * kBStep, kLboMN, kSboMN, kTypeMN)
                                      : ptx::make_smem_desc_sw128(b_src + ks * kBStep, 0u, kSbo);
-            ptx::umma<kTf32>(d_tmem, ad, bd, p.idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+            const uint32_t accum = (kb > 0 || ks > 0) ? 1u : 0u;
+            if constexpr (kCG == 2) ptx::umma_pair<kTf32>(d_tmem, ad, bd, p.idesc, accum);
+            else                    ptx::umma<kTf32>(d_tmem, ad, bd, p.idesc, accum);
           }
-          ptx::umma_commit(empty_bar(stage));          // frees this ring slot when the MMAs have read it
+          commit_both(empty_bar(stage));               // frees this ring slot (in both CTAs) once the MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        ptx::umma_commit(tfull_bar(acc));              // accumulator complete
+        commit_both(tfull_bar(acc));                   // accumulator complete (both CTAs' epilogues may start)
         acc ^= 1; if (acc == 0) acc_phase ^= 1u;
       }
     }
@@ -320,11 +354,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {
     // ===================== epilogue (4 warps, one TMEM lane quarter each) =====================
     const int q = warp & 3;                            // hardware rule: a warp reads lanes 32*(warp%4)..+31
+    const uint32_t tempty_leader = (kCG == 2) ? ptx::map_to_cta(tempty_bar(0), 0u) : tempty_bar(0);
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
-    for (long long tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+    for (long long tile = unit; ok && tile < total_tiles; tile += n_units) {
       int b, mb, nb;
       decode_tile(p, tile, b, mb, nb);
-      const int row = mb * kBlockM + q * 32 + lane;
+      const int row = mb * kTileM + static_cast<int>(cta_rank) * kBlockM + q * 32 + lane;
       const bool row_ok = row < p.M;
       const int n0 = nb * kBlockN;
       if (!ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { ok = false; break; }
@@ -344,7 +379,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if constexpr (kCG == 2) ptx::mbar_arrive_cluster(tempty_leader + 8u * acc);
+        else                    ptx::mbar_arrive(tempty_bar(acc));
+      }
       acc ^= 1; if (acc == 0) acc_phase ^= 1u;
     }
   }
@@ -357,11 +395,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     while (clock64() - t0 < 2000000ll) { __nanosleep(1000); }
     __syncthreads();
   }
+  if constexpr (kCG == 2) {
+    // Neither CTA may leave (or free TMEM) while its partner can still signal it or read its shared memory.
+    ptx::tc_fence_before_sync();
+    ptx::cluster_sync_all();
+  }
   if (warp == 1) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+    if constexpr (kCG == 2) ptx::tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+    else                    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
 }
+
 
 // ------------------------------------------------------------------------------------------------
 // Host side: tensor maps, configuration choice, launch.
@@ -413,10 +458,10 @@ bool tensor_vec_ok(const void* p, long long ld, long long batch_stride, int dt) 
   return aligned16(p) && (ld * esz) % 16 == 0 && (batch_stride * esz) % 16 == 0;
 }
 
-template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages>
+template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG>
 cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
-  using Cfg = TcCfg<kElemBytes, kBlockN, kStages>;
-  auto kernel = gemm_tc_kernel<kElemBytes, kAMN, kBMN, kBlockN, kStages>;
+  using Cfg = TcCfg<kElemBytes, kBlockN, kStages, kCG>;
+  auto kernel = gemm_tc_kernel<kElemBytes, kAMN, kBMN, kBlockN, kStages, kCG>;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [&] {
@@ -424,11 +469,13 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   });
   if (attr_err != cudaSuccess) return attr_err;
 
-  p.m_blocks = (g.M + kBlockM - 1) / kBlockM;
+  constexpr int kTileM = kBlockM * kCG;
+  constexpr int kLocalN = kBlockN / kCG;
+  p.m_blocks = (g.M + kTileM - 1) / kTileM;
   p.n_blocks = (g.N + kBlockN - 1) / kBlockN;
   p.k_blocks = (g.K + Cfg::kBlockK - 1) / Cfg::kBlockK;
   const int ab_format = g.in_dtype == kF32 ? 2 : (g.in_dtype == kBF16 ? 1 : 0);
-  p.idesc = ptx::make_idesc(ab_format, kAMN, kBMN, kBlockM, kBlockN);
+  p.idesc = ptx::make_idesc(ab_format, kAMN, kBMN, kTileM, kBlockN);
 
   CUtensorMap tmA, tmB;
   bool ok;
@@ -436,46 +483,69 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   if (!kAMN) ok = make_operand_map(&tmA, g.in_dtype, g.A, g.K, g.M, g.lda, g.batch, g.strideA, Cfg::kBlockK, kBlockM, false);
   else       ok = make_operand_map(&tmA, g.in_dtype, g.A, g.M, g.K, g.lda, g.batch, g.strideA, Cfg::kBlockK, Cfg::kBlockK, kWide);
   if (!ok) return cudaErrorInvalidValue;
-  if (!kBMN) ok = make_operand_map(&tmB, g.in_dtype, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, Cfg::kBlockK, kBlockN, false);
+  if (!kBMN) ok = make_operand_map(&tmB, g.in_dtype, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, Cfg::kBlockK, kLocalN, false);
   else       ok = make_operand_map(&tmB, g.in_dtype, g.B, g.N, g.K, g.ldb, g.batch, g.strideB, Cfg::kBlockK, Cfg::kBlockK, kWide);
   if (!ok) return cudaErrorInvalidValue;
 
   const long long tiles = static_cast<long long>(g.batch) * p.m_blocks * p.n_blocks;
-  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-  kernel<<<grid, kNumThreads, Cfg::kSmemBytes, s>>>(tmA, tmB, p);
-  return cudaGetLastError();
+  const long long units = sm_count() / kCG;                 // one CTA (or CTA pair) per SM (pair of SMs)
+  const int grid = static_cast<int>((tiles < units ? tiles : units) * kCG);
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, p);
 }
 
+struct TileChoice { int block_n, cta_group; };
+
 template <int kElemBytes, bool kAMN, bool kBMN>
-cudaError_t launch_bn(const GemmProblem& g, TcParams& p, int block_n, cudaStream_t s) {
-  if (block_n == 128) return launch_cfg<kElemBytes, kAMN, kBMN, 128, 6>(g, p, s);
-  return launch_cfg<kElemBytes, kAMN, kBMN, 256, 4>(g, p, s);
+cudaError_t launch_bn(const GemmProblem& g, TcParams& p, TileChoice t, cudaStream_t s) {
+  if (t.cta_group == 2) {
+    if (t.block_n == 128) return launch_cfg<kElemBytes, kAMN, kBMN, 128, 9, 2>(g, p, s);
+    return launch_cfg<kElemBytes, kAMN, kBMN, 256, 7, 2>(g, p, s);
+  }
+  if (t.block_n == 128) return launch_cfg<kElemBytes, kAMN, kBMN, 128, 6, 1>(g, p, s);
+  return launch_cfg<kElemBytes, kAMN, kBMN, 256, 4, 1>(g, p, s);
 }
 
 template <int kElemBytes>
-cudaError_t launch_major(const GemmProblem& g, TcParams& p, int block_n, cudaStream_t s) {
-  if (g.a_mn) return g.b_mn ? launch_bn<kElemBytes, true, true>(g, p, block_n, s)
-                            : launch_bn<kElemBytes, true, false>(g, p, block_n, s);
-  return g.b_mn ? launch_bn<kElemBytes, false, true>(g, p, block_n, s)
-                : launch_bn<kElemBytes, false, false>(g, p, block_n, s);
+cudaError_t launch_major(const GemmProblem& g, TcParams& p, TileChoice t, cudaStream_t s) {
+  if (g.a_mn) return g.b_mn ? launch_bn<kElemBytes, true, true>(g, p, t, s)
+                            : launch_bn<kElemBytes, true, false>(g, p, t, s);
+  return g.b_mn ? launch_bn<kElemBytes, false, true>(g, p, t, s)
+                : launch_bn<kElemBytes, false, false>(g, p, t, s);
 }
 
-// 256-wide tiles run the tensor pipe at full rate; 128-wide tiles are limited by shared-memory operand
-// bandwidth but quantise better onto the SMs.  Pick the better estimate.
-int choose_block_n(const GemmProblem& g) {
-  if (const char* e = getenv("GE2B_BLOCK_N")) {
-    const int v = atoi(e);
-    if (v == 128 || v == 256) return v;
-  }
-  if (g.N <= 128) return 128;
+// Tile choice.  Wide (256) tiles run the tensor pipe at full rate; narrow (128) tiles quantise better onto the
+// SMs.  CTA pairs need at least two row blocks to be worth their while.  GE2B_BLOCK_N / GE2B_CTA_GROUP override.
+TileChoice choose_tile(const GemmProblem& g) {
+  TileChoice t{256, 1};
+  int force_bn = 0, force_cg = 0;
+  if (const char* e = getenv("GE2B_BLOCK_N")) { const int v = atoi(e); if (v == 128 || v == 256) force_bn = v; }
+  if (const char* e = getenv("GE2B_CTA_GROUP")) { const int v = atoi(e); if (v == 1 || v == 2) force_cg = v; }
+  t.cta_group = force_cg ? force_cg : 1;
   const double sms = sm_count();
-  const long long mb = (g.M + kBlockM - 1) / kBlockM;
-  auto cost = [&](int bn, double rate) {
+  auto cost = [&](int bn, int cg, double rate) {
+    const long long mb = (g.M + 128 * cg - 1) / (128 * cg);
     const long long tiles = static_cast<long long>(g.batch) * mb * ((g.N + bn - 1) / bn);
-    const double waves = static_cast<double>((tiles + static_cast<long long>(sms) - 1) / static_cast<long long>(sms));
+    const long long units = static_cast<long long>(sms) / cg;
+    const double waves = static_cast<double>((tiles + units - 1) / units);
     return waves * bn / rate;      // time units: one 128-wide tile at full rate = 128
   };
-  return cost(256, 1.0) <= cost(128, 0.85) ? 256 : 128;
+  if (force_bn) { t.block_n = force_bn; return t; }
+  if (g.N <= 128) { t.block_n = 128; return t; }
+  t.block_n = cost(256, t.cta_group, 1.0) <= cost(128, t.cta_group, t.cta_group == 2 ? 0.95 : 0.85) ? 256 : 128;
+  return t;
 }
 
 }  // namespace
@@ -506,8 +576,8 @@ cudaError_t launch_gemm_tc(const GemmProblem& g, cudaStream_t s) {
   p.bias_vec = g.epi.bias && aligned16(g.epi.bias);
   p.status = device_status_ptr();
   if (!p.status) return cudaErrorInvalidDevice;
-  const int bn = choose_block_n(g);
-  return g.in_dtype == kF32 ? launch_major<4>(g, p, bn, s) : launch_major<2>(g, p, bn, s);
+  const TileChoice t = choose_tile(g);
+  return g.in_dtype == kF32 ? launch_major<4>(g, p, t, s) : launch_major<2>(g, p, t, s);
 }
 
 }  // namespace ge2b
