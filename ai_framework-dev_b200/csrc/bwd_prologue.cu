@@ -8,6 +8,7 @@
 // memory, and issues one fp32 atomic per column (or row) per CTA.  The bias gradient is always formed
 // from the fp32 value of gZ, before gZ is rounded to its storage type.  The buffer gZ is scratch memory
 // that the two backward GEMMs read afterwards.
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include "epilogue_math.cuh"
@@ -62,7 +63,8 @@ __device__ __forceinline__ void store8(void* base, long long off, int dt, bool v
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         if (dt == kBF16) {
-          w[t] = static_cast<unsigned>(f32_to_bf16_bits(v[2 * t])) | (static_cast<unsigned>(f32_to_bf16_bits(v[2 * t + 1])) << 16);
+          const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * t], v[2 * t + 1]);
+          w[t] = *reinterpret_cast<const unsigned*>(&h);
         } else {
           const __half2 h = __floats2half2_rn(v[2 * t], v[2 * t + 1]);
           w[t] = *reinterpret_cast<const unsigned*>(&h);
@@ -77,7 +79,7 @@ __device__ __forceinline__ void store8(void* base, long long off, int dt, bool v
   }
 }
 
-template <int ACT>
+template <int ACT, bool kFast>
 __global__ void __launch_bounds__(kTX * kTY)
 bwd_prologue_kernel(const ProParams pp) {
   const BwdPrologueArgs& a = pp.a;
@@ -102,7 +104,7 @@ bwd_prologue_kernel(const ProParams pp) {
       load8(a.Z, static_cast<long long>(m) * a.ldZ + col0, a.z_dtype, pp.z_vec != 0, ncols, z);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        gz[j] = (j < ncols) ? gy[j] * act_bwd<ACT>(z[j], a.leaky) : 0.f;
+        gz[j] = (j < ncols) ? gy[j] * act_bwd<ACT, kFast>(z[j], a.leaky) : 0.f;
         colsum[j] += gz[j];
         rowsum += gz[j];
       }
@@ -166,14 +168,22 @@ cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s) {
   pp.gz_vec = vec_ok(a.gZ, a.ldgZ, a.gz_dtype);
   pp.gc_vec = vec_ok(a.gC, a.ldgC, a.gc_dtype);
   dim3 block(kTX, kTY), grid((a.N + kTileCols - 1) / kTileCols, (a.M + kTileRows - 1) / kTileRows);
+  // gZ stored in 16 bits: the exp-based derivative forms are accurate enough (see epilogue_math.cuh)
+  const bool fast = a.gz_dtype != kF32;
+#define GE2B_LAUNCH_PRO(ACT_)                                                                   \
+  do {                                                                                          \
+    if (fast) bwd_prologue_kernel<ACT_, true><<<grid, block, 0, s>>>(pp);                       \
+    else      bwd_prologue_kernel<ACT_, false><<<grid, block, 0, s>>>(pp);                      \
+  } while (0)
   switch (a.act) {
-    case kActReLU:    bwd_prologue_kernel<kActReLU><<<grid, block, 0, s>>>(pp); break;
-    case kActLeaky:   bwd_prologue_kernel<kActLeaky><<<grid, block, 0, s>>>(pp); break;
-    case kActGELU:    bwd_prologue_kernel<kActGELU><<<grid, block, 0, s>>>(pp); break;
-    case kActSigmoid: bwd_prologue_kernel<kActSigmoid><<<grid, block, 0, s>>>(pp); break;
-    case kActTanh:    bwd_prologue_kernel<kActTanh><<<grid, block, 0, s>>>(pp); break;
-    default:          bwd_prologue_kernel<kActNone><<<grid, block, 0, s>>>(pp); break;
+    case kActReLU:    GE2B_LAUNCH_PRO(kActReLU); break;
+    case kActLeaky:   GE2B_LAUNCH_PRO(kActLeaky); break;
+    case kActGELU:    GE2B_LAUNCH_PRO(kActGELU); break;
+    case kActSigmoid: GE2B_LAUNCH_PRO(kActSigmoid); break;
+    case kActTanh:    GE2B_LAUNCH_PRO(kActTanh); break;
+    default:          GE2B_LAUNCH_PRO(kActNone); break;
   }
+#undef GE2B_LAUNCH_PRO
   return cudaGetLastError();
 }
 

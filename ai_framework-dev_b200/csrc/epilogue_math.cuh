@@ -25,33 +25,62 @@ __device__ __forceinline__ float sigmoid_stable(float x) {
   return z / (1.f + z);
 }
 
-template <int ACT>
+// kFast selects exp-based forms of tanh and sigmoid (two special-function instructions and no branches, absolute
+// error about 1e-7).  It is used only where the result is rounded to a 16-bit type afterwards; fp32 results keep
+// tanhf and the two-branch sigmoid so that they match the reference's device code.
+__device__ __forceinline__ float tanh_fast(float x) {
+#ifdef GE2B_TANH_EXP
+  return 1.f - __fdividef(2.f, 1.f + __expf(2.f * x));      // exp -> inf gives 1, exp -> 0 gives -1
+#else
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));        // one special-function instruction, rel. error 2^-11
+  return y;
+#endif
+}
+__device__ __forceinline__ float sigmoid_fast(float x) {
+#ifdef GE2B_TANH_EXP
+  return __fdividef(1.f, 1.f + __expf(-x));
+#else
+  return fmaf(0.5f, tanh_fast(0.5f * x), 0.5f);
+#endif
+}
+
+template <int ACT, bool kFast = false>
 __device__ __forceinline__ float act_fwd(float x, float leaky) {
   if constexpr (ACT == kActReLU)         return x > 0.f ? x : 0.f;
   else if constexpr (ACT == kActLeaky)   return x > 0.f ? x : leaky * x;
-  else if constexpr (ACT == kActGELU)    return 0.5f * x * (1.f + tanhf(gelu_inner(x)));
-  else if constexpr (ACT == kActSigmoid) return sigmoid_stable(x);
-  else if constexpr (ACT == kActTanh)    return tanhf(x);
+  else if constexpr (ACT == kActGELU) {
+    if constexpr (kFast) {
+      const float c = 0.7978845608f, k1 = 0.044715f;
+      const float w = fmaf(x * x, c * k1, c);               // t = x * (c + c*k1*x^2)
+      const float h = 0.5f * x;
+      return fmaf(h, tanh_fast(x * w), h);
+    } else {
+      return 0.5f * x * (1.f + tanhf(gelu_inner(x)));
+    }
+  }
+  else if constexpr (ACT == kActSigmoid) return kFast ? sigmoid_fast(x) : sigmoid_stable(x);
+  else if constexpr (ACT == kActTanh)    return kFast ? tanh_fast(x) : tanhf(x);
   else                                   return x;
 }
 
-template <int ACT>
+template <int ACT, bool kFast = false>
 __device__ __forceinline__ float act_bwd(float x, float leaky) {
   if constexpr (ACT == kActReLU)       return x > 0.f ? 1.f : 0.f;
   else if constexpr (ACT == kActLeaky) return x > 0.f ? 1.f : leaky;
   else if constexpr (ACT == kActGELU) {
     const float c = 0.7978845608f, k1 = 0.044715f;
     const float x2 = x * x;
-    float th = tanhf(gelu_inner(x));
+    float th = kFast ? tanh_fast(gelu_inner(x)) : tanhf(gelu_inner(x));
     th = fminf(fmaxf(th, -0.999999f), 0.999999f);
     const float sech2 = 1.f - th * th;
     const float dt = c * (1.f + 3.f * k1 * x2);
     return 0.5f * (1.f + th) + 0.5f * x * sech2 * dt;
   } else if constexpr (ACT == kActSigmoid) {
-    const float s = sigmoid_stable(x);
+    const float s = kFast ? sigmoid_fast(x) : sigmoid_stable(x);
     return s * (1.f - s);
   } else if constexpr (ACT == kActTanh) {
-    const float th = tanhf(x);
+    const float th = kFast ? tanh_fast(x) : tanhf(x);
     return 1.f - th * th;
   } else {
     return 1.f;

@@ -2,12 +2,13 @@
 //
 // This is the B200 replacement for the reference's fp32 SIMT forward kernel
 // (backends/cuda/ops/gemm/kernels/regemm_gemm_bias_act.cu:254-395) and for the two cublasSgemm
-// calls of its backward (regemm_backward.cu:265-291).  One persistent CTA per SM, 192 threads:
+// calls of its backward (regemm_backward.cu:265-291).  One persistent CTA per SM, 320 threads:
 //   warp 0      TMA producer: 128-byte-swizzled operand tiles into a shared-memory ring
 //   warp 1      MMA issuer:   tcgen05.mma (kind::f16 for bf16/f16, kind::tf32 for fp32) into TMEM;
 //               also owns TMEM allocation
-//   warps 2..5  epilogue:     tcgen05.ld of the finished accumulator, alpha/beta.C/bias/activation,
-//               optional pre-activation stash, one store of D
+//   warps 2..9  epilogue:     tcgen05.ld of the finished accumulator, alpha/beta.C/bias/activation,
+//               optional pre-activation stash, one store of D; two warps per TMEM lane quarter, each
+//               taking one half of the tile's columns
 // The accumulator is double-buffered in TMEM (2 x BLOCK_N columns) so the epilogue of tile i overlaps
 // the main loop of tile i+1.  Operands may be stored with either the reduction index or the M/N index
 // contiguous, which lets forward (X.W), dX (gZ.W^T) and dW (X^T.gZ) all read the caller's row-major
@@ -29,9 +30,10 @@ namespace ge2b {
 namespace {
 
 constexpr int kBlockM        = 128;   // UMMA M (one TMEM lane per output row)
-constexpr int kNumThreads    = 192;
-constexpr int kEpilogueWarp0 = 2;
+constexpr int kNumThreads    = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
+constexpr int kEpiWarps      = 8;     // two per TMEM lane quarter: each takes one half of the tile columns
 constexpr int kGroupM        = 8;     // tile rasterisation: groups of 8 row-blocks sweep the columns
+constexpr int kStoreStageWarp = 4096; // 32 rows x 32 columns x 4 bytes: one epilogue warp's transpose buffer
 
 struct TcParams {
   int M, N, K, batch;
@@ -40,6 +42,7 @@ struct TcParams {
   uint32_t idesc;
   EpilogueArgs epi;
   int d_vec, z_vec, c_vec, bias_vec;   // 16-byte vector access allowed for that tensor
+  int debug_mode;
   int* status;
 };
 
@@ -52,7 +55,8 @@ struct TcCfg {
   static constexpr int kStageBytes = kAStage + kBStage;
   static constexpr int kTmemCols   = (kCG == 2) ? 512 : 2 * kBlockN;   // pairs take all columns so both CTAs get base 0
   static constexpr int kBarBytes   = 256;
-  static constexpr int kSmemBytes  = kStages * kStageBytes + kBarBytes + 1024;   // +1024: manual alignment
+  static constexpr int kStoreStage = kEpiWarps * kStoreStageWarp;       // per-warp transpose buffers of the epilogue
+  static constexpr int kSmemBytes  = kStages * kStageBytes + kBarBytes + kStoreStage + 1024;   // +1024: alignment
   static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
   static_assert(kSmemBytes <= 232448, "operand ring exceeds the shared memory of one SM");
   static_assert(8 * (2 * kStages + 4) + 16 <= kBarBytes, "barrier block too small");
@@ -122,16 +126,69 @@ __device__ __forceinline__ void load_row_frag(const void* base, long long off, i
   }
 }
 
-template <int ACT>
-__device__ __forceinline__ void apply_act32(float (&v)[32], float leaky) {
+// Coalesced store of a 32-row x 32-column fragment held one row per lane.  Rows go through a per-warp
+// shared-memory buffer (16-byte chunks, XOR-swizzled so that neither side has bank conflicts) and leave as
+// 16-byte stores in which consecutive lanes cover consecutive bytes of a row, i.e. whole 32-byte sectors,
+// instead of 32 lanes each writing 16 bytes of a different row.
+__device__ __forceinline__ void store_frag_coalesced(uint8_t* stage, void* base, long long batch_off, long long ld,
+                                                     int dt, const float (&v)[32], int row0, int col0, int M,
+                                                     int lane) {
+  const int esz = (dt == kF32) ? 4 : 2;
+  const int chunks = 2 * esz;                       // 16-byte chunks per 32-column row: 4 (16-bit) or 8 (fp32)
+  const int swz = (chunks == 4) ? ((lane >> 1) & 3) : (lane & 7);
+  uint8_t* my_row = stage + lane * (chunks * 16);
+  if (dt == kF32) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = act_fwd<ACT>(v[j], leaky);
+    for (int c = 0; c < 8; ++c)
+      *reinterpret_cast<float4*>(my_row + ((c ^ swz) * 16)) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t w[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float lo = v[8 * c + 2 * t], hi = v[8 * c + 2 * t + 1];
+        if (dt == kBF16) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+          w[t] = *reinterpret_cast<uint32_t*>(&h);
+        } else {
+          __half2 h = __floats2half2_rn(lo, hi);
+          w[t] = *reinterpret_cast<uint32_t*>(&h);
+        }
+      }
+      *reinterpret_cast<uint4*>(my_row + ((c ^ swz) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  __syncwarp();
+  const int rows_per_pass = 32 / chunks;            // 8 or 4 rows per store instruction
+  const int c = lane % chunks;
+  uint8_t* gbase = reinterpret_cast<uint8_t*>(base) + (batch_off + col0) * esz + c * 16;
+#pragma unroll
+  for (int pass = 0; pass < 8; ++pass) {
+    if (pass * rows_per_pass >= 32) break;
+    const int r = pass * rows_per_pass + lane / chunks;
+    const int rs = (chunks == 4) ? ((r >> 1) & 3) : (r & 7);
+    const uint4 val = *reinterpret_cast<const uint4*>(stage + r * (chunks * 16) + ((c ^ rs) * 16));
+    if (row0 + r < M) *reinterpret_cast<uint4*>(gbase + static_cast<long long>(row0 + r) * ld * esz) = val;
+  }
+  __syncwarp();
+}
+
+template <int ACT>
+__device__ __forceinline__ void apply_act32(float (&v)[32], float leaky, bool fast) {
+  if (fast) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = act_fwd<ACT, true>(v[j], leaky);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = act_fwd<ACT, false>(v[j], leaky);
+  }
 }
 
 // Epilogue math for one 32-column fragment of one row (order of operations follows the reference's
 // Epilogue::apply, backends/cuda/ops/_common/shim/traits.hpp:30-73): alpha, + beta*C, + bias, stash Z, act.
 __device__ __forceinline__ void epilogue_frag(const TcParams& p, float (&v)[32], int b, int row, int col0, int ncols,
-                                              bool row_ok) {
+                                              bool row_ok, uint8_t* stage, int lane) {
   const EpilogueArgs& e = p.epi;
   if (e.alpha != 1.f) {
 #pragma unroll
@@ -167,20 +224,36 @@ __device__ __forceinline__ void epilogue_frag(const TcParams& p, float (&v)[32],
       for (int j = 0; j < 32; ++j) v[j] += bs;
     }
   }
-  if (e.Z != nullptr && row_ok)
-    store_row_frag(e.Z, static_cast<long long>(b) * e.strideZ + static_cast<long long>(row) * e.ldz + col0, e.z_dtype,
-                   v, ncols, p.z_vec != 0);
+  if (e.Z != nullptr && p.debug_mode != 3) {
+    if (p.z_vec && ncols == 32)
+      store_frag_coalesced(stage, e.Z, static_cast<long long>(b) * e.strideZ, e.ldz, e.z_dtype, v, row - lane, col0,
+                           p.M, lane);
+    else if (row_ok)
+      store_row_frag(e.Z, static_cast<long long>(b) * e.strideZ + static_cast<long long>(row) * e.ldz + col0,
+                     e.z_dtype, v, ncols, false);
+  }
+  const bool fast = e.d_dtype != kF32;       // the result is rounded to 16 bits: exp-based tanh / sigmoid suffice
   switch (e.act) {
-    case kActReLU:    apply_act32<kActReLU>(v, e.leaky); break;
-    case kActLeaky:   apply_act32<kActLeaky>(v, e.leaky); break;
-    case kActGELU:    apply_act32<kActGELU>(v, e.leaky); break;
-    case kActSigmoid: apply_act32<kActSigmoid>(v, e.leaky); break;
-    case kActTanh:    apply_act32<kActTanh>(v, e.leaky); break;
+    case kActReLU:    apply_act32<kActReLU>(v, e.leaky, false); break;
+    case kActLeaky:   apply_act32<kActLeaky>(v, e.leaky, false); break;
+    case kActGELU:    apply_act32<kActGELU>(v, e.leaky, fast); break;
+    case kActSigmoid: apply_act32<kActSigmoid>(v, e.leaky, fast); break;
+    case kActTanh:    apply_act32<kActTanh>(v, e.leaky, fast); break;
     default: break;
   }
-  if (row_ok)
+  if (p.debug_mode == 3) {     // experiment: everything but the stores
+    float acc_sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc_sum += v[j];
+    if (acc_sum == 123.456f) reinterpret_cast<float*>(e.D)[0] = acc_sum;
+    return;
+  }
+  if (p.d_vec && ncols == 32)
+    store_frag_coalesced(stage, e.D, static_cast<long long>(b) * e.strideD, e.ldd, e.d_dtype, v, row - lane, col0, p.M,
+                         lane);
+  else if (row_ok)
     store_row_frag(e.D, static_cast<long long>(b) * e.strideD + static_cast<long long>(row) * e.ldd + col0, e.d_dtype,
-                   v, ncols, p.d_vec != 0);
+                   v, ncols, false);
 }
 
 // Persistent tile order: within a batch slice, groups of kGroupM row-blocks sweep all column-blocks,
@@ -226,6 +299,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(bar_blk + 8 * (2 * kStages + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_blk + 8 * (2 * kStages + 4) + 8);
+  uint8_t* store_stage = bar_blk + Cfg::kBarBytes;    // 4 x kStoreStageWarp, 16-byte aligned
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -236,7 +310,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), 4 * kCG); }
+    for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), kEpiWarps * kCG); }
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
@@ -263,6 +337,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 0) {
     // ===================== TMA producer (every CTA stages its own share) =====================
     if (lane == 0) {
+      const uint32_t full_leader0 = (kCG == 2) ? ptx::map_to_cta(full_bar(0), 0u) : full_bar(0);
       int stage = 0; uint32_t phase = 0; bool ok = true;
       for (long long tile = unit; ok && tile < total_tiles; tile += n_units) {
         int b, mb, nb;
@@ -274,7 +349,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           // The pair's first CTA owns the "full" barrier and announces the bytes of both CTAs.
           if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes * kCG);
-          const uint32_t fb = (kCG == 2) ? ptx::map_to_cta(full_bar(stage), 0u) : full_bar(stage);
+          const uint32_t fb = full_leader0 + 8u * stage;
           const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
           const uint32_t b_dst = a_dst + Cfg::kAStage;
           const int k0 = kb * Cfg::kBlockK;
@@ -314,39 +389,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       constexpr uint32_t kTypeMN = kTf32 ? 1u : 2u;
       constexpr uint32_t kAStep = kAMN ? Cfg::kUmmaK * 128 : 32;
       constexpr uint32_t kBStep = kBMN ? Cfg::kUmmaK * 128 : 32;
-      auto commit_both = [&](uint32_t local_bar) {
-        if constexpr (kCG == 2) {
-          ptx::umma_commit_pair(ptx::map_to_cta(local_bar, 0u));
-          ptx::umma_commit_pair(ptx::map_to_cta(local_bar, 1u));
-        } else {
-          ptx::umma_commit(local_bar);
-        }
-      };
+      // Everything that does not change from one k-block to the next is computed once: the issuing thread shares
+      // its scheduler with an epilogue warp, so the per-k-block instruction stream has to stay short.
+      const uint64_t a_desc0 = kAMN ? ptx::make_smem_desc_sw128(smem_base, kLboMN, kSboMN, kTypeMN)
+                                    : ptx::make_smem_desc_sw128(smem_base, 0u, kSbo);
+      const uint64_t b_desc0 = kBMN ? ptx::make_smem_desc_sw128(smem_base + Cfg::kAStage, kLboMN, kSboMN, kTypeMN)
+                                    : ptx::make_smem_desc_sw128(smem_base + Cfg::kAStage, 0u, kSbo);
+      constexpr uint64_t kStageEnc = Cfg::kStageBytes >> 4;       // descriptor address field counts 16-byte units
+      constexpr uint64_t kAStepEnc = kAStep >> 4, kBStepEnc = kBStep >> 4;
+      const uint32_t empty0 = empty_bar(0), tfull0 = tfull_bar(0);
+      const uint32_t empty_peer0 = (kCG == 2) ? ptx::map_to_cta(empty0, 1u) : 0u;
+      const uint32_t tfull_peer0 = (kCG == 2) ? ptx::map_to_cta(tfull0, 1u) : 0u;
+      const uint32_t idesc = p.idesc;
+      const int k_blocks = p.k_blocks;
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
       for (long long tile = unit; ok && tile < total_tiles; tile += n_units) {
-        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        if (p.debug_mode != 4 && !ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kBlockN;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
           if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after_sync();
-          const uint32_t a_src = smem_base + stage * Cfg::kStageBytes;
-          const uint32_t b_src = a_src + Cfg::kAStage;
+          const uint64_t ad = a_desc0 + stage * kStageEnc;
+          const uint64_t bd = b_desc0 + stage * kStageEnc;
 #pragma unroll
           for (int ks = 0; ks < Cfg::kBlockK / Cfg::kUmmaK; ++ks) {
-            const uint64_t ad = kAMN ? ptx::make_smem_desc_sw128(a_src + ks * kAStep, kLboMN, kSboMN, kTypeMN)
-                                     : ptx::make_smem_desc_sw128(a_src + ks * kAStep, 0u, kSbo);
-            const uint64_t bd = kBMN ? ptx::make_smem_desc_sw128(b_src + ks * kBStep, kLboMN, kSboMN, kTypeMN)
-                                     : ptx::make_smem_desc_sw128(b_src + ks * kBStep, 0u, kSbo);
             const uint32_t accum = (kb > 0 || ks > 0) ? 1u : 0u;
-            if constexpr (kCG == 2) ptx::umma_pair<kTf32>(d_tmem, ad, bd, p.idesc, accum);
-            else                    ptx::umma<kTf32>(d_tmem, ad, bd, p.idesc, accum);
+            if constexpr (kCG == 2) ptx::umma_pair<kTf32>(d_tmem, ad + ks * kAStepEnc, bd + ks * kBStepEnc, idesc, accum);
+            else                    ptx::umma<kTf32>(d_tmem, ad + ks * kAStepEnc, bd + ks * kBStepEnc, idesc, accum);
           }
-          commit_both(empty_bar(stage));               // frees this ring slot (in both CTAs) once the MMAs have read it
+          // frees this ring slot (in both CTAs of a pair) once the MMAs have read it
+          if constexpr (kCG == 2) {
+            ptx::umma_commit_pair(empty0 + 8u * stage);
+            ptx::umma_commit_pair(empty_peer0 + 8u * stage);
+          } else {
+            ptx::umma_commit(empty0 + 8u * stage);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        commit_both(tfull_bar(acc));                   // accumulator complete (both CTAs' epilogues may start)
+        // accumulator complete: the epilogue warps (of both CTAs) may start
+        if constexpr (kCG == 2) {
+          ptx::umma_commit_pair(tfull0 + 8u * acc);
+          ptx::umma_commit_pair(tfull_peer0 + 8u * acc);
+        } else {
+          ptx::umma_commit(tfull0 + 8u * acc);
+        }
         acc ^= 1; if (acc == 0) acc_phase ^= 1u;
       }
     }
@@ -354,6 +442,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {
     // ===================== epilogue (4 warps, one TMEM lane quarter each) =====================
     const int q = warp & 3;                            // hardware rule: a warp reads lanes 32*(warp%4)..+31
+    const int half = (warp - 2) >> 2;                  // which half of the tile's columns this warp owns
+    constexpr int kHalfChunks = kBlockN / 64;          // 32-column chunks per half
+    uint8_t* my_stage = store_stage + (warp - 2) * kStoreStageWarp;
     const uint32_t tempty_leader = (kCG == 2) ? ptx::map_to_cta(tempty_bar(0), 0u) : tempty_bar(0);
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     for (long long tile = unit; ok && tile < total_tiles; tile += n_units) {
@@ -364,24 +455,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int n0 = nb * kBlockN;
       if (!ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
-      const uint32_t t_row = tmem_base + acc * kBlockN + (static_cast<uint32_t>(q * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < kBlockN; c += 32) {
-        const int col0 = n0 + c;
-        if (col0 >= p.N) break;                        // uniform over the warp
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(t_row + c, r);
-        ptx::tmem_wait_ld();
+      const uint32_t t_row = tmem_base + acc * kBlockN + half * (kBlockN / 2) + (static_cast<uint32_t>(q * 32) << 16);
+      const int nh0 = n0 + half * (kBlockN / 2);       // first column of this warp's half
+      // Software pipeline over 32-column chunks: the TMEM load of chunk c+1 is in flight while chunk c is being
+      // processed, and the accumulator is handed back to the MMA warp as soon as its last chunk is in registers.
+      const int n_chunks = (p.debug_mode == 1) ? 0 : max(0, min(kHalfChunks, (p.N - nh0 + 31) / 32));
+      auto release_acc = [&]() {
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (kCG == 2) ptx::mbar_arrive_cluster(tempty_leader + 8u * acc);
+          else                    ptx::mbar_arrive(tempty_bar(acc));
+        }
+      };
+      auto chunk_step = [&](int c, uint32_t (&cur)[32], uint32_t (&nxt)[32]) {
+        ptx::tmem_wait_ld();                           // `cur` has landed
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        epilogue_frag(p, v, b, row, col0, min(32, p.N - col0), row_ok);
-      }
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (kCG == 2) ptx::mbar_arrive_cluster(tempty_leader + 8u * acc);
-        else                    ptx::mbar_arrive(tempty_bar(acc));
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(cur[j]);
+        if (c + 1 < n_chunks) ptx::tmem_ld_32x32(t_row + (c + 1) * 32, nxt);
+        else                  release_acc();
+        const int col0 = nh0 + c * 32;
+        if (p.debug_mode == 2) {   // experiment: TMEM loads only
+          if (v[0] == 123.456f && v[31] == 1.f) reinterpret_cast<float*>(p.epi.D)[0] = v[5];
+          return;
+        }
+        epilogue_frag(p, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane);
+      };
+      uint32_t r0[32], r1[32];
+      if (n_chunks == 0) release_acc();
+      else ptx::tmem_ld_32x32(t_row, r0);
+#pragma unroll 1
+      for (int c = 0; c < n_chunks; c += 2) {
+        chunk_step(c, r0, r1);
+        if (c + 1 < n_chunks) chunk_step(c + 1, r1, r0);
       }
       acc ^= 1; if (acc == 0) acc_phase ^= 1u;
     }
@@ -511,8 +618,8 @@ struct TileChoice { int block_n, cta_group; };
 template <int kElemBytes, bool kAMN, bool kBMN>
 cudaError_t launch_bn(const GemmProblem& g, TcParams& p, TileChoice t, cudaStream_t s) {
   if (t.cta_group == 2) {
-    if (t.block_n == 128) return launch_cfg<kElemBytes, kAMN, kBMN, 128, 9, 2>(g, p, s);
-    return launch_cfg<kElemBytes, kAMN, kBMN, 256, 7, 2>(g, p, s);
+    if (t.block_n == 128) return launch_cfg<kElemBytes, kAMN, kBMN, 128, 8, 2>(g, p, s);
+    return launch_cfg<kElemBytes, kAMN, kBMN, 256, 6, 2>(g, p, s);
   }
   if (t.block_n == 128) return launch_cfg<kElemBytes, kAMN, kBMN, 128, 6, 1>(g, p, s);
   return launch_cfg<kElemBytes, kAMN, kBMN, 256, 4, 1>(g, p, s);
@@ -533,7 +640,9 @@ TileChoice choose_tile(const GemmProblem& g) {
   int force_bn = 0, force_cg = 0;
   if (const char* e = getenv("GE2B_BLOCK_N")) { const int v = atoi(e); if (v == 128 || v == 256) force_bn = v; }
   if (const char* e = getenv("GE2B_CTA_GROUP")) { const int v = atoi(e); if (v == 1 || v == 2) force_cg = v; }
-  t.cta_group = force_cg ? force_cg : 1;
+  // A CTA pair (256 rows per tile, half of B per CTA, deeper ring) is the faster form whenever the problem has at
+  // least two 128-row blocks; below that the second CTA of a pair would only compute padding.
+  t.cta_group = force_cg ? force_cg : (g.M > 128 ? 2 : 1);
   const double sms = sm_count();
   auto cost = [&](int bn, int cg, double rate) {
     const long long mb = (g.M + 128 * cg - 1) / (128 * cg);
@@ -544,7 +653,8 @@ TileChoice choose_tile(const GemmProblem& g) {
   };
   if (force_bn) { t.block_n = force_bn; return t; }
   if (g.N <= 128) { t.block_n = 128; return t; }
-  t.block_n = cost(256, t.cta_group, 1.0) <= cost(128, t.cta_group, t.cta_group == 2 ? 0.95 : 0.85) ? 256 : 128;
+  // measured on B200: 128-wide tiles reach about 0.72 (single CTA) / 0.6 (pair) of the 256-wide tile's rate
+  t.block_n = cost(256, t.cta_group, 1.0) <= cost(128, t.cta_group, t.cta_group == 2 ? 0.6 : 0.72) ? 256 : 128;
   return t;
 }
 
@@ -575,6 +685,7 @@ cudaError_t launch_gemm_tc(const GemmProblem& g, cudaStream_t s) {
   p.c_vec = tensor_vec_ok(g.epi.C, g.epi.ldc, g.epi.strideC, g.epi.d_dtype);
   p.bias_vec = g.epi.bias && aligned16(g.epi.bias);
   p.status = device_status_ptr();
+  if (const char* e = getenv("GE2B_DEBUG_MODE")) p.debug_mode = atoi(e);
   if (!p.status) return cudaErrorInvalidDevice;
   const TileChoice t = choose_tile(g);
   return g.in_dtype == kF32 ? launch_major<4>(g, p, t, s) : launch_major<2>(g, p, t, s);
