@@ -41,7 +41,7 @@ class ParamsTyped(C.Structure):
                 ("dtype", C.c_int), ("z_dtype", C.c_int), ("math", C.c_int),
                 ("trans_b", C.c_int), ("batch", C.c_int),
                 ("strideA", C.c_longlong), ("strideB", C.c_longlong), ("strideC", C.c_longlong),
-                ("strideD", C.c_longlong), ("strideZ", C.c_longlong)]
+                ("strideD", C.c_longlong), ("strideZ", C.c_longlong), ("trans_a", C.c_int)]
 
 
 class ParamsBwdTyped(C.Structure):
@@ -62,7 +62,7 @@ EXPORTS = [
     "ge2_launch", "ge2_launch_gemm_bias_act_f32", "ge2_launch_gemm_bias_act_tc_f16",
     "ge2_launch_gemm_bias_act_f32_ex", "ge2_launch_gemm_bias_act_bwd_f32_ex",
     "ge2_launch_gemm_bias_act_typed", "ge2_launch_gemm_bias_act_bwd_typed",
-    "ge2b_backward_scratch_bytes", "ge2b_device_status", "ge2b_sm_count", "ge2b_version",
+    "ge2b_backward_scratch_bytes", "ge2b_device_status", "ge2b_sm_count", "ge2b_set_sm_limit", "ge2b_version",
     "ge2b_last_route", "ge2b_launches_total",
     "ge2b_dense_plan_create", "ge2b_dense_plan_step", "ge2b_dense_plan_destroy",
     "ge2_launch_gemm_bias_act_bwd_noalloc",
@@ -95,6 +95,8 @@ def load_library() -> C.CDLL:
     lib.ge2b_device_status.argtypes = [C.c_int]
     lib.ge2b_device_status.restype = C.c_int
     lib.ge2b_sm_count.restype = C.c_int
+    lib.ge2b_set_sm_limit.argtypes = [C.c_int]
+    lib.ge2b_set_sm_limit.restype = None
     lib.ge2b_version.restype = C.c_char_p
     lib.ge2b_last_route.restype = C.c_int
     lib.ge2b_launches_total.restype = C.c_longlong

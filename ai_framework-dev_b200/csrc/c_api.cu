@@ -36,7 +36,7 @@ int forward_from_bufs(const ge2_uintptr* bufs, int n, const ge2_gemm_bias_act_pa
   if (px.has_bias) f.bias = reinterpret_cast<const float*>(bufs[i++]);
   if (px.save_preact) f.Z = reinterpret_cast<void*>(bufs[i++]);
   f.M = px.M; f.N = px.N; f.K = px.K;
-  f.lda = px.lda > 0 ? px.lda : (long long)px.K;
+  f.lda = px.lda > 0 ? px.lda : (long long)(f.trans_a ? px.M : px.K);
   f.ldb = px.ldb > 0 ? px.ldb : (long long)(f.trans_b ? px.K : px.N);
   f.ldc = px.ldc > 0 ? px.ldc : (long long)px.N;
   f.ldd = px.ldd > 0 ? px.ldd : (long long)px.N;
@@ -110,6 +110,7 @@ int ge2_launch_gemm_bias_act_typed(const ge2_uintptr* bufs, int n, void* stream)
   f.dtype = pt->dtype; f.z_dtype = pt->z_dtype;
   f.math = (pt->dtype == GE2_DT_F32) ? (pt->math == GE2_MATH_TENSOR ? 1 : 0) : 1;
   f.trans_b = pt->trans_b != 0;
+  f.trans_a = pt->trans_a != 0;
   const int rc = forward_from_bufs(bufs, n, pt->base, f);
   if (rc != kOk) return rc;
   f.batch = pt->batch > 1 ? pt->batch : 1;
@@ -188,6 +189,7 @@ size_t ge2b_backward_scratch_bytes(long long M, long long N) {
 }
 int ge2b_device_status(int clear) { return device_status_word(clear != 0); }
 int ge2b_sm_count(void) { return sm_count(); }
+void ge2b_set_sm_limit(int n) { set_sm_limit(n); }
 const char* ge2b_version(void) { return "ge2_b200 0.1 (sm_100a)"; }
 
 // Not part of the public header: introspection used by the test-suite and the benchmark.

@@ -49,10 +49,10 @@ int dense_forward(const DenseForward& f, cudaStream_t s) {
   GemmProblem g{};
   g.M = f.M; g.N = f.N; g.K = f.K; g.batch = batch;
   g.in_dtype = f.dtype; g.math = f.math;
-  g.a_mn = false; g.b_mn = !f.trans_b;
+  g.a_mn = f.trans_a; g.b_mn = !f.trans_b;
   g.A = f.A; g.lda = f.lda; g.strideA = batch > 1 ? f.strideA : 0;
   g.B = f.B; g.ldb = f.ldb; g.strideB = batch > 1 ? f.strideB : 0;
-  if (g.lda < f.K || g.ldb < (f.trans_b ? f.K : f.N) || f.ldd < f.N) return kBadArgs;
+  if (g.lda < (f.trans_a ? f.M : f.K) || g.ldb < (f.trans_b ? f.K : f.N) || f.ldd < f.N) return kBadArgs;
   EpilogueArgs& e = g.epi;
   e.D = f.D; e.ldd = f.ldd; e.strideD = batch > 1 ? f.strideD : 0;
   e.Z = f.Z; e.ldz = f.Z ? (f.ldz > 0 ? f.ldz : f.ldd) : 0; e.strideZ = batch > 1 ? f.strideZ : 0;

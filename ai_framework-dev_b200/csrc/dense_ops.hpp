@@ -11,6 +11,7 @@ struct DenseForward {
   int M = 0, N = 0, K = 0, batch = 1;
   int dtype = kF32, z_dtype = kF32;
   int math = 0;                         // fp32 tensors: 0 exact FMA, 1 TF32 tensor cores
+  bool trans_a = false;                 // A given as [K,M]
   bool trans_b = false;                 // B given as [N,K]
   const void* A = nullptr; long long lda = 0, strideA = 0;
   const void* B = nullptr; long long ldb = 0, strideB = 0;

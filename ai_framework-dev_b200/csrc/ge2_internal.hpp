@@ -75,5 +75,7 @@ int  device_status_word(bool clear);
 int* device_status_ptr();   // device address of the status word for the current device
 
 int  sm_count();            // cached multiprocessor count of the current device
+int  sm_budget();           // SMs the persistent GEMM may occupy: sm_count() unless lowered by set_sm_limit()
+void set_sm_limit(int n);   // n <= 0 restores "all SMs"; process-wide
 
 }  // namespace ge2b

@@ -595,7 +595,7 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   if (!ok) return cudaErrorInvalidValue;
 
   const long long tiles = static_cast<long long>(g.batch) * p.m_blocks * p.n_blocks;
-  const long long units = sm_count() / kCG;                 // one CTA (or CTA pair) per SM (pair of SMs)
+  const long long units = sm_budget() / kCG > 0 ? sm_budget() / kCG : 1;   // one CTA (or CTA pair) per SM (pair of SMs)
   const int grid = static_cast<int>((tiles < units ? tiles : units) * kCG);
 
   cudaLaunchConfig_t cfg = {};
@@ -643,7 +643,7 @@ TileChoice choose_tile(const GemmProblem& g) {
   // A CTA pair (256 rows per tile, half of B per CTA, deeper ring) is the faster form whenever the problem has at
   // least two 128-row blocks; below that the second CTA of a pair would only compute padding.
   t.cta_group = force_cg ? force_cg : (g.M > 128 ? 2 : 1);
-  const double sms = sm_count();
+  const double sms = sm_budget();
   auto cost = [&](int bn, int cg, double rate) {
     const long long mb = (g.M + 128 * cg - 1) / (128 * cg);
     const long long tiles = static_cast<long long>(g.batch) * mb * ((g.N + bn - 1) / bn);

@@ -2,6 +2,7 @@
 // report into, and the cached multiprocessor count used to size persistent grids.
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "ge2_internal.hpp"
@@ -58,6 +59,18 @@ int sm_count() {
     g_sm_count[d] = n;
   }
   return g_sm_count[d];
+}
+
+namespace {
+std::atomic<int> g_sm_limit{0};
+}
+
+void set_sm_limit(int n) { g_sm_limit.store(n > 0 ? n : 0, std::memory_order_relaxed); }
+
+int sm_budget() {
+  const int all = sm_count();
+  const int lim = g_sm_limit.load(std::memory_order_relaxed);
+  return (lim > 0 && lim < all) ? lim : all;
 }
 
 }  // namespace ge2b

@@ -94,10 +94,14 @@ def _prep_bias(bias, M: int, N: int) -> Optional[torch.Tensor]:
 
 
 def forward_into(A, B, *, out, bias=None, act="none", with_bias=False, leaky_slope=0.01, save_z=False, z_out=None,
-                 stream=None, math="fp32", alpha=1.0, trans_b=False) -> None:
-    """out = act(alpha * A @ B + bias); with save_z the pre-activation goes to z_out (which may be `out` itself
-    only when act is 'none').  Allocates nothing."""
-    M, K = _check_2d(A, "A")
+                 stream=None, math="fp32", alpha=1.0, trans_b=False, trans_a=False) -> None:
+    """out = act(alpha * op(A) @ op(B) + bias); with save_z the pre-activation goes to z_out (which may be `out`
+    itself only when act is 'none').  trans_a / trans_b read A as [K,M] / B as [N,K] in place (no copy).
+    Allocates nothing."""
+    if trans_a:
+        K, M = _check_2d(A, "A")
+    else:
+        M, K = _check_2d(A, "A")
     if trans_b:
         N, K2 = _check_2d(B, "B")
     else:
@@ -134,6 +138,7 @@ def forward_into(A, B, *, out, bias=None, act="none", with_bias=False, leaky_slo
     p.z_dtype = _dt(z_out, "z_out") if z_out is not None else dt
     p.math = _math_code(math)
     p.trans_b = 1 if trans_b else 0
+    p.trans_a = 1 if trans_a else 0
     p.batch = 1
     ptrs = [A.data_ptr(), B.data_ptr(), out.data_ptr()]
     if bias is not None:

@@ -103,6 +103,7 @@ typedef struct {
   int trans_b;                /* 1: B is given as [N,K] row-major (the Q.K^T form); ldb default becomes K */
   int batch;                  /* <= 1: a single GEMM */
   long long strideA, strideB, strideC, strideD, strideZ; /* elements between slices; 0 broadcasts an input */
+  int trans_a;                /* 1: A is given as [K,M] row-major (the X^T.gZ form); lda default becomes M */
 } ge2_gemm_typed_params_t;
 
 /* Same bufs layout as ge2_launch_gemm_bias_act_f32_ex with &ge2_gemm_typed_params_t last.  Stands in for the
@@ -159,6 +160,10 @@ size_t ge2b_backward_scratch_bytes(long long M, long long N);
  * Synchronises the device.  clear != 0 resets it. */
 int ge2b_device_status(int clear);
 int ge2b_sm_count(void);
+/* The tensor-core GEMM is a persistent kernel sized to every SM of the device.  A caller that runs a collective
+ * (NCCL) concurrently with a GEMM can leave it room: subsequent GEMM launches of this process occupy at most
+ * `n` SMs.  n <= 0 restores the default.  No counterpart in the reference (single GPU, single stream). */
+void ge2b_set_sm_limit(int n);
 const char* ge2b_version(void);
 
 /* Introspection for tests and benchmarks: which kernel family the calling thread's most recent GEMM went to
