@@ -65,6 +65,7 @@ EXPORTS = [
     "ge2b_backward_scratch_bytes", "ge2b_device_status", "ge2b_sm_count", "ge2b_set_sm_limit", "ge2b_version",
     "ge2b_last_route", "ge2b_launches_total",
     "ge2b_dense_plan_create", "ge2b_dense_plan_step", "ge2b_dense_plan_destroy",
+    "ge2b_dense_plan_submit", "ge2b_dense_plan_wait",
     "ge2_launch_gemm_bias_act_bwd_noalloc",
 ]
 
@@ -105,6 +106,10 @@ def load_library() -> C.CDLL:
     lib.ge2b_dense_plan_create.restype = C.c_int
     lib.ge2b_dense_plan_step.argtypes = [C.c_void_p] * 9
     lib.ge2b_dense_plan_step.restype = C.c_int
+    lib.ge2b_dense_plan_submit.argtypes = [C.c_void_p] * 9
+    lib.ge2b_dense_plan_submit.restype = C.c_int
+    lib.ge2b_dense_plan_wait.argtypes = [C.c_void_p]
+    lib.ge2b_dense_plan_wait.restype = C.c_int
     lib.ge2b_dense_plan_destroy.argtypes = [C.c_void_p]
     lib.ge2b_dense_plan_destroy.restype = None
     _LIB = lib

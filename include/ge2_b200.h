@@ -139,6 +139,12 @@ int ge2b_dense_plan_create(ge2b_dense_plan** out, int M, int K, int N, ge2_dtype
                            float leaky_slope, int has_bias, ge2_math_t math);
 int ge2b_dense_plan_step(ge2b_dense_plan* plan, const void* X, const void* W, const float* bias, const void* dY,
                          void* Y, void* dX, void* dW, float* db);
+/* The same step split in two: `submit` enqueues the copies and kernels and returns; `wait` blocks until the OLDEST
+ * submitted step's results are in its host buffers.  Up to two steps may be in flight (a third submit first waits
+ * for the oldest); the host buffers of a step must stay untouched until its wait returns. */
+int ge2b_dense_plan_submit(ge2b_dense_plan* plan, const void* X, const void* W, const float* bias, const void* dY,
+                           void* Y, void* dX, void* dW, float* db);
+int ge2b_dense_plan_wait(ge2b_dense_plan* plan);
 void ge2b_dense_plan_destroy(ge2b_dense_plan* plan);
 
 /* Backward for callers that may not allocate device memory and have no scratch of their own to pass: the gZ

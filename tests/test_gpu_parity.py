@@ -376,3 +376,40 @@ def test_fp32_path_against_reference_gpu_kernels(pkg, lib, oracle, act):
     for got, want in ((g["gA"], gAr), (g["gB"], gBr), (g["gBias"].ravel(), gbr)):
         err = ((got - want).abs() / want.abs().clamp_min(1.0)).max().item()
         assert err <= 1e-5 * 30, err   # different summation orders over 256..512 terms of O(1) products
+
+
+# --------------------------------------------------------------------------- host-buffer plan
+def test_host_plan_step_and_pipelined_submit(pkg, lib, oracle):
+    """ge2b_dense_plan_*: host pointers in, host pointers out; `step` and the two-in-flight submit/wait form
+    must give the results of the device-resident calls."""
+    L = pkg._lib
+    M, K, N = 512, 256, 384
+    X, W, b, dY = oracle.dense_inputs(M, K, N, seed=9)
+    hX, hW, hdY = (torch.from_numpy(oracle.bf16_round(a)).bfloat16().pin_memory() for a in (X, W, dY))
+    hb = torch.from_numpy(b).pin_memory()
+    plan = C.c_void_p()
+    assert lib.ge2b_dense_plan_create(C.byref(plan), M, K, N, L.DT_BF16, L.ACT["gelu"], 0.01, 1, L.MATH_TENSOR) == 0
+    try:
+        outs = [(torch.zeros((M, N), dtype=torch.bfloat16).pin_memory(), torch.zeros((M, K), dtype=torch.bfloat16).pin_memory(),
+                 torch.zeros((K, N), dtype=torch.bfloat16).pin_memory(), torch.zeros((N,), dtype=torch.float32).pin_memory())
+                for _ in range(3)]
+        y, dx, dw, db = outs[0]
+        assert lib.ge2b_dense_plan_step(plan, hX.data_ptr(), hW.data_ptr(), hb.data_ptr(), hdY.data_ptr(), y.data_ptr(),
+                                        dx.data_ptr(), dw.data_ptr(), db.data_ptr()) == 0
+        dX_, dW_, b_, dY_ = hX.cuda(), hW.cuda(), hb.cuda(), hdY.cuda()
+        Yd, Zd = pkg.ops_gemm.forward(dX_, dW_, b_, act="gelu", return_z=True)
+        gd = pkg.ops_gemm.backward(dX_, dW_, dY_, Zd, act="gelu", want_gBias=True)
+        torch.cuda.synchronize()
+        assert torch.equal(y, Yd.cpu()) and torch.equal(dx, gd["gA"].cpu()) and torch.equal(dw, gd["gB"].cpu())
+        np.testing.assert_allclose(db.numpy(), gd["gBias"].cpu().numpy().ravel(), rtol=1e-4, atol=3e-4)
+        # three submits with two buffer sets in flight, then drain
+        for i in (1, 2):
+            o = outs[i]
+            assert lib.ge2b_dense_plan_submit(plan, hX.data_ptr(), hW.data_ptr(), hb.data_ptr(), hdY.data_ptr(),
+                                              o[0].data_ptr(), o[1].data_ptr(), o[2].data_ptr(), o[3].data_ptr()) == 0
+        assert lib.ge2b_dense_plan_wait(plan) == 0 and lib.ge2b_dense_plan_wait(plan) == 0
+        assert lib.ge2b_dense_plan_wait(plan) == 0          # nothing outstanding: no-op
+        for i in (1, 2):
+            assert torch.equal(outs[i][0], y) and torch.equal(outs[i][1], dx) and torch.equal(outs[i][2], dw)
+    finally:
+        lib.ge2b_dense_plan_destroy(plan)
