@@ -20,7 +20,9 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <map>
 #include <mutex>
+#include <utility>
 
 #include "epilogue_math.cuh"
 #include "ge2_internal.hpp"
@@ -42,7 +44,13 @@ struct TcParams {
   uint32_t idesc;
   EpilogueArgs epi;
   int d_vec, z_vec, c_vec, bias_vec;   // 16-byte vector access allowed for that tensor
-  int debug_mode;
+  // Split-K tail: the last, partly filled wave of tiles is cut into `split` slices of the reduction so that it
+  // occupies all SMs.  Items [0, main_tiles) are whole tiles; item main_tiles + s * tail_tiles + r is slice s of
+  // tail tile r.  Slices s > 0 leave fp32 partial sums in `ws` and count into flags[r]; slice 0 adds them and
+  // runs the epilogue.
+  int main_tiles, tail_tiles, split;
+  float* ws;
+  int* flags;
   int* status;
 };
 
@@ -224,7 +232,7 @@ __device__ __forceinline__ void epilogue_frag(const TcParams& p, float (&v)[32],
       for (int j = 0; j < 32; ++j) v[j] += bs;
     }
   }
-  if (e.Z != nullptr && p.debug_mode != 3) {
+  if (e.Z != nullptr) {
     if (p.z_vec && ncols == 32)
       store_frag_coalesced(stage, e.Z, static_cast<long long>(b) * e.strideZ, e.ldz, e.z_dtype, v, row - lane, col0,
                            p.M, lane);
@@ -240,13 +248,6 @@ __device__ __forceinline__ void epilogue_frag(const TcParams& p, float (&v)[32],
     case kActSigmoid: apply_act32<kActSigmoid>(v, e.leaky, fast); break;
     case kActTanh:    apply_act32<kActTanh>(v, e.leaky, fast); break;
     default: break;
-  }
-  if (p.debug_mode == 3) {     // experiment: everything but the stores
-    float acc_sum = 0.f;
-#pragma unroll
-    for (int j = 0; j < 32; ++j) acc_sum += v[j];
-    if (acc_sum == 123.456f) reinterpret_cast<float*>(e.D)[0] = acc_sum;
-    return;
   }
   if (p.d_vec && ncols == 32)
     store_frag_coalesced(stage, e.D, static_cast<long long>(b) * e.strideD, e.ldd, e.d_dtype, v, row - lane, col0, p.M,
@@ -269,6 +270,32 @@ __device__ __forceinline__ void decode_tile(const TcParams& p, long long tile, i
   const int r = t - g * group_sz;
   mb = first_m + r % rows_in_group;
   nb = r / rows_in_group;
+}
+
+// One unit of work of the persistent loop: a tile and the range of k-blocks to reduce over.
+struct WorkItem {
+  int b, mb, nb;
+  int kb0, kb1;       // k-block range
+  int slice, tail;    // slice of a split tile (0 when the tile is whole), index of the tail tile
+  bool split;
+};
+
+__device__ __forceinline__ WorkItem decode_work(const TcParams& p, long long item) {
+  WorkItem w;
+  long long tile = item;
+  w.slice = 0; w.tail = 0; w.split = false;
+  w.kb0 = 0; w.kb1 = p.k_blocks;
+  if (item >= p.main_tiles) {
+    const int t = static_cast<int>(item - p.main_tiles);
+    w.slice = t / p.tail_tiles;
+    w.tail = t - w.slice * p.tail_tiles;
+    w.split = true;
+    tile = p.main_tiles + w.tail;
+    w.kb0 = static_cast<int>(static_cast<long long>(w.slice) * p.k_blocks / p.split);
+    w.kb1 = static_cast<int>(static_cast<long long>(w.slice + 1) * p.k_blocks / p.split);
+  }
+  decode_tile(p, tile, w.b, w.mb, w.nb);
+  return w;
 }
 
 // kCG = 1: one CTA per tile (128 x kBlockN).  kCG = 2: a pair of CTAs on neighbouring SMs shares one
@@ -332,20 +359,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
 
-  const long long total_tiles = static_cast<long long>(p.batch) * p.m_blocks * p.n_blocks;
+  const long long total_items = static_cast<long long>(p.main_tiles) + static_cast<long long>(p.tail_tiles) * p.split;
 
   if (warp == 0) {
     // ===================== TMA producer (every CTA stages its own share) =====================
     if (lane == 0) {
       const uint32_t full_leader0 = (kCG == 2) ? ptx::map_to_cta(full_bar(0), 0u) : full_bar(0);
       int stage = 0; uint32_t phase = 0; bool ok = true;
-      for (long long tile = unit; ok && tile < total_tiles; tile += n_units) {
-        int b, mb, nb;
-        decode_tile(p, tile, b, mb, nb);
-        const int m0 = mb * kTileM + static_cast<int>(cta_rank) * kBlockM;
-        const int n0 = nb * kBlockN + static_cast<int>(cta_rank) * kLocalN;
+      for (long long item = unit; ok && item < total_items; item += n_units) {
+        const WorkItem w = decode_work(p, item);
+        const int b = w.b;
+        const int m0 = w.mb * kTileM + static_cast<int>(cta_rank) * kBlockM;
+        const int n0 = w.nb * kBlockN + static_cast<int>(cta_rank) * kLocalN;
         const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           // The pair's first CTA owns the "full" barrier and announces the bytes of both CTAs.
           if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes * kCG);
@@ -401,10 +428,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t empty_peer0 = (kCG == 2) ? ptx::map_to_cta(empty0, 1u) : 0u;
       const uint32_t tfull_peer0 = (kCG == 2) ? ptx::map_to_cta(tfull0, 1u) : 0u;
       const uint32_t idesc = p.idesc;
-      const int k_blocks = p.k_blocks;
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
-      for (long long tile = unit; ok && tile < total_tiles; tile += n_units) {
-        if (p.debug_mode != 4 && !ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+      for (long long item = unit; ok && item < total_items; item += n_units) {
+        int k_blocks = p.k_blocks;
+        if (item >= p.main_tiles) { const WorkItem w = decode_work(p, item); k_blocks = w.kb1 - w.kb0; }
+        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kBlockN;
         for (int kb = 0; kb < k_blocks; ++kb) {
@@ -447,19 +475,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* my_stage = store_stage + (warp - 2) * kStoreStageWarp;
     const uint32_t tempty_leader = (kCG == 2) ? ptx::map_to_cta(tempty_bar(0), 0u) : tempty_bar(0);
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
-    for (long long tile = unit; ok && tile < total_tiles; tile += n_units) {
-      int b, mb, nb;
-      decode_tile(p, tile, b, mb, nb);
-      const int row = mb * kTileM + static_cast<int>(cta_rank) * kBlockM + q * 32 + lane;
+    for (long long item = unit; ok && item < total_items; item += n_units) {
+      const WorkItem w = decode_work(p, item);
+      const int b = w.b;
+      const int row_in_tile = static_cast<int>(cta_rank) * kBlockM + q * 32 + lane;
+      const int row = w.mb * kTileM + row_in_tile;
       const bool row_ok = row < p.M;
-      const int n0 = nb * kBlockN;
+      const int n0 = w.nb * kBlockN;
+      // fp32 partial sums of split tiles: [slice-1][tail tile][row in tile][column in tile]
+      const size_t tile_elems = static_cast<size_t>(kTileM) * kBlockN;
+      float* ws_row = nullptr;
+      if (w.split)
+        ws_row = p.ws + (static_cast<size_t>(w.slice > 0 ? w.slice - 1 : 0) * p.tail_tiles + w.tail) * tile_elems +
+                 static_cast<size_t>(row_in_tile) * kBlockN + half * (kBlockN / 2);
       if (!ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const uint32_t t_row = tmem_base + acc * kBlockN + half * (kBlockN / 2) + (static_cast<uint32_t>(q * 32) << 16);
       const int nh0 = n0 + half * (kBlockN / 2);       // first column of this warp's half
-      // Software pipeline over 32-column chunks: the TMEM load of chunk c+1 is in flight while chunk c is being
-      // processed, and the accumulator is handed back to the MMA warp as soon as its last chunk is in registers.
-      const int n_chunks = (p.debug_mode == 1) ? 0 : max(0, min(kHalfChunks, (p.N - nh0 + 31) / 32));
+      const int n_chunks = max(0, min(kHalfChunks, (p.N - nh0 + 31) / 32));
+      if (w.split && w.slice == 0) {
+        // wait until every epilogue warp of the other slices has published its partial sums (bounded)
+        const int expect = (p.split - 1) * kEpiWarps * kCG;
+        const volatile int* flag = p.flags + w.tail;
+        const long long t0 = clock64();
+        while (*flag < expect) {
+          __nanosleep(200);
+          if (*abort_flag != 0 || clock64() - t0 > ptx::kWaitBudgetCycles) { *abort_flag = 1; break; }
+        }
+        __threadfence();
+      }
       auto release_acc = [&]() {
         ptx::tc_fence_before_sync();
         __syncwarp();
@@ -468,27 +512,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           else                    ptx::mbar_arrive(tempty_bar(acc));
         }
       };
-      auto chunk_step = [&](int c, uint32_t (&cur)[32], uint32_t (&nxt)[32]) {
-        ptx::tmem_wait_ld();                           // `cur` has landed
+      // Two warps share each scheduler, so one warp's TMEM load latency is covered by the other's arithmetic; the
+      // accumulator goes back to the MMA warp as soon as this warp's last chunk is in registers.
+      auto chunk_step = [&](int c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(t_row + c * 32, r);
+        ptx::tmem_wait_ld();
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(cur[j]);
-        if (c + 1 < n_chunks) ptx::tmem_ld_32x32(t_row + (c + 1) * 32, nxt);
-        else                  release_acc();
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (c + 1 == n_chunks) release_acc();
         const int col0 = nh0 + c * 32;
-        if (p.debug_mode == 2) {   // experiment: TMEM loads only
-          if (v[0] == 123.456f && v[31] == 1.f) reinterpret_cast<float*>(p.epi.D)[0] = v[5];
-          return;
+        if (w.split) {
+          if (w.slice > 0) {                           // publish this slice's partial sums and go on
+            if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                __stcg(reinterpret_cast<float4*>(ws_row + c * 32) + j,
+                       make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+            }
+            return;
+          }
+          for (int sl = 0; row_ok && sl + 1 < p.split; ++sl) {   // slice 0: add the others' partial sums
+            const float* src = ws_row + static_cast<size_t>(sl) * p.tail_tiles * tile_elems + c * 32;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 f = __ldcg(reinterpret_cast<const float4*>(src) + j);
+              v[4 * j] += f.x; v[4 * j + 1] += f.y; v[4 * j + 2] += f.z; v[4 * j + 3] += f.w;
+            }
+          }
         }
         epilogue_frag(p, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane);
       };
-      uint32_t r0[32], r1[32];
       if (n_chunks == 0) release_acc();
-      else ptx::tmem_ld_32x32(t_row, r0);
 #pragma unroll 1
-      for (int c = 0; c < n_chunks; c += 2) {
-        chunk_step(c, r0, r1);
-        if (c + 1 < n_chunks) chunk_step(c + 1, r1, r0);
+      for (int c = 0; c < n_chunks; ++c) chunk_step(c);
+      if (w.split && w.slice > 0) {                    // this warp's share of the partial tile is written
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.flags + w.tail, 1);
       }
       acc ^= 1; if (acc == 0) acc_phase ^= 1u;
     }
@@ -565,6 +627,33 @@ bool tensor_vec_ok(const void* p, long long ld, long long batch_stride, int dt) 
   return aligned16(p) && (ld * esz) % 16 == 0 && (batch_stride * esz) % 16 == 0;
 }
 
+// Scratch of the split-K tail (fp32 partial tiles + one arrival counter per tail tile).  One buffer per
+// (device, stream), created the first time a launch on that stream needs it and kept for the life of the process:
+// launches on one stream are ordered, launches on different streams get different buffers.  Creating it allocates
+// device memory, so the first split launch on a stream must happen outside stream capture (warm the shape up once).
+struct SplitScratch { float* ws = nullptr; int* flags = nullptr; size_t ws_bytes = 0; };
+constexpr size_t kSplitWsBytes = 64u << 20;
+constexpr int kSplitMaxTail = 256;
+
+SplitScratch* split_scratch(cudaStream_t s) {
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, SplitScratch> table;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  SplitScratch& sc = table[{dev, s}];
+  if (!sc.ws) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
+    if (cudaMalloc(reinterpret_cast<void**>(&sc.ws), kSplitWsBytes) != cudaSuccess) { sc.ws = nullptr; return nullptr; }
+    if (cudaMalloc(reinterpret_cast<void**>(&sc.flags), kSplitMaxTail * sizeof(int)) != cudaSuccess) {
+      cudaFree(sc.ws); sc.ws = nullptr; return nullptr;
+    }
+    sc.ws_bytes = kSplitWsBytes;
+  }
+  return &sc;
+}
+
 template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG>
 cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   using Cfg = TcCfg<kElemBytes, kBlockN, kStages, kCG>;
@@ -596,7 +685,34 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
 
   const long long tiles = static_cast<long long>(g.batch) * p.m_blocks * p.n_blocks;
   const long long units = sm_budget() / kCG > 0 ? sm_budget() / kCG : 1;   // one CTA (or CTA pair) per SM (pair of SMs)
-  const int grid = static_cast<int>((tiles < units ? tiles : units) * kCG);
+
+  // Split-K: a problem whose tiles fill at most half of the machine is cut along the reduction as well.
+  p.main_tiles = static_cast<int>(tiles);
+  p.tail_tiles = 0;
+  p.split = 1;
+  const long long rem = tiles % units;
+  static const bool split_off = [] { const char* e = getenv("GE2B_SPLITK"); return e && atoi(e) == 0; }();
+  // Only problems smaller than one wave are split: with several waves the measured gain of splitting just the last
+  // one (half a wave at 4096^3) was eaten by the exchange of partial sums and the slower full-machine wave.
+  if (!split_off && tiles < units && 2 * rem <= units && rem <= kSplitMaxTail) {
+    long long sp = units / rem;
+    if (sp > 8) sp = 8;
+    if (sp > p.k_blocks / 8) sp = p.k_blocks / 8;               // keep at least 8 k-blocks per slice
+    const size_t need = static_cast<size_t>(sp > 1 ? sp - 1 : 0) * rem * kTileM * kBlockN * sizeof(float);
+    if (sp >= 2 && need <= kSplitWsBytes) {
+      if (SplitScratch* sc = split_scratch(s)) {
+        if (cudaMemsetAsync(sc->flags, 0, static_cast<size_t>(rem) * sizeof(int), s) != cudaSuccess)
+          return cudaErrorUnknown;
+        p.main_tiles = static_cast<int>(tiles - rem);
+        p.tail_tiles = static_cast<int>(rem);
+        p.split = static_cast<int>(sp);
+        p.ws = sc->ws;
+        p.flags = sc->flags;
+      }
+    }
+  }
+  const long long items = static_cast<long long>(p.main_tiles) + static_cast<long long>(p.tail_tiles) * p.split;
+  const int grid = static_cast<int>((items < units ? items : units) * kCG);
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
@@ -685,7 +801,6 @@ cudaError_t launch_gemm_tc(const GemmProblem& g, cudaStream_t s) {
   p.c_vec = tensor_vec_ok(g.epi.C, g.epi.ldc, g.epi.strideC, g.epi.d_dtype);
   p.bias_vec = g.epi.bias && aligned16(g.epi.bias);
   p.status = device_status_ptr();
-  if (const char* e = getenv("GE2B_DEBUG_MODE")) p.debug_mode = atoi(e);
   if (!p.status) return cudaErrorInvalidDevice;
   const TileChoice t = choose_tile(g);
   return g.in_dtype == kF32 ? launch_major<4>(g, p, t, s) : launch_major<2>(g, p, t, s);

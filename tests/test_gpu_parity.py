@@ -413,3 +413,15 @@ def test_host_plan_step_and_pipelined_submit(pkg, lib, oracle):
             assert torch.equal(outs[i][0], y) and torch.equal(outs[i][1], dx) and torch.equal(outs[i][2], dw)
     finally:
         lib.ge2b_dense_plan_destroy(plan)
+
+
+@pytest.mark.parametrize("shape", [(16, 8192, 2048), (64, 4096, 1024), (128, 8192, 8192), (300, 2048, 512)])
+def test_split_reduction_for_small_grids(pkg, lib, oracle, shape):
+    """Few output tiles, long reduction: the launch splits the reduction across SMs and adds fp32 partial sums."""
+    M, K, N = shape
+    errs = tc_case(pkg, lib, oracle, M, K, N, torch.bfloat16, "fp32", "gelu", seed=5)
+    assert all(e <= FRO_TOL for e in errs.values()), errs
+    # the same call twice gives the same bits (fixed order of the partial sums)
+    X = torch.randn(M, K, device="cuda").bfloat16()
+    W = (torch.randn(K, N, device="cuda") / 32).bfloat16()
+    assert torch.equal(pkg.ops_gemm.forward(X, W), pkg.ops_gemm.forward(X, W))
