@@ -1,581 +1,12 @@
-// Tensor-core GEMM with fused epilogue for sm_100a:  D[b] = act(alpha * A[b].B[b] + beta * C[b] + bias).
-//
-// This is the B200 replacement for the reference's fp32 SIMT forward kernel
-// (backends/cuda/ops/gemm/kernels/regemm_gemm_bias_act.cu:254-395) and for the two cublasSgemm
-// calls of its backward (regemm_backward.cu:265-291).  One persistent CTA per SM, 320 threads:
-//   warp 0      TMA producer: 128-byte-swizzled operand tiles into a shared-memory ring
-//   warp 1      MMA issuer:   tcgen05.mma (kind::f16 for bf16/f16, kind::tf32 for fp32) into TMEM;
-//               also owns TMEM allocation
-//   warps 2..9  epilogue:     tcgen05.ld of the finished accumulator, alpha/beta.C/bias/activation,
-//               optional pre-activation stash, one store of D; two warps per TMEM lane quarter, each
-//               taking one half of the tile's columns
-// The accumulator is double-buffered in TMEM (2 x BLOCK_N columns) so the epilogue of tile i overlaps
-// the main loop of tile i+1.  Operands may be stored with either the reduction index or the M/N index
-// contiguous, which lets forward (X.W), dX (gZ.W^T) and dW (X^T.gZ) all read the caller's row-major
-// tensors directly, and a third tensor-map dimension carries the batch of the strided-batched form.
-// No TMA load uses cluster multicast.
-#include <cuda.h>
-#include <cuda_bf16.h>
-#include <cuda_fp16.h>
-#include <cuda_runtime.h>
-
-#include <cstdio>
+// Tensor-core GEMM: host-side helpers (tensor maps, split-K scratch), tile choice and dispatch.  The kernel template
+// lives in gemm_tc_kernel.cuh and is instantiated by the gemm_tc_inst_*.cu files.
 #include <map>
-#include <mutex>
 #include <utility>
 
-#include "epilogue_math.cuh"
-#include "ge2_internal.hpp"
-#include "sm100_ptx.cuh"
+#include "gemm_tc_kernel.cuh"
 
 namespace ge2b {
-namespace {
-
-constexpr int kBlockM        = 128;   // UMMA M (one TMEM lane per output row)
-constexpr int kNumThreads    = 320;   // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
-constexpr int kEpiWarps      = 8;     // two per TMEM lane quarter: each takes one half of the tile columns
-constexpr int kGroupM        = 8;     // tile rasterisation: groups of 8 row-blocks sweep the columns
-constexpr int kStoreStageWarp = 4096; // 32 rows x 32 columns x 4 bytes: one epilogue warp's transpose buffer
-
-struct TcParams {
-  int M, N, K, batch;
-  int m_blocks, n_blocks, k_blocks;
-  int a_bcast, b_bcast;     // operand has batch stride 0: always read slice 0
-  uint32_t idesc;
-  EpilogueArgs epi;
-  int d_vec, z_vec, c_vec, bias_vec;   // 16-byte vector access allowed for that tensor
-  // Split-K tail: the last, partly filled wave of tiles is cut into `split` slices of the reduction so that it
-  // occupies all SMs.  Items [0, main_tiles) are whole tiles; item main_tiles + s * tail_tiles + r is slice s of
-  // tail tile r.  Slices s > 0 leave fp32 partial sums in `ws` and count into flags[r]; slice 0 adds them and
-  // runs the epilogue.
-  int main_tiles, tail_tiles, split;
-  float* ws;
-  int* flags;
-  int* status;
-};
-
-template <int kElemBytes, int kBlockN, int kStages, int kCG>
-struct TcCfg {
-  static constexpr int kBlockK     = 128 / kElemBytes;    // one 128-byte swizzle row of the reduction index
-  static constexpr int kUmmaK      = 32 / kElemBytes;     // reduction depth of one tcgen05.mma
-  static constexpr int kAStage     = kBlockM * 128;             // this CTA's 128 rows of A
-  static constexpr int kBStage     = (kBlockN / kCG) * 128;     // this CTA's share of B
-  static constexpr int kStageBytes = kAStage + kBStage;
-  static constexpr int kTmemCols   = (kCG == 2) ? 512 : 2 * kBlockN;   // pairs take all columns so both CTAs get base 0
-  static constexpr int kBarBytes   = 256;
-  static constexpr int kStoreStage = kEpiWarps * kStoreStageWarp;       // per-warp transpose buffers of the epilogue
-  static constexpr int kSmemBytes  = kStages * kStageBytes + kBarBytes + kStoreStage + 1024;   // +1024: alignment
-  static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
-  static_assert(kSmemBytes <= 232448, "operand ring exceeds the shared memory of one SM");
-  static_assert(8 * (2 * kStages + 4) + 16 <= kBarBytes, "barrier block too small");
-};
-
-// ---- row-fragment stores: one thread owns `n` (<= 32) consecutive columns of one output row ----
-__device__ __forceinline__ void store_row_frag(void* base, long long off, int dt, const float (&v)[32], int n,
-                                               bool vec) {
-  if (dt == kF32) {
-    float* p = reinterpret_cast<float*>(base) + off;
-    if (vec && n == 32) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        reinterpret_cast<float4*>(p)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < n) p[j] = v[j];
-    }
-  } else {
-    unsigned short* p = reinterpret_cast<unsigned short*>(base) + off;
-    if (vec && n == 32) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t w[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float lo = v[8 * j + 2 * t], hi = v[8 * j + 2 * t + 1];
-          if (dt == kBF16) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-            w[t] = *reinterpret_cast<uint32_t*>(&h);
-          } else {
-            __half2 h = __floats2half2_rn(lo, hi);
-            w[t] = *reinterpret_cast<uint32_t*>(&h);
-          }
-        }
-        reinterpret_cast<uint4*>(p)[j] = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < n) {
-          if (dt == kBF16) p[j] = f32_to_bf16_bits(v[j]);
-          else             reinterpret_cast<__half*>(p)[j] = __float2half_rn(v[j]);
-        }
-    }
-  }
-}
-
-__device__ __forceinline__ void load_row_frag(const void* base, long long off, int dt, float (&v)[32], int n,
-                                              bool vec) {
-  if (dt == kF32) {
-    const float* p = reinterpret_cast<const float*>(base) + off;
-    if (vec && n == 32) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 f = reinterpret_cast<const float4*>(p)[j];
-        v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = (j < n) ? p[j] : 0.f;
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = (j < n) ? load_as_f32(base, off + j, dt) : 0.f;
-  }
-}
-
-// Coalesced store of a 32-row x 32-column fragment held one row per lane.  Rows go through a per-warp
-// shared-memory buffer (16-byte chunks, XOR-swizzled so that neither side has bank conflicts) and leave as
-// 16-byte stores in which consecutive lanes cover consecutive bytes of a row, i.e. whole 32-byte sectors,
-// instead of 32 lanes each writing 16 bytes of a different row.
-__device__ __forceinline__ void store_frag_coalesced(uint8_t* stage, void* base, long long batch_off, long long ld,
-                                                     int dt, const float (&v)[32], int row0, int col0, int M,
-                                                     int lane) {
-  const int esz = (dt == kF32) ? 4 : 2;
-  const int chunks = 2 * esz;                       // 16-byte chunks per 32-column row: 4 (16-bit) or 8 (fp32)
-  const int swz = (chunks == 4) ? ((lane >> 1) & 3) : (lane & 7);
-  uint8_t* my_row = stage + lane * (chunks * 16);
-  if (dt == kF32) {
-#pragma unroll
-    for (int c = 0; c < 8; ++c)
-      *reinterpret_cast<float4*>(my_row + ((c ^ swz) * 16)) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
-  } else {
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t w[4];
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const float lo = v[8 * c + 2 * t], hi = v[8 * c + 2 * t + 1];
-        if (dt == kBF16) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-          w[t] = *reinterpret_cast<uint32_t*>(&h);
-        } else {
-          __half2 h = __floats2half2_rn(lo, hi);
-          w[t] = *reinterpret_cast<uint32_t*>(&h);
-        }
-      }
-      *reinterpret_cast<uint4*>(my_row + ((c ^ swz) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-  }
-  __syncwarp();
-  const int rows_per_pass = 32 / chunks;            // 8 or 4 rows per store instruction
-  const int c = lane % chunks;
-  uint8_t* gbase = reinterpret_cast<uint8_t*>(base) + (batch_off + col0) * esz + c * 16;
-#pragma unroll
-  for (int pass = 0; pass < 8; ++pass) {
-    if (pass * rows_per_pass >= 32) break;
-    const int r = pass * rows_per_pass + lane / chunks;
-    const int rs = (chunks == 4) ? ((r >> 1) & 3) : (r & 7);
-    const uint4 val = *reinterpret_cast<const uint4*>(stage + r * (chunks * 16) + ((c ^ rs) * 16));
-    if (row0 + r < M) *reinterpret_cast<uint4*>(gbase + static_cast<long long>(row0 + r) * ld * esz) = val;
-  }
-  __syncwarp();
-}
-
-template <int ACT>
-__device__ __forceinline__ void apply_act32(float (&v)[32], float leaky, bool fast) {
-  if (fast) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = act_fwd<ACT, true>(v[j], leaky);
-  } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = act_fwd<ACT, false>(v[j], leaky);
-  }
-}
-
-// Epilogue math for one 32-column fragment of one row (order of operations follows the reference's
-// Epilogue::apply, backends/cuda/ops/_common/shim/traits.hpp:30-73): alpha, + beta*C, + bias, stash Z, act.
-__device__ __forceinline__ void epilogue_frag(const TcParams& p, float (&v)[32], int b, int row, int col0, int ncols,
-                                              bool row_ok, uint8_t* stage, int lane) {
-  const EpilogueArgs& e = p.epi;
-  if (e.alpha != 1.f) {
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] *= e.alpha;
-  }
-  if (e.C != nullptr && e.beta != 0.f && row_ok) {
-    float c[32];
-    load_row_frag(e.C, static_cast<long long>(b) * e.strideC + static_cast<long long>(row) * e.ldc + col0, e.d_dtype,
-                  c, ncols, p.c_vec != 0);
-#pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = fmaf(e.beta, c[j], v[j]);
-  }
-  if (e.bias != nullptr) {
-    if (e.bias_kind == kBiasPerN) {
-      if (p.bias_vec && ncols == 32) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float4 f = __ldg(reinterpret_cast<const float4*>(e.bias + col0) + j);
-          v[4 * j] += f.x; v[4 * j + 1] += f.y; v[4 * j + 2] += f.z; v[4 * j + 3] += f.w;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (j < ncols) v[j] += __ldg(e.bias + col0 + j);
-      }
-    } else if (e.bias_kind == kBiasPerM) {
-      const float bm = row_ok ? __ldg(e.bias + row) : 0.f;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] += bm;
-    } else if (e.bias_kind == kBiasScalar) {
-      const float bs = __ldg(e.bias);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] += bs;
-    }
-  }
-  if (e.Z != nullptr) {
-    if (p.z_vec && ncols == 32)
-      store_frag_coalesced(stage, e.Z, static_cast<long long>(b) * e.strideZ, e.ldz, e.z_dtype, v, row - lane, col0,
-                           p.M, lane);
-    else if (row_ok)
-      store_row_frag(e.Z, static_cast<long long>(b) * e.strideZ + static_cast<long long>(row) * e.ldz + col0,
-                     e.z_dtype, v, ncols, false);
-  }
-  const bool fast = e.d_dtype != kF32;       // the result is rounded to 16 bits: exp-based tanh / sigmoid suffice
-  switch (e.act) {
-    case kActReLU:    apply_act32<kActReLU>(v, e.leaky, false); break;
-    case kActLeaky:   apply_act32<kActLeaky>(v, e.leaky, false); break;
-    case kActGELU:    apply_act32<kActGELU>(v, e.leaky, fast); break;
-    case kActSigmoid: apply_act32<kActSigmoid>(v, e.leaky, fast); break;
-    case kActTanh:    apply_act32<kActTanh>(v, e.leaky, fast); break;
-    default: break;
-  }
-  if (p.d_vec && ncols == 32)
-    store_frag_coalesced(stage, e.D, static_cast<long long>(b) * e.strideD, e.ldd, e.d_dtype, v, row - lane, col0, p.M,
-                         lane);
-  else if (row_ok)
-    store_row_frag(e.D, static_cast<long long>(b) * e.strideD + static_cast<long long>(row) * e.ldd + col0, e.d_dtype,
-                   v, ncols, false);
-}
-
-// Persistent tile order: within a batch slice, groups of kGroupM row-blocks sweep all column-blocks,
-// so CTAs that run together share operand tiles through L2.
-__device__ __forceinline__ void decode_tile(const TcParams& p, long long tile, int& b, int& mb, int& nb) {
-  const int per_batch = p.m_blocks * p.n_blocks;
-  b = static_cast<int>(tile / per_batch);
-  const int t = static_cast<int>(tile - static_cast<long long>(b) * per_batch);
-  const int group_sz = kGroupM * p.n_blocks;
-  const int g = t / group_sz;
-  const int first_m = g * kGroupM;
-  const int rows_in_group = min(kGroupM, p.m_blocks - first_m);
-  const int r = t - g * group_sz;
-  mb = first_m + r % rows_in_group;
-  nb = r / rows_in_group;
-}
-
-// One unit of work of the persistent loop: a tile and the range of k-blocks to reduce over.
-struct WorkItem {
-  int b, mb, nb;
-  int kb0, kb1;       // k-block range
-  int slice, tail;    // slice of a split tile (0 when the tile is whole), index of the tail tile
-  bool split;
-};
-
-__device__ __forceinline__ WorkItem decode_work(const TcParams& p, long long item) {
-  WorkItem w;
-  long long tile = item;
-  w.slice = 0; w.tail = 0; w.split = false;
-  w.kb0 = 0; w.kb1 = p.k_blocks;
-  if (item >= p.main_tiles) {
-    const int t = static_cast<int>(item - p.main_tiles);
-    w.slice = t / p.tail_tiles;
-    w.tail = t - w.slice * p.tail_tiles;
-    w.split = true;
-    tile = p.main_tiles + w.tail;
-    w.kb0 = static_cast<int>(static_cast<long long>(w.slice) * p.k_blocks / p.split);
-    w.kb1 = static_cast<int>(static_cast<long long>(w.slice + 1) * p.k_blocks / p.split);
-  }
-  decode_tile(p, tile, w.b, w.mb, w.nb);
-  return w;
-}
-
-// kCG = 1: one CTA per tile (128 x kBlockN).  kCG = 2: a pair of CTAs on neighbouring SMs shares one
-// 256 x kBlockN tile: each CTA stages its own 128 rows of A and its own half of B, the MMAs are issued by the
-// pair's first CTA and write 128 accumulator rows into each CTA's TMEM, and each CTA runs the epilogue of its
-// own rows.  Halving B's shared-memory footprint per CTA buys a deeper operand ring.
-template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG>
-__global__ void __launch_bounds__(kNumThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
-  using Cfg = TcCfg<kElemBytes, kBlockN, kStages, kCG>;
-  constexpr bool kTf32 = (kElemBytes == 4);
-  constexpr int kTileM = kBlockM * kCG;          // rows of one scheduled tile
-  constexpr int kLocalN = kBlockN / kCG;         // B rows/columns staged by one CTA
-
-  extern __shared__ uint8_t smem_raw[];
-  // 128-byte swizzle needs 1024-byte aligned tile bases.
-  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
-  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
-  uint8_t* smem = smem_raw + pad;
-  const uint32_t smem_base = raw_addr + pad;
-
-  // Barrier block lives after the operand ring.
-  uint8_t* bar_blk = smem + kStages * Cfg::kStageBytes;
-  const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes;
-  auto full_bar   = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar  = [&](int s) { return bar_base + 8u * (kStages + s); };
-  auto tfull_bar  = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
-  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(bar_blk + 8 * (2 * kStages + 4));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_blk + 8 * (2 * kStages + 4) + 8);
-  uint8_t* store_stage = bar_blk + Cfg::kBarBytes;    // 4 x kStoreStageWarp, 16-byte aligned
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const uint32_t cta_rank = (kCG == 2) ? ptx::cluster_ctarank() : 0u;
-  const bool leader = (cta_rank == 0);
-  const int unit = (kCG == 2) ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);   // tile walker id
-  const int n_units = (kCG == 2) ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), kEpiWarps * kCG); }
-    *abort_flag = 0;
-    ptx::fence_barrier_init();
-    ptx::fence_proxy_async_smem();
-    ptx::prefetch_tensormap(&tmA);
-    ptx::prefetch_tensormap(&tmB);
-  }
-  if (warp == 1) {
-    if constexpr (kCG == 2) {
-      ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), Cfg::kTmemCols);
-      ptx::tmem_relinquish_pair();
-    } else {
-      ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), Cfg::kTmemCols);
-      ptx::tmem_relinquish();
-    }
-  }
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  if constexpr (kCG == 2) ptx::cluster_sync_all();   // the peer's barriers exist before anything signals them
-  ptx::tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_holder;
-
-  const long long total_items = static_cast<long long>(p.main_tiles) + static_cast<long long>(p.tail_tiles) * p.split;
-
-  if (warp == 0) {
-    // ===================== TMA producer (every CTA stages its own share) =====================
-    if (lane == 0) {
-      const uint32_t full_leader0 = (kCG == 2) ? ptx::map_to_cta(full_bar(0), 0u) : full_bar(0);
-      int stage = 0; uint32_t phase = 0; bool ok = true;
-      for (long long item = unit; ok && item < total_items; item += n_units) {
-        const WorkItem w = decode_work(p, item);
-        const int b = w.b;
-        const int m0 = w.mb * kTileM + static_cast<int>(cta_rank) * kBlockM;
-        const int n0 = w.nb * kBlockN + static_cast<int>(cta_rank) * kLocalN;
-        const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
-        for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
-          // The pair's first CTA owns the "full" barrier and announces the bytes of both CTAs.
-          if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes * kCG);
-          const uint32_t fb = full_leader0 + 8u * stage;
-          const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
-          const uint32_t b_dst = a_dst + Cfg::kAStage;
-          const int k0 = kb * Cfg::kBlockK;
-          auto load = [&](uint32_t dst, const void* tm, int c0, int c1, int c2) {
-            if constexpr (kCG == 2) ptx::tma_load_3d_pair(dst, tm, fb, c0, c1, c2);
-            else                    ptx::tma_load_3d(dst, tm, fb, c0, c1, c2);
-          };
-          if constexpr (!kAMN) {
-            load(a_dst, &tmA, k0, m0, ba);                                      // box {kBlockK, 128}
-          } else {
-#pragma unroll
-            for (int j = 0; j < kBlockM / Cfg::kBlockK; ++j)                    // boxes {kBlockK(m), kBlockK(k)}
-              load(a_dst + j * (Cfg::kBlockK * 128), &tmA, m0 + j * Cfg::kBlockK, k0, ba);
-          }
-          if constexpr (!kBMN) {
-            load(b_dst, &tmB, k0, n0, bb);                                      // box {kBlockK, kLocalN}
-          } else {
-#pragma unroll
-            for (int j = 0; j < kLocalN / Cfg::kBlockK; ++j)
-              load(b_dst + j * (Cfg::kBlockK * 128), &tmB, n0 + j * Cfg::kBlockK, k0, bb);
-          }
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
-        }
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    // ===================== MMA issuer (first CTA of the pair only) =====================
-    if (lane == 0 && leader) {
-      // Descriptor geometry.  Reduction-contiguous tiles: rows of 128 bytes, 8-row groups 1024 bytes apart,
-      // a k-step of one MMA is 32 bytes inside the swizzled row.  M/N-contiguous tiles: each 128-byte row holds
-      // one reduction index, 8 reduction rows form a 1024-byte group, and the next block of 128 bytes along M/N
-      // starts kBlockK rows later; a k-step is kUmmaK rows.
-      // 32-bit operands with M/N contiguous use the 32-byte-unit swizzle, whose pattern repeats every 4 rows.
-      constexpr uint32_t kLboMN = Cfg::kBlockK * 128, kSbo = 1024;
-      constexpr uint32_t kSboMN = kTf32 ? 512 : 1024;
-      constexpr uint32_t kTypeMN = kTf32 ? 1u : 2u;
-      constexpr uint32_t kAStep = kAMN ? Cfg::kUmmaK * 128 : 32;
-      constexpr uint32_t kBStep = kBMN ? Cfg::kUmmaK * 128 : 32;
-      // Everything that does not change from one k-block to the next is computed once: the issuing thread shares
-      // its scheduler with an epilogue warp, so the per-k-block instruction stream has to stay short.
-      const uint64_t a_desc0 = kAMN ? ptx::make_smem_desc_sw128(smem_base, kLboMN, kSboMN, kTypeMN)
-                                    : ptx::make_smem_desc_sw128(smem_base, 0u, kSbo);
-      const uint64_t b_desc0 = kBMN ? ptx::make_smem_desc_sw128(smem_base + Cfg::kAStage, kLboMN, kSboMN, kTypeMN)
-                                    : ptx::make_smem_desc_sw128(smem_base + Cfg::kAStage, 0u, kSbo);
-      constexpr uint64_t kStageEnc = Cfg::kStageBytes >> 4;       // descriptor address field counts 16-byte units
-      constexpr uint64_t kAStepEnc = kAStep >> 4, kBStepEnc = kBStep >> 4;
-      const uint32_t empty0 = empty_bar(0), tfull0 = tfull_bar(0);
-      const uint32_t empty_peer0 = (kCG == 2) ? ptx::map_to_cta(empty0, 1u) : 0u;
-      const uint32_t tfull_peer0 = (kCG == 2) ? ptx::map_to_cta(tfull0, 1u) : 0u;
-      const uint32_t idesc = p.idesc;
-      int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
-      for (long long item = unit; ok && item < total_items; item += n_units) {
-        int k_blocks = p.k_blocks;
-        if (item >= p.main_tiles) { const WorkItem w = decode_work(p, item); k_blocks = w.kb1 - w.kb0; }
-        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
-        ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * kBlockN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) { ok = false; break; }
-          ptx::tc_fence_after_sync();
-          const uint64_t ad = a_desc0 + stage * kStageEnc;
-          const uint64_t bd = b_desc0 + stage * kStageEnc;
-#pragma unroll
-          for (int ks = 0; ks < Cfg::kBlockK / Cfg::kUmmaK; ++ks) {
-            const uint32_t accum = (kb > 0 || ks > 0) ? 1u : 0u;
-            if constexpr (kCG == 2) ptx::umma_pair<kTf32>(d_tmem, ad + ks * kAStepEnc, bd + ks * kBStepEnc, idesc, accum);
-            else                    ptx::umma<kTf32>(d_tmem, ad + ks * kAStepEnc, bd + ks * kBStepEnc, idesc, accum);
-          }
-          // frees this ring slot (in both CTAs of a pair) once the MMAs have read it
-          if constexpr (kCG == 2) {
-            ptx::umma_commit_pair(empty0 + 8u * stage);
-            ptx::umma_commit_pair(empty_peer0 + 8u * stage);
-          } else {
-            ptx::umma_commit(empty0 + 8u * stage);
-          }
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
-        }
-        if (!ok) break;
-        // accumulator complete: the epilogue warps (of both CTAs) may start
-        if constexpr (kCG == 2) {
-          ptx::umma_commit_pair(tfull0 + 8u * acc);
-          ptx::umma_commit_pair(tfull_peer0 + 8u * acc);
-        } else {
-          ptx::umma_commit(tfull0 + 8u * acc);
-        }
-        acc ^= 1; if (acc == 0) acc_phase ^= 1u;
-      }
-    }
-    __syncwarp();
-  } else {
-    // ===================== epilogue (4 warps, one TMEM lane quarter each) =====================
-    const int q = warp & 3;                            // hardware rule: a warp reads lanes 32*(warp%4)..+31
-    const int half = (warp - 2) >> 2;                  // which half of the tile's columns this warp owns
-    constexpr int kHalfChunks = kBlockN / 64;          // 32-column chunks per half
-    uint8_t* my_stage = store_stage + (warp - 2) * kStoreStageWarp;
-    const uint32_t tempty_leader = (kCG == 2) ? ptx::map_to_cta(tempty_bar(0), 0u) : tempty_bar(0);
-    int acc = 0; uint32_t acc_phase = 0; bool ok = true;
-    for (long long item = unit; ok && item < total_items; item += n_units) {
-      const WorkItem w = decode_work(p, item);
-      const int b = w.b;
-      const int row_in_tile = static_cast<int>(cta_rank) * kBlockM + q * 32 + lane;
-      const int row = w.mb * kTileM + row_in_tile;
-      const bool row_ok = row < p.M;
-      const int n0 = w.nb * kBlockN;
-      // fp32 partial sums of split tiles: [slice-1][tail tile][row in tile][column in tile]
-      const size_t tile_elems = static_cast<size_t>(kTileM) * kBlockN;
-      float* ws_row = nullptr;
-      if (w.split)
-        ws_row = p.ws + (static_cast<size_t>(w.slice > 0 ? w.slice - 1 : 0) * p.tail_tiles + w.tail) * tile_elems +
-                 static_cast<size_t>(row_in_tile) * kBlockN + half * (kBlockN / 2);
-      if (!ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { ok = false; break; }
-      ptx::tc_fence_after_sync();
-      const uint32_t t_row = tmem_base + acc * kBlockN + half * (kBlockN / 2) + (static_cast<uint32_t>(q * 32) << 16);
-      const int nh0 = n0 + half * (kBlockN / 2);       // first column of this warp's half
-      const int n_chunks = max(0, min(kHalfChunks, (p.N - nh0 + 31) / 32));
-      if (w.split && w.slice == 0) {
-        // wait until every epilogue warp of the other slices has published its partial sums (bounded)
-        const int expect = (p.split - 1) * kEpiWarps * kCG;
-        const volatile int* flag = p.flags + w.tail;
-        const long long t0 = clock64();
-        while (*flag < expect) {
-          __nanosleep(200);
-          if (*abort_flag != 0 || clock64() - t0 > ptx::kWaitBudgetCycles) { *abort_flag = 1; break; }
-        }
-        __threadfence();
-      }
-      auto release_acc = [&]() {
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-          if constexpr (kCG == 2) ptx::mbar_arrive_cluster(tempty_leader + 8u * acc);
-          else                    ptx::mbar_arrive(tempty_bar(acc));
-        }
-      };
-      // Two warps share each scheduler, so one warp's TMEM load latency is covered by the other's arithmetic; the
-      // accumulator goes back to the MMA warp as soon as this warp's last chunk is in registers.
-      auto chunk_step = [&](int c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(t_row + c * 32, r);
-        ptx::tmem_wait_ld();
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (c + 1 == n_chunks) release_acc();
-        const int col0 = nh0 + c * 32;
-        if (w.split) {
-          if (w.slice > 0) {                           // publish this slice's partial sums and go on
-            if (row_ok) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                __stcg(reinterpret_cast<float4*>(ws_row + c * 32) + j,
-                       make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
-            }
-            return;
-          }
-          for (int sl = 0; row_ok && sl + 1 < p.split; ++sl) {   // slice 0: add the others' partial sums
-            const float* src = ws_row + static_cast<size_t>(sl) * p.tail_tiles * tile_elems + c * 32;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 f = __ldcg(reinterpret_cast<const float4*>(src) + j);
-              v[4 * j] += f.x; v[4 * j + 1] += f.y; v[4 * j + 2] += f.z; v[4 * j + 3] += f.w;
-            }
-          }
-        }
-        epilogue_frag(p, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane);
-      };
-      if (n_chunks == 0) release_acc();
-#pragma unroll 1
-      for (int c = 0; c < n_chunks; ++c) chunk_step(c);
-      if (w.split && w.slice > 0) {                    // this warp's share of the partial tile is written
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) atomicAdd(p.flags + w.tail, 1);
-      }
-      acc ^= 1; if (acc == 0) acc_phase ^= 1u;
-    }
-  }
-
-  __syncthreads();
-  if (*abort_flag != 0) {
-    // A wait ran out: give copies still in flight time to land before shared memory is released.
-    if (threadIdx.x == 0) atomicOr(p.status, kErrWaitTimeout);
-    const long long t0 = clock64();
-    while (clock64() - t0 < 2000000ll) { __nanosleep(1000); }
-    __syncthreads();
-  }
-  if constexpr (kCG == 2) {
-    // Neither CTA may leave (or free TMEM) while its partner can still signal it or read its shared memory.
-    ptx::tc_fence_before_sync();
-    ptx::cluster_sync_all();
-  }
-  if (warp == 1) {
-    ptx::tc_fence_after_sync();
-    if constexpr (kCG == 2) ptx::tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
-    else                    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
-  }
-}
-
+namespace tc {
 
 // ------------------------------------------------------------------------------------------------
 // Host side: tensor maps, configuration choice, launch.
@@ -584,7 +15,7 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-EncodeTiledFn encode_tiled_fn() {
+static EncodeTiledFn encode_tiled_fn_impl() {
   static EncodeTiledFn fn = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {
@@ -601,7 +32,7 @@ EncodeTiledFn encode_tiled_fn() {
 // out-of-range elements read as zero (which makes ragged K, M and N tiles correct without special code).
 bool make_operand_map(CUtensorMap* map, int dtype, const void* base, long long inner, long long rows, long long ld,
                       long long batch, long long batch_stride, int box_inner, int box_rows, bool swizzle_32b_units) {
-  EncodeTiledFn enc = encode_tiled_fn();
+  EncodeTiledFn enc = encode_tiled_fn_impl();
   if (!enc) return false;
   const int esz = dtype_bytes(dtype);
   const CUtensorMapDataType dt = dtype == kF32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
@@ -631,9 +62,6 @@ bool tensor_vec_ok(const void* p, long long ld, long long batch_stride, int dt) 
 // (device, stream), created the first time a launch on that stream needs it and kept for the life of the process:
 // launches on one stream are ordered, launches on different streams get different buffers.  Creating it allocates
 // device memory, so the first split launch on a stream must happen outside stream capture (warm the shape up once).
-struct SplitScratch { float* ws = nullptr; int* flags = nullptr; size_t ws_bytes = 0; };
-constexpr size_t kSplitWsBytes = 64u << 20;
-constexpr int kSplitMaxTail = 256;
 
 SplitScratch* split_scratch(cudaStream_t s) {
   static std::mutex mu;
@@ -654,92 +82,13 @@ SplitScratch* split_scratch(cudaStream_t s) {
   return &sc;
 }
 
-template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG>
-cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
-  using Cfg = TcCfg<kElemBytes, kBlockN, kStages, kCG>;
-  auto kernel = gemm_tc_kernel<kElemBytes, kAMN, kBMN, kBlockN, kStages, kCG>;
-  static std::once_flag once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [&] {
-    attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-  });
-  if (attr_err != cudaSuccess) return attr_err;
 
-  constexpr int kTileM = kBlockM * kCG;
-  constexpr int kLocalN = kBlockN / kCG;
-  p.m_blocks = (g.M + kTileM - 1) / kTileM;
-  p.n_blocks = (g.N + kBlockN - 1) / kBlockN;
-  p.k_blocks = (g.K + Cfg::kBlockK - 1) / Cfg::kBlockK;
-  const int ab_format = g.in_dtype == kF32 ? 2 : (g.in_dtype == kBF16 ? 1 : 0);
-  p.idesc = ptx::make_idesc(ab_format, kAMN, kBMN, kTileM, kBlockN);
+bool driver_has_tensor_maps() { return encode_tiled_fn_impl() != nullptr; }
 
-  CUtensorMap tmA, tmB;
-  bool ok;
-  constexpr bool kWide = (kElemBytes == 4);   // M/N-contiguous 32-bit tiles are swizzled in 32-byte units
-  if (!kAMN) ok = make_operand_map(&tmA, g.in_dtype, g.A, g.K, g.M, g.lda, g.batch, g.strideA, Cfg::kBlockK, kBlockM, false);
-  else       ok = make_operand_map(&tmA, g.in_dtype, g.A, g.M, g.K, g.lda, g.batch, g.strideA, Cfg::kBlockK, Cfg::kBlockK, kWide);
-  if (!ok) return cudaErrorInvalidValue;
-  if (!kBMN) ok = make_operand_map(&tmB, g.in_dtype, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, Cfg::kBlockK, kLocalN, false);
-  else       ok = make_operand_map(&tmB, g.in_dtype, g.B, g.N, g.K, g.ldb, g.batch, g.strideB, Cfg::kBlockK, Cfg::kBlockK, kWide);
-  if (!ok) return cudaErrorInvalidValue;
+}  // namespace tc
 
-  const long long tiles = static_cast<long long>(g.batch) * p.m_blocks * p.n_blocks;
-  const long long units = sm_budget() / kCG > 0 ? sm_budget() / kCG : 1;   // one CTA (or CTA pair) per SM (pair of SMs)
-
-  // Split-K: a problem whose tiles fill at most half of the machine is cut along the reduction as well.
-  p.main_tiles = static_cast<int>(tiles);
-  p.tail_tiles = 0;
-  p.split = 1;
-  const long long rem = tiles % units;
-  static const bool split_off = [] { const char* e = getenv("GE2B_SPLITK"); return e && atoi(e) == 0; }();
-  // Only problems smaller than one wave are split: with several waves the measured gain of splitting just the last
-  // one (half a wave at 4096^3) was eaten by the exchange of partial sums and the slower full-machine wave.
-  if (!split_off && tiles < units && 2 * rem <= units && rem <= kSplitMaxTail) {
-    long long sp = units / rem;
-    if (sp > 8) sp = 8;
-    if (sp > p.k_blocks / 8) sp = p.k_blocks / 8;               // keep at least 8 k-blocks per slice
-    const size_t need = static_cast<size_t>(sp > 1 ? sp - 1 : 0) * rem * kTileM * kBlockN * sizeof(float);
-    if (sp >= 2 && need <= kSplitWsBytes) {
-      if (SplitScratch* sc = split_scratch(s)) {
-        if (cudaMemsetAsync(sc->flags, 0, static_cast<size_t>(rem) * sizeof(int), s) != cudaSuccess)
-          return cudaErrorUnknown;
-        p.main_tiles = static_cast<int>(tiles - rem);
-        p.tail_tiles = static_cast<int>(rem);
-        p.split = static_cast<int>(sp);
-        p.ws = sc->ws;
-        p.flags = sc->flags;
-      }
-    }
-  }
-  const long long items = static_cast<long long>(p.main_tiles) + static_cast<long long>(p.tail_tiles) * p.split;
-  const int grid = static_cast<int>((items < units ? items : units) * kCG);
-
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(kNumThreads, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = kCG;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, p);
-}
-
-struct TileChoice { int block_n, cta_group; };
-
-template <int kElemBytes, bool kAMN, bool kBMN>
-cudaError_t launch_bn(const GemmProblem& g, TcParams& p, TileChoice t, cudaStream_t s) {
-  if (t.cta_group == 2) {
-    if (t.block_n == 128) return launch_cfg<kElemBytes, kAMN, kBMN, 128, 8, 2>(g, p, s);
-    return launch_cfg<kElemBytes, kAMN, kBMN, 256, 6, 2>(g, p, s);
-  }
-  if (t.block_n == 128) return launch_cfg<kElemBytes, kAMN, kBMN, 128, 6, 1>(g, p, s);
-  return launch_cfg<kElemBytes, kAMN, kBMN, 256, 4, 1>(g, p, s);
-}
+namespace {
+using namespace tc;
 
 template <int kElemBytes>
 cudaError_t launch_major(const GemmProblem& g, TcParams& p, TileChoice t, cudaStream_t s) {
@@ -767,10 +116,11 @@ TileChoice choose_tile(const GemmProblem& g) {
     const double waves = static_cast<double>((tiles + units - 1) / units);
     return waves * bn / rate;      // time units: one 128-wide tile at full rate = 128
   };
-  if (force_bn) { t.block_n = force_bn; return t; }
-  if (g.N <= 128) { t.block_n = 128; return t; }
-  // measured on B200: 128-wide tiles reach about 0.72 (single CTA) / 0.6 (pair) of the 256-wide tile's rate
-  t.block_n = cost(256, t.cta_group, 1.0) <= cost(128, t.cta_group, t.cta_group == 2 ? 0.6 : 0.72) ? 256 : 128;
+  // measured on B200: a 128-wide tile reaches about 0.72 of the 256-wide tile's rate (single CTA; the pair form
+  // of the narrow tile was slower still and is not built)
+  if (force_bn) { t.block_n = force_bn; if (t.block_n == 128) t.cta_group = 1; return t; }
+  if (g.N <= 128) { t.block_n = 128; t.cta_group = 1; return t; }
+  if (cost(256, t.cta_group, 1.0) > cost(128, 1, 0.72)) { t.block_n = 128; t.cta_group = 1; }
   return t;
 }
 
@@ -785,7 +135,7 @@ bool gemm_tc_supported(const GemmProblem& g, const char** why) {
   if ((g.lda * esz) % 16 || (g.ldb * esz) % 16) return fail("operand row pitch not a multiple of 16 bytes");
   if ((g.strideA * esz) % 16 || (g.strideB * esz) % 16) return fail("batch stride not a multiple of 16 bytes");
   if (g.strideA < 0 || g.strideB < 0) return fail("negative batch stride");
-  if (!encode_tiled_fn()) return fail("driver lacks cuTensorMapEncodeTiled");
+  if (!tc::driver_has_tensor_maps()) return fail("driver lacks cuTensorMapEncodeTiled");
   if (!g.epi.D) return fail("no output");
   return true;
 }

@@ -206,7 +206,8 @@ def run_ours(args):
     comm_sms = int(os.environ.get("GE2B_BENCH_COMM_SMS", "0"))   # SMs left free for NCCL during the overlapped GEMM
     fwd_events = []
 
-    dw_chunks = max(1, int(os.environ.get("GE2B_BENCH_DW_CHUNKS", "2")))   # row blocks of dW reduced as they finish
+    # row blocks of dW whose all-reduce starts as each finishes; a single GPU has nothing to overlap and uses one
+    dw_chunks = max(1, int(os.environ.get("GE2B_BENCH_DW_CHUNKS", "2" if world > 1 else "1")))
     rows_per_chunk = K // dw_chunks
 
     def step(timed):
@@ -377,6 +378,100 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------------------ shape sweep
+def run_sweep(args):
+    """Shape sweep of BASELINE.json configs[4] (squares and decode-like skinny M, four activations, bf16 and fp32
+    via TF32 / exact) and the batched attention GEMMs of configs[3].  One JSON line per point; not the contract line."""
+    import ctypes as C
+    import torch
+    pkg = importlib.import_module("ai_framework-dev_b200")
+    lib = pkg.load_library()
+    og = pkg.ops_gemm
+    torch.cuda.set_device(0)
+    ref = None
+    so = ROOT / "oracle" / "_ref" / "libref_gemm.so"
+    if so.exists():
+        ref = C.CDLL(str(so))
+        ref.ref_gpu_forward.restype = C.c_int
+        ref.ref_gpu_forward.argtypes = [C.c_void_p] * 3 + [C.c_longlong] + [C.c_void_p] * 2 + [C.c_int] * 4 + [C.c_float, C.c_void_p]
+        ref.ref_gpu_backward.restype = C.c_int
+        ref.ref_gpu_backward.argtypes = [C.c_void_p] * 7 + [C.c_longlong, C.c_void_p] + [C.c_int] * 4 + [C.c_float, C.c_void_p]
+    act_code = {"none": 0, "relu": 1, "gelu": 3, "sigmoid": 4}
+
+    def timeit(fn, iters, reps=8):
+        """median over `iters` samples of the mean time of `reps` back-to-back launches (host launch cost amortised)"""
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / reps)
+        return statistics.median(ts)
+
+    def dense_point(Mx, Nx, Kx, dtype, math, act, iters, with_ref=False):
+        tdt = torch.bfloat16 if dtype == "bf16" else torch.float32
+        X = torch.randn((Mx, Kx), device="cuda").to(tdt)
+        W = ((torch.rand((Kx, Nx), device="cuda") * 2 - 1) * (6.0 / Kx) ** 0.5).to(tdt)
+        b = torch.rand((Nx,), device="cuda") * 0.2 - 0.1
+        dY = torch.randn((Mx, Nx), device="cuda").to(tdt)
+        Y, Z, work = (torch.empty((Mx, Nx), device="cuda", dtype=tdt) for _ in range(3))
+        dX = torch.empty_like(X)
+        dW = torch.empty_like(W)
+        db = torch.empty((1, Nx), device="cuda")
+        f = lambda: og.forward_into(X, W, out=Y, bias=b, with_bias=True, act=act, save_z=True, z_out=Z, math=math)  # noqa: E731
+        g = lambda: og.backward_into(X, W, dY, Z, act=act, with_bias=True, gA_out=dX, gB_out=dW, gBias_out=db,  # noqa: E731
+                                     work_dZ=work, math=math)
+        tf, tb = timeit(f, iters), timeit(g, iters)
+        line = {"sweep": "dense", "M": Mx, "N": Nx, "K": Kx, "dtype": dtype, "math": math, "act": act,
+                "fwd_ms": round(tf, 4), "fwd_tflops": round(2.0 * Mx * Nx * Kx / tf / 1e9, 1),
+                "bwd_ms": round(tb, 4), "bwd_tflops": round(4.0 * Mx * Nx * Kx / tb / 1e9, 1),
+                "fwd_bwd_tflops": round(6.0 * Mx * Nx * Kx / (tf + tb) / 1e9, 1),
+                "route": {1: "exact fp32 (CUDA cores)", 2: "tcgen05"}.get(lib.ge2b_last_route())}
+        if with_ref and ref is not None and dtype == "fp32":
+            scratch = torch.empty((Mx, Nx), device="cuda")
+            rf = lambda: ref.ref_gpu_forward(X.data_ptr(), W.data_ptr(), b.data_ptr(), Nx, Y.data_ptr(), Z.data_ptr(),  # noqa: E731
+                                             Mx, Kx, Nx, act_code[act], 0.01, None)
+            rb = lambda: ref.ref_gpu_backward(X.data_ptr(), W.data_ptr(), dY.data_ptr(), Z.data_ptr(), dX.data_ptr(),  # noqa: E731
+                                              dW.data_ptr(), db.data_ptr(), Nx, scratch.data_ptr(), Mx, Kx, Nx,
+                                              act_code[act], 0.01, None)
+            trf, trb = timeit(rf, max(2, iters // 2)), timeit(rb, max(2, iters // 2))
+            line["reference_gpu_kernels"] = {"fwd_ms": round(trf, 4), "fwd_tflops": round(2.0 * Mx * Nx * Kx / trf / 1e9, 2),
+                                             "bwd_ms": round(trb, 4), "bwd_tflops": round(4.0 * Mx * Nx * Kx / trb / 1e9, 2)}
+        print(json.dumps(line), flush=True)
+
+    for n in (1024, 2048, 4096, 8192, 16384):
+        for dtype, math in (("bf16", "fp32"), ("fp32", "tf32")):
+            for act in ("none", "relu", "gelu", "sigmoid"):
+                dense_point(n, n, n, dtype, math, act, 5 if n <= 8192 else 2)
+    for m in (16, 32, 64, 128):
+        for dtype, math in (("bf16", "fp32"), ("fp32", "tf32")):
+            dense_point(m, 8192, 8192, dtype, math, "gelu", 7)
+    for n in (256, 1024, 2048, 4096):          # the parity path and the reference's own kernels on the same box
+        dense_point(n, n if n > 256 else 512, n if n > 256 else 512, "fp32", "fp32", "relu", 3, with_ref=True)
+
+    # batched attention GEMMs: B*H = 128 slices, L = 2048, d = 128, bf16, fp32 accumulate
+    Bn, H, L, d = 8, 16, 2048, 128
+    Q, Kt, V = (torch.randn((Bn, H, L, d), device="cuda").bfloat16() for _ in range(3))
+    P = torch.softmax(torch.randn((Bn, H, L, L), device="cuda"), dim=-1).bfloat16()
+    S = torch.empty((Bn, H, L, L), device="cuda", dtype=torch.bfloat16)
+    O = torch.empty((Bn, H, L, d), device="cuda", dtype=torch.bfloat16)
+    t_qk = timeit(lambda: og.forward_batched(Q, Kt, out=S, trans_b=True, alpha=1.0 / d ** 0.5), 7)
+    t_pv = timeit(lambda: og.forward_batched(P, V, out=O), 7)
+    flop = 2.0 * Bn * H * L * L * d
+    print(json.dumps({"sweep": "batched_attention", "B": Bn, "H": H, "L": L, "d": d, "dtype": "bf16",
+                      "qk_ms": round(t_qk, 4), "qk_tflops": round(flop / t_qk / 1e9, 1),
+                      "qk_GBs": round((2 * Q.numel() * 2 + S.numel() * 2) / t_qk / 1e6, 1),
+                      "pv_ms": round(t_pv, 4), "pv_tflops": round(flop / t_pv / 1e9, 1),
+                      "pv_GBs": round((P.numel() * 2 + 2 * V.numel() * 2) / t_pv / 1e6, 1)}), flush=True)
+    assert lib.ge2b_device_status(0) == 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -386,8 +481,11 @@ def main():
     ap.add_argument("--profile", default="", choices=["", "fwd", "step"],
                     help="run a short fixed launch sequence (for ncu) instead of the benchmark")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU-oracle leg (profiling runs)")
+    ap.add_argument("--sweep", action="store_true", help="print the shape sweep (one JSON line per point) and exit")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.sweep:
+        run_sweep(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_ours(args)
