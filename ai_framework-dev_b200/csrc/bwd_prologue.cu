@@ -79,7 +79,8 @@ __device__ __forceinline__ void store8(void* base, long long off, int dt, bool v
   }
 }
 
-template <int ACT, bool kFast>
+// kRowSum: the bias gradient needs sums along rows (per-row or scalar bias); the common per-column case does not.
+template <int ACT, bool kFast, bool kRowSum>
 __global__ void __launch_bounds__(kTX * kTY)
 bwd_prologue_kernel(const ProParams pp) {
   const BwdPrologueArgs& a = pp.a;
@@ -102,11 +103,20 @@ bwd_prologue_kernel(const ProParams pp) {
       float gy[8], z[8], gz[8];
       load8(a.gY, static_cast<long long>(m) * a.ldgY + col0, a.gy_dtype, pp.gy_vec != 0, ncols, gy);
       load8(a.Z, static_cast<long long>(m) * a.ldZ + col0, a.z_dtype, pp.z_vec != 0, ncols, z);
+      if (ncols == 8) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        gz[j] = (j < ncols) ? gy[j] * act_bwd<ACT, kFast>(z[j], a.leaky) : 0.f;
-        colsum[j] += gz[j];
-        rowsum += gz[j];
+        for (int j = 0; j < 8; ++j) {
+          gz[j] = gy[j] * act_bwd<ACT, kFast>(z[j], a.leaky);
+          colsum[j] += gz[j];
+          if constexpr (kRowSum) rowsum += gz[j];
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          gz[j] = (j < ncols) ? gy[j] * act_bwd<ACT, kFast>(z[j], a.leaky) : 0.f;
+          colsum[j] += gz[j];
+          if constexpr (kRowSum) rowsum += gz[j];
+        }
       }
       store8(a.gZ, static_cast<long long>(m) * a.ldgZ + col0, a.gz_dtype, pp.gz_vec != 0, ncols, gz);
       if (a.gC != nullptr) {
@@ -116,13 +126,15 @@ bwd_prologue_kernel(const ProParams pp) {
         store8(a.gC, static_cast<long long>(m) * a.ldgC + col0, a.gc_dtype, pp.gc_vec != 0, ncols, gc);
       }
     }
-    if (want_bias && a.bias_kind == kBiasPerM) {
-      // all 32 lanes of a warp share the row: one atomic per (row, CTA)
+    if constexpr (kRowSum) {
+      if (want_bias && a.bias_kind == kBiasPerM) {
+        // all 32 lanes of a warp share the row: one atomic per (row, CTA)
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) rowsum += __shfl_xor_sync(0xffffffffu, rowsum, o);
-      if (threadIdx.x == 0 && m < a.M) atomicAdd(a.gBias + m, rowsum);
+        for (int o = 16; o > 0; o >>= 1) rowsum += __shfl_xor_sync(0xffffffffu, rowsum, o);
+        if (threadIdx.x == 0 && m < a.M) atomicAdd(a.gBias + m, rowsum);
+      }
+      total += rowsum;
     }
-    total += rowsum;
   }
 
   if (!want_bias || a.bias_kind == kBiasPerM) return;
@@ -170,10 +182,16 @@ cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s) {
   dim3 block(kTX, kTY), grid((a.N + kTileCols - 1) / kTileCols, (a.M + kTileRows - 1) / kTileRows);
   // gZ stored in 16 bits: the exp-based derivative forms are accurate enough (see epilogue_math.cuh)
   const bool fast = a.gz_dtype != kF32;
+  const bool rowsum = a.gBias != nullptr && (a.bias_kind == kBiasPerM || a.bias_kind == kBiasScalar);
 #define GE2B_LAUNCH_PRO(ACT_)                                                                   \
   do {                                                                                          \
-    if (fast) bwd_prologue_kernel<ACT_, true><<<grid, block, 0, s>>>(pp);                       \
-    else      bwd_prologue_kernel<ACT_, false><<<grid, block, 0, s>>>(pp);                      \
+    if (fast) {                                                                                 \
+      if (rowsum) bwd_prologue_kernel<ACT_, true, true><<<grid, block, 0, s>>>(pp);             \
+      else        bwd_prologue_kernel<ACT_, true, false><<<grid, block, 0, s>>>(pp);            \
+    } else {                                                                                    \
+      if (rowsum) bwd_prologue_kernel<ACT_, false, true><<<grid, block, 0, s>>>(pp);            \
+      else        bwd_prologue_kernel<ACT_, false, false><<<grid, block, 0, s>>>(pp);           \
+    }                                                                                           \
   } while (0)
   switch (a.act) {
     case kActReLU:    GE2B_LAUNCH_PRO(kActReLU); break;

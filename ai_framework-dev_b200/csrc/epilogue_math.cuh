@@ -71,7 +71,14 @@ __device__ __forceinline__ float act_bwd(float x, float leaky) {
   else if constexpr (ACT == kActGELU) {
     const float c = 0.7978845608f, k1 = 0.044715f;
     const float x2 = x * x;
-    float th = kFast ? tanh_fast(gelu_inner(x)) : tanhf(gelu_inner(x));
+    if constexpr (kFast) {
+      // tanh.approx stays inside [-1, 1], so 1 - th^2 cannot go negative and the clamp is not needed
+      const float th = tanh_fast(x * fmaf(x2, c * k1, c));
+      const float sech2 = fmaf(-th, th, 1.f);
+      const float hxdt = (0.5f * x) * fmaf(x2, 3.f * c * k1, c);
+      return fmaf(hxdt, sech2, fmaf(0.5f, th, 0.5f));
+    }
+    float th = tanhf(gelu_inner(x));
     th = fminf(fmaxf(th, -0.999999f), 0.999999f);
     const float sech2 = 1.f - th * th;
     const float dt = c * (1.f + 3.f * k1 * x2);
