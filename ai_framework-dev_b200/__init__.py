@@ -8,6 +8,9 @@ There is no CPU fallback: importing works anywhere, computing needs the built li
 from . import _lib  # noqa: F401
 from . import ops_gemm  # noqa: F401
 from .dense import Dense  # noqa: F401
+from . import train  # noqa: F401
+from .train import DenseStackTrainer, softmax_ce_fused, sgd_update  # noqa: F401
 from ._lib import load_library, library_path  # noqa: F401
 
-__all__ = ["ops_gemm", "Dense", "load_library", "library_path"]
+__all__ = ["ops_gemm", "Dense", "train", "DenseStackTrainer", "softmax_ce_fused", "sgd_update", "load_library",
+           "library_path"]

@@ -44,6 +44,18 @@ class ParamsTyped(C.Structure):
                 ("strideD", C.c_longlong), ("strideZ", C.c_longlong), ("trans_a", C.c_int)]
 
 
+class ParamsSoftmaxCE(C.Structure):
+    _fields_ = [("M", C.c_int), ("C", C.c_int), ("ld_logits", C.c_int), ("ld_dlogits", C.c_int),
+                ("dtype", C.c_int), ("grad_dtype", C.c_int), ("reduction", C.c_int), ("ignore_index", C.c_int),
+                ("grad_scale", C.c_float), ("mean_denominator", C.c_int)]
+
+
+class ParamsSGD(C.Structure):
+    _fields_ = [("n", C.c_longlong), ("grad_dtype", C.c_int), ("low_dtype", C.c_int),
+                ("lr", C.c_float), ("momentum", C.c_float), ("dampening", C.c_float), ("nesterov", C.c_int),
+                ("weight_decay", C.c_float), ("decay_mode", C.c_int), ("grad_scale", C.c_float)]
+
+
 class ParamsBwdTyped(C.Structure):
     _fields_ = [("base", ParamsBwd),
                 ("dtype", C.c_int), ("z_dtype", C.c_int), ("math", C.c_int),
@@ -67,6 +79,7 @@ EXPORTS = [
     "ge2b_dense_plan_create", "ge2b_dense_plan_step", "ge2b_dense_plan_destroy",
     "ge2b_dense_plan_submit", "ge2b_dense_plan_wait",
     "ge2_launch_gemm_bias_act_bwd_noalloc",
+    "ge2_launch_softmax_ce_fused", "ge2_launch_sgd_update",
 ]
 
 
@@ -85,7 +98,7 @@ def load_library() -> C.CDLL:
     for name in ("ge2_launch_gemm_bias_act_f32", "ge2_launch_gemm_bias_act_tc_f16",
                  "ge2_launch_gemm_bias_act_f32_ex", "ge2_launch_gemm_bias_act_bwd_f32_ex",
                  "ge2_launch_gemm_bias_act_typed", "ge2_launch_gemm_bias_act_bwd_typed",
-                 "ge2_launch_gemm_bias_act_bwd_noalloc"):
+                 "ge2_launch_gemm_bias_act_bwd_noalloc", "ge2_launch_softmax_ce_fused", "ge2_launch_sgd_update"):
         fn = getattr(lib, name)
         fn.argtypes = launch_sig
         fn.restype = C.c_int

@@ -1,0 +1,189 @@
+"""The training step around the dense layers: fused softmax cross-entropy, the SGD update, and a static,
+graph-captured step driver for a stack of Dense layers.
+
+Mirrors, for this path only, what the reference assembles in Python:
+  * losses/softmax_ce.py + ops/cross_entropy.py  -> `softmax_ce_fused`
+  * optim/sgd.py (fp32 master parameters)        -> `sgd_update`
+  * layers/sequential.py:416-497 (compile / one_step), graph/capture_plan.py:250-287 (pre-allocated y, z, gA, gW, gB
+    and work buffers per Dense layer), graph/runtime.py:24-148 (forward -> loss -> backward -> optimizer on one
+    stream) and graph/graph_exec.py:51-152 (warm-up, capture, instantiate, replay) -> `DenseStackTrainer`
+Device arrays are torch tensors; every kernel is launched through the C ABI of libge2_b200.so.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import _lib, ops_gemm
+from ._lib import DT_BF16, DT_F16, DT_F32
+
+_DT = {torch.float32: DT_F32, torch.float16: DT_F16, torch.bfloat16: DT_BF16}
+_RED = {"none": 0, "mean": 1, "sum": 2}
+
+
+def _stream_ptr(stream) -> int:
+    if stream is None:
+        return int(torch.cuda.current_stream().cuda_stream)
+    return int(stream.cuda_stream) if isinstance(stream, torch.cuda.Stream) else int(stream)
+
+
+def softmax_ce_fused(logits: torch.Tensor, labels: torch.Tensor, *, dlogits: torch.Tensor,
+                     loss: Optional[torch.Tensor] = None, reduction: str = "mean", ignore_index: int = -1,
+                     grad_scale: Optional[float] = None, mean_denominator: int = 0, stream=None) -> None:
+    """loss = CE(softmax(logits), labels) and dlogits = (softmax - onehot) * grad_scale in one pass.
+    labels are int32.  grad_scale defaults to 1/rows for "mean" and 1 otherwise; pass 1/global_batch (and
+    mean_denominator = global_batch) when the rows are one shard of a data-parallel batch."""
+    M, C = logits.shape
+    if labels.dtype != torch.int32 or labels.numel() != M:
+        raise ValueError("labels must be int32 of length M")
+    if tuple(dlogits.shape) != (M, C):
+        raise ValueError("dlogits must have the shape of logits")
+    if loss is not None and (loss.dtype != torch.float32 or loss.numel() != (M if reduction == "none" else 1)):
+        raise ValueError("loss must be float32 with M elements (reduction none) or 1 element")
+    p = _lib.ParamsSoftmaxCE()
+    p.M, p.C = M, C
+    p.ld_logits, p.ld_dlogits = logits.stride(0), dlogits.stride(0)
+    p.dtype, p.grad_dtype = _DT[logits.dtype], _DT[dlogits.dtype]
+    p.reduction = _RED[reduction]
+    p.ignore_index = ignore_index
+    denom = mean_denominator if mean_denominator > 0 else M
+    p.grad_scale = float(grad_scale) if grad_scale is not None else (1.0 / denom if reduction == "mean" else 1.0)
+    p.mean_denominator = mean_denominator
+    bufs = _lib.make_bufs([logits.data_ptr(), labels.data_ptr(), dlogits.data_ptr(),
+                           loss.data_ptr() if loss is not None else 0], p)
+    _lib.check(_lib.load_library().ge2_launch_softmax_ce_fused(bufs, len(bufs), _stream_ptr(stream)), "softmax_ce")
+
+
+def sgd_update(param: torch.Tensor, grad: torch.Tensor, *, lr: float, velocity: Optional[torch.Tensor] = None,
+               momentum: float = 0.0, dampening: float = 0.0, nesterov: bool = False, weight_decay: float = 0.0,
+               decay: str = "decoupled", grad_scale: float = 1.0, low: Optional[torch.Tensor] = None,
+               stream=None) -> None:
+    """In-place SGD on fp32 `param`; `low` (bf16 / f16, same element count) receives the rounded result."""
+    if param.dtype != torch.float32 or not param.is_contiguous() or not grad.is_contiguous():
+        raise ValueError("param must be contiguous float32 and grad contiguous")
+    if grad.numel() != param.numel() or (low is not None and low.numel() != param.numel()):
+        raise ValueError("size mismatch")
+    p = _lib.ParamsSGD()
+    p.n = param.numel()
+    p.grad_dtype = _DT[grad.dtype]
+    p.low_dtype = _DT[low.dtype] if low is not None else DT_BF16
+    p.lr, p.momentum, p.dampening = float(lr), float(momentum), float(dampening)
+    p.nesterov = 1 if nesterov else 0
+    p.weight_decay = float(weight_decay)
+    p.decay_mode = 0 if weight_decay == 0.0 else {"l2": 1, "decoupled": 2}[decay]
+    p.grad_scale = float(grad_scale)
+    bufs = _lib.make_bufs([param.data_ptr(), grad.data_ptr(), velocity.data_ptr() if velocity is not None else 0,
+                           low.data_ptr() if low is not None else 0], p)
+    _lib.check(_lib.load_library().ge2_launch_sgd_update(bufs, len(bufs), _stream_ptr(stream)), "sgd_update")
+
+
+class DenseStackTrainer:
+    """Dense(d0->d1, act0) ... Dense(d_{n-1}->d_n, act_{n-1}) -> softmax cross-entropy (mean) -> SGD.
+
+    All buffers are allocated in `compile`; `one_step` copies a batch into the static input buffers and runs the
+    step: eagerly, or (single process) by replaying a CUDA graph captured once.  With a process group the batch
+    rows are one shard of the global batch: each layer's dW and db are all-reduced (sum) on a side stream as soon
+    as they are written, under the dX GEMM and the deeper layers' backward; the loss gradient is scaled by
+    1/global_batch so every replica applies the same update.
+    """
+
+    def __init__(self, dims: Sequence[int], acts: Sequence[str], batch: int, *, dtype=torch.bfloat16, lr=1e-3,
+                 seed=0, device="cuda", group=None, global_batch: Optional[int] = None, bias_init_zero=True):
+        assert len(acts) == len(dims) - 1
+        self.dims, self.acts, self.batch = list(dims), [a.lower() for a in acts], int(batch)
+        self.dtype, self.lr, self.device = dtype, float(lr), device
+        self.group = group
+        self.world = torch.distributed.get_world_size(group) if group is not None else 1
+        self.global_batch = int(global_batch) if global_batch else self.batch * self.world
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        self.W32: List[torch.Tensor] = []
+        self.W: List[torch.Tensor] = []
+        self.b: List[torch.Tensor] = []
+        for i in range(len(dims) - 1):
+            lim = math.sqrt(6.0 / dims[i])                       # Kaiming-uniform, as the benchmark config states
+            w = ((torch.rand((dims[i], dims[i + 1]), generator=gen) * 2 - 1) * lim).to(device)
+            self.W32.append(w.float().contiguous())
+            self.W.append(w.to(dtype).contiguous())
+            bias = torch.zeros(dims[i + 1]) if bias_init_zero else (torch.rand(dims[i + 1], generator=gen) * 0.2 - 0.1)
+            self.b.append(bias.float().to(device))
+        self.graph = None
+        self.compiled = False
+
+    # ---- plan (pre-allocated, pointer-stable buffers) ----
+    def compile(self, capture: bool = True) -> None:
+        B, dev, dt = self.batch, self.device, self.dtype
+        n = len(self.W)
+        self.X = torch.zeros((B, self.dims[0]), device=dev, dtype=dt)
+        self.labels = torch.zeros((B,), device=dev, dtype=torch.int32)
+        self.y = [torch.empty((B, self.dims[i + 1]), device=dev, dtype=dt) for i in range(n)]
+        self.z = [torch.empty((B, self.dims[i + 1]), device=dev, dtype=dt) for i in range(n)]
+        self.work = [torch.empty((B, self.dims[i + 1]), device=dev, dtype=dt) for i in range(n)]
+        self.gA = [torch.empty((B, self.dims[i]), device=dev, dtype=dt) for i in range(n)]
+        self.gW = [torch.empty_like(w) for w in self.W]
+        self.gB = [torch.empty((1, self.dims[i + 1]), device=dev, dtype=torch.float32) for i in range(n)]
+        self.dlogits = torch.empty((B, self.dims[-1]), device=dev, dtype=dt)
+        self.loss = torch.zeros((1,), device=dev, dtype=torch.float32)
+        self.comm = torch.cuda.Stream(device=dev) if self.world > 1 else None
+        self.compiled = True
+        for _ in range(2):            # warm-up outside capture: function attributes, lazy scratch, NCCL channels
+            self.run_step()
+        torch.cuda.synchronize()
+        if capture and self.world == 1:
+            cap = torch.cuda.Stream(device=dev)
+            cap.wait_stream(torch.cuda.current_stream())
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, stream=cap):
+                self.run_step()
+            torch.cuda.current_stream().wait_stream(cap)
+
+    # ---- one step on the current stream ----
+    def run_step(self) -> None:
+        n = len(self.W)
+        cur = self.X
+        for i in range(n):
+            ops_gemm.forward_into(cur, self.W[i], out=self.y[i], bias=self.b[i], with_bias=True, act=self.acts[i],
+                                  save_z=True, z_out=self.z[i])
+            cur = self.y[i]
+        softmax_ce_fused(self.y[-1], self.labels, dlogits=self.dlogits, loss=self.loss, reduction="mean",
+                         grad_scale=1.0 / self.global_batch, mean_denominator=self.global_batch)
+        g = self.dlogits
+        stream = torch.cuda.current_stream()
+        for i in reversed(range(n)):
+            x_in = self.X if i == 0 else self.y[i - 1]
+            # gZ (into work) + db + dW first, so their all-reduce can start before dX is computed
+            ops_gemm.backward_into(x_in, self.W[i], g, self.z[i], act=self.acts[i], with_bias=True,
+                                   gB_out=self.gW[i], gBias_out=self.gB[i], work_dZ=self.work[i])
+            if self.world > 1:
+                self.comm.wait_stream(stream)
+                with torch.cuda.stream(self.comm):
+                    torch.distributed.all_reduce(self.gW[i], group=self.group)
+                    torch.distributed.all_reduce(self.gB[i], group=self.group)
+            ops_gemm.backward_into(x_in, self.W[i], g, self.z[i], act=self.acts[i], gA_out=self.gA[i],
+                                   work_dZ=self.work[i], reuse_dZ=True)
+            g = self.gA[i]
+        if self.world > 1:
+            stream.wait_stream(self.comm)
+        for i in range(n):
+            sgd_update(self.W32[i], self.gW[i], lr=self.lr, low=self.W[i])
+            sgd_update(self.b[i], self.gB[i], lr=self.lr)
+
+    def launch(self) -> None:
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.run_step()
+
+    def one_step(self, X: torch.Tensor, labels: torch.Tensor) -> float:
+        """Copies the batch into the static buffers, runs one step and returns the (local-shard) mean loss."""
+        if not self.compiled:
+            self.compile()
+        self.X.copy_(X, non_blocking=True)
+        self.labels.copy_(labels, non_blocking=True)
+        self.launch()
+        return float(self.loss.item())
+
+    def flop_per_step(self) -> float:
+        """2*B*sum(d_i*d_{i+1}) forward, twice that backward (dX is computed for the first layer too)."""
+        return 6.0 * self.batch * sum(self.dims[i] * self.dims[i + 1] for i in range(len(self.W)))

@@ -147,6 +147,43 @@ int ge2b_dense_plan_submit(ge2b_dense_plan* plan, const void* X, const void* W, 
 int ge2b_dense_plan_wait(ge2b_dense_plan* plan);
 void ge2b_dense_plan_destroy(ge2b_dense_plan* plan);
 
+/* ------------------------------------------------------------------------------------------------
+ * The two passes either side of the dense layers in a training step.
+ * ------------------------------------------------------------------------------------------------ */
+typedef struct {
+  int M, C;                   /* rows (samples), classes */
+  int ld_logits, ld_dlogits;  /* <= 0: C */
+  ge2_dtype_t dtype;          /* of the logits */
+  ge2_dtype_t grad_dtype;     /* of dlogits */
+  int reduction;              /* 0 none (loss[M]), 1 mean, 2 sum (loss[1]) */
+  int ignore_index;           /* rows with this label give zero loss and zero gradient; -1 disables */
+  float grad_scale;           /* dlogits = (softmax - onehot) * grad_scale; pass 1/batch for a mean loss */
+  int mean_denominator;       /* <= 0: M.  The global batch when the rows are one shard of it. */
+} ge2_softmax_ce_params_t;
+
+/* Fused softmax + cross-entropy from logits, forward and backward in one pass.
+ * bufs = [logits, labels(int32), dlogits, loss|0, &ge2_softmax_ce_params_t].
+ * Replaces SoftmaxCEFusedForwardBackwardCudaLaunch (backends/cuda/ops/cross_entropy/api.hpp:46-56,
+ * kernels.cu:287-372).  Like the reference's native op, a mean divides by the row count including ignored rows. */
+int ge2_launch_softmax_ce_fused(const ge2_uintptr* bufs, int n, void* stream);
+
+typedef struct {
+  long long n;                /* elements */
+  ge2_dtype_t grad_dtype;     /* of the gradient */
+  ge2_dtype_t low_dtype;      /* of the optional low-precision copy of the parameters */
+  float lr, momentum, dampening;
+  int nesterov;
+  float weight_decay;
+  int decay_mode;             /* 0 none, 1 L2 (added to the gradient), 2 decoupled */
+  float grad_scale;           /* 0 is read as 1 */
+} ge2_sgd_params_t;
+
+/* SGD step on fp32 master parameters.  bufs = [param(fp32), grad, velocity(fp32)|0, param_low|0, &ge2_sgd_params_t].
+ * Replaces SGDCudaLaunch's kernel (backends/cuda/ops/optimizer/kernels.cu:33-66; L2 decay) and the Python optimizer's
+ * element-wise kernel (python/graph_executor_v2/optim/sgd.py:16-64; decoupled decay); param_low receives the updated
+ * parameters rounded to `low_dtype` for the next forward pass. */
+int ge2_launch_sgd_update(const ge2_uintptr* bufs, int n, void* stream);
+
 /* Backward for callers that may not allocate device memory and have no scratch of their own to pass: the gZ
  * scratch is a fixed GE2B_NOALLOC_SCRATCH_BYTES array inside the library's device image (held by every GPU that
  * loads the library, until the process exits).  This entry point has no counterpart in the reference, whose

@@ -215,6 +215,67 @@ def backward_f64(A, B, gY, Z, act="none", leaky=0.01):
     return {"gZ": gZ, "gA": gZ @ B.T, "gB": A.T @ gZ, "gBias": gZ.sum(axis=0)}
 
 
+def softmax_ce_f64(logits, labels, grad_scale=None, ignore_index=-1, denom=None):
+    """Per-row loss and dlogits = (softmax - onehot) * grad_scale in float64.  Ignored rows give zeros; the mean
+    divides by `denom` (default: all rows, ignored ones included, as the reference's native op does)."""
+    x = np.asarray(logits, np.float64)
+    M, Cn = x.shape
+    denom = M if denom is None else denom
+    grad_scale = 1.0 / denom if grad_scale is None else grad_scale
+    m = x.max(axis=1, keepdims=True)
+    e = np.exp(x - m)
+    s = e.sum(axis=1, keepdims=True)
+    lab = np.asarray(labels, np.int64)
+    live = (lab != ignore_index) & (lab >= 0) & (lab < Cn)
+    safe = np.where(live, lab, 0)
+    loss_rows = np.where(live, (m[:, 0] + np.log(s[:, 0])) - x[np.arange(M), safe], 0.0)
+    d = e / s
+    d[np.arange(M), safe] -= 1.0
+    d = d * grad_scale * live[:, None]
+    return loss_rows, d
+
+
+def sgd_f64(p, g, v=None, lr=1e-3, momentum=0.0, dampening=0.0, nesterov=False, weight_decay=0.0, decay="decoupled",
+            grad_scale=1.0):
+    p = np.asarray(p, np.float64)
+    g = grad_scale * np.asarray(g, np.float64)
+    if weight_decay and decay == "l2":
+        g = g + weight_decay * p
+    step = g
+    if momentum > 0 and v is not None:
+        v = momentum * np.asarray(v, np.float64) + (1 - dampening) * g
+        step = g + momentum * v if nesterov else v
+    dec = lr * weight_decay * p if (weight_decay and decay == "decoupled") else 0.0
+    return p - lr * step - dec, v
+
+
+def mlp_step_f64(W32, b, X, labels, acts, lr, global_batch=None, lowp=None):
+    """One training step of Dense stack -> softmax-CE (mean) -> SGD in float64.  W32/b are lists (float64 master
+    copies); the forward uses `lowp(W)` (e.g. bf16 rounding) when given.  Returns (loss, new_W32, new_b, grads)."""
+    n = len(W32)
+    B = X.shape[0]
+    gb = B if global_batch is None else global_batch
+    a, zs, ins = np.asarray(X, np.float64), [], []
+    for i in range(n):
+        Wf = np.asarray(lowp(W32[i].astype(np.float32)), np.float64) if lowp else W32[i]
+        ins.append(a)
+        z = a @ Wf + b[i]
+        zs.append(z)
+        a = act_f64(acts[i], z)
+    loss_rows, g = softmax_ce_f64(a, labels, grad_scale=1.0 / gb)
+    loss = loss_rows.sum() / gb
+    newW, newb, grads = list(W32), list(b), [None] * n
+    for i in reversed(range(n)):
+        Wf = np.asarray(lowp(W32[i].astype(np.float32)), np.float64) if lowp else W32[i]
+        gz = g * act_deriv_f64(acts[i], zs[i])
+        gW, gbias = ins[i].T @ gz, gz.sum(axis=0)
+        g = gz @ Wf.T
+        grads[i] = (gW, gbias)
+        newW[i] = W32[i] - lr * gW
+        newb[i] = b[i] - lr * gbias
+    return loss, newW, newb, grads
+
+
 def rel_fro(x, ref) -> float:
     x = np.asarray(x, np.float64)
     ref = np.asarray(ref, np.float64)
