@@ -112,7 +112,9 @@ class DenseStackTrainer:
         self.compiled = False
 
     # ---- plan (pre-allocated, pointer-stable buffers) ----
-    def compile(self, capture: bool = True) -> None:
+    def compile(self, capture=True) -> None:
+        """capture: False = eager steps; True = CUDA graph when there is no process group; "with_collectives" =
+        capture the step including its all-reduces."""
         B, dev, dt = self.batch, self.device, self.dtype
         n = len(self.W)
         self.X = torch.zeros((B, self.dims[0]), device=dev, dtype=dt)
@@ -130,11 +132,12 @@ class DenseStackTrainer:
         for _ in range(2):            # warm-up outside capture: function attributes, lazy scratch, NCCL channels
             self.run_step()
         torch.cuda.synchronize()
-        if capture and self.world == 1:
+        if capture and (self.world == 1 or capture == "with_collectives"):
             cap = torch.cuda.Stream(device=dev)
             cap.wait_stream(torch.cuda.current_stream())
             self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph, stream=cap):
+            # thread-local capture mode: the collective library's watchdog thread may touch the CUDA API meanwhile
+            with torch.cuda.graph(self.graph, stream=cap, capture_error_mode="thread_local"):
                 self.run_step()
             torch.cuda.current_stream().wait_stream(cap)
 

@@ -266,7 +266,8 @@ def run_ours(args):
     # One step = a fixed sequence of 5 kernels (+ collectives): it is captured once into a CUDA graph and the timed
     # region replays it, so host launch cost (which exceeds the device time once NCCL calls are added) is off the path.
     # (single-GPU runs only: the multi-rank step with NCCL calls is launched eagerly)
-    use_graph = os.environ.get("GE2B_BENCH_GRAPH", "1") == "1" and world == 1
+    nccl_graph = os.environ.get("GE2B_NCCL_GRAPH", "1") == "1"      # also capture multi-rank steps (with their NCCL calls)
+    use_graph = os.environ.get("GE2B_BENCH_GRAPH", "1") == "1" and (world == 1 or nccl_graph)
     launches_per_step = None
     graph = None
     if use_graph:
@@ -274,7 +275,7 @@ def run_ours(args):
         cap.wait_stream(torch.cuda.current_stream())
         l0 = lib.ge2b_launches_total()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=cap):
+        with torch.cuda.graph(graph, stream=cap, capture_error_mode="thread_local"):
             step(False)
         launches_per_step = lib.ge2b_launches_total() - l0
         torch.cuda.current_stream().wait_stream(cap)
@@ -349,6 +350,36 @@ def run_ours(args):
     # plausibility of the plan's results against the device-resident run
     assert torch.equal(Y_o, Y.cpu()), "host-plan Y differs from the device-resident forward"
 
+    # ---- the 3-layer MLP training step of BASELINE.json configs[2]: global batch 8192 sharded along M (strong scaling)
+    mlp = None
+    if not args.skip_mlp and 8192 % world == 0:
+        tr = pkg.DenseStackTrainer([1024, 4096, 4096, 1024], ["relu", "gelu", "none"], 8192 // world, lr=1e-3, seed=0,
+                                   device=dev, group=dist.group.WORLD if world > 1 else None, global_batch=8192)
+        tr.compile(capture="with_collectives" if (world > 1 and nccl_graph) else True)
+        gen.manual_seed(100 + rank)
+        tr.X.copy_(torch.randn((8192 // world, 1024), generator=gen).bfloat16())
+        tr.labels.copy_(torch.randint(0, 1024, (8192 // world,), generator=gen, dtype=torch.int32))
+        for _ in range(3):
+            tr.launch()
+        barrier()
+        mlp_steps = max(1, min(args.steps, 50))
+        m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        m0.record()
+        for _ in range(mlp_steps):
+            tr.launch()
+        m1.record()
+        barrier()
+        mms = torch.tensor([m0.elapsed_time(m1)], device=dev)
+        if world > 1:
+            dist.all_reduce(mms, op=dist.ReduceOp.MAX)
+        per = float(mms.item()) / mlp_steps
+        mlp = {"workload": "3-layer MLP training step, global batch 8192, 1024-4096-4096-1024, ReLU/GELU/none, bf16 weights "
+                           "with fp32 master, softmax cross-entropy, SGD lr=1e-3; batch rows sharded over the GPUs",
+               "steps_per_s": 1e3 / per, "ms_per_step": per, "scaling": "strong",
+               "tflops": world * tr.flop_per_step() / (per * 1e-3) / 1e12,
+               "launch_mode": "cuda graph replay" if tr.graph is not None else "eager", "loss": float(tr.loss.item())}
+        assert lib.ge2b_device_status(0) == 0
+
     if rank == 0:
         peak, peak_kind = measured_peak()
         achieved = FLOP_FWD_LAUNCH / (fwd_ms * 1e-3) / 1e12
@@ -370,12 +401,20 @@ def run_ours(args):
                          "peak_source": f"MEASURED_PEAKS.json bf16_tflops, {peak_kind}",
                          "frac_of_nominal_2250": achieved / 2250.0},
         }
+        if mlp is not None:
+            line["mlp_step"] = mlp
         if world == 1 and not args.skip_cpu_baseline:
             line["cpu_baseline"] = run_cpu_baseline()
         print(json.dumps(line), flush=True)
     if world > 1:
+        # Leave without tearing the communicator down: destroying a process group whose collectives live in
+        # instantiated CUDA graphs was seen to block at exit.  Everything has been synchronised and printed.
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 # ------------------------------------------------------------------------------------------------ shape sweep
@@ -481,6 +520,7 @@ def main():
     ap.add_argument("--profile", default="", choices=["", "fwd", "step"],
                     help="run a short fixed launch sequence (for ncu) instead of the benchmark")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU-oracle leg (profiling runs)")
+    ap.add_argument("--skip-mlp", action="store_true", help="omit the MLP training-step leg")
     ap.add_argument("--sweep", action="store_true", help="print the shape sweep (one JSON line per point) and exit")
     args = ap.parse_args()
     if args.sweep:
