@@ -41,8 +41,8 @@ CONFIG = {
     "l2": "no flush: a step touches 8 tensors x 32 MiB = 256 MiB, twice the 126 MB L2",
 }
 FALLBACK_PEAK_TFLOPS = 1590.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one forward launch at this workload (see profiles/); None until captured
-FWD_LAUNCH_DRAM_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one forward launch at this workload, from the ncu capture
+FWD_LAUNCH_DRAM_BYTES = 138.1e6   # 102.4 MB read + 35.7 MB written (profiles/gemm_tc_fwd_4096_bf16_pair.md)
 
 
 def measured_peak():
@@ -203,7 +203,7 @@ def run_ours(args):
     db = torch.empty((1, N), device=dev, dtype=torch.float32)
     comm = torch.cuda.Stream(device=dev) if world > 1 else None
     sm_total = lib.ge2b_sm_count()
-    comm_sms = int(os.environ.get("GE2B_BENCH_COMM_SMS", "0"))   # SMs left free for NCCL during the overlapped GEMM
+    comm_sms = int(os.environ.get("GE2B_BENCH_COMM_SMS", "16"))   # SMs left free for NCCL during the overlapped GEMM
     fwd_events = []
 
     # row blocks of dW whose all-reduce starts as each finishes; a single GPU has nothing to overlap and uses one
