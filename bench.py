@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the dense-layer hot path on B200.
 
-Workload (BASELINE.json configs[1]): dense layer forward + backward, M = N = K = 4096, bf16 tensors with fp32
+Workload: dense layer forward + backward, M = N = K = 4096, bf16 tensors with fp32
 accumulation, fp32 bias, tanh-GELU epilogue; outputs Y, Z (pre-activation), dX, dW, db.  One step = one forward
 and one backward over one batch.  Work counted per step: 6*M*N*K flop (2 forward + 4 backward); epilogue,
 bias and reduction arithmetic is not counted.
@@ -42,7 +42,7 @@ CONFIG = {
 }
 FALLBACK_PEAK_TFLOPS = 1590.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one forward launch at this workload, from the ncu capture
-FWD_LAUNCH_DRAM_BYTES = 138.1e6   # 102.4 MB read + 35.7 MB written (profiles/gemm_tc_fwd_4096_bf16_pair.md)
+FWD_LAUNCH_DRAM_BYTES = 138.1e6   # 102.4 MB read + 35.7 MB written (ncu --set full of `bench.py --profile fwd`)
 
 
 def measured_peak():
@@ -350,7 +350,7 @@ def run_ours(args):
     # plausibility of the plan's results against the device-resident run
     assert torch.equal(Y_o, Y.cpu()), "host-plan Y differs from the device-resident forward"
 
-    # ---- the 3-layer MLP training step of BASELINE.json configs[2]: global batch 8192 sharded along M (strong scaling)
+    # ---- the 3-layer MLP training step: global batch 8192 sharded along M (strong scaling)
     mlp = None
     if not args.skip_mlp and 8192 % world == 0:
         tr = pkg.DenseStackTrainer([1024, 4096, 4096, 1024], ["relu", "gelu", "none"], 8192 // world, lr=1e-3, seed=0,
@@ -419,8 +419,8 @@ def run_ours(args):
 
 # ------------------------------------------------------------------------------------------------ shape sweep
 def run_sweep(args):
-    """Shape sweep of BASELINE.json configs[4] (squares and decode-like skinny M, four activations, bf16 and fp32
-    via TF32 / exact) and the batched attention GEMMs of configs[3].  One JSON line per point; not the contract line."""
+    """Shape sweep (squares and decode-like skinny M, four activations, bf16 and fp32
+    via TF32 / exact) and the batched attention GEMMs (B*H = 128, L = 2048, d = 128).  One JSON line per point; not the contract line."""
     import ctypes as C
     import torch
     pkg = importlib.import_module("ai_framework-dev_b200")
