@@ -79,6 +79,22 @@ def sgd_update(param: torch.Tensor, grad: torch.Tensor, *, lr: float, velocity: 
     _lib.check(_lib.load_library().ge2_launch_sgd_update(bufs, len(bufs), _stream_ptr(stream)), "sgd_update")
 
 
+def shard_rows(global_batch: int, world: int, rank: int):
+    """Row range [begin, end) of `rank`'s shard of a batch split along M over `world` replicas (contiguous blocks,
+    the first `global_batch % world` ranks get one extra row)."""
+    if world < 1 or not (0 <= rank < world) or global_batch < 0:
+        raise ValueError("bad shard request")
+    base, extra = divmod(global_batch, world)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def loss_grad_scale(global_batch: int) -> float:
+    """Scale of the loss gradient on every replica for a mean loss over the GLOBAL batch: summing the replicas'
+    dW / db then gives the full-batch gradient, whatever the shard sizes."""
+    return 1.0 / float(global_batch)
+
+
 class DenseStackTrainer:
     """Dense(d0->d1, act0) ... Dense(d_{n-1}->d_n, act_{n-1}) -> softmax cross-entropy (mean) -> SGD.
 
@@ -150,7 +166,7 @@ class DenseStackTrainer:
                                   save_z=True, z_out=self.z[i])
             cur = self.y[i]
         softmax_ce_fused(self.y[-1], self.labels, dlogits=self.dlogits, loss=self.loss, reduction="mean",
-                         grad_scale=1.0 / self.global_batch, mean_denominator=self.global_batch)
+                         grad_scale=loss_grad_scale(self.global_batch), mean_denominator=self.global_batch)
         g = self.dlogits
         stream = torch.cuda.current_stream()
         for i in reversed(range(n)):
