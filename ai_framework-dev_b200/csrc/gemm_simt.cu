@@ -62,6 +62,10 @@ __global__ void gemm_simt_small_kernel(const SimtParams p) {
 }
 
 // 128x128 output tile, 16-deep k tiles, 8x8 outputs per thread (two 4-wide strips in each direction).
+// kVec: fp32 operands whose base, pitch and extent along the contiguous index are multiples of 4 elements are
+// fetched as float4 (a float4 is then entirely inside or outside the matrix); everything else goes element-wise.
+// The arithmetic, and so every result bit, is the same in both forms.
+template <bool kVec>
 __global__ void __launch_bounds__(kThreads)
 gemm_simt_tiled_kernel(const SimtParams p) {
   __shared__ __align__(16) float As[2][kTK][kTM + kPad];
@@ -79,37 +83,79 @@ gemm_simt_tiled_kernel(const SimtParams p) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 
+  // staging registers: 8 elements of A and 8 of B per thread (as 2 float4 each in the vector form)
   float ra[8], rb[8];
   auto fetch = [&](int k0) {
+    if constexpr (kVec) {
+      const float* A = reinterpret_cast<const float*>(p.A) + a0;
+      const float* B = reinterpret_cast<const float*>(p.B) + b0;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = tid + i * kThreads;
-      int m, k;
-      if (p.a_mn) { m = idx & (kTM - 1); k = idx >> 7; } else { k = idx & (kTK - 1); m = idx >> 4; }
-      const int gm = m0 + m, gk = k0 + k;
-      ra[i] = (gm < p.M && gk < p.K)
-                  ? load_as_f32(p.A, a0 + (p.a_mn ? static_cast<long long>(gk) * p.lda + gm
-                                                  : static_cast<long long>(gm) * p.lda + gk), p.in_dtype)
-                  : 0.f;
-      int n, kk;
-      if (p.b_mn) { n = idx & (kTN - 1); kk = idx >> 7; } else { kk = idx & (kTK - 1); n = idx >> 4; }
-      const int gn = n0 + n, gkb = k0 + kk;
-      rb[i] = (gn < p.N && gkb < p.K)
-                  ? load_as_f32(p.B, b0 + (p.b_mn ? static_cast<long long>(gkb) * p.ldb + gn
-                                                  : static_cast<long long>(gn) * p.ldb + gkb), p.in_dtype)
-                  : 0.f;
+      for (int i = 0; i < 2; ++i) {
+        const int idx = tid + i * kThreads;                    // 512 float4 per operand tile
+        float4 va = make_float4(0.f, 0.f, 0.f, 0.f), vb = va;
+        if (p.a_mn) { const int k = idx >> 5, m = (idx & 31) * 4;   // [k][m..m+3]
+          if (k0 + k < p.K && m0 + m < p.M) va = *reinterpret_cast<const float4*>(A + static_cast<long long>(k0 + k) * p.lda + m0 + m);
+        } else      { const int m = idx >> 2, k = (idx & 3) * 4;    // [m][k..k+3]
+          if (m0 + m < p.M && k0 + k < p.K) va = *reinterpret_cast<const float4*>(A + static_cast<long long>(m0 + m) * p.lda + k0 + k);
+        }
+        if (p.b_mn) { const int k = idx >> 5, n = (idx & 31) * 4;
+          if (k0 + k < p.K && n0 + n < p.N) vb = *reinterpret_cast<const float4*>(B + static_cast<long long>(k0 + k) * p.ldb + n0 + n);
+        } else      { const int n = idx >> 2, k = (idx & 3) * 4;
+          if (n0 + n < p.N && k0 + k < p.K) vb = *reinterpret_cast<const float4*>(B + static_cast<long long>(n0 + n) * p.ldb + k0 + k);
+        }
+        ra[4 * i] = va.x; ra[4 * i + 1] = va.y; ra[4 * i + 2] = va.z; ra[4 * i + 3] = va.w;
+        rb[4 * i] = vb.x; rb[4 * i + 1] = vb.y; rb[4 * i + 2] = vb.z; rb[4 * i + 3] = vb.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int idx = tid + i * kThreads;
+        int m, k;
+        if (p.a_mn) { m = idx & (kTM - 1); k = idx >> 7; } else { k = idx & (kTK - 1); m = idx >> 4; }
+        const int gm = m0 + m, gk = k0 + k;
+        ra[i] = (gm < p.M && gk < p.K)
+                    ? load_as_f32(p.A, a0 + (p.a_mn ? static_cast<long long>(gk) * p.lda + gm
+                                                    : static_cast<long long>(gm) * p.lda + gk), p.in_dtype)
+                    : 0.f;
+        int n, kk;
+        if (p.b_mn) { n = idx & (kTN - 1); kk = idx >> 7; } else { kk = idx & (kTK - 1); n = idx >> 4; }
+        const int gn = n0 + n, gkb = k0 + kk;
+        rb[i] = (gn < p.N && gkb < p.K)
+                    ? load_as_f32(p.B, b0 + (p.b_mn ? static_cast<long long>(gkb) * p.ldb + gn
+                                                    : static_cast<long long>(gn) * p.ldb + gkb), p.in_dtype)
+                    : 0.f;
+      }
     }
   };
   auto stash = [&](int buf) {
+    if constexpr (kVec) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int idx = tid + i * kThreads;
-      int m, k;
-      if (p.a_mn) { m = idx & (kTM - 1); k = idx >> 7; } else { k = idx & (kTK - 1); m = idx >> 4; }
-      As[buf][k][m] = ra[i];
-      int n, kk;
-      if (p.b_mn) { n = idx & (kTN - 1); kk = idx >> 7; } else { kk = idx & (kTK - 1); n = idx >> 4; }
-      Bs[buf][kk][n] = rb[i];
+      for (int i = 0; i < 2; ++i) {
+        const int idx = tid + i * kThreads;
+        if (p.a_mn) { const int k = idx >> 5, m = (idx & 31) * 4;
+          *reinterpret_cast<float4*>(&As[buf][k][m]) = make_float4(ra[4 * i], ra[4 * i + 1], ra[4 * i + 2], ra[4 * i + 3]);
+        } else      { const int m = idx >> 2, k = (idx & 3) * 4;
+#pragma unroll
+          for (int t = 0; t < 4; ++t) As[buf][k + t][m] = ra[4 * i + t];
+        }
+        if (p.b_mn) { const int k = idx >> 5, n = (idx & 31) * 4;
+          *reinterpret_cast<float4*>(&Bs[buf][k][n]) = make_float4(rb[4 * i], rb[4 * i + 1], rb[4 * i + 2], rb[4 * i + 3]);
+        } else      { const int n = idx >> 2, k = (idx & 3) * 4;
+#pragma unroll
+          for (int t = 0; t < 4; ++t) Bs[buf][k + t][n] = rb[4 * i + t];
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int idx = tid + i * kThreads;
+        int m, k;
+        if (p.a_mn) { m = idx & (kTM - 1); k = idx >> 7; } else { k = idx & (kTK - 1); m = idx >> 4; }
+        As[buf][k][m] = ra[i];
+        int n, kk;
+        if (p.b_mn) { n = idx & (kTN - 1); kk = idx >> 7; } else { kk = idx & (kTK - 1); n = idx >> 4; }
+        Bs[buf][kk][n] = rb[i];
+      }
     }
   };
 
@@ -165,7 +211,12 @@ cudaError_t launch_gemm_simt(const GemmProblem& g, cudaStream_t s) {
     gemm_simt_small_kernel<<<grid, block, 0, s>>>(p);
   } else {
     dim3 grid((g.N + kTN - 1) / kTN, (g.M + kTM - 1) / kTM, g.batch);
-    gemm_simt_tiled_kernel<<<grid, kThreads, 0, s>>>(p);
+    auto mult4 = [](long long v) { return (v & 3) == 0; };
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    const bool vec = g.in_dtype == kF32 && al16(g.A) && al16(g.B) && mult4(g.lda) && mult4(g.ldb) &&
+                     mult4(g.strideA) && mult4(g.strideB) && mult4(g.a_mn ? g.M : g.K) && mult4(g.b_mn ? g.N : g.K);
+    if (vec) gemm_simt_tiled_kernel<true><<<grid, kThreads, 0, s>>>(p);
+    else     gemm_simt_tiled_kernel<false><<<grid, kThreads, 0, s>>>(p);
   }
   return cudaGetLastError();
 }
