@@ -75,7 +75,7 @@ EXPORTS = [
     "ge2_launch_gemm_bias_act_f32_ex", "ge2_launch_gemm_bias_act_bwd_f32_ex",
     "ge2_launch_gemm_bias_act_typed", "ge2_launch_gemm_bias_act_bwd_typed",
     "ge2b_backward_scratch_bytes", "ge2b_device_status", "ge2b_sm_count", "ge2b_set_sm_limit", "ge2b_version",
-    "ge2b_last_route", "ge2b_launches_total",
+    "ge2b_last_route", "ge2b_launches_total", "ge2b_register_gemm_kernels",
     "ge2b_dense_plan_create", "ge2b_dense_plan_step", "ge2b_dense_plan_destroy",
     "ge2b_dense_plan_submit", "ge2b_dense_plan_wait",
     "ge2_launch_gemm_bias_act_bwd_noalloc",

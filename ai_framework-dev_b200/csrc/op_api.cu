@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <limits>
+#include <stdexcept>
 
 #include "../../include/ge2_op_api.hpp"
 #include "dense_ops.hpp"
@@ -198,6 +199,60 @@ Status GemmCudaBackward(const Tensor& A, const Tensor& B, const Tensor* C, const
   b.scratch = ws ? ws->scratch : nullptr;
   b.scratch_bytes = ws ? ws->scratch_bytes : 0;
   return from_rc(ge2b::dense_backward(b, reinterpret_cast<cudaStream_t>(stream)));
+}
+
+namespace {
+ge2b::DenseForward forward_from_params(const GemmBiasActParamsEx& p) {
+  ge2b::DenseForward f;
+  f.M = p.M; f.N = p.N; f.K = p.K;
+  f.dtype = ge2b::kF32; f.z_dtype = ge2b::kF32; f.math = 0;
+  f.A = p.A; f.lda = p.lda; f.B = p.B; f.ldb = p.ldb;
+  f.C = p.C; f.ldc = p.ldc;
+  f.D = p.D; f.ldd = p.ldd;
+  f.Z = (p.save_preact && p.Z) ? p.Z : nullptr; f.ldz = p.ldZ == 0 ? p.ldd : p.ldZ;
+  f.bias = static_cast<const float*>(p.bias);
+  f.bias_kind = p.bias ? static_cast<int>(p.bias_kind) : kBiasNone;
+  f.act = static_cast<int>(p.act); f.leaky = p.leaky_slope;
+  f.alpha = p.alpha; f.beta = p.C ? p.beta : 0.f;
+  return f;
+}
+}  // namespace
+
+void gemm_bias_act_f32_ex(const GemmBiasActParamsEx& p, CUstream_st* stream) {
+  (void)ge2b::dense_forward(forward_from_params(p), reinterpret_cast<cudaStream_t>(stream));
+}
+
+void launch_gemm_bias_act_f32_smoke_ex(const GemmBiasActParamsEx& p, CUstream_st* stream) {
+  gemm_bias_act_f32_ex(p, stream);     // the router picks the one-thread-per-output kernel by the same size rule
+}
+
+void gemm_bias_act_f32(const GemmBiasActParams& p, CUstream_st* stream) {
+  GemmBiasActParamsEx e{};
+  e.M = p.M; e.N = p.N; e.K = p.K;
+  e.A = p.A; e.lda = p.lda; e.B = p.B; e.ldb = p.ldb; e.C = p.C; e.ldc = p.ldc; e.D = p.D; e.ldd = p.ldd;
+  e.alpha = p.alpha; e.beta = p.beta; e.bias = p.bias; e.bias_kind = p.bias_kind; e.act = p.act;
+  e.leaky_slope = p.leaky_slope; e.Z = nullptr; e.ldZ = 0; e.save_preact = 0;
+  gemm_bias_act_f32_ex(e, stream);
+}
+
+void gemm_bias_act_bwd_f32(const GemmBiasActBwdParams& p, CUstream_st* stream) {
+  if (p.M <= 0 || p.N <= 0 || p.K <= 0) throw std::invalid_argument("invalid dims");
+  if (!p.gY || !p.Z) throw std::invalid_argument("gY/Z is null");
+  if (p.ldgY < p.N || p.ldZ < p.N) throw std::invalid_argument("ldgY/ldZ < N");
+  if (p.gZ_scratch && p.ldgZ != 0 && p.ldgZ != p.N) throw std::invalid_argument("gZ_scratch provided but ldgZ != N");
+  ge2b::DenseBackward b;
+  b.M = p.M; b.N = p.N; b.K = p.K;
+  b.dtype = ge2b::kF32; b.z_dtype = ge2b::kF32; b.math = 0;
+  b.A = p.A; b.lda = p.lda; b.B = p.B; b.ldb = p.ldb; b.C = p.C; b.ldc = p.ldc;
+  b.gY = p.gY; b.ldgY = p.ldgY; b.Z = p.Z; b.ldZ = p.ldZ;
+  b.gA = p.gA; b.ldgA = p.ldgA; b.gB = p.gB; b.ldgB = p.ldgB; b.gC = p.gC; b.ldgC = p.ldgC;
+  b.gBias = static_cast<float*>(p.gBias);
+  b.bias_kind = p.gBias ? static_cast<int>(p.bias_kind) : kBiasNone;
+  b.act = static_cast<int>(p.act); b.leaky = p.leaky_slope;
+  b.alpha = p.alpha; b.beta = p.beta;
+  b.scratch = p.gZ_scratch; b.scratch_bytes = 0;
+  if (ge2b::dense_backward(b, reinterpret_cast<cudaStream_t>(stream)) == ge2b::kBadArgs)
+    throw std::invalid_argument("gemm_bias_act_bwd_f32: inconsistent arguments");
 }
 
 }  // namespace ai::cuda::shim

@@ -209,6 +209,10 @@ int ge2b_sm_count(void);
 void ge2b_set_sm_limit(int n);
 const char* ge2b_version(void);
 
+/* Fills the C++ kernel registries of include/ge2_dispatch.hpp with this library's entries (idempotent).  Stands where
+ * the reference declares, and never defines, ai_backend_cuda_register_all (src/bindings/py_api.cpp:43). */
+void ge2b_register_gemm_kernels(void);
+
 /* Introspection for tests and benchmarks: which kernel family the calling thread's most recent GEMM went to
  * (0 none, 1 exact-fp32 CUDA-core kernel, 2 tcgen05 tensor-core kernel) and how many kernels this library
  * has launched in the process. */

@@ -91,6 +91,67 @@ constexpr std::size_t GemmRequiredBackwardScratchBytes(std::int64_t M, std::int6
   return (M <= 0 || N <= 0) ? 0 : static_cast<std::size_t>(M) * static_cast<std::size_t>(N) * sizeof(float);
 }
 
+// ---- parameter blocks of the layer below the Tensor API (backends/cuda/ops/gemm/api.hpp:19-93); the legacy C ABI
+//      adapters fill these and call the three functions declared after them.  fp32, row-major, device pointers. ----
+struct GemmBiasActParams {
+  int M, N, K;
+  const void* A; int lda;
+  const void* B; int ldb;
+  const void* C; int ldc;           // optional addend, used when beta != 0
+  void* D; int ldd;
+  float alpha, beta;                // D = act(alpha * A.B + beta * C + bias)
+  const void* bias;
+  BiasKind bias_kind;
+  ActKind act;
+  float leaky_slope;
+};
+
+struct GemmBiasActParamsEx {
+  int M, N, K;
+  const void* A; int lda;
+  const void* B; int ldb;
+  const void* C; int ldc;
+  void* D; int ldd;
+  float alpha, beta;
+  const void* bias;
+  BiasKind bias_kind;
+  ActKind act;
+  float leaky_slope;
+  void* Z; int ldZ;                 // pre-activation stash; ldZ == 0 means ldd
+  int save_preact;
+  void* lt_workspace{nullptr};      // carried, unused
+  std::size_t lt_workspace_bytes{0};
+};
+
+struct GemmBiasActBwdParams {
+  int M, N, K;
+  const void* A; int lda;
+  const void* B; int ldb;
+  const void* C; int ldc;
+  const void* Z; int ldZ;
+  const void* gY; int ldgY;
+  void* gA; int ldgA;
+  void* gB; int ldgB;
+  void* gC; int ldgC;
+  void* gBias;
+  float* gZ_scratch; int ldgZ;      // row-major with ld = N; null: stream-ordered allocation
+  float alpha{1.f};
+  float beta{0.f};
+  BiasKind bias_kind{BiasKind::None};
+  ActKind act{ActKind::None};
+  float leaky_slope{0.01f};
+  void* lt_workspace{nullptr};
+  std::size_t lt_workspace_bytes{0};
+};
+
+// Replace regemm_gemm_bias_act.cu:516-526 and regemm_backward.cu:151-301.  As in the reference they return nothing;
+// launch errors surface through cudaGetLastError(), and the backward throws std::invalid_argument on bad sizes
+// or null gY / Z.
+void gemm_bias_act_f32(const GemmBiasActParams& p, CUstream_st* stream);
+void gemm_bias_act_f32_ex(const GemmBiasActParamsEx& p, CUstream_st* stream);
+void gemm_bias_act_bwd_f32(const GemmBiasActBwdParams& p, CUstream_st* stream);
+void launch_gemm_bias_act_f32_smoke_ex(const GemmBiasActParamsEx& p, CUstream_st* stream);
+
 // Y[M,N] = act(A[M,K] . B[K,N] + bias); with attrs.save_z the pre-activation is written to *Z_saved.
 Status GemmCudaLaunch(const Tensor& A, const Tensor& B, const Tensor* Bias, Tensor& Y, const GemmAttrs& attrs,
                       StreamHandle stream, Tensor* Z_saved = nullptr, const GemmWorkspace* ws = nullptr);

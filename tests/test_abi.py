@@ -53,3 +53,13 @@ def test_missing_library_is_a_loud_error(pkg, monkeypatch, tmp_path):
     monkeypatch.setattr(L, "library_path", lambda: tmp_path / "nope.so")
     with pytest.raises(RuntimeError, match="no CPU or eager fallback"):
         L.load_library()
+
+
+def test_cpp_registry_and_operator_api_validation(pkg, lib, tmp_path):
+    """Compiles tests/cpp/dispatch_check.cpp against the library (g++, host only) and runs it."""
+    exe = tmp_path / "dispatch_check"
+    libdir = pkg.library_path().parent
+    subprocess.run(["g++", "-std=c++17", "-O1", "-I", str(ROOT / "include"), str(ROOT / "tests" / "cpp" / "dispatch_check.cpp"),
+                    "-o", str(exe), "-L", str(libdir), "-lge2_b200", f"-Wl,-rpath,{libdir}"], check=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", r.stdout + r.stderr
