@@ -63,3 +63,18 @@ def test_cpp_registry_and_operator_api_validation(pkg, lib, tmp_path):
                     "-o", str(exe), "-L", str(libdir), "-lge2_b200", f"-Wl,-rpath,{libdir}"], check=True)
     r = subprocess.run([str(exe)], capture_output=True, text=True)
     assert r.returncode == 0 and r.stdout.strip() == "ok", r.stdout + r.stderr
+
+
+@pytest.mark.gpu
+def test_cpp_parameter_block_and_registry_on_gpu(pkg, lib, tmp_path):
+    """Compiles tests/cpp/param_block_gpu_check.cpp (g++, links the library and cudart) and runs it on the device:
+    gemm_bias_act_f32 / _f32_ex / _bwd_f32 with the reference's parameter blocks and gemm_run_ex / gemm_bwd_run
+    through the registry, Z and the ReLU output bit-exact against an ascending-k fmaf loop."""
+    exe = tmp_path / "param_block_gpu_check"
+    libdir = pkg.library_path().parent
+    subprocess.run(["g++", "-std=c++17", "-O1", "-I", str(ROOT / "include"), "-I", "/usr/local/cuda/include",
+                    str(ROOT / "tests" / "cpp" / "param_block_gpu_check.cpp"), "-o", str(exe),
+                    "-L", str(libdir), "-lge2_b200", "-L", "/usr/local/cuda/lib64", "-lcudart",
+                    f"-Wl,-rpath,{libdir}"], check=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.strip() == "ok", r.stdout + r.stderr
