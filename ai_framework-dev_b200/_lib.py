@@ -62,6 +62,15 @@ class ParamsBwdTyped(C.Structure):
                 ("scratch_bytes", C.c_size_t), ("reuse_gz", C.c_int)]
 
 
+class ParamsConv2D(C.Structure):
+    _fields_ = [("N", C.c_int), ("Cin", C.c_int), ("H", C.c_int), ("W", C.c_int),
+                ("Cout", C.c_int), ("Kh", C.c_int), ("Kw", C.c_int),
+                ("stride_h", C.c_int), ("stride_w", C.c_int), ("pad_h", C.c_int), ("pad_w", C.c_int),
+                ("dil_h", C.c_int), ("dil_w", C.c_int), ("groups", C.c_int),
+                ("act_kind", C.c_int), ("leaky_slope", C.c_float), ("with_bias", C.c_int), ("save_z", C.c_int),
+                ("dtype", C.c_int), ("z_dtype", C.c_int), ("math", C.c_int)]
+
+
 # numbering of the C ABI
 BIAS_SCALAR, BIAS_PER_M, BIAS_PER_N = 0, 1, 2
 ACT = {"none": 0, "relu": 1, "leaky_relu": 2, "leakyrelu": 2, "lrelu": 2, "gelu": 3, "sigmoid": 4, "tanh": 5}
@@ -80,6 +89,7 @@ EXPORTS = [
     "ge2b_dense_plan_submit", "ge2b_dense_plan_wait",
     "ge2_launch_gemm_bias_act_bwd_noalloc",
     "ge2_launch_softmax_ce_fused", "ge2_launch_sgd_update",
+    "ge2b_conv2d_forward", "ge2b_conv2d_backward", "ge2b_conv2d_output_size",
 ]
 
 
@@ -125,6 +135,12 @@ def load_library() -> C.CDLL:
     lib.ge2b_dense_plan_wait.restype = C.c_int
     lib.ge2b_dense_plan_destroy.argtypes = [C.c_void_p]
     lib.ge2b_dense_plan_destroy.restype = None
+    lib.ge2b_conv2d_forward.argtypes = [C.POINTER(ParamsConv2D)] + [C.c_void_p] * 6
+    lib.ge2b_conv2d_forward.restype = C.c_int
+    lib.ge2b_conv2d_backward.argtypes = [C.POINTER(ParamsConv2D)] + [C.c_void_p] * 8
+    lib.ge2b_conv2d_backward.restype = C.c_int
+    lib.ge2b_conv2d_output_size.argtypes = [C.POINTER(ParamsConv2D), C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    lib.ge2b_conv2d_output_size.restype = C.c_int
     _LIB = lib
     return lib
 

@@ -1,0 +1,399 @@
+// 2-D convolution (NCHW tensors, OIHW weights, groups = 1) on the dense-layer GEMM kernels.
+//
+// The reference (backends/cuda/ops/conv2d/launcher.cu:115-462, kernels.cu:12-167) loops over the images of a batch
+// and, per image, runs im2col -> GEMM -> transpose, after packing the weight into [K, Cout]; its backward adds
+// two more transposes, a per-image GemmCudaBackward, col2im and an atomic transpose-add into the packed weight
+// gradient.  Here the whole batch takes
+//   forward   one im2col pass into Col[K][N][HWp] (output positions contiguous), then ONE strided-batched GEMM launch
+//             Y[n] (Cout x HWo) = act(W (Cout x K) . Col[n] (K x HWo) + bias[co]) that writes NCHW directly: the OIHW
+//             weight is already the row-major Cout x K matrix, the per-channel bias is the kernel's per-row bias, and
+//             the pre-activation stash is the same launch's second output.  No weight packing, no transposes.
+//   backward  gZ = dY * act'(Z) with per-(image, channel) row sums folded into dB; dW (Cout x K) as ONE launch whose
+//             reduction runs over the output positions of every image (no atomics, no per-image partial results);
+//             dCol[n] = W^T . gZ[n] as one batched launch into the Col buffer, then a gather-form col2im into dX.
+//   1x1, stride 1, no padding: Col[n] is X[n] itself, so neither pass materialises anything.
+// fp32 tensors run the exact fp32 kernel (same ascending-k fmaf chain per output as the reference's GEMM, so Z is
+// bit-identical) unless math = tensor asks for TF32; bf16 / f16 tensors run on the tcgen05 kernel.
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../../include/ge2_b200.h"
+#include "../../include/ge2_conv2d_api.hpp"
+#include "dense_ops.hpp"
+#include "epilogue_math.cuh"
+
+namespace ge2b {
+namespace {
+
+struct ConvGeom {
+  int N, Cin, H, W, Cout, Kh, Kw;
+  int sh, sw, ph, pw, dh, dw;
+  int Ho, Wo, HWo, HWp, K;      // HWp: HWo rounded up so that every Col / gZ row starts on a 32-byte boundary
+};
+
+constexpr int kColThreads = 128;
+
+// Col[k][n][hw] = X[n][c][ho*sh - ph + kh*dh][wo*sw - pw + kw*dw] (zero outside the image and in the padding columns
+// hw >= HWo).  grid.x = K * N (one (k, n) row per block column), grid.y covers HWp.
+__global__ void __launch_bounds__(kColThreads)
+im2col_batched_kernel(const void* __restrict__ X, void* __restrict__ Col, const ConvGeom g, const int dt) {
+  const int kn = blockIdx.x;
+  const int k = kn / g.N, n = kn - k * g.N;
+  const int kw = k % g.Kw;
+  const int t = k / g.Kw;
+  const int kh = t % g.Kh, c = t / g.Kh;
+  const long long x_base = (static_cast<long long>(n) * g.Cin + c) * g.H * g.W;
+  const long long col_base = static_cast<long long>(kn) * g.HWp;
+  for (int hw = blockIdx.y * kColThreads + threadIdx.x; hw < g.HWp; hw += gridDim.y * kColThreads) {
+    float v = 0.f;
+    if (hw < g.HWo) {
+      const int ho = hw / g.Wo, wo = hw - ho * g.Wo;
+      const int hi = ho * g.sh - g.ph + kh * g.dh;
+      const int wi = wo * g.sw - g.pw + kw * g.dw;
+      if (static_cast<unsigned>(hi) < static_cast<unsigned>(g.H) && static_cast<unsigned>(wi) < static_cast<unsigned>(g.W))
+        v = load_as_f32(X, x_base + static_cast<long long>(hi) * g.W + wi, dt);
+    }
+    // values are copied, never rounded: the store converts back to the dtype it was loaded from
+    store_from_f32(Col, col_base + hw, dt, v);
+  }
+}
+
+// dX[n][c][h][w] = sum over the (kh, kw) taps whose output position exists of dCol[(c,kh,kw)][n][ho*Wo + wo];
+// fp32 accumulation in tap order (kh outer, kw inner), one thread per input pixel, plain store (no atomics).
+__global__ void __launch_bounds__(256)
+col2im_batched_kernel(const void* __restrict__ dCol, void* __restrict__ dX, const ConvGeom g, const int dt) {
+  const long long total = static_cast<long long>(g.N) * g.Cin * g.H * g.W;
+  for (long long idx = blockIdx.x * 256ll + threadIdx.x; idx < total; idx += gridDim.x * 256ll) {
+    const int w = static_cast<int>(idx % g.W);
+    long long t = idx / g.W;
+    const int h = static_cast<int>(t % g.H); t /= g.H;
+    const int c = static_cast<int>(t % g.Cin);
+    const int n = static_cast<int>(t / g.Cin);
+    float acc = 0.f;
+    for (int kh = 0; kh < g.Kh; ++kh) {
+      const int hn = h + g.ph - kh * g.dh;
+      if (hn < 0 || hn % g.sh) continue;
+      const int ho = hn / g.sh;
+      if (ho >= g.Ho) continue;
+      for (int kw = 0; kw < g.Kw; ++kw) {
+        const int wn = w + g.pw - kw * g.dw;
+        if (wn < 0 || wn % g.sw) continue;
+        const int wo = wn / g.sw;
+        if (wo >= g.Wo) continue;
+        const int k = (c * g.Kh + kh) * g.Kw + kw;
+        acc += load_as_f32(dCol, (static_cast<long long>(k) * g.N + n) * g.HWp + ho * g.Wo + wo, dt);
+      }
+    }
+    store_from_f32(dX, idx, dt, acc);
+  }
+}
+
+// dB[co] = sum_n rows[n * Cout + co]  (rows: per-(image, channel) sums of gZ left by the prologue kernel)
+__global__ void fold_db_kernel(const float* __restrict__ rows, float* __restrict__ dB, int N, int Cout) {
+  const int co = blockIdx.x * blockDim.x + threadIdx.x;
+  if (co >= Cout) return;
+  float acc = 0.f;
+  for (int n = 0; n < N; ++n) acc += rows[static_cast<long long>(n) * Cout + co];
+  dB[co] = acc;
+}
+
+int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+bool make_geom(const ge2b_conv2d_params_t& p, ConvGeom& g) {
+  g.N = p.N; g.Cin = p.Cin; g.H = p.H; g.W = p.W; g.Cout = p.Cout; g.Kh = p.Kh; g.Kw = p.Kw;
+  g.sh = p.stride_h; g.sw = p.stride_w; g.ph = p.pad_h; g.pw = p.pad_w; g.dh = p.dil_h; g.dw = p.dil_w;
+  if (g.N <= 0 || g.Cin <= 0 || g.H <= 0 || g.W <= 0 || g.Cout <= 0 || g.Kh <= 0 || g.Kw <= 0) return false;
+  if (g.sh <= 0 || g.sw <= 0 || g.dh <= 0 || g.dw <= 0 || g.ph < 0 || g.pw < 0) return false;
+  // output size as in conv2d/launcher.cu:137-138
+  g.Ho = (g.H + 2 * g.ph - g.dh * (g.Kh - 1) - 1) / g.sh + 1;
+  g.Wo = (g.W + 2 * g.pw - g.dw * (g.Kw - 1) - 1) / g.sw + 1;
+  if (g.Ho <= 0 || g.Wo <= 0) return false;
+  const long long hwo = static_cast<long long>(g.Ho) * g.Wo, k = static_cast<long long>(g.Cin) * g.Kh * g.Kw;
+  if (hwo > (1ll << 30) || k > (1ll << 30)) return false;
+  g.HWo = static_cast<int>(hwo);
+  g.HWp = round_up(g.HWo, 8);
+  g.K = static_cast<int>(k);
+  return true;
+}
+
+bool pointwise(const ConvGeom& g) {
+  return g.Kh == 1 && g.Kw == 1 && g.sh == 1 && g.sw == 1 && g.ph == 0 && g.pw == 0;
+}
+
+cudaError_t launch_im2col(const void* X, void* Col, const ConvGeom& g, int dt, cudaStream_t s) {
+  const long long rows = static_cast<long long>(g.K) * g.N;
+  if (rows > 0x7fffffffll) return cudaErrorInvalidValue;
+  int gy = (g.HWp + kColThreads - 1) / kColThreads;
+  if (gy > 65535) gy = 65535;
+  im2col_batched_kernel<<<dim3(static_cast<unsigned>(rows), gy), kColThreads, 0, s>>>(X, Col, g, dt);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+namespace {
+
+int dtype_ok(int dt) { return dt == kF32 || dt == kF16 || dt == kBF16; }
+
+// Stream-ordered scratch that frees itself on every return path.
+struct AsyncBuf {
+  void* p = nullptr;
+  cudaStream_t s;
+  explicit AsyncBuf(cudaStream_t st) : s(st) {}
+  bool alloc(size_t bytes) { return cudaMallocAsync(&p, bytes ? bytes : 16, s) == cudaSuccess; }
+  ~AsyncBuf() { if (p) cudaFreeAsync(p, s); }
+  AsyncBuf(const AsyncBuf&) = delete;
+  AsyncBuf& operator=(const AsyncBuf&) = delete;
+};
+
+}  // namespace
+
+int conv2d_forward(const ge2b_conv2d_params_t& p, const void* X, const void* W, const float* bias, void* Y, void* Z,
+                   cudaStream_t s) {
+  ConvGeom g;
+  if (!X || !W || !Y || !dtype_ok(p.dtype) || !make_geom(p, g)) return kBadArgs;
+  if (p.groups != 1) return kUnimplemented;
+  const int zdt = Z ? p.z_dtype : p.dtype;
+  if (Z && !(zdt == p.dtype || zdt == kF32)) return kBadArgs;
+  const int esz = dtype_bytes(p.dtype);
+
+  AsyncBuf col(s);
+  const void* B = X;
+  long long ldb = static_cast<long long>(g.H) * g.W, strideB = static_cast<long long>(g.Cin) * g.H * g.W;
+  if (!pointwise(g)) {
+    if (!col.alloc(static_cast<size_t>(g.K) * g.N * g.HWp * esz)) return kCudaError;
+    if (launch_im2col(X, col.p, g, p.dtype, s) != cudaSuccess) return kCudaError;
+    B = col.p; ldb = static_cast<long long>(g.N) * g.HWp; strideB = g.HWp;
+  }
+  DenseForward f;
+  f.M = g.Cout; f.N = g.HWo; f.K = g.K; f.batch = g.N;
+  f.dtype = p.dtype; f.z_dtype = zdt; f.math = p.math;
+  f.A = W; f.lda = g.K; f.strideA = 0;                       // the weight is shared by every image
+  f.B = B; f.ldb = ldb; f.strideB = strideB;
+  f.D = Y; f.ldd = g.HWo; f.strideD = static_cast<long long>(g.Cout) * g.HWo;
+  f.Z = Z; f.ldz = g.HWo; f.strideZ = f.strideD;
+  f.bias = (bias && p.with_bias) ? bias : nullptr; f.bias_kind = f.bias ? kBiasPerM : kBiasNone;
+  f.act = p.act_kind; f.leaky = p.leaky_slope;
+  return dense_forward(f, s);
+}
+
+int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W, const void* dY, const void* Z,
+                    void* dW, float* dB, void* dX, cudaStream_t s) {
+  ConvGeom g;
+  if (!X || !W || !dY || !Z || !dtype_ok(p.dtype) || !make_geom(p, g)) return kBadArgs;
+  if (p.groups != 1) return kUnimplemented;
+  if (!(p.z_dtype == p.dtype || p.z_dtype == kF32)) return kBadArgs;
+  const int esz = dtype_bytes(p.dtype);
+  const long long img_rows = static_cast<long long>(g.N) * g.Cout;
+  if (img_rows > 0x7fffffffll) return kBadArgs;
+
+  // ---- gZ = dY * act'(Z), rows = (image, channel), columns = output positions; row sums feed dB ----
+  AsyncBuf gz(s), rows(s);
+  if (!gz.alloc(static_cast<size_t>(img_rows) * g.HWp * esz)) return kCudaError;
+  const bool want_db = dB != nullptr;
+  if (want_db) {
+    if (!rows.alloc(static_cast<size_t>(img_rows) * sizeof(float))) return kCudaError;
+    if (cudaMemsetAsync(rows.p, 0, static_cast<size_t>(img_rows) * sizeof(float), s) != cudaSuccess) return kCudaError;
+  }
+  BwdPrologueArgs pa{};
+  pa.M = static_cast<int>(img_rows); pa.N = g.HWo;
+  pa.gY = dY; pa.ldgY = g.HWo; pa.gy_dtype = p.dtype;
+  pa.Z = Z; pa.ldZ = g.HWo; pa.z_dtype = p.z_dtype;
+  pa.gZ = gz.p; pa.ldgZ = g.HWp; pa.gz_dtype = p.dtype;
+  pa.gBias = want_db ? static_cast<float*>(rows.p) : nullptr; pa.bias_kind = want_db ? kBiasPerM : kBiasNone;
+  pa.act = p.act_kind; pa.leaky = p.leaky_slope;
+  if (launch_bwd_prologue(pa, s) != cudaSuccess) return kCudaError;
+  if (want_db) {
+    fold_db_kernel<<<(g.Cout + 127) / 128, 128, 0, s>>>(static_cast<const float*>(rows.p), dB, g.N, g.Cout);
+    if (cudaGetLastError() != cudaSuccess) return kCudaError;
+  }
+  if (!dW && !dX) return kOk;
+
+  const bool pw = pointwise(g);
+  AsyncBuf col(s);
+  const long long gz_stride = static_cast<long long>(g.Cout) * g.HWp;
+  const void* B = X;
+  long long ldb = static_cast<long long>(g.H) * g.W, strideB = static_cast<long long>(g.Cin) * g.H * g.W;
+  if (!pw) {
+    if (!col.alloc(static_cast<size_t>(g.K) * g.N * g.HWp * esz)) return kCudaError;
+    B = col.p; ldb = static_cast<long long>(g.N) * g.HWp; strideB = g.HWp;
+  }
+
+  if (dW) {
+    if (!pw && launch_im2col(X, col.p, g, p.dtype, s) != cudaSuccess) return kCudaError;
+    // dW (Cout x K) = sum_n gZ[n] (Cout x HWo) . Col[n]^T (HWo x K)
+    GemmProblem q{};
+    q.M = g.Cout; q.N = g.K; q.K = g.HWo; q.batch = g.N;
+    q.in_dtype = p.dtype; q.math = p.math;
+    q.a_mn = false; q.b_mn = false;                            // both operands have the reduction index contiguous
+    q.A = gz.p; q.lda = g.HWp; q.strideA = gz_stride;
+    q.B = B; q.ldb = ldb; q.strideB = strideB;
+    q.reduce_batch = true;
+    q.epi.D = dW; q.epi.ldd = g.K; q.epi.d_dtype = p.dtype; q.epi.z_dtype = p.dtype;
+    q.epi.alpha = 1.f; q.epi.act = kActNone; q.epi.bias_kind = kBiasNone;
+    int rc = run_gemm_problem(q, s);
+    if (rc == kUnimplemented) {
+      // exact-fp32 route: one launch per image, accumulating into dW (beta = 1 from the second image on)
+      for (int n = 0; n < g.N; ++n) {
+        DenseForward f;
+        f.M = g.Cout; f.N = g.K; f.K = g.HWo; f.batch = 1;
+        f.dtype = p.dtype; f.z_dtype = p.dtype; f.math = p.math;
+        f.trans_b = true;
+        f.A = static_cast<const uint8_t*>(gz.p) + static_cast<size_t>(n) * gz_stride * esz; f.lda = g.HWp;
+        f.B = static_cast<const uint8_t*>(B) + static_cast<size_t>(n) * strideB * esz; f.ldb = ldb;
+        f.C = dW; f.ldc = g.K; f.beta = n > 0 ? 1.f : 0.f;
+        f.D = dW; f.ldd = g.K;
+        rc = dense_forward(f, s);
+        if (rc != kOk) return rc;
+      }
+    } else if (rc != kOk) {
+      return rc;
+    }
+  }
+
+  if (dX) {
+    // dCol[n] (K x HWo) = W^T (K x Cout) . gZ[n] (Cout x HWo); for a pointwise convolution dCol[n] is dX[n]
+    DenseForward f;
+    f.M = g.K; f.N = g.HWo; f.K = g.Cout; f.batch = g.N;
+    f.dtype = p.dtype; f.z_dtype = p.dtype; f.math = p.math;
+    f.trans_a = true;                                          // W is stored Cout x K: reduction index outermost
+    f.A = W; f.lda = g.K; f.strideA = 0;
+    f.B = gz.p; f.ldb = g.HWp; f.strideB = gz_stride;
+    if (pw) { f.D = dX; f.ldd = g.HWo; f.strideD = static_cast<long long>(g.Cin) * g.HWo; }
+    else    { f.D = col.p; f.ldd = static_cast<long long>(g.N) * g.HWp; f.strideD = g.HWp; }
+    const int rc = dense_forward(f, s);
+    if (rc != kOk) return rc;
+    if (!pw) {
+      const long long total = static_cast<long long>(g.N) * g.Cin * g.H * g.W;
+      long long blocks = (total + 255) / 256;
+      if (blocks > (1 << 20)) blocks = 1 << 20;
+      col2im_batched_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(col.p, dX, g, p.dtype);
+      if (cudaGetLastError() != cudaSuccess) return kCudaError;
+    }
+  }
+  return kOk;
+}
+
+}  // namespace ge2b
+
+extern "C" {
+
+int ge2b_conv2d_forward(const ge2b_conv2d_params_t* p, const void* X, const void* W, const float* bias, void* Y, void* Z,
+                        void* stream) {
+  if (!p) return ge2b::kBadArgs;
+  return ge2b::conv2d_forward(*p, X, W, bias, Y, (p->save_z ? Z : nullptr), reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ge2b_conv2d_backward(const ge2b_conv2d_params_t* p, const void* X, const void* W, const void* dY, const void* Z,
+                         void* dW, float* dB, void* dX, void* stream) {
+  if (!p) return ge2b::kBadArgs;
+  return ge2b::conv2d_backward(*p, X, W, dY, Z, dW, dB, dX, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int ge2b_conv2d_output_size(const ge2b_conv2d_params_t* p, int* Ho, int* Wo) {
+  ge2b::ConvGeom g;
+  if (!p || !ge2b::make_geom(*p, g)) return ge2b::kBadArgs;
+  if (Ho) *Ho = g.Ho;
+  if (Wo) *Wo = g.Wo;
+  return ge2b::kOk;
+}
+
+}  // extern "C"
+
+// ---- C++ operator API (validation order and Status codes of conv2d/launcher.cu:115-158, 236-280) ----
+namespace ai {
+namespace {
+
+namespace shim = cuda::shim;
+
+bool is4(const Tensor& t, shim::DType dt) {
+  return t.device == shim::Device::CUDA && t.desc.dtype == dt && t.desc.layout == shim::Layout::RowMajor &&
+         t.desc.shape.size() == 4;
+}
+bool float_dtype(shim::DType d) { return d == shim::DType::F32 || d == shim::DType::F16 || d == shim::DType::BF16; }
+bool shape_is(const Tensor& t, std::int64_t a, std::int64_t b, std::int64_t c, std::int64_t d) {
+  return t.desc.shape[0] == a && t.desc.shape[1] == b && t.desc.shape[2] == c && t.desc.shape[3] == d;
+}
+Status from_rc(int rc) {
+  switch (rc) {
+    case ge2b::kOk:            return Status::Ok;
+    case ge2b::kBadArgs:       return Status::Invalid;
+    case ge2b::kUnimplemented: return Status::Unimplemented;
+    default:                   return Status::CUDA_ERROR;
+  }
+}
+bool fill_params(const Tensor& X, const Tensor& W, const Conv2DAttrs& a, ge2b_conv2d_params_t& p) {
+  for (int i = 0; i < 4; ++i)
+    if (X.desc.shape[i] <= 0 || X.desc.shape[i] > 0x7fffffff || W.desc.shape[i] <= 0 || W.desc.shape[i] > 0x7fffffff)
+      return false;
+  p.N = static_cast<int>(X.desc.shape[0]); p.Cin = static_cast<int>(X.desc.shape[1]);
+  p.H = static_cast<int>(X.desc.shape[2]); p.W = static_cast<int>(X.desc.shape[3]);
+  p.Cout = static_cast<int>(W.desc.shape[0]); p.Kh = static_cast<int>(W.desc.shape[2]); p.Kw = static_cast<int>(W.desc.shape[3]);
+  p.stride_h = a.stride_h; p.stride_w = a.stride_w; p.pad_h = a.pad_h; p.pad_w = a.pad_w; p.dil_h = a.dil_h; p.dil_w = a.dil_w;
+  p.groups = a.groups;
+  p.act_kind = static_cast<int>(a.act); p.leaky_slope = a.leaky_slope;
+  p.with_bias = a.with_bias ? 1 : 0; p.save_z = a.save_z ? 1 : 0;
+  p.dtype = static_cast<int>(X.desc.dtype); p.z_dtype = p.dtype;
+  p.math = (X.desc.dtype == shim::DType::F32) ? ge2b::default_fp32_math() : 1;
+  return true;
+}
+
+}  // namespace
+
+Status Conv2DCudaLaunch(const Tensor& X, const Tensor& W, const Tensor* B, Tensor& Y, const Conv2DAttrs& a,
+                        StreamHandle stream, Tensor* Z_saved, const Conv2DWorkspaceFwd* /*ws_fwd*/) {
+  const shim::DType dt = X.desc.dtype;
+  if (!float_dtype(dt) || !is4(X, dt) || !is4(Y, dt)) return Status::Invalid;
+  if (!is4(W, dt)) return Status::Invalid;
+  if (a.groups != 1) return Status::Unimplemented;
+  if (W.desc.shape[1] != X.desc.shape[1]) return Status::ShapeMismatch;
+  ge2b_conv2d_params_t p{};
+  if (!fill_params(X, W, a, p)) return Status::Invalid;
+  int Ho = 0, Wo = 0;
+  const bool geom_ok = ge2b_conv2d_output_size(&p, &Ho, &Wo) == 0;
+  if (geom_ok && !shape_is(Y, p.N, p.Cout, Ho, Wo)) return Status::ShapeMismatch;
+  if (!geom_ok) return Status::Invalid;
+  const bool want_z = a.save_z && Z_saved != nullptr;
+  if (want_z) {
+    const shim::DType zdt = Z_saved->desc.dtype;
+    if (!(zdt == dt || zdt == shim::DType::F32) || !is4(*Z_saved, zdt)) return Status::Invalid;
+    if (!shape_is(*Z_saved, p.N, p.Cout, Ho, Wo)) return Status::ShapeMismatch;
+    p.z_dtype = static_cast<int>(zdt);
+  }
+  p.save_z = want_z ? 1 : 0;
+  const float* bias = (B && B->data && a.with_bias) ? static_cast<const float*>(B->data) : nullptr;
+  if (bias && B->desc.dtype != shim::DType::F32) return Status::Invalid;
+  p.with_bias = bias ? 1 : 0;
+  return from_rc(ge2b_conv2d_forward(&p, X.data, W.data, bias, Y.data, want_z ? Z_saved->data : nullptr, stream));
+}
+
+Status Conv2DCudaBackwardLaunch(const Tensor& X, const Tensor& W, const Tensor& dY, const Tensor& Z, Tensor* dW,
+                                Tensor* dB, Tensor* dX, const Conv2DAttrs& a, StreamHandle stream,
+                                const Conv2DWorkspaceBwd* /*ws_bwd*/) {
+  const shim::DType dt = X.desc.dtype;
+  const shim::DType zdt = Z.desc.dtype;
+  if (!float_dtype(dt) || !is4(X, dt) || !is4(W, dt) || !is4(dY, dt) || !(zdt == dt || zdt == shim::DType::F32) ||
+      !is4(Z, zdt))
+    return Status::Invalid;
+  if (a.groups != 1) return Status::Unimplemented;
+  if (W.desc.shape[1] != X.desc.shape[1]) return Status::ShapeMismatch;
+  ge2b_conv2d_params_t p{};
+  if (!fill_params(X, W, a, p)) return Status::Invalid;
+  p.z_dtype = static_cast<int>(zdt);
+  int Ho = 0, Wo = 0;
+  const bool geom_ok = ge2b_conv2d_output_size(&p, &Ho, &Wo) == 0;
+  if (geom_ok && (!shape_is(dY, p.N, p.Cout, Ho, Wo) || !shape_is(Z, p.N, p.Cout, Ho, Wo))) return Status::ShapeMismatch;
+  if (dW && (!is4(*dW, dt) || !shape_is(*dW, p.Cout, p.Cin, p.Kh, p.Kw))) return Status::ShapeMismatch;
+  if (dB && !(dB->device == shim::Device::CUDA && dB->desc.dtype == shim::DType::F32 && dB->desc.shape.size() == 1 &&
+              dB->desc.shape[0] == p.Cout))
+    return Status::ShapeMismatch;
+  if (dX && (!is4(*dX, dt) || !shape_is(*dX, p.N, p.Cin, p.H, p.W))) return Status::ShapeMismatch;
+  if (!geom_ok) return Status::Invalid;
+  // the bias gradient is produced only when the layer has a bias (launcher.cu:412-418)
+  float* db = (dB && a.with_bias) ? static_cast<float*>(dB->data) : nullptr;
+  return from_rc(ge2b_conv2d_backward(&p, X.data, W.data, dY.data, Z.data, dW ? dW->data : nullptr, db,
+                                      dX ? dX->data : nullptr, stream));
+}
+
+}  // namespace ai

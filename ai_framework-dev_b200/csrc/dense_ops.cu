@@ -34,6 +34,14 @@ int run_gemm(const GemmProblem& g, cudaStream_t s) {
 
 }  // namespace
 
+int run_gemm_problem(const GemmProblem& g, cudaStream_t s) {
+  if (g.reduce_batch && g.batch > 1) {
+    const bool want_tc = (g.in_dtype != kF32) || g.math == 1;
+    if (!want_tc || !gemm_tc_supported(g, nullptr)) return kUnimplemented;
+  }
+  return run_gemm(g, s);
+}
+
 int last_route() { return t_last_route; }
 long long launches_total() { return g_launches.load(std::memory_order_relaxed); }
 

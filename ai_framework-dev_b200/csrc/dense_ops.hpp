@@ -50,6 +50,9 @@ int last_route();                 // thread-local: route of the most recent GEMM
 long long launches_total();       // process-wide count of kernels launched by this library
 
 int dense_forward(const DenseForward& f, cudaStream_t s);
+// Routes a fully described problem (used by the convolution, which needs the batch-reducing form).  A problem with
+// reduce_batch that the tensor-core path cannot take (exact fp32, unaligned pitch) returns kUnimplemented.
+int run_gemm_problem(const GemmProblem& g, cudaStream_t s);
 int dense_backward(const DenseBackward& b, cudaStream_t s);
 
 // fp32 tensors default to exact arithmetic; GE2B_FP32_MATH=tf32 in the environment opts the operator API

@@ -51,6 +51,9 @@ struct GemmProblem {
   const void* A; long long lda, strideA;
   const void* B; long long ldb, strideB;
   EpilogueArgs epi;
+  // The batch index joins the reduction: D = act(alpha * sum_b A[b].B[b] + ...), one output matrix.  Tensor-core
+  // path only (used by the convolution's weight gradient, which sums over the images of a batch).
+  bool reduce_batch = false;
 };
 
 // gZ = gY * act'(Z) with the column/row/total reduction into gBias.

@@ -111,7 +111,7 @@ TileChoice choose_tile(const GemmProblem& g) {
   const double sms = sm_budget();
   auto cost = [&](int bn, int cg, double rate) {
     const long long mb = (g.M + 128 * cg - 1) / (128 * cg);
-    const long long tiles = static_cast<long long>(g.batch) * mb * ((g.N + bn - 1) / bn);
+    const long long tiles = static_cast<long long>(g.reduce_batch ? 1 : g.batch) * mb * ((g.N + bn - 1) / bn);
     const long long units = static_cast<long long>(sms) / cg;
     const double waves = static_cast<double>((tiles + units - 1) / units);
     return waves * bn / rate;      // time units: one 128-wide tile at full rate = 128
@@ -142,7 +142,7 @@ bool gemm_tc_supported(const GemmProblem& g, const char** why) {
 
 cudaError_t launch_gemm_tc(const GemmProblem& g, cudaStream_t s) {
   TcParams p{};
-  p.M = g.M; p.N = g.N; p.K = g.K; p.batch = g.batch;
+  p.M = g.M; p.N = g.N; p.K = g.K; p.batch = g.reduce_batch ? 1 : g.batch;
   p.a_bcast = (g.batch > 1 && g.strideA == 0) ? 1 : 0;
   p.b_bcast = (g.batch > 1 && g.strideB == 0) ? 1 : 0;
   p.epi = g.epi;

@@ -44,6 +44,8 @@ struct TcParams {
   int M, N, K, batch;
   int m_blocks, n_blocks, k_blocks;
   int a_bcast, b_bcast;     // operand has batch stride 0: always read slice 0
+  int kb_per_slice;         // > 0: the reduction runs over every batch slice in turn (k_blocks = slices * this);
+                            // one output matrix, `batch` is 1 for the tile schedule
   uint32_t idesc;
   EpilogueArgs epi;
   int d_vec, z_vec, c_vec, bias_vec;   // 16-byte vector access allowed for that tensor
@@ -51,7 +53,13 @@ struct TcParams {
   // occupies all SMs.  Items [0, main_tiles) are whole tiles; item main_tiles + s * tail_tiles + r is slice s of
   // tail tile r.  Slices s > 0 leave fp32 partial sums in `ws` and count into flags[r]; slice 0 adds them and
   // runs the epilogue.
+  //
+  // Narrow tail (common variant, CTA pairs with 256-column tiles): the tiles of a partly filled last wave are cut
+  // into two 128-column halves instead, so that twice as many pairs finish the launch together and nothing is
+  // exchanged.  Item main_tiles + i is half (i & 1) of tail tile i / 2; `split` is 2 and `idesc_half` describes the
+  // 256 x 128 MMA.
   int main_tiles, tail_tiles, split;
+  uint32_t idesc_half;
   float* ws;
   int* flags;
   int* status;
@@ -281,12 +289,14 @@ struct WorkItem {
   int kb0, kb1;       // k-block range
   int slice, tail;    // slice of a split tile (0 when the tile is whole), index of the tail tile
   bool split;
+  bool narrow;        // a 128-column half of a tail tile (narrow-tail form)
+  int n_off;          // first column of the item inside its tile: 0, or 128 for the second half
 };
 
 __device__ __forceinline__ WorkItem decode_work(const TcParams& p, long long item) {
   WorkItem w;
   long long tile = item;
-  w.slice = 0; w.tail = 0; w.split = false;
+  w.slice = 0; w.tail = 0; w.split = false; w.narrow = false; w.n_off = 0;
   w.kb0 = 0; w.kb1 = p.k_blocks;
   if (item >= p.main_tiles) {
     const int t = static_cast<int>(item - p.main_tiles);
@@ -301,14 +311,23 @@ __device__ __forceinline__ WorkItem decode_work(const TcParams& p, long long ite
   return w;
 }
 
-template <bool kSplit>
+template <bool kSplit, bool kNarrow>
 __device__ __forceinline__ WorkItem get_work(const TcParams& p, long long item) {
   if constexpr (kSplit) {
     return decode_work(p, item);
   } else {
     WorkItem w;
-    w.slice = 0; w.tail = 0; w.split = false; w.kb0 = 0; w.kb1 = p.k_blocks;
-    decode_tile(p, item, w.b, w.mb, w.nb);
+    w.slice = 0; w.tail = 0; w.split = false; w.kb0 = 0; w.kb1 = p.k_blocks; w.narrow = false; w.n_off = 0;
+    long long tile = item;
+    if constexpr (kNarrow) {
+      if (item >= p.main_tiles) {
+        const long long i = item - p.main_tiles;
+        tile = p.main_tiles + (i >> 1);
+        w.narrow = true;
+        w.n_off = static_cast<int>(i & 1) * 128;
+      }
+    }
+    decode_tile(p, tile, w.b, w.mb, w.nb);
     return w;
   }
 }
@@ -321,9 +340,12 @@ __device__ __forceinline__ WorkItem get_work(const TcParams& p, long long item) 
 // own rows.  Halving B's shared-memory footprint per CTA buys a deeper operand ring.
 template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG, bool kSplit>
 __global__ void __launch_bounds__(kNumThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const TcParams p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmBh, const TcParams p) {
+  // tmBh: B with a box of half as many rows, for the narrow tail's reduction-contiguous B (otherwise a copy of tmB).
   using Cfg = TcCfg<kElemBytes, kBlockN, kStages, kCG>;
   constexpr bool kTf32 = (kElemBytes == 4);
+  constexpr bool kNarrow = (!kSplit && kCG == 2 && kBlockN == 256);   // see TcParams
   constexpr int kTileM = kBlockM * kCG;          // rows of one scheduled tile
   constexpr int kLocalN = kBlockN / kCG;         // B rows/columns staged by one CTA
 
@@ -384,19 +406,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t full_leader0 = (kCG == 2) ? ptx::map_to_cta(full_bar(0), 0u) : full_bar(0);
       int stage = 0; uint32_t phase = 0; bool ok = true;
       for (long long item = unit; ok && item < total_items; item += n_units) {
-        const WorkItem w = get_work<kSplit>(p, item);
+        const WorkItem w = get_work<kSplit, kNarrow>(p, item);
         const int b = w.b;
         const int m0 = w.mb * kTileM + static_cast<int>(cta_rank) * kBlockM;
-        const int n0 = w.nb * kBlockN + static_cast<int>(cta_rank) * kLocalN;
-        const int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
+        const bool narrow = kNarrow && w.narrow;
+        const int local_n = narrow ? kLocalN / 2 : kLocalN;          // B rows / columns this CTA stages
+        const int n0 = w.nb * kBlockN + w.n_off + static_cast<int>(cta_rank) * local_n;
+        const uint32_t stage_tx = (Cfg::kAStage + (narrow ? Cfg::kBStage / 2 : Cfg::kBStage)) * kCG;
+        int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           // The pair's first CTA owns the "full" barrier and announces the bytes of both CTAs.
-          if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes * kCG);
+          if (leader) ptx::mbar_arrive_expect_tx(full_bar(stage), stage_tx);
           const uint32_t fb = full_leader0 + 8u * stage;
           const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
           const uint32_t b_dst = a_dst + Cfg::kAStage;
-          const int k0 = kb * Cfg::kBlockK;
+          int k0 = kb * Cfg::kBlockK;
+          if (p.kb_per_slice > 0) {                    // reduction over the batch: slice first, then k inside it
+            const int sl = kb / p.kb_per_slice;
+            k0 = (kb - sl * p.kb_per_slice) * Cfg::kBlockK;
+            ba = p.a_bcast ? 0 : sl; bb = p.b_bcast ? 0 : sl;
+          }
           auto load = [&](uint32_t dst, const void* tm, int c0, int c1, int c2) {
             if constexpr (kCG == 2) ptx::tma_load_3d_pair(dst, tm, fb, c0, c1, c2);
             else                    ptx::tma_load_3d(dst, tm, fb, c0, c1, c2);
@@ -409,11 +439,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               load(a_dst + j * (Cfg::kBlockK * 128), &tmA, m0 + j * Cfg::kBlockK, k0, ba);
           }
           if constexpr (!kBMN) {
-            load(b_dst, &tmB, k0, n0, bb);                                      // box {kBlockK, kLocalN}
+            if (narrow) load(b_dst, &tmBh, k0, n0, bb);                         // box {kBlockK, kLocalN / 2}
+            else        load(b_dst, &tmB, k0, n0, bb);                          // box {kBlockK, kLocalN}
           } else {
 #pragma unroll
             for (int j = 0; j < kLocalN / Cfg::kBlockK; ++j)
-              load(b_dst + j * (Cfg::kBlockK * 128), &tmB, n0 + j * Cfg::kBlockK, k0, bb);
+              if (j * Cfg::kBlockK < local_n)
+                load(b_dst + j * (Cfg::kBlockK * 128), &tmB, n0 + j * Cfg::kBlockK, k0, bb);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -444,10 +476,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t empty0 = empty_bar(0), tfull0 = tfull_bar(0);
       const uint32_t empty_peer0 = (kCG == 2) ? ptx::map_to_cta(empty0, 1u) : 0u;
       const uint32_t tfull_peer0 = (kCG == 2) ? ptx::map_to_cta(tfull0, 1u) : 0u;
-      const uint32_t idesc = p.idesc;
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
       for (long long item = unit; ok && item < total_items; item += n_units) {
         int k_blocks = p.k_blocks;
+        const uint32_t idesc = (kNarrow && item >= p.main_tiles) ? p.idesc_half : p.idesc;
         if constexpr (kSplit) {
           if (item >= p.main_tiles) { const WorkItem w = decode_work(p, item); k_blocks = w.kb1 - w.kb0; }
         }
@@ -490,22 +522,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ===================== epilogue (4 warps, one TMEM lane quarter each) =====================
     const int q = warp & 3;                            // hardware rule: a warp reads lanes 32*(warp%4)..+31
     const int half = (warp - 2) >> 2;                  // which half of the tile's columns this warp owns
-    constexpr int kHalfChunks = kBlockN / 64;          // 32-column chunks per half
     uint8_t* my_stage = store_stage + (warp - 2) * kStoreStageWarp;
     const uint32_t tempty_leader = (kCG == 2) ? ptx::map_to_cta(tempty_bar(0), 0u) : tempty_bar(0);
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     for (long long item = unit; ok && item < total_items; item += n_units) {
-      const WorkItem w = get_work<kSplit>(p, item);
+      const WorkItem w = get_work<kSplit, kNarrow>(p, item);
       const int b = w.b;
       const int row_in_tile = static_cast<int>(cta_rank) * kBlockM + q * 32 + lane;
       const int row = w.mb * kTileM + row_in_tile;
       const bool row_ok = row < p.M;
-      const int n0 = w.nb * kBlockN;
+      const int n0 = w.nb * kBlockN + w.n_off;
+      const int half_cols = (kNarrow && w.narrow) ? kBlockN / 4 : kBlockN / 2;   // columns of this warp's half
       if (!ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
-      const uint32_t t_row = tmem_base + acc * kBlockN + half * (kBlockN / 2) + (static_cast<uint32_t>(q * 32) << 16);
-      const int nh0 = n0 + half * (kBlockN / 2);       // first column of this warp's half
-      const int n_chunks = max(0, min(kHalfChunks, (p.N - nh0 + 31) / 32));
+      const uint32_t t_row = tmem_base + acc * kBlockN + half * half_cols + (static_cast<uint32_t>(q * 32) << 16);
+      const int nh0 = n0 + half * half_cols;           // first column of this warp's half
+      const int n_chunks = max(0, min(half_cols / 32, (p.N - nh0 + 31) / 32));
       auto release_acc = [&]() {
         ptx::tc_fence_before_sync();
         __syncwarp();
@@ -643,10 +675,16 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   p.m_blocks = (g.M + kTileM - 1) / kTileM;
   p.n_blocks = (g.N + kBlockN - 1) / kBlockN;
   p.k_blocks = (g.K + Cfg::kBlockK - 1) / Cfg::kBlockK;
+  p.kb_per_slice = 0;
+  if (g.reduce_batch && g.batch > 1) {
+    p.kb_per_slice = p.k_blocks;
+    p.k_blocks *= g.batch;
+  }
   const int ab_format = g.in_dtype == kF32 ? 2 : (g.in_dtype == kBF16 ? 1 : 0);
   p.idesc = ptx::make_idesc(ab_format, kAMN, kBMN, kTileM, kBlockN);
+  p.idesc_half = ptx::make_idesc(ab_format, kAMN, kBMN, kTileM, kBlockN / 2);
 
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmBh;
   bool ok;
   constexpr bool kWide = (kElemBytes == 4);   // M/N-contiguous 32-bit tiles are swizzled in 32-byte units
   if (!kAMN) ok = make_operand_map(&tmA, g.in_dtype, g.A, g.K, g.M, g.lda, g.batch, g.strideA, Cfg::kBlockK, kBlockM, false);
@@ -656,7 +694,7 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   else       ok = make_operand_map(&tmB, g.in_dtype, g.B, g.N, g.K, g.ldb, g.batch, g.strideB, Cfg::kBlockK, Cfg::kBlockK, kWide);
   if (!ok) return cudaErrorInvalidValue;
 
-  const long long tiles = static_cast<long long>(g.batch) * p.m_blocks * p.n_blocks;
+  const long long tiles = static_cast<long long>(p.batch) * p.m_blocks * p.n_blocks;
   const long long units = sm_budget() / kCG > 0 ? sm_budget() / kCG : 1;   // one CTA (or CTA pair) per SM (pair of SMs)
 
   // Split-K: a problem whose tiles fill at most half of the machine is cut along the reduction as well.
@@ -684,6 +722,19 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
       }
     }
   }
+  // Narrow tail: several waves whose last one fills at most half of the pairs.
+  bool narrow_tail = false;
+  static const bool narrow_off = [] { const char* e = getenv("GE2B_NARROW_TAIL"); return e && atoi(e) == 0; }();
+  if (kCG == 2 && kBlockN == 256 && !narrow_off && p.split == 1 && tiles > units && rem > 0 && 2 * rem <= units) {
+    narrow_tail = true;
+    p.main_tiles = static_cast<int>(tiles - rem);
+    p.tail_tiles = static_cast<int>(rem);
+    p.split = 2;
+  }
+  tmBh = tmB;
+  if (narrow_tail && !kBMN &&
+      !make_operand_map(&tmBh, g.in_dtype, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, Cfg::kBlockK, kLocalN / 2, false))
+    return cudaErrorInvalidValue;
   const long long items = static_cast<long long>(p.main_tiles) + static_cast<long long>(p.tail_tiles) * p.split;
   const int grid = static_cast<int>((items < units ? items : units) * kCG);
 
@@ -699,7 +750,8 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return p.split > 1 ? cudaLaunchKernelEx(&cfg, kernel_split, tmA, tmB, p) : cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, p);
+  return (p.split > 1 && !narrow_tail) ? cudaLaunchKernelEx(&cfg, kernel_split, tmA, tmB, tmBh, p)
+                                       : cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmBh, p);
 }
 
 struct TileChoice { int block_n, cta_group; };

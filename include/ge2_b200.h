@@ -213,6 +213,36 @@ const char* ge2b_version(void);
  * the reference declares, and never defines, ai_backend_cuda_register_all (src/bindings/py_api.cpp:43). */
 void ge2b_register_gemm_kernels(void);
 
+/* ---- 2-D convolution on the GEMM kernels (NCHW tensors, OIHW weight, groups = 1) ----
+ * Replaces Conv2DCudaLaunch / Conv2DCudaBackwardLaunch (backends/cuda/ops/conv2d/api.hpp:44-64, launcher.cu:115-462):
+ * same attributes (Conv2DAttrs, api.hpp:6-16) and the same output-size rule, but one im2col pass and one batched
+ * GEMM launch for the whole batch instead of a per-image loop, and no caller-provided workspace (scratch is
+ * allocated and freed in stream order).  dtype tags every tensor (GE2_DTYPE_*); bias and dB stay fp32; Z may be fp32
+ * or dtype.  math as in ge2_params_typed_t.  dB is the sum over the whole batch (the reference's per-image
+ * GemmCudaBackward zeroes the bias gradient on every call, launcher.cu:420-431 with regemm_backward.cu:196, so its
+ * dB holds the last image only). */
+typedef struct {
+  int N, Cin, H, W;          /* input  [N, Cin, H, W] */
+  int Cout, Kh, Kw;          /* weight [Cout, Cin, Kh, Kw] */
+  int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  int groups;                /* must be 1 (anything else: -99, as the reference returns Unimplemented) */
+  int act_kind;              /* GE2_ACT_* */
+  float leaky_slope;
+  int with_bias;
+  int save_z;                /* forward: also write the pre-activation to Z */
+  int dtype, z_dtype, math;
+} ge2b_conv2d_params_t;
+
+/* Y [N, Cout, Ho, Wo] = act(conv(X, W) + bias[co]).  Returns 0, -1 (bad arguments), -2 (CUDA error), -99. */
+int ge2b_conv2d_forward(const ge2b_conv2d_params_t* p, const void* X, const void* W, const float* bias, void* Y, void* Z,
+                        void* stream);
+/* (X, W, dY, Z) -> dW [Cout, Cin, Kh, Kw], dB [Cout] fp32, dX [N, Cin, H, W]; any output may be null.  Outputs are
+ * overwritten (not accumulated into). */
+int ge2b_conv2d_backward(const ge2b_conv2d_params_t* p, const void* X, const void* W, const void* dY, const void* Z,
+                         void* dW, float* dB, void* dX, void* stream);
+/* Ho, Wo for the geometry in p (conv2d/launcher.cu:137-138). */
+int ge2b_conv2d_output_size(const ge2b_conv2d_params_t* p, int* Ho, int* Wo);
+
 /* Introspection for tests and benchmarks: which kernel family the calling thread's most recent GEMM went to
  * (0 none, 1 exact-fp32 CUDA-core kernel, 2 tcgen05 tensor-core kernel) and how many kernels this library
  * has launched in the process. */

@@ -30,3 +30,8 @@ def lib(pkg):
     from __graft_entry__ import build
     build()
     return pkg.load_library()
+
+
+@pytest.fixture(scope="session")
+def conv_oracle():
+    return importlib.import_module("oracle.conv2d_oracle")

@@ -1,0 +1,250 @@
+"""GPU parity tests of the convolution built on the dense-layer kernels.  Every call goes through the C ABI
+(ge2b_conv2d_forward / _backward) and is compared with the CPU oracle (oracle/conv2d_oracle.py, pinned against
+torch on the CPU by tests/test_oracle_conv2d.py) and, where it was built, with the reference's own conv2d op compiled
+for sm_100a (oracle/_ref/libref_conv.so).
+
+Tolerances:
+  fp32 tensors, exact path   pre-activation Z bit-identical to the oracle's fp32 restatement and to the reference op;
+                             Y identical for none / relu, within 1e-6 relative otherwise; gradients <= 1e-5 relative
+                             Frobenius error against float64
+  bf16 / TF32 tensor cores   relative Frobenius error <= 2e-2 against float64 on the rounded inputs
+"""
+import ctypes as C
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+FRO_TOL = 2e-2
+ACT_CODE = {"none": 0, "relu": 1, "leaky_relu": 2, "gelu": 3, "sigmoid": 4, "tanh": 5}
+
+GEOMS = {
+    # name: N, Cin, H, W, Cout, Kh, Kw, stride, padding, dilation
+    "3x3_same":      (3, 8, 14, 14, 16, 3, 3, (1, 1), (1, 1), (1, 1)),
+    "3x3_stride2":   (2, 5, 17, 15, 7, 3, 3, (2, 2), (1, 1), (1, 1)),
+    "5x3_dilated":   (2, 4, 16, 18, 6, 5, 3, (1, 2), (2, 1), (1, 2)),
+    "1x1_pointwise": (4, 16, 12, 12, 24, 1, 1, (1, 1), (0, 0), (1, 1)),
+    "1x1_odd_hw":    (2, 8, 7, 9, 5, 1, 1, (1, 1), (0, 0), (1, 1)),
+    "7x7_stem":      (2, 3, 32, 32, 16, 7, 7, (2, 2), (3, 3), (1, 1)),
+    "wide":          (2, 64, 20, 20, 96, 3, 3, (1, 1), (1, 1), (1, 1)),
+}
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def host(t):
+    return t.detach().float().cpu().numpy()
+
+
+@pytest.fixture(autouse=True)
+def _status_clean(lib):
+    yield
+    torch.cuda.synchronize()
+    assert lib.ge2b_device_status(1) == 0, "a bounded wait inside a kernel timed out"
+
+
+def _kw(g):
+    return dict(stride=g[7], padding=g[8], dilation=g[9])
+
+
+# --------------------------------------------------------------------------- fp32, exact path
+@pytest.mark.parametrize("act", ["none", "relu", "gelu", "tanh"])
+@pytest.mark.parametrize("name", sorted(GEOMS))
+def test_fp32_forward_bit_exact_preactivation(pkg, lib, oracle, conv_oracle, name, act):
+    g = GEOMS[name]
+    X, Wt, b, _ = conv_oracle.conv_inputs(*g[:7], seed=3, **_kw(g))
+    Y, Z = pkg.ops_conv2d.forward(dev(X), dev(Wt), dev(b), with_bias=True, act=act, save_z=True, **_kw(g))
+    torch.cuda.synchronize()
+    Y32, Z32 = conv_oracle.forward_f32(X, Wt, b, act=act, **_kw(g))
+    assert np.array_equal(host(Z), Z32)
+    if act in ("none", "relu"):
+        assert np.array_equal(host(Y), Y32)
+    else:
+        assert oracle.rel_fro(host(Y), Y32) <= 1e-6
+
+
+@pytest.mark.parametrize("act", ["none", "gelu", "sigmoid"])
+@pytest.mark.parametrize("name", sorted(GEOMS))
+def test_fp32_backward_vs_float64(pkg, lib, oracle, conv_oracle, name, act):
+    g = GEOMS[name]
+    X, Wt, b, dY = conv_oracle.conv_inputs(*g[:7], seed=4, **_kw(g))
+    _, Z64 = conv_oracle.forward_f64(X, Wt, b, act=act, **_kw(g))
+    Z = Z64.astype(np.float32)
+    out = pkg.ops_conv2d.backward(dev(X), dev(Wt), dev(dY), dev(Z), with_bias=True, act=act, want_gB=True, **_kw(g))
+    torch.cuda.synchronize()
+    ref = conv_oracle.backward_f64(X, Wt, dY, Z, act=act, **_kw(g))
+    assert oracle.rel_fro(host(out["gX"]), ref["gX"]) <= 1e-5
+    assert oracle.rel_fro(host(out["gW"]), ref["gW"]) <= 1e-5
+    assert oracle.rel_fro(host(out["gB"]), ref["gB"]) <= 1e-5
+
+
+def test_optional_outputs_and_no_bias(pkg, lib, oracle, conv_oracle):
+    g = GEOMS["3x3_stride2"]
+    X, Wt, _, dY = conv_oracle.conv_inputs(*g[:7], seed=5, **_kw(g))
+    Y = pkg.ops_conv2d.forward(dev(X), dev(Wt), None, act="relu", **_kw(g))
+    Y64, Z64 = conv_oracle.forward_f64(X, Wt, None, act="relu", **_kw(g))
+    assert oracle.rel_fro(host(Y), Y64) <= 1e-6
+    Z = dev(Z64.astype(np.float32))
+    ref = conv_oracle.backward_f64(X, Wt, dY, Z64.astype(np.float32), act="relu", **_kw(g))
+    only_w = pkg.ops_conv2d.backward(dev(X), dev(Wt), dev(dY), Z, act="relu", want_gX=False, **_kw(g))
+    assert only_w["gX"] is None and only_w["gB"] is None
+    assert oracle.rel_fro(host(only_w["gW"]), ref["gW"]) <= 1e-5
+    only_x = pkg.ops_conv2d.backward(dev(X), dev(Wt), dev(dY), Z, act="relu", want_gW=False, **_kw(g))
+    assert only_x["gW"] is None
+    assert oracle.rel_fro(host(only_x["gX"]), ref["gX"]) <= 1e-5
+
+
+def test_argument_errors(pkg, lib):
+    X = torch.zeros(1, 3, 8, 8, device="cuda")
+    W = torch.zeros(4, 3, 3, 3, device="cuda")
+    with pytest.raises(NotImplementedError):
+        pkg.ops_conv2d.forward(X, W, groups=3)
+    with pytest.raises(ValueError):
+        pkg.ops_conv2d.forward(X, torch.zeros(4, 2, 3, 3, device="cuda"))
+    with pytest.raises(ValueError):
+        pkg.ops_conv2d.forward(X, torch.zeros(4, 3, 9, 9, device="cuda"))       # empty output
+    p = pkg._lib.ParamsConv2D()
+    assert lib.ge2b_conv2d_forward(C.byref(p), None, None, None, None, None, None) == -1
+    p.N, p.Cin, p.H, p.W, p.Cout, p.Kh, p.Kw = 1, 3, 8, 8, 4, 3, 3
+    p.stride_h = p.stride_w = p.dil_h = p.dil_w = 1
+    p.groups = 2
+    Y = torch.zeros(1, 4, 6, 6, device="cuda")
+    assert lib.ge2b_conv2d_forward(C.byref(p), X.data_ptr(), W.data_ptr(), None, Y.data_ptr(), None, None) == -99
+
+
+# --------------------------------------------------------------------------- tensor-core paths
+@pytest.mark.parametrize("dtype,math", [(torch.bfloat16, "fp32"), (torch.float32, "tf32")])
+@pytest.mark.parametrize("name", ["3x3_same", "1x1_pointwise", "7x7_stem", "wide"])
+def test_tensor_core_forward_backward(pkg, lib, oracle, conv_oracle, name, dtype, math):
+    g = GEOMS[name]
+    X, Wt, b, dY = conv_oracle.conv_inputs(*g[:7], seed=6, **_kw(g))
+    if dtype == torch.bfloat16:
+        X, Wt, dY = (oracle.bf16_round(a) for a in (X, Wt, dY))
+    tX, tW, tdY = dev(X, dtype), dev(Wt, dtype), dev(dY, dtype)
+    Y, Z = pkg.ops_conv2d.forward(tX, tW, dev(b), with_bias=True, act="gelu", save_z=True, math=math,
+                                  z_dtype=torch.float32, **_kw(g))
+    out = pkg.ops_conv2d.backward(tX, tW, tdY, Z, with_bias=True, act="gelu", want_gB=True, math=math, **_kw(g))
+    torch.cuda.synchronize()
+    Y64, Z64 = conv_oracle.forward_f64(X, Wt, b, act="gelu", **_kw(g))
+    ref = conv_oracle.backward_f64(X, Wt, dY, host(Z), act="gelu", **_kw(g))
+    errs = {"Y": oracle.rel_fro(host(Y), Y64), "Z": oracle.rel_fro(host(Z), Z64),
+            "gX": oracle.rel_fro(host(out["gX"]), ref["gX"]), "gW": oracle.rel_fro(host(out["gW"]), ref["gW"]),
+            "gB": oracle.rel_fro(host(out["gB"]), ref["gB"])}
+    assert all(e <= FRO_TOL for e in errs.values()), errs
+
+
+def test_bf16_layer_sized_case(pkg, lib, oracle, conv_oracle):
+    """A ResNet-like layer (N=8, 64 -> 64 channels, 56 x 56, 3 x 3): the weight gradient's reduction runs over
+    8 * 3136 positions in one launch; float64 reference on sampled output channels."""
+    N, Cin, H, W, Cout, Kh, Kw = 8, 64, 56, 56, 64, 3, 3
+    kw = dict(stride=(1, 1), padding=(1, 1), dilation=(1, 1))
+    X, Wt, b, dY = conv_oracle.conv_inputs(N, Cin, H, W, Cout, Kh, Kw, seed=7, **kw)
+    X, Wt, dY = (oracle.bf16_round(a) for a in (X, Wt, dY))
+    tX, tW, tdY = dev(X, torch.bfloat16), dev(Wt, torch.bfloat16), dev(dY, torch.bfloat16)
+    Y, Z = pkg.ops_conv2d.forward(tX, tW, dev(b), with_bias=True, act="relu", save_z=True, **kw)
+    assert lib.ge2b_last_route() == 2
+    out = pkg.ops_conv2d.backward(tX, tW, tdY, Z, with_bias=True, act="relu", want_gB=True, **kw)
+    torch.cuda.synchronize()
+    xt = torch.from_numpy(X).double().requires_grad_(True)
+    wt = torch.from_numpy(Wt).double().requires_grad_(True)
+    z = torch.nn.functional.conv2d(xt, wt, torch.from_numpy(b).double(), padding=1)
+    assert oracle.rel_fro(host(Z), z.detach().numpy()) <= FRO_TOL
+    gz = torch.from_numpy(dY).double() * (Z.double().cpu() > 0)
+    z.backward(gz)
+    assert oracle.rel_fro(host(out["gX"]), xt.grad.numpy()) <= FRO_TOL
+    assert oracle.rel_fro(host(out["gW"]), wt.grad.numpy()) <= FRO_TOL
+    assert oracle.rel_fro(host(out["gB"]), gz.sum(dim=(0, 2, 3)).numpy()) <= FRO_TOL
+
+
+# --------------------------------------------------------------------------- against the reference's own GPU op
+def _ref_conv():
+    path = ROOT / "oracle" / "_ref" / "libref_conv.so"
+    if not path.exists():
+        pytest.skip("oracle/_ref/libref_conv.so not built (needs the reference tree at build time)")
+    lib = C.CDLL(str(path))
+    ints = [C.c_int] * 13
+    lib.ref_conv_forward.argtypes = [C.c_void_p] * 5 + ints + [C.c_int, C.c_float, C.c_void_p]
+    lib.ref_conv_forward.restype = C.c_int
+    lib.ref_conv_backward.argtypes = [C.c_void_p] * 7 + ints + [C.c_int, C.c_float, C.c_void_p]
+    lib.ref_conv_backward.restype = C.c_int
+    return lib
+
+
+@pytest.mark.parametrize("act", ["relu", "gelu"])
+@pytest.mark.parametrize("name", ["3x3_same", "3x3_stride2", "5x3_dilated", "1x1_pointwise"])
+def test_fp32_path_against_reference_gpu_op(pkg, lib, oracle, conv_oracle, name, act):
+    ref = _ref_conv()
+    g = GEOMS[name]
+    N, Cin, H, W, Cout, Kh, Kw, st, pd, dl = g
+    X, Wt, b, dY = conv_oracle.conv_inputs(*g[:7], seed=8, **_kw(g))
+    tX, tW, tb, tdY = dev(X), dev(Wt), dev(b), dev(dY)
+    Y, Z = pkg.ops_conv2d.forward(tX, tW, tb, with_bias=True, act=act, save_z=True, **_kw(g))
+    rY, rZ = torch.empty_like(Y), torch.empty_like(Z)
+    geom = (N, Cin, H, W, Cout, Kh, Kw, st[0], st[1], pd[0], pd[1], dl[0], dl[1])
+    assert ref.ref_conv_forward(tX.data_ptr(), tW.data_ptr(), tb.data_ptr(), rY.data_ptr(), rZ.data_ptr(), *geom,
+                                ACT_CODE[act], 0.01, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(Z, rZ)                      # same fmaf chain per output
+    assert oracle.rel_fro(host(Y), host(rY)) <= 1e-6
+
+    out = pkg.ops_conv2d.backward(tX, tW, tdY, Z, with_bias=True, act=act, want_gB=True, **_kw(g))
+    rdW, rdX, rdB = torch.empty_like(tW), torch.empty_like(tX), torch.empty(Cout, device="cuda")
+    assert ref.ref_conv_backward(tX.data_ptr(), tW.data_ptr(), tdY.data_ptr(), rZ.data_ptr(), rdW.data_ptr(),
+                                 rdB.data_ptr(), rdX.data_ptr(), *geom, ACT_CODE[act], 0.01, None) == 0
+    torch.cuda.synchronize()
+    assert oracle.rel_fro(host(out["gX"]), host(rdX)) <= 3e-4
+    assert oracle.rel_fro(host(out["gW"]), host(rdW)) <= 3e-4
+    # The reference's bias gradient holds the last image only (its per-image backward zeroes it each time), so the
+    # comparable quantity is the last image's share of the sum.
+    gz_last = conv_oracle.backward_f64(X[-1:], Wt, dY[-1:], host(Z)[-1:], act=act, **_kw(g))["gB"]
+    assert oracle.rel_fro(host(rdB), gz_last) <= 3e-4
+    full = conv_oracle.backward_f64(X, Wt, dY, host(Z), act=act, **_kw(g))["gB"]
+    assert oracle.rel_fro(host(out["gB"]), full) <= 1e-5
+
+
+# --------------------------------------------------------------------------- the reference's own binding, linked here
+def test_reference_conv2d_binding_runs_on_this_library(pkg, lib, oracle, conv_oracle):
+    dropin = ROOT / "oracle" / "_ref" / "dropin"
+    if not list((dropin / "graph_executor_v2" / "ops").glob("_ops_conv2d*")):
+        pytest.skip("oracle/_ref/dropin/_ops_conv2d not built (needs the reference tree at build time)")
+    sys.path.insert(0, str(dropin))
+    try:
+        from graph_executor_v2.ops import _ops_common as c, _ops_conv2d as cv  # noqa: F401
+    finally:
+        sys.path.remove(str(dropin))
+    g = GEOMS["3x3_same"]
+    X, Wt, b, dY = conv_oracle.conv_inputs(*g[:7], seed=9, **_kw(g))
+    tX, tW, tb, tdY = dev(X), dev(Wt), dev(b), dev(dY)
+    N, Cin, H, W, Cout, Kh, Kw = g[:7]
+    Ho, Wo = conv_oracle.out_hw(H, W, Kh, Kw, **_kw(g))
+    Y = torch.empty(N, Cout, Ho, Wo, device="cuda")
+    Z = torch.empty_like(Y)
+    at = cv.Conv2DAttrs()
+    at.pad_h = at.pad_w = 1
+    at.with_bias = True
+    at.act = cv.ActKind.ReLU
+    at.save_z = True
+    dummy = torch.zeros(64, device="cuda").data_ptr()     # the binding insists on non-null workspaces; unused here
+    cv.forward(tX.data_ptr(), list(X.shape), tW.data_ptr(), list(Wt.shape), Y.data_ptr(), list(Y.shape),
+               tb.data_ptr(), Z.data_ptr(), at, 0, dCol_ptr=dummy, W_KC_ptr=dummy, Y_tmp_ptr=dummy, Z_rows_ptr=dummy)
+    torch.cuda.synchronize()
+    Y32, Z32 = conv_oracle.forward_f32(X, Wt, b, act="relu", **_kw(g))
+    assert np.array_equal(host(Z), Z32) and np.array_equal(host(Y), Y32)
+    dW, dX, dB = torch.empty_like(tW), torch.empty_like(tX), torch.empty(Cout, device="cuda")
+    cv.backward(tX.data_ptr(), list(X.shape), tW.data_ptr(), list(Wt.shape), tdY.data_ptr(), list(Y.shape),
+                Z.data_ptr(), list(Y.shape), dW.data_ptr(), dB.data_ptr(), dX.data_ptr(), at, 0,
+                dCol_ptr=dummy, dTmp_ptr=dummy, W_CK_ptr=dummy, dWpack_ptr=dummy, dY_HT_ptr=dummy, gy_rows_ptr=dummy,
+                Z_rows_ptr=dummy)
+    torch.cuda.synchronize()
+    ref = conv_oracle.backward_f64(X, Wt, dY, Z32, act="relu", **_kw(g))
+    assert oracle.rel_fro(host(dX), ref["gX"]) <= 1e-5
+    assert oracle.rel_fro(host(dW), ref["gW"]) <= 1e-5
+    assert oracle.rel_fro(host(dB), ref["gB"]) <= 1e-5

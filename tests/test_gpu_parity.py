@@ -425,3 +425,27 @@ def test_split_reduction_for_small_grids(pkg, lib, oracle, shape):
     X = torch.randn(M, K, device="cuda").bfloat16()
     W = (torch.randn(K, N, device="cuda") / 32).bfloat16()
     assert torch.equal(pkg.ops_gemm.forward(X, W), pkg.ops_gemm.forward(X, W))
+
+
+# --------------------------------------------------------------------------- narrow tail of a partly filled last wave
+@pytest.mark.parametrize("dtype,math", [(torch.bfloat16, "fp32"), (torch.float32, "tf32")])
+@pytest.mark.parametrize("shape", [(2304, 2304, 2304), (2300, 2056, 2200)])
+def test_narrow_tail_tiles(pkg, lib, oracle, dtype, math, shape):
+    """9 x 9 = 81 tiles of 256 x 256 on 74 CTA pairs: the 7 tiles left after the first wave run as 14 halves of 128
+    columns.  Forward, dX and dW each have that tile count, so all three operand orders take the path; the ragged
+    shape leaves the second half of the last column block partly (N) or wholly (K) outside the matrix."""
+    M, K, N = shape
+    errs = tc_case(pkg, lib, oracle, M, K, N, dtype, math, "gelu", seed=11)
+    assert all(e <= FRO_TOL for e in errs.values()), errs
+
+
+def test_narrow_tail_batched(pkg, lib, oracle):
+    """3 slices x 25 tiles = 75 tiles: one tail tile in the last slice, with K^T as a transposed operand."""
+    rng = np.random.default_rng(4)
+    Q = oracle.bf16_round(rng.standard_normal((3, 1280, 64), dtype=np.float32))
+    Kx = oracle.bf16_round(rng.standard_normal((3, 1280, 64), dtype=np.float32))
+    S = torch.empty((3, 1280, 1280), device="cuda", dtype=torch.bfloat16)
+    pkg.ops_gemm.forward_batched(dev(Q, torch.bfloat16), dev(Kx, torch.bfloat16), out=S, trans_b=True, alpha=0.125)
+    torch.cuda.synchronize()
+    S64 = 0.125 * np.einsum("bld,bmd->blm", Q.astype(np.float64), Kx.astype(np.float64))
+    assert oracle.rel_fro(host(S), S64) <= FRO_TOL
