@@ -61,7 +61,7 @@ int main() {
     }
   // expected backward
   std::vector<float> gZ(M * N), gA(M * K, 0.f), gB(K * N, 0.f), gBias(N, 0.f);
-  for (int i = 0; i < M * N; ++i) gZ[i] = Z[i] > 0.f ? gY[i] : 0.f;
+  for (int i = 0; i < M * N; ++i) gZ[i] = gY[i] * (Z[i] > 0.f ? 1.f : 0.f);   // keeps the sign of a zero product
   for (int m = 0; m < M; ++m)
     for (int k = 0; k < K; ++k) { double s = 0; for (int n = 0; n < N; ++n) s += double(gZ[m * N + n]) * B[k * N + n]; gA[m * K + k] = float(s); }
   for (int k = 0; k < K; ++k)
