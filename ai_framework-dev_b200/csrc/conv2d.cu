@@ -35,57 +35,68 @@ struct ConvGeom {
 constexpr int kColThreads = 128;
 
 // Col[k][n][hw] = X[n][c][ho*sh - ph + kh*dh][wo*sw - pw + kw*dw] (zero outside the image and in the padding columns
-// hw >= HWo).  grid.x = K * N (one (k, n) row per block column), grid.y covers HWp.
+// hw >= HWo).  One block per (k, n) row; a thread gathers 16 bytes' worth of consecutive output positions and
+// writes them with one store.  T is the element's storage type: values are copied bit for bit.
+template <typename T>
 __global__ void __launch_bounds__(kColThreads)
-im2col_batched_kernel(const void* __restrict__ X, void* __restrict__ Col, const ConvGeom g, const int dt) {
+im2col_batched_kernel(const T* __restrict__ X, T* __restrict__ Col, const ConvGeom g) {
+  constexpr int V = 16 / sizeof(T);
   const int kn = blockIdx.x;
   const int k = kn / g.N, n = kn - k * g.N;
   const int kw = k % g.Kw;
   const int t = k / g.Kw;
   const int kh = t % g.Kh, c = t / g.Kh;
-  const long long x_base = (static_cast<long long>(n) * g.Cin + c) * g.H * g.W;
-  const long long col_base = static_cast<long long>(kn) * g.HWp;
-  for (int hw = blockIdx.y * kColThreads + threadIdx.x; hw < g.HWp; hw += gridDim.y * kColThreads) {
-    float v = 0.f;
-    if (hw < g.HWo) {
-      const int ho = hw / g.Wo, wo = hw - ho * g.Wo;
-      const int hi = ho * g.sh - g.ph + kh * g.dh;
-      const int wi = wo * g.sw - g.pw + kw * g.dw;
-      if (static_cast<unsigned>(hi) < static_cast<unsigned>(g.H) && static_cast<unsigned>(wi) < static_cast<unsigned>(g.W))
-        v = load_as_f32(X, x_base + static_cast<long long>(hi) * g.W + wi, dt);
+  const T* __restrict__ xc = X + (static_cast<long long>(n) * g.Cin + c) * g.H * g.W;
+  T* __restrict__ col = Col + static_cast<long long>(kn) * g.HWp;
+  const int h_off = kh * g.dh - g.ph, w_off = kw * g.dw - g.pw;
+  for (int v = threadIdx.x; v < g.HWp / V; v += kColThreads) {
+    const int hw0 = v * V;
+    int ho = hw0 / g.Wo, wo = hw0 - ho * g.Wo;
+    alignas(16) T vals[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      T val = T(0);
+      const int hi = ho * g.sh + h_off, wi = wo * g.sw + w_off;
+      if (hw0 + j < g.HWo && static_cast<unsigned>(hi) < static_cast<unsigned>(g.H) &&
+          static_cast<unsigned>(wi) < static_cast<unsigned>(g.W))
+        val = __ldg(xc + hi * g.W + wi);
+      vals[j] = val;
+      if (++wo == g.Wo) { wo = 0; ++ho; }
     }
-    // values are copied, never rounded: the store converts back to the dtype it was loaded from
-    store_from_f32(Col, col_base + hw, dt, v);
+    *reinterpret_cast<uint4*>(col + hw0) = *reinterpret_cast<const uint4*>(vals);
   }
 }
 
 // dX[n][c][h][w] = sum over the (kh, kw) taps whose output position exists of dCol[(c,kh,kw)][n][ho*Wo + wo];
 // fp32 accumulation in tap order (kh outer, kw inner), one thread per input pixel, plain store (no atomics).
+// grid.x = (n, c) plane, grid.y covers the plane's pixels.  kUnit: stride 1 in both directions (no divisions per tap).
+template <bool kUnit>
 __global__ void __launch_bounds__(256)
 col2im_batched_kernel(const void* __restrict__ dCol, void* __restrict__ dX, const ConvGeom g, const int dt) {
-  const long long total = static_cast<long long>(g.N) * g.Cin * g.H * g.W;
-  for (long long idx = blockIdx.x * 256ll + threadIdx.x; idx < total; idx += gridDim.x * 256ll) {
-    const int w = static_cast<int>(idx % g.W);
-    long long t = idx / g.W;
-    const int h = static_cast<int>(t % g.H); t /= g.H;
-    const int c = static_cast<int>(t % g.Cin);
-    const int n = static_cast<int>(t / g.Cin);
+  const int plane = blockIdx.x;
+  const int n = plane / g.Cin, c = plane - n * g.Cin;
+  const int HW = g.H * g.W;
+  const long long out_base = static_cast<long long>(plane) * HW;
+  for (int pix = blockIdx.y * 256 + threadIdx.x; pix < HW; pix += gridDim.y * 256) {
+    const int h = pix / g.W, w = pix - h * g.W;
     float acc = 0.f;
     for (int kh = 0; kh < g.Kh; ++kh) {
       const int hn = h + g.ph - kh * g.dh;
-      if (hn < 0 || hn % g.sh) continue;
-      const int ho = hn / g.sh;
-      if (ho >= g.Ho) continue;
+      int ho;
+      if constexpr (kUnit) { ho = hn; }
+      else { if (hn < 0 || hn % g.sh) continue; ho = hn / g.sh; }
+      if (static_cast<unsigned>(ho) >= static_cast<unsigned>(g.Ho)) continue;
       for (int kw = 0; kw < g.Kw; ++kw) {
         const int wn = w + g.pw - kw * g.dw;
-        if (wn < 0 || wn % g.sw) continue;
-        const int wo = wn / g.sw;
-        if (wo >= g.Wo) continue;
+        int wo;
+        if constexpr (kUnit) { wo = wn; }
+        else { if (wn < 0 || wn % g.sw) continue; wo = wn / g.sw; }
+        if (static_cast<unsigned>(wo) >= static_cast<unsigned>(g.Wo)) continue;
         const int k = (c * g.Kh + kh) * g.Kw + kw;
         acc += load_as_f32(dCol, (static_cast<long long>(k) * g.N + n) * g.HWp + ho * g.Wo + wo, dt);
       }
     }
-    store_from_f32(dX, idx, dt, acc);
+    store_from_f32(dX, out_base + pix, dt, acc);
   }
 }
 
@@ -117,16 +128,22 @@ bool make_geom(const ge2b_conv2d_params_t& p, ConvGeom& g) {
   return true;
 }
 
-bool pointwise(const ConvGeom& g) {
-  return g.Kh == 1 && g.Kw == 1 && g.sh == 1 && g.sw == 1 && g.ph == 0 && g.pw == 0;
+// A 1x1 / stride-1 / unpadded convolution reads X[n] (Cin x HW) as its column matrix; taken when the rows of that
+// matrix start on 16-byte boundaries (otherwise the padded copy is what lets the tensor-core path run).
+bool pointwise(const ConvGeom& g, int esz) {
+  return g.Kh == 1 && g.Kw == 1 && g.sh == 1 && g.sw == 1 && g.ph == 0 && g.pw == 0 &&
+         (static_cast<long long>(g.H) * g.W * esz) % 16 == 0;
 }
 
 cudaError_t launch_im2col(const void* X, void* Col, const ConvGeom& g, int dt, cudaStream_t s) {
   const long long rows = static_cast<long long>(g.K) * g.N;
   if (rows > 0x7fffffffll) return cudaErrorInvalidValue;
-  int gy = (g.HWp + kColThreads - 1) / kColThreads;
-  if (gy > 65535) gy = 65535;
-  im2col_batched_kernel<<<dim3(static_cast<unsigned>(rows), gy), kColThreads, 0, s>>>(X, Col, g, dt);
+  if (dtype_bytes(dt) == 4)
+    im2col_batched_kernel<float><<<static_cast<unsigned>(rows), kColThreads, 0, s>>>(
+        static_cast<const float*>(X), static_cast<float*>(Col), g);
+  else
+    im2col_batched_kernel<unsigned short><<<static_cast<unsigned>(rows), kColThreads, 0, s>>>(
+        static_cast<const unsigned short*>(X), static_cast<unsigned short*>(Col), g);
   return cudaGetLastError();
 }
 
@@ -141,7 +158,10 @@ struct AsyncBuf {
   void* p = nullptr;
   cudaStream_t s;
   explicit AsyncBuf(cudaStream_t st) : s(st) {}
-  bool alloc(size_t bytes) { return cudaMallocAsync(&p, bytes ? bytes : 16, s) == cudaSuccess; }
+  bool alloc(size_t bytes) {
+    keep_async_pool_cached();
+    return cudaMallocAsync(&p, bytes ? bytes : 16, s) == cudaSuccess;
+  }
   ~AsyncBuf() { if (p) cudaFreeAsync(p, s); }
   AsyncBuf(const AsyncBuf&) = delete;
   AsyncBuf& operator=(const AsyncBuf&) = delete;
@@ -161,7 +181,7 @@ int conv2d_forward(const ge2b_conv2d_params_t& p, const void* X, const void* W, 
   AsyncBuf col(s);
   const void* B = X;
   long long ldb = static_cast<long long>(g.H) * g.W, strideB = static_cast<long long>(g.Cin) * g.H * g.W;
-  if (!pointwise(g)) {
+  if (!pointwise(g, esz)) {
     if (!col.alloc(static_cast<size_t>(g.K) * g.N * g.HWp * esz)) return kCudaError;
     if (launch_im2col(X, col.p, g, p.dtype, s) != cudaSuccess) return kCudaError;
     B = col.p; ldb = static_cast<long long>(g.N) * g.HWp; strideB = g.HWp;
@@ -210,7 +230,7 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
   }
   if (!dW && !dX) return kOk;
 
-  const bool pw = pointwise(g);
+  const bool pw = pointwise(g, esz);
   AsyncBuf col(s);
   const long long gz_stride = static_cast<long long>(g.Cout) * g.HWp;
   const void* B = X;
@@ -265,10 +285,13 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
     const int rc = dense_forward(f, s);
     if (rc != kOk) return rc;
     if (!pw) {
-      const long long total = static_cast<long long>(g.N) * g.Cin * g.H * g.W;
-      long long blocks = (total + 255) / 256;
-      if (blocks > (1 << 20)) blocks = 1 << 20;
-      col2im_batched_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(col.p, dX, g, p.dtype);
+      const long long planes = static_cast<long long>(g.N) * g.Cin;
+      if (planes > 0x7fffffffll) return kBadArgs;
+      int gy = (g.H * g.W + 255) / 256;
+      if (gy > 4096) gy = 4096;
+      const dim3 grid(static_cast<unsigned>(planes), gy);
+      if (g.sh == 1 && g.sw == 1) col2im_batched_kernel<true><<<grid, 256, 0, s>>>(col.p, dX, g, p.dtype);
+      else                        col2im_batched_kernel<false><<<grid, 256, 0, s>>>(col.p, dX, g, p.dtype);
       if (cudaGetLastError() != cudaSuccess) return kCudaError;
     }
   }

@@ -88,6 +88,7 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
   if (gZ) {
     if (b.scratch_bytes > 0 && b.scratch_bytes < need) return kBadArgs;
   } else {
+    keep_async_pool_cached();
     if (cudaMallocAsync(&gZ, need, s) != cudaSuccess) return kCudaError;
     owned = true;
   }

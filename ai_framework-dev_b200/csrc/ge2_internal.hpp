@@ -79,6 +79,7 @@ int* device_status_ptr();   // device address of the status word for the current
 
 int  sm_count();            // cached multiprocessor count of the current device
 int  sm_budget();           // SMs the persistent GEMM may occupy: sm_count() unless lowered by set_sm_limit()
+void keep_async_pool_cached();   // call before cudaMallocAsync: the default pool then keeps freed scratch for reuse
 void set_sm_limit(int n);   // n <= 0 restores "all SMs"; process-wide
 
 }  // namespace ge2b

@@ -58,7 +58,7 @@ bool tensor_vec_ok(const void* p, long long ld, long long batch_stride, int dt) 
   return aligned16(p) && (ld * esz) % 16 == 0 && (batch_stride * esz) % 16 == 0;
 }
 
-// Scratch of the split-K tail (fp32 partial tiles + one arrival counter per tail tile).  One buffer per
+// Scratch of split-K launches (fp32 partial tiles + one arrival counter per tile and epilogue-warp slot).  One buffer per
 // (device, stream), created the first time a launch on that stream needs it and kept for the life of the process:
 // launches on one stream are ordered, launches on different streams get different buffers.  Creating it allocates
 // device memory, so the first split launch on a stream must happen outside stream capture (warm the shape up once).
@@ -74,7 +74,7 @@ SplitScratch* split_scratch(cudaStream_t s) {
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
     if (cudaMalloc(reinterpret_cast<void**>(&sc.ws), kSplitWsBytes) != cudaSuccess) { sc.ws = nullptr; return nullptr; }
-    if (cudaMalloc(reinterpret_cast<void**>(&sc.flags), kSplitMaxTail * sizeof(int)) != cudaSuccess) {
+    if (cudaMalloc(reinterpret_cast<void**>(&sc.flags), kSplitMaxTail * kEpiWarps * 2 * sizeof(int)) != cudaSuccess) {
       cudaFree(sc.ws); sc.ws = nullptr; return nullptr;
     }
     sc.ws_bytes = kSplitWsBytes;

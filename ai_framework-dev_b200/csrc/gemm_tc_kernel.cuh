@@ -49,10 +49,13 @@ struct TcParams {
   uint32_t idesc;
   EpilogueArgs epi;
   int d_vec, z_vec, c_vec, bias_vec;   // 16-byte vector access allowed for that tensor
-  // Split-K tail: the last, partly filled wave of tiles is cut into `split` slices of the reduction so that it
-  // occupies all SMs.  Items [0, main_tiles) are whole tiles; item main_tiles + s * tail_tiles + r is slice s of
-  // tail tile r.  Slices s > 0 leave fp32 partial sums in `ws` and count into flags[r]; slice 0 adds them and
-  // runs the epilogue.
+  // Split-K (problems smaller than one wave): every tile is cut into `split` slices of the reduction so that the
+  // launch occupies all SMs.  Items [0, main_tiles) are whole tiles (none today: main_tiles is 0 whenever split > 1);
+  // item main_tiles + s * tail_tiles + r is slice s of tail tile r.  Every slice leaves its fp32 partial tile in
+  // `ws`.  With few slices (fin_in_kernel) each epilogue warp then counts itself into flags[tile][warp slot], and the
+  // warp that arrives last adds the slices' partials of its part of the tile, in slice order, and runs the epilogue;
+  // with many slices splitk_finalize_kernel, launched right after, does that with the whole machine.  Either way the
+  // result does not depend on arrival order and no CTA waits for another one.
   //
   // Narrow tail (common variant, CTA pairs with 256-column tiles): the tiles of a partly filled last wave are cut
   // into two 128-column halves instead, so that twice as many pairs finish the launch together and nothing is
@@ -62,6 +65,7 @@ struct TcParams {
   uint32_t idesc_half;
   float* ws;
   int* flags;
+  int fin_in_kernel;
   int* status;
 };
 
@@ -568,23 +572,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (c + 1 < n_chunks) chunk_step(c + 1, r1, r0);
         }
       } else {
-        // fp32 partial sums of split tiles: [slice-1][tail tile][row in tile][column in tile]
+        // fp32 partial sums of split tiles: [slice][tail tile][row in tile][column in tile]
         const size_t tile_elems = static_cast<size_t>(kTileM) * kBlockN;
         float* ws_row = nullptr;
         if (w.split)
-          ws_row = p.ws + (static_cast<size_t>(w.slice > 0 ? w.slice - 1 : 0) * p.tail_tiles + w.tail) * tile_elems +
+          ws_row = p.ws + (static_cast<size_t>(w.slice) * p.tail_tiles + w.tail) * tile_elems +
                    static_cast<size_t>(row_in_tile) * kBlockN + half * (kBlockN / 2);
-        if (w.split && w.slice == 0) {
-          // wait until every epilogue warp of the other slices has published its partial sums (bounded)
-          const int expect = (p.split - 1) * kEpiWarps * kCG;
-          const volatile int* flag = p.flags + w.tail;
-          const long long t0 = clock64();
-          while (*flag < expect) {
-            __nanosleep(200);
-            if (*abort_flag != 0 || clock64() - t0 > ptx::kWaitBudgetCycles) { *abort_flag = 1; break; }
-          }
-          __threadfence();
-        }
         if (n_chunks == 0) release_acc();
 #pragma unroll 1
         for (int c = 0; c < n_chunks; ++c) {
@@ -596,7 +589,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           if (c + 1 == n_chunks) release_acc();
           const int col0 = nh0 + c * 32;
-          if (w.split && w.slice > 0) {                // publish this slice's partial sums and go on
+          if (w.split) {                               // leave this slice's partial sums
             if (row_ok) {
 #pragma unroll
               for (int j = 0; j < 8; ++j)
@@ -605,22 +598,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             continue;
           }
-          if (w.split) {
-            for (int sl = 0; row_ok && sl + 1 < p.split; ++sl) {   // slice 0: add the others' partial sums
-              const float* src = ws_row + static_cast<size_t>(sl) * p.tail_tiles * tile_elems + c * 32;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float4 f = __ldcg(reinterpret_cast<const float4*>(src) + j);
-                v[4 * j] += f.x; v[4 * j + 1] += f.y; v[4 * j + 2] += f.z; v[4 * j + 3] += f.w;
-              }
-            }
-          }
           epilogue_frag(p, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane);
         }
-        if (w.split && w.slice > 0) {                  // this warp's share of the partial tile is written
+        if (w.split && p.fin_in_kernel) {
+          // count this warp's part of the tile as written; the last of the `split` warps that own this part adds up
+          // all slices (slice order, so the sum is the same whoever comes last) and finishes the tile
           __threadfence();
           __syncwarp();
-          if (lane == 0) atomicAdd(p.flags + w.tail, 1);
+          int arrived = 0;
+          if (lane == 0)
+            arrived = atomicAdd(p.flags + w.tail * (kEpiWarps * kCG) + static_cast<int>(cta_rank) * kEpiWarps + (warp - 2), 1);
+          arrived = __shfl_sync(0xffffffffu, arrived, 0);
+          if (arrived == p.split - 1) {
+            __threadfence();
+            const float* sum_row = p.ws + static_cast<size_t>(w.tail) * tile_elems +
+                                   static_cast<size_t>(row_in_tile) * kBlockN + half * (kBlockN / 2);
+#pragma unroll 1
+            for (int c = 0; c < n_chunks; ++c) {
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = 0.f;
+              for (int sl = 0; row_ok && sl < p.split; ++sl) {
+                const float* src = sum_row + static_cast<size_t>(sl) * p.tail_tiles * tile_elems + c * 32;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float4 f = __ldcg(reinterpret_cast<const float4*>(src) + j);
+                  v[4 * j] += f.x; v[4 * j + 1] += f.y; v[4 * j + 2] += f.z; v[4 * j + 3] += f.w;
+                }
+              }
+              const int col0 = nh0 + c * 32;
+              epilogue_frag(p, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane);
+            }
+          }
         }
       }
       acc ^= 1; if (acc == 0) acc_phase ^= 1u;
@@ -648,12 +657,71 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 }
 
 
+// Second step of a split-K launch: adds the slices' partial tiles in slice order (so the result does not depend on
+// which CTA finished first) and applies the epilogue.  grid.x = tail tile, grid.y = row group of the tile; a thread
+// owns four consecutive columns, so the partial sums are read with coalesced 16-byte loads.
+template <int ACT>
+__device__ __forceinline__ float finalize_act(float v, float leaky, bool fast) {
+  return fast ? act_fwd<ACT, true>(v, leaky) : act_fwd<ACT, false>(v, leaky);
+}
+
+static __global__ void __launch_bounds__(256)
+splitk_finalize_kernel(const TcParams p, const int tile_m, const int tile_n) {
+  const int r = blockIdx.x;
+  int b, mb, nb;
+  decode_tile(p, static_cast<long long>(p.main_tiles) + r, b, mb, nb);
+  const int quads = tile_n / 4;
+  const int quad = threadIdx.x % quads;
+  const int rows_per_pass = 256 / quads;
+  const size_t tile_elems = static_cast<size_t>(tile_m) * tile_n;
+  const EpilogueArgs& e = p.epi;
+  const bool fast = e.d_dtype != kF32;
+  const int col0 = nb * tile_n + quad * 4;
+  if (col0 >= p.N) return;
+  for (int rt = blockIdx.y * rows_per_pass + threadIdx.x / quads; rt < tile_m; rt += gridDim.y * rows_per_pass) {
+    const int row = mb * tile_m + rt;
+    if (row >= p.M) break;
+    const float* src = p.ws + static_cast<size_t>(r) * tile_elems + static_cast<size_t>(rt) * tile_n + quad * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int sl = 0; sl < p.split; ++sl) {
+      const float4 f = __ldcg(reinterpret_cast<const float4*>(src + static_cast<size_t>(sl) * p.tail_tiles * tile_elems));
+      acc.x += f.x; acc.y += f.y; acc.z += f.z; acc.w += f.w;
+    }
+    float v[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int col = col0 + j;
+      if (col >= p.N) break;
+      float x = v[j] * e.alpha;
+      if (e.C != nullptr && e.beta != 0.f)
+        x = fmaf(e.beta, load_as_f32(e.C, static_cast<long long>(b) * e.strideC + static_cast<long long>(row) * e.ldc + col, e.d_dtype), x);
+      if (e.bias != nullptr) {
+        if (e.bias_kind == kBiasPerN)      x += __ldg(e.bias + col);
+        else if (e.bias_kind == kBiasPerM) x += __ldg(e.bias + row);
+        else if (e.bias_kind == kBiasScalar) x += __ldg(e.bias);
+      }
+      if (e.Z != nullptr)
+        store_from_f32(e.Z, static_cast<long long>(b) * e.strideZ + static_cast<long long>(row) * e.ldz + col, e.z_dtype, x);
+      switch (e.act) {
+        case kActReLU:    x = finalize_act<kActReLU>(x, e.leaky, false); break;
+        case kActLeaky:   x = finalize_act<kActLeaky>(x, e.leaky, false); break;
+        case kActGELU:    x = finalize_act<kActGELU>(x, e.leaky, fast); break;
+        case kActSigmoid: x = finalize_act<kActSigmoid>(x, e.leaky, fast); break;
+        case kActTanh:    x = finalize_act<kActTanh>(x, e.leaky, fast); break;
+        default: break;
+      }
+      store_from_f32(e.D, static_cast<long long>(b) * e.strideD + static_cast<long long>(row) * e.ldd + col, e.d_dtype, x);
+    }
+  }
+}
+
 // ---- host helpers defined in gemm_tc.cu ----
 bool make_operand_map(CUtensorMap* map, int dtype, const void* base, long long inner, long long rows, long long ld,
                       long long batch, long long batch_stride, int box_inner, int box_rows, bool swizzle_32b_units);
 struct SplitScratch { float* ws = nullptr; int* flags = nullptr; size_t ws_bytes = 0; };
 constexpr size_t kSplitWsBytes = 64u << 20;
 constexpr int kSplitMaxTail = 256;
+constexpr int kSplitInKernelMax = 8;   // more slices than this: the second kernel adds them up
 SplitScratch* split_scratch(cudaStream_t s);
 
 template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG>
@@ -707,18 +775,20 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   // one (half a wave at 4096^3) was eaten by the exchange of partial sums and the slower full-machine wave.
   if (!split_off && tiles < units && 2 * rem <= units && rem <= kSplitMaxTail) {
     long long sp = units / rem;
-    if (sp > 8) sp = 8;
+    if (sp > 32) sp = 32;
     if (sp > p.k_blocks / 8) sp = p.k_blocks / 8;               // keep at least 8 k-blocks per slice
-    const size_t need = static_cast<size_t>(sp > 1 ? sp - 1 : 0) * rem * kTileM * kBlockN * sizeof(float);
-    if (sp >= 2 && need <= kSplitWsBytes) {
+    while (sp >= 2 && static_cast<size_t>(sp) * rem * kTileM * kBlockN * sizeof(float) > kSplitWsBytes) --sp;
+    if (sp >= 2) {
       if (SplitScratch* sc = split_scratch(s)) {
-        if (cudaMemsetAsync(sc->flags, 0, static_cast<size_t>(rem) * sizeof(int), s) != cudaSuccess)
-          return cudaErrorUnknown;
         p.main_tiles = static_cast<int>(tiles - rem);
         p.tail_tiles = static_cast<int>(rem);
         p.split = static_cast<int>(sp);
         p.ws = sc->ws;
         p.flags = sc->flags;
+        p.fin_in_kernel = sp <= kSplitInKernelMax ? 1 : 0;
+        if (p.fin_in_kernel &&
+            cudaMemsetAsync(sc->flags, 0, static_cast<size_t>(rem) * kEpiWarps * kCG * sizeof(int), s) != cudaSuccess)
+          return cudaErrorUnknown;
       }
     }
   }
@@ -750,8 +820,16 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return (p.split > 1 && !narrow_tail) ? cudaLaunchKernelEx(&cfg, kernel_split, tmA, tmB, tmBh, p)
-                                       : cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmBh, p);
+  if (p.split > 1 && !narrow_tail) {
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel_split, tmA, tmB, tmBh, p);
+    if (e != cudaSuccess || p.fin_in_kernel) return e;
+    const int quads = kBlockN / 4, rows_per_pass = 256 / quads;
+    int gy = kTileM / rows_per_pass;                    // one pass per block when the grid is small ...
+    while (gy > 1 && static_cast<long long>(p.tail_tiles) * gy > 8ll * units) gy >>= 1;   // ... fewer blocks when it is not
+    splitk_finalize_kernel<<<dim3(p.tail_tiles, gy), 256, 0, s>>>(p, kTileM, kBlockN);
+    return cudaGetLastError();
+  }
+  return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmBh, p);
 }
 
 struct TileChoice { int block_n, cta_group; };

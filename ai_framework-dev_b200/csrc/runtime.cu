@@ -67,6 +67,20 @@ std::atomic<int> g_sm_limit{0};
 
 void set_sm_limit(int n) { g_sm_limit.store(n > 0 ? n : 0, std::memory_order_relaxed); }
 
+// Stream-ordered scratch (cudaMallocAsync) comes from the device's default memory pool, which by default hands its
+// memory back to the driver at every synchronisation; a step that allocates the same scratch again and again would
+// pay for fresh physical memory each time.  Raising the pool's release threshold (once per device) keeps it cached.
+void keep_async_pool_cached() {
+  static bool done[kMaxDevices] = {};
+  const int d = current_device();
+  if (d < 0 || d >= kMaxDevices || done[d]) return;
+  done[d] = true;
+  cudaMemPool_t pool = nullptr;
+  if (cudaDeviceGetDefaultMemPool(&pool, d) != cudaSuccess || !pool) { cudaGetLastError(); return; }
+  unsigned long long keep = ~0ull;
+  if (cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep) != cudaSuccess) cudaGetLastError();
+}
+
 int sm_budget() {
   const int all = sm_count();
   const int lim = g_sm_limit.load(std::memory_order_relaxed);

@@ -249,6 +249,22 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.profile == "conv":
+        # conv2d forward + backward of one ResNet-like layer (bf16, N=32, 64 -> 64 channels, 56 x 56, 3 x 3), twice
+        cv = pkg.ops_conv2d
+        cX = torch.randn(32, 64, 56, 56, device=dev).bfloat16()
+        cW = (torch.randn(64, 64, 3, 3, device=dev) / 24).bfloat16()
+        cb = torch.randn(64, device=dev)
+        cY = torch.empty(32, 64, 56, 56, device=dev, dtype=torch.bfloat16)
+        cZ, cdY = torch.empty_like(cY), torch.randn(32, 64, 56, 56, device=dev).bfloat16()
+        cgX, cgW, cgB = torch.empty_like(cX), torch.empty_like(cW), torch.empty(64, device=dev)
+        for _ in range(2):
+            cv.forward_into(cX, cW, out=cY, B=cb, with_bias=True, act="relu", save_z=True, Z_saved=cZ, padding=(1, 1))
+            cv.backward_into(cX, cW, cdY, cZ, with_bias=True, act="relu", gX_out=cgX, gW_out=cgW, gB_out=cgB,
+                             padding=(1, 1))
+        barrier()
+        print(json.dumps({"profile": "conv", "status": lib.ge2b_device_status(0)}), flush=True)
+        return
     if args.profile:
         # a short, fixed launch sequence for a profiler capture: 2 warm-up steps, then 2 more
         for _ in range(4):
@@ -509,6 +525,56 @@ def run_sweep(args):
                       "pv_ms": round(t_pv, 4), "pv_tflops": round(flop / t_pv / 1e9, 1),
                       "pv_GBs": round((P.numel() * 2 + 2 * V.numel() * 2) / t_pv / 1e6, 1)}), flush=True)
     assert lib.ge2b_device_status(0) == 0
+    run_conv_points(pkg, lib, timeit)
+
+
+CONV_POINTS = [  # name, N, Cin, H, W, Cout, k, stride, pad  (ResNet-50-like layer shapes, batch 32)
+    ("3x3 64->64 56x56", 32, 64, 56, 56, 64, 3, 1, 1), ("3x3 128->128 28x28 s2", 32, 128, 56, 56, 128, 3, 2, 1),
+    ("3x3 256->256 14x14", 32, 256, 14, 14, 256, 3, 1, 1), ("1x1 256->1024 14x14", 32, 256, 14, 14, 1024, 1, 1, 0),
+    ("7x7 3->64 224x224 s2", 32, 3, 224, 224, 64, 7, 2, 3)]
+
+
+def run_conv_points(pkg, lib, timeit):
+    """conv2d (+bias+ReLU, pre-activation saved) forward and backward on the GEMM kernels, and the reference's own
+    conv2d op (fp32, per-image loop) where its library was built.  One JSON line per point."""
+    import ctypes as C
+    import torch
+    cv = pkg.ops_conv2d
+    ref = None
+    so = ROOT / "oracle" / "_ref" / "libref_conv.so"
+    if so.exists():
+        ref = C.CDLL(str(so))
+        ref.ref_conv_forward.argtypes = [C.c_void_p] * 5 + [C.c_int] * 14 + [C.c_float, C.c_void_p]
+        ref.ref_conv_backward.argtypes = [C.c_void_p] * 7 + [C.c_int] * 14 + [C.c_float, C.c_void_p]
+    for name, N, Cin, H, W, Cout, k, st, pd in CONV_POINTS:
+        kw = dict(stride=(st, st), padding=(pd, pd))
+        Ho, Wo = cv.out_hw(H, W, k, k, **kw)
+        flop = 2.0 * N * Cout * Ho * Wo * Cin * k * k
+        for dt, math in ((torch.bfloat16, "fp32"), (torch.float32, "tf32"), (torch.float32, "fp32")):
+            X = torch.randn(N, Cin, H, W, device="cuda").to(dt)
+            Wt = (torch.randn(Cout, Cin, k, k, device="cuda") / (Cin * k * k) ** 0.5).to(dt)
+            b = torch.randn(Cout, device="cuda")
+            Y = torch.empty(N, Cout, Ho, Wo, device="cuda", dtype=dt)
+            Z, dY = torch.empty_like(Y), torch.randn(N, Cout, Ho, Wo, device="cuda").to(dt)
+            gX, gW, gB = torch.empty_like(X), torch.empty_like(Wt), torch.empty(Cout, device="cuda")
+            fwd = lambda: cv.forward_into(X, Wt, out=Y, B=b, with_bias=True, act="relu", save_z=True, Z_saved=Z,  # noqa: E731
+                                          math=math, **kw)
+            bwd = lambda: cv.backward_into(X, Wt, dY, Z, with_bias=True, act="relu", gX_out=gX, gW_out=gW,  # noqa: E731
+                                           gB_out=gB, math=math, **kw)
+            t_f, t_b = timeit(fwd, 5), timeit(bwd, 5)
+            rec = {"sweep": "conv2d", "layer": name, "N": N, "dtype": str(dt)[6:], "math": math,
+                   "fwd_ms": round(t_f, 4), "fwd_tflops": round(flop / t_f / 1e9, 1),
+                   "bwd_ms": round(t_b, 4), "bwd_tflops": round(2 * flop / t_b / 1e9, 1)}
+            if ref is not None and dt == torch.float32 and math == "fp32" and X.numel() < 5e7:
+                geom = (N, Cin, H, W, Cout, k, k, st, st, pd, pd, 1, 1)
+                rf = lambda: ref.ref_conv_forward(X.data_ptr(), Wt.data_ptr(), b.data_ptr(), Y.data_ptr(), Z.data_ptr(),  # noqa: E731
+                                                  *geom, 1, 0.01, None)
+                rb = lambda: ref.ref_conv_backward(X.data_ptr(), Wt.data_ptr(), dY.data_ptr(), Z.data_ptr(), gW.data_ptr(),  # noqa: E731
+                                                   gB.data_ptr(), gX.data_ptr(), *geom, 1, 0.01, None)
+                rec["reference_fwd_ms"] = round(timeit(rf, 1, reps=3), 3)
+                rec["reference_bwd_ms"] = round(timeit(rb, 1, reps=3), 3)
+            print(json.dumps(rec), flush=True)
+    assert lib.ge2b_device_status(0) == 0
 
 
 def main():
@@ -517,7 +583,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile", default="", choices=["", "fwd", "step"],
+    ap.add_argument("--profile", default="", choices=["", "fwd", "step", "conv"],
                     help="run a short fixed launch sequence (for ncu) instead of the benchmark")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU-oracle leg (profiling runs)")
     ap.add_argument("--skip-mlp", action="store_true", help="omit the MLP training-step leg")

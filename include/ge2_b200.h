@@ -217,7 +217,7 @@ void ge2b_register_gemm_kernels(void);
  * Replaces Conv2DCudaLaunch / Conv2DCudaBackwardLaunch (backends/cuda/ops/conv2d/api.hpp:44-64, launcher.cu:115-462):
  * same attributes (Conv2DAttrs, api.hpp:6-16) and the same output-size rule, but one im2col pass and one batched
  * GEMM launch for the whole batch instead of a per-image loop, and no caller-provided workspace (scratch is
- * allocated and freed in stream order).  dtype tags every tensor (GE2_DTYPE_*); bias and dB stay fp32; Z may be fp32
+ * allocated and freed in stream order).  dtype tags every tensor (GE2_DT_*); bias and dB stay fp32; Z may be fp32
  * or dtype.  math as in ge2_params_typed_t.  dB is the sum over the whole batch (the reference's per-image
  * GemmCudaBackward zeroes the bias gradient on every call, launcher.cu:420-431 with regemm_backward.cu:196, so its
  * dB holds the last image only). */
