@@ -50,6 +50,28 @@ bool make_operand_map(CUtensorMap* map, int dtype, const void* base, long long i
   return r == CUDA_SUCCESS;
 }
 
+// 3-D map {columns, rows, batch} over a row-major output for the epilogue's bulk stores: box of 32 x 32 elements
+// (64 x 32 in the `wide` form of 16-bit single-output launches), swizzled the way the epilogue lays its staging
+// buffer out (64-byte rows for 32 16-bit elements, 128-byte rows otherwise).
+bool make_output_map(CUtensorMap* map, int dtype, const void* base, long long cols, long long rows, long long ld,
+                     long long batch, long long batch_stride, bool wide) {
+  EncodeTiledFn enc = encode_tiled_fn_impl();
+  if (!enc) return false;
+  const int esz = dtype_bytes(dtype);
+  const CUtensorMapDataType dt = dtype == kF32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  if (batch_stride <= 0 || batch <= 1) { batch = 1; batch_stride = rows * ld; }
+  cuuint64_t dims[3]    = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * esz, static_cast<cuuint64_t>(batch_stride) * esz};
+  cuuint32_t box[3]     = {wide ? 64u : 32u, 32u, 1u};
+  cuuint32_t estr[3]    = {1u, 1u, 1u};
+  const CUresult r = enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         (esz == 4 || wide) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                         CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 bool tensor_vec_ok(const void* p, long long ld, long long batch_stride, int dt) {

@@ -48,7 +48,11 @@ struct TcParams {
                             // one output matrix, `batch` is 1 for the tile schedule
   uint32_t idesc;
   EpilogueArgs epi;
-  int d_vec, z_vec, c_vec, bias_vec;   // 16-byte vector access allowed for that tensor
+  int d_vec, z_vec, c_vec, bias_vec;   // base, pitch and batch stride 16-byte aligned: D / Z leave through TMA stores,
+                                       // C and bias are read with 16-byte loads
+  int store_dbl;                       // every stored tensor is 16-bit: the staging buffer is used as two halves
+  int store_wide;                      // D is the only output and 16-bit: two 32-column fragments leave as one
+                                       // 64-column (128-byte rows) bulk store; tmD then has a 64 x 32 box
   // Split-K (problems smaller than one wave): every tile is cut into `split` slices of the reduction so that the
   // launch occupies all SMs.  Items [0, main_tiles) are whole tiles (none today: main_tiles is 0 whenever split > 1);
   // item main_tiles + s * tail_tiles + r is slice s of tail tile r.  Every slice leaves its fp32 partial tile in
@@ -149,22 +153,35 @@ __device__ __forceinline__ void load_row_frag(const void* base, long long off, i
   }
 }
 
-// Coalesced store of a 32-row x 32-column fragment held one row per lane.  Rows go through a per-warp
-// shared-memory buffer (16-byte chunks, XOR-swizzled so that neither side has bank conflicts) and leave as
-// 16-byte stores in which consecutive lanes cover consecutive bytes of a row, i.e. whole 32-byte sectors,
-// instead of 32 lanes each writing 16 bytes of a different row.
-__device__ __forceinline__ void store_frag_coalesced(uint8_t* stage, void* base, long long batch_off, long long ld,
-                                                     int dt, const float (&v)[32], int row0, int col0, int M,
-                                                     int lane) {
-  const int esz = (dt == kF32) ? 4 : 2;
-  const int chunks = 2 * esz;                       // 16-byte chunks per 32-column row: 4 (16-bit) or 8 (fp32)
-  const int swz = (chunks == 4) ? ((lane >> 1) & 3) : (lane & 7);
-  uint8_t* my_row = stage + lane * (chunks * 16);
-  if (dt == kF32) {
+// Per-warp state of the epilogue's stores: the warp's 4 KB staging buffer and which half is next.
+struct EpiStage {
+  uint8_t* buf;
+  int slot;
+};
+
+// Store of a 32-row x 32-column fragment held one row per lane: the rows are written to the warp's staging buffer
+// in the TMA swizzle pattern (16-byte chunk index XOR (row >> 1) & 3 for 64-byte rows, XOR row & 7 for 128-byte rows,
+// which is also what keeps these shared-memory stores free of bank conflicts) and one lane issues a tiled bulk store
+// of the 32 x 32 box.  Rows >= M and columns >= N of the box are clipped by the tensor map.  With 16-bit tensors the
+// buffer holds two fragments and a store only has to wait for the one issued before the previous one.
+__device__ __forceinline__ void store_frag_tma(EpiStage& st, bool dbl, const CUtensorMap* tm, int dt, const float (&v)[32],
+                                               int row0, int col0, int b, int lane) {
+  const bool wide = (dt == kF32);
+  uint8_t* buf = st.buf + ((dbl && st.slot) ? 2048 : 0);
+  if (lane == 0) {
+    if (dbl) ptx::bulk_wait_group_read<1>();
+    else     ptx::bulk_wait_group_read<0>();
+  }
+  __syncwarp();
+  if (wide) {
+    const int swz = lane & 7;
+    uint8_t* my_row = buf + lane * 128;
 #pragma unroll
     for (int c = 0; c < 8; ++c)
       *reinterpret_cast<float4*>(my_row + ((c ^ swz) * 16)) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
   } else {
+    const int swz = (lane >> 1) & 3;
+    uint8_t* my_row = buf + lane * 64;
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       uint32_t w[4];
@@ -182,19 +199,51 @@ __device__ __forceinline__ void store_frag_coalesced(uint8_t* stage, void* base,
       *reinterpret_cast<uint4*>(my_row + ((c ^ swz) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
+  ptx::fence_proxy_async_smem();        // the bulk store reads shared memory through the async proxy
   __syncwarp();
-  const int rows_per_pass = 32 / chunks;            // 8 or 4 rows per store instruction
-  const int c = lane % chunks;
-  uint8_t* gbase = reinterpret_cast<uint8_t*>(base) + (batch_off + col0) * esz + c * 16;
-#pragma unroll
-  for (int pass = 0; pass < 8; ++pass) {
-    if (pass * rows_per_pass >= 32) break;
-    const int r = pass * rows_per_pass + lane / chunks;
-    const int rs = (chunks == 4) ? ((r >> 1) & 3) : (r & 7);
-    const uint4 val = *reinterpret_cast<const uint4*>(stage + r * (chunks * 16) + ((c ^ rs) * 16));
-    if (row0 + r < M) *reinterpret_cast<uint4*>(gbase + static_cast<long long>(row0 + r) * ld * esz) = val;
+  if (lane == 0) {
+    ptx::tma_store_3d(tm, ptx::smem_u32(buf), col0, row0, b);
+    ptx::bulk_commit_group();
   }
-  __syncwarp();
+  if (dbl) st.slot ^= 1;
+}
+
+// 16-bit, single output: fragments of two neighbouring 32-column chunks share one buffer of 128-byte rows
+// (chunk index XOR row & 7) and leave together, halving the number of bulk stores, proxy fences and waits.
+// `second` is the odd chunk of the pair, `flush` says that no further chunk follows (a ragged last pair: the
+// columns the missing half would cover lie beyond N and are clipped by the tensor map).
+__device__ __forceinline__ void store_frag_tma_wide(EpiStage& st, const CUtensorMap* tm, int dt, const float (&v)[32],
+                                                    int row0, int col0, int b, int lane, bool second, bool flush) {
+  if (!second) {
+    if (lane == 0) ptx::bulk_wait_group_read<0>();
+    __syncwarp();
+  }
+  const int swz = lane & 7;
+  uint8_t* my_row = st.buf + lane * 128;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t w[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float lo = v[8 * c + 2 * t], hi = v[8 * c + 2 * t + 1];
+      if (dt == kBF16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+        w[t] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __half2 h = __floats2half2_rn(lo, hi);
+        w[t] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+    *reinterpret_cast<uint4*>(my_row + (((second ? 4 + c : c) ^ swz) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  if (second || flush) {
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      ptx::tma_store_3d(tm, ptx::smem_u32(st.buf), second ? col0 - 32 : col0, row0, b);
+      ptx::bulk_commit_group();
+    }
+  }
 }
 
 template <int ACT>
@@ -210,8 +259,9 @@ __device__ __forceinline__ void apply_act32(float (&v)[32], float leaky, bool fa
 
 // Epilogue math for one 32-column fragment of one row (order of operations follows the reference's
 // Epilogue::apply, backends/cuda/ops/_common/shim/traits.hpp:30-73): alpha, + beta*C, + bias, stash Z, act.
-__device__ __forceinline__ void epilogue_frag(const TcParams& p, float (&v)[32], int b, int row, int col0, int ncols,
-                                              bool row_ok, uint8_t* stage, int lane) {
+__device__ __forceinline__ void epilogue_frag(const TcParams& p, const CUtensorMap* tmD, const CUtensorMap* tmZ,
+                                              float (&v)[32], int b, int row, int col0, int ncols, bool row_ok,
+                                              EpiStage& stage, int lane, bool second, bool last) {
   const EpilogueArgs& e = p.epi;
   if (e.alpha != 1.f) {
 #pragma unroll
@@ -248,9 +298,8 @@ __device__ __forceinline__ void epilogue_frag(const TcParams& p, float (&v)[32],
     }
   }
   if (e.Z != nullptr) {
-    if (p.z_vec && ncols == 32)
-      store_frag_coalesced(stage, e.Z, static_cast<long long>(b) * e.strideZ, e.ldz, e.z_dtype, v, row - lane, col0,
-                           p.M, lane);
+    if (p.z_vec)
+      store_frag_tma(stage, p.store_dbl != 0, tmZ, e.z_dtype, v, row - lane, col0, b, lane);
     else if (row_ok)
       store_row_frag(e.Z, static_cast<long long>(b) * e.strideZ + static_cast<long long>(row) * e.ldz + col0,
                      e.z_dtype, v, ncols, false);
@@ -264,9 +313,10 @@ __device__ __forceinline__ void epilogue_frag(const TcParams& p, float (&v)[32],
     case kActTanh:    apply_act32<kActTanh>(v, e.leaky, fast); break;
     default: break;
   }
-  if (p.d_vec && ncols == 32)
-    store_frag_coalesced(stage, e.D, static_cast<long long>(b) * e.strideD, e.ldd, e.d_dtype, v, row - lane, col0, p.M,
-                         lane);
+  if (p.store_wide)
+    store_frag_tma_wide(stage, tmD, e.d_dtype, v, row - lane, col0, b, lane, second, last);
+  else if (p.d_vec)
+    store_frag_tma(stage, p.store_dbl != 0, tmD, e.d_dtype, v, row - lane, col0, b, lane);
   else if (row_ok)
     store_row_frag(e.D, static_cast<long long>(b) * e.strideD + static_cast<long long>(row) * e.ldd + col0, e.d_dtype,
                    v, ncols, false);
@@ -345,8 +395,10 @@ __device__ __forceinline__ WorkItem get_work(const TcParams& p, long long item) 
 template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG, bool kSplit>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-               const __grid_constant__ CUtensorMap tmBh, const TcParams p) {
+               const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmD,
+               const __grid_constant__ CUtensorMap tmZ, const TcParams p) {
   // tmBh: B with a box of half as many rows, for the narrow tail's reduction-contiguous B (otherwise a copy of tmB).
+  // tmD / tmZ: the outputs as {columns, rows, batch} with a 32 x 32 box (valid when p.d_vec / p.z_vec).
   using Cfg = TcCfg<kElemBytes, kBlockN, kStages, kCG>;
   constexpr bool kTf32 = (kElemBytes == 4);
   constexpr bool kNarrow = (!kSplit && kCG == 2 && kBlockN == 256);   // see TcParams
@@ -360,16 +412,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint8_t* smem = smem_raw + pad;
   const uint32_t smem_base = raw_addr + pad;
 
-  // Barrier block lives after the operand ring.
-  uint8_t* bar_blk = smem + kStages * Cfg::kStageBytes;
-  const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes;
+  // After the operand ring: the epilogue's staging buffers (1024-byte aligned, as the swizzled TMA stores need),
+  // then the barrier block.
+  uint8_t* store_stage = smem + kStages * Cfg::kStageBytes;
+  uint8_t* bar_blk = store_stage + Cfg::kStoreStage;
+  const uint32_t bar_base = smem_base + kStages * Cfg::kStageBytes + Cfg::kStoreStage;
   auto full_bar   = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar  = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tfull_bar  = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(bar_blk + 8 * (2 * kStages + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_blk + 8 * (2 * kStages + 4) + 8);
-  uint8_t* store_stage = bar_blk + Cfg::kBarBytes;    // 4 x kStoreStageWarp, 16-byte aligned
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -526,7 +579,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ===================== epilogue (4 warps, one TMEM lane quarter each) =====================
     const int q = warp & 3;                            // hardware rule: a warp reads lanes 32*(warp%4)..+31
     const int half = (warp - 2) >> 2;                  // which half of the tile's columns this warp owns
-    uint8_t* my_stage = store_stage + (warp - 2) * kStoreStageWarp;
+    EpiStage my_stage{store_stage + (warp - 2) * kStoreStageWarp, 0};
     const uint32_t tempty_leader = (kCG == 2) ? ptx::map_to_cta(tempty_bar(0), 0u) : tempty_bar(0);
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     for (long long item = unit; ok && item < total_items; item += n_units) {
@@ -561,7 +614,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (c + 1 < n_chunks) ptx::tmem_ld_32x32(t_row + (c + 1) * 32, nxt);
           else                  release_acc();
           const int col0 = nh0 + c * 32;
-          epilogue_frag(p, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane);
+          epilogue_frag(p, &tmD, &tmZ, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane, (c & 1) != 0,
+                        c + 1 == n_chunks);
         };
         uint32_t r0[32], r1[32];
         if (n_chunks == 0) release_acc();
@@ -598,7 +652,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             continue;
           }
-          epilogue_frag(p, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane);
+          epilogue_frag(p, &tmD, &tmZ, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane, (c & 1) != 0,
+                        c + 1 == n_chunks);
         }
         if (w.split && p.fin_in_kernel) {
           // count this warp's part of the tile as written; the last of the `split` warps that own this part adds up
@@ -627,13 +682,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
               }
               const int col0 = nh0 + c * 32;
-              epilogue_frag(p, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane);
+              epilogue_frag(p, &tmD, &tmZ, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane, (c & 1) != 0,
+                        c + 1 == n_chunks);
             }
           }
         }
       }
       acc ^= 1; if (acc == 0) acc_phase ^= 1u;
     }
+    // this warp's bulk stores must have left shared memory (and reached global memory) before the CTA goes away
+    if (lane == 0) ptx::bulk_wait_group_all();
+    __syncwarp();
   }
 
   __syncthreads();
@@ -718,6 +777,8 @@ splitk_finalize_kernel(const TcParams p, const int tile_m, const int tile_n) {
 // ---- host helpers defined in gemm_tc.cu ----
 bool make_operand_map(CUtensorMap* map, int dtype, const void* base, long long inner, long long rows, long long ld,
                       long long batch, long long batch_stride, int box_inner, int box_rows, bool swizzle_32b_units);
+bool make_output_map(CUtensorMap* map, int dtype, const void* base, long long cols, long long rows, long long ld,
+                     long long batch, long long batch_stride, bool wide);
 struct SplitScratch { float* ws = nullptr; int* flags = nullptr; size_t ws_bytes = 0; };
 constexpr size_t kSplitWsBytes = 64u << 20;
 constexpr int kSplitMaxTail = 256;
@@ -761,6 +822,18 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   if (!kBMN) ok = make_operand_map(&tmB, g.in_dtype, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, Cfg::kBlockK, kLocalN, false);
   else       ok = make_operand_map(&tmB, g.in_dtype, g.B, g.N, g.K, g.ldb, g.batch, g.strideB, Cfg::kBlockK, Cfg::kBlockK, kWide);
   if (!ok) return cudaErrorInvalidValue;
+
+  // Outputs as tensor maps for the epilogue's bulk stores (when base, pitch and batch stride allow).
+  CUtensorMap tmD = tmA, tmZ = tmA;
+  p.store_wide = (p.d_vec && g.epi.Z == nullptr && g.epi.d_dtype != kF32) ? 1 : 0;
+  if (p.d_vec && !make_output_map(&tmD, g.epi.d_dtype, g.epi.D, g.N, g.M, g.epi.ldd, p.batch, g.epi.strideD,
+                                  p.store_wide != 0)) {
+    p.d_vec = 0;
+    p.store_wide = 0;
+  }
+  if (p.z_vec && !make_output_map(&tmZ, g.epi.z_dtype, g.epi.Z, g.N, g.M, g.epi.ldz, p.batch, g.epi.strideZ, false))
+    p.z_vec = 0;
+  p.store_dbl = (g.epi.d_dtype != kF32 && (g.epi.Z == nullptr || g.epi.z_dtype != kF32)) ? 1 : 0;
 
   const long long tiles = static_cast<long long>(p.batch) * p.m_blocks * p.n_blocks;
   const long long units = sm_budget() / kCG > 0 ? sm_budget() / kCG : 1;   // one CTA (or CTA pair) per SM (pair of SMs)
@@ -821,7 +894,7 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (p.split > 1 && !narrow_tail) {
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel_split, tmA, tmB, tmBh, p);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel_split, tmA, tmB, tmBh, tmD, tmZ, p);
     if (e != cudaSuccess || p.fin_in_kernel) return e;
     const int quads = kBlockN / 4, rows_per_pass = 256 / quads;
     int gy = kTileM / rows_per_pass;                    // one pass per block when the grid is small ...
@@ -829,7 +902,7 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
     splitk_finalize_kernel<<<dim3(p.tail_tiles, gy), 256, 0, s>>>(p, kTileM, kBlockN);
     return cudaGetLastError();
   }
-  return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmBh, p);
+  return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmBh, tmD, tmZ, p);
 }
 
 struct TileChoice { int block_n, cta_group; };

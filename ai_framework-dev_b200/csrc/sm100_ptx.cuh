@@ -70,6 +70,22 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap,
       : "memory");
 }
 
+// Tiled store shared -> global (3-D: inner, rows, batch).  Elements outside the tensor are not written, so ragged
+// tiles need no predicates.  The issuing thread owns the bulk group: it commits it, and later waits either for the
+// store's READS of shared memory (before the buffer is overwritten) or for its completion (before the kernel ends).
+__device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src_smem, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
+      ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---------------- tcgen05 / TMEM ----------------
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
@@ -143,9 +159,11 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Arrive on an mbarrier that lives in another CTA of the cluster.
+// Arrive on an mbarrier that lives in another CTA of the cluster.  CTA-scope release (the default): the barriers
+// signalled this way hand over TMEM or shared-memory slots, which the tcgen05 / async-proxy fences order; a
+// cluster-scope release would also wait for the warp's earlier global stores.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 // TMA load of a CTA pair: data lands in the issuing CTA, completion bytes are credited to `cluster_bar`,
 // which may live in the peer CTA.
