@@ -133,26 +133,40 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
     return e;
   };
 
+  GemmProblem ga{}, gb{};
   if (b.gA) {   // gA[M,K] = alpha * gZ[M,N] . B[K,N]^T : reduction over N, contiguous in both operands
     if (b.ldb < b.N || b.ldgA < b.K) return finish(kBadArgs);
-    GemmProblem g{};
-    g.M = b.M; g.N = b.K; g.K = b.N; g.batch = 1;
-    g.in_dtype = b.dtype; g.math = b.math;
-    g.a_mn = false; g.A = gZ;  g.lda = b.N;
-    g.b_mn = false; g.B = b.B; g.ldb = b.ldb;
-    g.epi = plain_epilogue(b.gA, b.ldgA);
-    const int rc = run_gemm(g, s);
-    if (rc != kOk) return finish(rc);
+    ga.M = b.M; ga.N = b.K; ga.K = b.N; ga.batch = 1;
+    ga.in_dtype = b.dtype; ga.math = b.math;
+    ga.a_mn = false; ga.A = gZ;  ga.lda = b.N;
+    ga.b_mn = false; ga.B = b.B; ga.ldb = b.ldb;
+    ga.epi = plain_epilogue(b.gA, b.ldgA);
   }
   if (b.gB) {   // gB[K,N] = alpha * A[M,K]^T . gZ[M,N] : reduction over M, the outer index of both operands
     if (b.lda < b.K || b.ldgB < b.N) return finish(kBadArgs);
-    GemmProblem g{};
-    g.M = b.K; g.N = b.N; g.K = b.M; g.batch = 1;
-    g.in_dtype = b.dtype; g.math = b.math;
-    g.a_mn = true; g.A = b.A; g.lda = b.lda;
-    g.b_mn = true; g.B = gZ;  g.ldb = b.N;
-    g.epi = plain_epilogue(b.gB, b.ldgB);
-    const int rc = run_gemm(g, s);
+    gb.M = b.K; gb.N = b.N; gb.K = b.M; gb.batch = 1;
+    gb.in_dtype = b.dtype; gb.math = b.math;
+    gb.a_mn = true; gb.A = b.A; gb.lda = b.lda;
+    gb.b_mn = true; gb.B = gZ;  gb.ldb = b.N;
+    gb.epi = plain_epilogue(b.gB, b.ldgB);
+  }
+  // Both gradients wanted on the tensor-core path: one launch walks the tiles of both (see launch_gemm_tc_dual).
+  if (b.gA && b.gB && ((b.dtype != kF32) || b.math == 1)) {
+    const cudaError_t e = launch_gemm_tc_dual(ga, gb, s);
+    if (e == cudaSuccess) {
+      t_last_route = kRouteTensor;
+      g_launches.fetch_add(1, std::memory_order_relaxed);
+      return finish(kOk);
+    }
+    if (e != cudaErrorNotSupported) return finish(kCudaError);
+    cudaGetLastError();
+  }
+  if (b.gA) {
+    const int rc = run_gemm(ga, s);
+    if (rc != kOk) return finish(rc);
+  }
+  if (b.gB) {
+    const int rc = run_gemm(gb, s);
     if (rc != kOk) return finish(rc);
   }
   return finish(kOk);

@@ -71,6 +71,10 @@ struct BwdPrologueArgs {
 cudaError_t launch_gemm_simt(const GemmProblem& g, cudaStream_t s);      // exact fp32-accumulate FMA path (any dtype, any ld)
 bool        gemm_tc_supported(const GemmProblem& g, const char** why);   // alignment / dtype rules of the TMA + tcgen05 path
 cudaError_t launch_gemm_tc(const GemmProblem& g, cudaStream_t s);        // TMA + tcgen05 + TMEM path
+// dX = gZ.W^T and dW = X^T.gZ of one dense layer as ONE persistent launch (their tiles form one list, so only the
+// combined list's last wave is partly filled).  Returns cudaErrorNotSupported when the pair does not qualify; the
+// caller then launches the two problems one after the other.
+cudaError_t launch_gemm_tc_dual(const GemmProblem& dx, const GemmProblem& dw, cudaStream_t s);
 cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s);
 
 // Reads (and optionally clears) the device status word of the current device. Synchronises.

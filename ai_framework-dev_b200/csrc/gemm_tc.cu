@@ -162,6 +162,44 @@ bool gemm_tc_supported(const GemmProblem& g, const char** why) {
   return true;
 }
 
+namespace {
+void fill_common(const GemmProblem& g, tc::TcParams& p) {
+  p.M = g.M; p.N = g.N; p.K = g.K; p.batch = g.reduce_batch ? 1 : g.batch;
+  p.a_bcast = (g.batch > 1 && g.strideA == 0) ? 1 : 0;
+  p.b_bcast = (g.batch > 1 && g.strideB == 0) ? 1 : 0;
+  p.epi = g.epi;
+  p.d_vec = tensor_vec_ok(g.epi.D, g.epi.ldd, g.epi.strideD, g.epi.d_dtype);
+  p.z_vec = tensor_vec_ok(g.epi.Z, g.epi.ldz, g.epi.strideZ, g.epi.z_dtype);
+  p.c_vec = tensor_vec_ok(g.epi.C, g.epi.ldc, g.epi.strideC, g.epi.d_dtype);
+  p.bias_vec = g.epi.bias && aligned16(g.epi.bias);
+  p.status = device_status_ptr();
+}
+}  // namespace
+
+cudaError_t launch_gemm_tc_dual(const GemmProblem& dx, const GemmProblem& dw, cudaStream_t s) {
+  static const bool off = [] { const char* e = getenv("GE2B_DUAL_BWD"); return e && atoi(e) == 0; }();
+  if (off) return cudaErrorNotSupported;
+  // the pair form: both problems unbatched, same element size, the orders of a dense backward, large enough for
+  // CTA pairs, plain epilogues with TMA-storable 16-byte aligned outputs
+  if (dx.batch != 1 || dw.batch != 1 || dx.in_dtype != dw.in_dtype) return cudaErrorNotSupported;
+  if (dx.a_mn || dx.b_mn || !dw.a_mn || !dw.b_mn) return cudaErrorNotSupported;
+  if (dx.M <= 128 || dw.M <= 128 || dx.N <= 128 || dw.N <= 128) return cudaErrorNotSupported;
+  if (!gemm_tc_supported(dx, nullptr) || !gemm_tc_supported(dw, nullptr)) return cudaErrorNotSupported;
+  if (dx.epi.Z || dw.epi.Z || dx.epi.d_dtype != dw.epi.d_dtype) return cudaErrorNotSupported;
+  TcParams p1{}, p2{};
+  fill_common(dx, p1);
+  fill_common(dw, p2);
+  if (!p1.status || !p1.d_vec || !p2.d_vec) return cudaErrorNotSupported;
+  // worth it only when the combined list quantises better than the two lists do separately
+  const long long units = sm_budget() / 2 > 0 ? sm_budget() / 2 : 1;
+  auto tiles = [](const GemmProblem& g) { return static_cast<long long>((g.M + 255) / 256) * ((g.N + 255) / 256); };
+  auto waves = [&](long long t) { return (t + units - 1) / units; };
+  if (tiles(dx) + tiles(dw) < units) return cudaErrorNotSupported;   // small problems are better off with split-K each
+  if (waves(tiles(dx) + tiles(dw)) >= waves(tiles(dx)) + waves(tiles(dw))) return cudaErrorNotSupported;
+  return dx.in_dtype == kF32 ? tc::launch_dual_cfg<4, false, false, true, true>(dx, p1, dw, p2, s)
+                             : tc::launch_dual_cfg<2, false, false, true, true>(dx, p1, dw, p2, s);
+}
+
 cudaError_t launch_gemm_tc(const GemmProblem& g, cudaStream_t s) {
   TcParams p{};
   p.M = g.M; p.N = g.N; p.K = g.K; p.batch = g.reduce_batch ? 1 : g.batch;

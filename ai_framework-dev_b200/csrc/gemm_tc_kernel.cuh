@@ -73,6 +73,16 @@ struct TcParams {
   int* status;
 };
 
+// Second problem of a dual launch: one persistent grid walks the tiles of two independent GEMMs (the dense layer's
+// dX = gZ.W^T and dW = X^T.gZ) as one list, so that only the last wave of the combined list is partly filled.
+// The second problem may store its operands in other orders than the first; it has a plain epilogue.
+struct DualParams {
+  CUtensorMap tmA, tmB, tmD;
+  TcParams p;
+};
+
+template <bool kValue> struct BoolC { static constexpr bool value = kValue; };
+
 template <int kElemBytes, int kBlockN, int kStages, int kCG>
 struct TcCfg {
   static constexpr int kBlockK     = 128 / kElemBytes;    // one 128-byte swizzle row of the reduction index
@@ -392,11 +402,15 @@ __device__ __forceinline__ WorkItem get_work(const TcParams& p, long long item) 
 // 256 x kBlockN tile: each CTA stages its own 128 rows of A and its own half of B, the MMAs are issued by the
 // pair's first CTA and write 128 accumulator rows into each CTA's TMEM, and each CTA runs the epilogue of its
 // own rows.  Halving B's shared-memory footprint per CTA buys a deeper operand ring.
-template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG, bool kSplit>
+// kDual: a second problem (d2, operand orders kAMN2 / kBMN2) follows the first in the item list; see DualParams.
+template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG, bool kSplit, bool kDual = false,
+          bool kAMN2 = false, bool kBMN2 = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmBh, const __grid_constant__ CUtensorMap tmD,
-               const __grid_constant__ CUtensorMap tmZ, const TcParams p) {
+               const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ TcParams p,
+               const __grid_constant__ DualParams d2) {
+  static_assert(!(kDual && kSplit), "a dual launch has no split-K form");
   // tmBh: B with a box of half as many rows, for the narrow tail's reduction-contiguous B (otherwise a copy of tmB).
   // tmD / tmZ: the outputs as {columns, rows, batch} with a 32 x 32 box (valid when p.d_vec / p.z_vec).
   using Cfg = TcCfg<kElemBytes, kBlockN, kStages, kCG>;
@@ -455,22 +469,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
 
-  const long long total_items = static_cast<long long>(p.main_tiles) + static_cast<long long>(p.tail_tiles) * p.split;
+  const long long items1 = static_cast<long long>(p.main_tiles) + static_cast<long long>(p.tail_tiles) * p.split;
+  const long long total_items = items1 + (kDual ? static_cast<long long>(d2.p.main_tiles) : 0ll);
 
   if (warp == 0) {
     // ===================== TMA producer (every CTA stages its own share) =====================
     if (lane == 0) {
       const uint32_t full_leader0 = (kCG == 2) ? ptx::map_to_cta(full_bar(0), 0u) : full_bar(0);
       int stage = 0; uint32_t phase = 0; bool ok = true;
-      for (long long item = unit; ok && item < total_items; item += n_units) {
-        const WorkItem w = get_work<kSplit, kNarrow>(p, item);
+      // One item (tile or slice of a tile) of problem `pp`, whose operands are stored in the orders AMN / BMN.
+      auto produce = [&](auto amn_c, auto bmn_c, const TcParams& pp, const CUtensorMap* mA, const CUtensorMap* mB,
+                         const CUtensorMap* mBh, const WorkItem& w) {
+        constexpr bool AMN = decltype(amn_c)::value, BMN = decltype(bmn_c)::value;
         const int b = w.b;
         const int m0 = w.mb * kTileM + static_cast<int>(cta_rank) * kBlockM;
         const bool narrow = kNarrow && w.narrow;
         const int local_n = narrow ? kLocalN / 2 : kLocalN;          // B rows / columns this CTA stages
         const int n0 = w.nb * kBlockN + w.n_off + static_cast<int>(cta_rank) * local_n;
         const uint32_t stage_tx = (Cfg::kAStage + (narrow ? Cfg::kBStage / 2 : Cfg::kBStage)) * kCG;
-        int ba = p.a_bcast ? 0 : b, bb = p.b_bcast ? 0 : b;
+        int ba = pp.a_bcast ? 0 : b, bb = pp.b_bcast ? 0 : b;
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) { ok = false; break; }
           // The pair's first CTA owns the "full" barrier and announces the bytes of both CTAs.
@@ -479,33 +496,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t a_dst = smem_base + stage * Cfg::kStageBytes;
           const uint32_t b_dst = a_dst + Cfg::kAStage;
           int k0 = kb * Cfg::kBlockK;
-          if (p.kb_per_slice > 0) {                    // reduction over the batch: slice first, then k inside it
-            const int sl = kb / p.kb_per_slice;
-            k0 = (kb - sl * p.kb_per_slice) * Cfg::kBlockK;
-            ba = p.a_bcast ? 0 : sl; bb = p.b_bcast ? 0 : sl;
+          if (pp.kb_per_slice > 0) {                   // reduction over the batch: slice first, then k inside it
+            const int sl = kb / pp.kb_per_slice;
+            k0 = (kb - sl * pp.kb_per_slice) * Cfg::kBlockK;
+            ba = pp.a_bcast ? 0 : sl; bb = pp.b_bcast ? 0 : sl;
           }
           auto load = [&](uint32_t dst, const void* tm, int c0, int c1, int c2) {
             if constexpr (kCG == 2) ptx::tma_load_3d_pair(dst, tm, fb, c0, c1, c2);
             else                    ptx::tma_load_3d(dst, tm, fb, c0, c1, c2);
           };
-          if constexpr (!kAMN) {
-            load(a_dst, &tmA, k0, m0, ba);                                      // box {kBlockK, 128}
+          if constexpr (!AMN) {
+            load(a_dst, mA, k0, m0, ba);                                        // box {kBlockK, 128}
           } else {
 #pragma unroll
             for (int j = 0; j < kBlockM / Cfg::kBlockK; ++j)                    // boxes {kBlockK(m), kBlockK(k)}
-              load(a_dst + j * (Cfg::kBlockK * 128), &tmA, m0 + j * Cfg::kBlockK, k0, ba);
+              load(a_dst + j * (Cfg::kBlockK * 128), mA, m0 + j * Cfg::kBlockK, k0, ba);
           }
-          if constexpr (!kBMN) {
-            if (narrow) load(b_dst, &tmBh, k0, n0, bb);                         // box {kBlockK, kLocalN / 2}
-            else        load(b_dst, &tmB, k0, n0, bb);                          // box {kBlockK, kLocalN}
+          if constexpr (!BMN) {
+            if (narrow) load(b_dst, mBh, k0, n0, bb);                           // box {kBlockK, kLocalN / 2}
+            else        load(b_dst, mB, k0, n0, bb);                            // box {kBlockK, kLocalN}
           } else {
 #pragma unroll
             for (int j = 0; j < kLocalN / Cfg::kBlockK; ++j)
               if (j * Cfg::kBlockK < local_n)
-                load(b_dst + j * (Cfg::kBlockK * 128), &tmB, n0 + j * Cfg::kBlockK, k0, bb);
+                load(b_dst + j * (Cfg::kBlockK * 128), mB, n0 + j * Cfg::kBlockK, k0, bb);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
+      };
+      for (long long item = unit; ok && item < total_items; item += n_units) {
+        if constexpr (kDual) {
+          if (item >= items1) {
+            produce(BoolC<kAMN2>{}, BoolC<kBMN2>{}, d2.p, &d2.tmA, &d2.tmB, &d2.tmB,
+                    get_work<false, false>(d2.p, item - items1));
+            continue;
+          }
+        }
+        produce(BoolC<kAMN>{}, BoolC<kBMN>{}, p, &tmA, &tmB, &tmBh, get_work<kSplit, kNarrow>(p, item));
       }
     }
     __syncwarp();
@@ -520,27 +547,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       constexpr uint32_t kLboMN = Cfg::kBlockK * 128, kSbo = 1024;
       constexpr uint32_t kSboMN = kTf32 ? 512 : 1024;
       constexpr uint32_t kTypeMN = kTf32 ? 1u : 2u;
-      constexpr uint32_t kAStep = kAMN ? Cfg::kUmmaK * 128 : 32;
-      constexpr uint32_t kBStep = kBMN ? Cfg::kUmmaK * 128 : 32;
-      // Everything that does not change from one k-block to the next is computed once: the issuing thread shares
-      // its scheduler with an epilogue warp, so the per-k-block instruction stream has to stay short.
-      const uint64_t a_desc0 = kAMN ? ptx::make_smem_desc_sw128(smem_base, kLboMN, kSboMN, kTypeMN)
-                                    : ptx::make_smem_desc_sw128(smem_base, 0u, kSbo);
-      const uint64_t b_desc0 = kBMN ? ptx::make_smem_desc_sw128(smem_base + Cfg::kAStage, kLboMN, kSboMN, kTypeMN)
-                                    : ptx::make_smem_desc_sw128(smem_base + Cfg::kAStage, 0u, kSbo);
       constexpr uint64_t kStageEnc = Cfg::kStageBytes >> 4;       // descriptor address field counts 16-byte units
-      constexpr uint64_t kAStepEnc = kAStep >> 4, kBStepEnc = kBStep >> 4;
       const uint32_t empty0 = empty_bar(0), tfull0 = tfull_bar(0);
       const uint32_t empty_peer0 = (kCG == 2) ? ptx::map_to_cta(empty0, 1u) : 0u;
       const uint32_t tfull_peer0 = (kCG == 2) ? ptx::map_to_cta(tfull0, 1u) : 0u;
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
-      for (long long item = unit; ok && item < total_items; item += n_units) {
-        int k_blocks = p.k_blocks;
-        const uint32_t idesc = (kNarrow && item >= p.main_tiles) ? p.idesc_half : p.idesc;
-        if constexpr (kSplit) {
-          if (item >= p.main_tiles) { const WorkItem w = decode_work(p, item); k_blocks = w.kb1 - w.kb0; }
-        }
-        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+      // The k-loop of one item whose operands are stored in the orders AMN / BMN.  Everything that does not change
+      // from one k-block to the next is computed before the loop: the issuing thread shares its scheduler with an
+      // epilogue warp, so the per-k-block instruction stream has to stay short.
+      auto issue = [&](auto amn_c, auto bmn_c, uint32_t idesc, int k_blocks) {
+        constexpr bool AMN = decltype(amn_c)::value, BMN = decltype(bmn_c)::value;
+        constexpr uint64_t kAStepEnc = (AMN ? Cfg::kUmmaK * 128 : 32) >> 4, kBStepEnc = (BMN ? Cfg::kUmmaK * 128 : 32) >> 4;
+        const uint64_t a_desc0 = AMN ? ptx::make_smem_desc_sw128(smem_base, kLboMN, kSboMN, kTypeMN)
+                                     : ptx::make_smem_desc_sw128(smem_base, 0u, kSbo);
+        const uint64_t b_desc0 = BMN ? ptx::make_smem_desc_sw128(smem_base + Cfg::kAStage, kLboMN, kSboMN, kTypeMN)
+                                     : ptx::make_smem_desc_sw128(smem_base + Cfg::kAStage, 0u, kSbo);
+        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) { ok = false; return; }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * kBlockN;
         for (int kb = 0; kb < k_blocks; ++kb) {
@@ -563,7 +585,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        if (!ok) break;
+        if (!ok) return;
         // accumulator complete: the epilogue warps (of both CTAs) may start
         if constexpr (kCG == 2) {
           ptx::umma_commit_pair(tfull0 + 8u * acc);
@@ -572,6 +594,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           ptx::umma_commit(tfull0 + 8u * acc);
         }
         acc ^= 1; if (acc == 0) acc_phase ^= 1u;
+      };
+      for (long long item = unit; ok && item < total_items; item += n_units) {
+        if constexpr (kDual) {
+          if (item >= items1) { issue(BoolC<kAMN2>{}, BoolC<kBMN2>{}, d2.p.idesc, d2.p.k_blocks); continue; }
+        }
+        int k_blocks = p.k_blocks;
+        const uint32_t idesc = (kNarrow && item >= p.main_tiles) ? p.idesc_half : p.idesc;
+        if constexpr (kSplit) {
+          if (item >= p.main_tiles) { const WorkItem w = decode_work(p, item); k_blocks = w.kb1 - w.kb0; }
+        }
+        issue(BoolC<kAMN>{}, BoolC<kBMN>{}, idesc, k_blocks);
       }
     }
     __syncwarp();
@@ -583,18 +616,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t tempty_leader = (kCG == 2) ? ptx::map_to_cta(tempty_bar(0), 0u) : tempty_bar(0);
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     for (long long item = unit; ok && item < total_items; item += n_units) {
-      const WorkItem w = get_work<kSplit, kNarrow>(p, item);
+      const bool second = kDual && item >= items1;              // item of the second problem of a dual launch
+      const TcParams& pp = second ? d2.p : p;
+      const CUtensorMap* mD = second ? &d2.tmD : &tmD;
+      const WorkItem w = second ? get_work<false, false>(d2.p, item - items1) : get_work<kSplit, kNarrow>(p, item);
       const int b = w.b;
       const int row_in_tile = static_cast<int>(cta_rank) * kBlockM + q * 32 + lane;
       const int row = w.mb * kTileM + row_in_tile;
-      const bool row_ok = row < p.M;
+      const bool row_ok = row < pp.M;
       const int n0 = w.nb * kBlockN + w.n_off;
       const int half_cols = (kNarrow && w.narrow) ? kBlockN / 4 : kBlockN / 2;   // columns of this warp's half
       if (!ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const uint32_t t_row = tmem_base + acc * kBlockN + half * half_cols + (static_cast<uint32_t>(q * 32) << 16);
       const int nh0 = n0 + half * half_cols;           // first column of this warp's half
-      const int n_chunks = max(0, min(half_cols / 32, (p.N - nh0 + 31) / 32));
+      const int n_chunks = max(0, min(half_cols / 32, (pp.N - nh0 + 31) / 32));
       auto release_acc = [&]() {
         ptx::tc_fence_before_sync();
         __syncwarp();
@@ -614,7 +650,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (c + 1 < n_chunks) ptx::tmem_ld_32x32(t_row + (c + 1) * 32, nxt);
           else                  release_acc();
           const int col0 = nh0 + c * 32;
-          epilogue_frag(p, &tmD, &tmZ, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane, (c & 1) != 0,
+          epilogue_frag(pp, mD, &tmZ, v, b, row, col0, min(32, pp.N - col0), row_ok, my_stage, lane, (c & 1) != 0,
                         c + 1 == n_chunks);
         };
         uint32_t r0[32], r1[32];
@@ -630,7 +666,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const size_t tile_elems = static_cast<size_t>(kTileM) * kBlockN;
         float* ws_row = nullptr;
         if (w.split)
-          ws_row = p.ws + (static_cast<size_t>(w.slice) * p.tail_tiles + w.tail) * tile_elems +
+          ws_row = pp.ws + (static_cast<size_t>(w.slice) * pp.tail_tiles + w.tail) * tile_elems +
                    static_cast<size_t>(row_in_tile) * kBlockN + half * (kBlockN / 2);
         if (n_chunks == 0) release_acc();
 #pragma unroll 1
@@ -652,29 +688,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
             continue;
           }
-          epilogue_frag(p, &tmD, &tmZ, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane, (c & 1) != 0,
+          epilogue_frag(pp, mD, &tmZ, v, b, row, col0, min(32, pp.N - col0), row_ok, my_stage, lane, (c & 1) != 0,
                         c + 1 == n_chunks);
         }
-        if (w.split && p.fin_in_kernel) {
+        if (w.split && pp.fin_in_kernel) {
           // count this warp's part of the tile as written; the last of the `split` warps that own this part adds up
           // all slices (slice order, so the sum is the same whoever comes last) and finishes the tile
           __threadfence();
           __syncwarp();
           int arrived = 0;
           if (lane == 0)
-            arrived = atomicAdd(p.flags + w.tail * (kEpiWarps * kCG) + static_cast<int>(cta_rank) * kEpiWarps + (warp - 2), 1);
+            arrived = atomicAdd(pp.flags + w.tail * (kEpiWarps * kCG) + static_cast<int>(cta_rank) * kEpiWarps + (warp - 2), 1);
           arrived = __shfl_sync(0xffffffffu, arrived, 0);
-          if (arrived == p.split - 1) {
+          if (arrived == pp.split - 1) {
             __threadfence();
-            const float* sum_row = p.ws + static_cast<size_t>(w.tail) * tile_elems +
+            const float* sum_row = pp.ws + static_cast<size_t>(w.tail) * tile_elems +
                                    static_cast<size_t>(row_in_tile) * kBlockN + half * (kBlockN / 2);
 #pragma unroll 1
             for (int c = 0; c < n_chunks; ++c) {
               float v[32];
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = 0.f;
-              for (int sl = 0; row_ok && sl < p.split; ++sl) {
-                const float* src = sum_row + static_cast<size_t>(sl) * p.tail_tiles * tile_elems + c * 32;
+              for (int sl = 0; row_ok && sl < pp.split; ++sl) {
+                const float* src = sum_row + static_cast<size_t>(sl) * pp.tail_tiles * tile_elems + c * 32;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                   const float4 f = __ldcg(reinterpret_cast<const float4*>(src) + j);
@@ -682,7 +718,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 }
               }
               const int col0 = nh0 + c * 32;
-              epilogue_frag(p, &tmD, &tmZ, v, b, row, col0, min(32, p.N - col0), row_ok, my_stage, lane, (c & 1) != 0,
+              epilogue_frag(pp, mD, &tmZ, v, b, row, col0, min(32, pp.N - col0), row_ok, my_stage, lane, (c & 1) != 0,
                         c + 1 == n_chunks);
             }
           }
@@ -785,6 +821,57 @@ constexpr int kSplitMaxTail = 256;
 constexpr int kSplitInKernelMax = 8;   // more slices than this: the second kernel adds them up
 SplitScratch* split_scratch(cudaStream_t s);
 
+struct ProblemMaps { CUtensorMap tmA, tmB, tmD, tmZ; };
+
+// Fills the geometry fields of `p` and the tensor maps of one problem for the given tile configuration.
+template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG>
+bool prepare_problem(const GemmProblem& g, TcParams& p, ProblemMaps& m) {
+  using Cfg = TcCfg<kElemBytes, kBlockN, kStages, kCG>;
+  constexpr int kTileM = kBlockM * kCG;
+  constexpr int kLocalN = kBlockN / kCG;
+  p.m_blocks = (g.M + kTileM - 1) / kTileM;
+  p.n_blocks = (g.N + kBlockN - 1) / kBlockN;
+  p.k_blocks = (g.K + Cfg::kBlockK - 1) / Cfg::kBlockK;
+  p.kb_per_slice = 0;
+  if (g.reduce_batch && g.batch > 1) {
+    p.kb_per_slice = p.k_blocks;
+    p.k_blocks *= g.batch;
+  }
+  const int ab_format = g.in_dtype == kF32 ? 2 : (g.in_dtype == kBF16 ? 1 : 0);
+  p.idesc = ptx::make_idesc(ab_format, kAMN, kBMN, kTileM, kBlockN);
+  p.idesc_half = ptx::make_idesc(ab_format, kAMN, kBMN, kTileM, kBlockN / 2);
+
+  bool ok;
+  constexpr bool kWide = (kElemBytes == 4);   // M/N-contiguous 32-bit tiles are swizzled in 32-byte units
+  if (!kAMN) ok = make_operand_map(&m.tmA, g.in_dtype, g.A, g.K, g.M, g.lda, g.batch, g.strideA, Cfg::kBlockK, kBlockM, false);
+  else       ok = make_operand_map(&m.tmA, g.in_dtype, g.A, g.M, g.K, g.lda, g.batch, g.strideA, Cfg::kBlockK, Cfg::kBlockK, kWide);
+  if (!ok) return false;
+  if (!kBMN) ok = make_operand_map(&m.tmB, g.in_dtype, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, Cfg::kBlockK, kLocalN, false);
+  else       ok = make_operand_map(&m.tmB, g.in_dtype, g.B, g.N, g.K, g.ldb, g.batch, g.strideB, Cfg::kBlockK, Cfg::kBlockK, kWide);
+  if (!ok) return false;
+
+  // Outputs as tensor maps for the epilogue's bulk stores (when base, pitch and batch stride allow).
+  m.tmD = m.tmA; m.tmZ = m.tmA;
+  p.store_wide = (p.d_vec && g.epi.Z == nullptr && g.epi.d_dtype != kF32) ? 1 : 0;
+  if (p.d_vec && !make_output_map(&m.tmD, g.epi.d_dtype, g.epi.D, g.N, g.M, g.epi.ldd, p.batch, g.epi.strideD,
+                                  p.store_wide != 0)) {
+    p.d_vec = 0;
+    p.store_wide = 0;
+  }
+  if (p.z_vec && !make_output_map(&m.tmZ, g.epi.z_dtype, g.epi.Z, g.N, g.M, g.epi.ldz, p.batch, g.epi.strideZ, false))
+    p.z_vec = 0;
+  p.store_dbl = (g.epi.d_dtype != kF32 && (g.epi.Z == nullptr || g.epi.z_dtype != kF32)) ? 1 : 0;
+  p.main_tiles = static_cast<int>(static_cast<long long>(p.batch) * p.m_blocks * p.n_blocks);
+  p.tail_tiles = 0;
+  p.split = 1;
+  return true;
+}
+
+inline const DualParams& no_second_problem() {
+  static const DualParams none{};
+  return none;
+}
+
 template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG>
 cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   using Cfg = TcCfg<kElemBytes, kBlockN, kStages, kCG>;
@@ -801,47 +888,15 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
 
   constexpr int kTileM = kBlockM * kCG;
   constexpr int kLocalN = kBlockN / kCG;
-  p.m_blocks = (g.M + kTileM - 1) / kTileM;
-  p.n_blocks = (g.N + kBlockN - 1) / kBlockN;
-  p.k_blocks = (g.K + Cfg::kBlockK - 1) / Cfg::kBlockK;
-  p.kb_per_slice = 0;
-  if (g.reduce_batch && g.batch > 1) {
-    p.kb_per_slice = p.k_blocks;
-    p.k_blocks *= g.batch;
-  }
-  const int ab_format = g.in_dtype == kF32 ? 2 : (g.in_dtype == kBF16 ? 1 : 0);
-  p.idesc = ptx::make_idesc(ab_format, kAMN, kBMN, kTileM, kBlockN);
-  p.idesc_half = ptx::make_idesc(ab_format, kAMN, kBMN, kTileM, kBlockN / 2);
-
-  CUtensorMap tmA, tmB, tmBh;
-  bool ok;
-  constexpr bool kWide = (kElemBytes == 4);   // M/N-contiguous 32-bit tiles are swizzled in 32-byte units
-  if (!kAMN) ok = make_operand_map(&tmA, g.in_dtype, g.A, g.K, g.M, g.lda, g.batch, g.strideA, Cfg::kBlockK, kBlockM, false);
-  else       ok = make_operand_map(&tmA, g.in_dtype, g.A, g.M, g.K, g.lda, g.batch, g.strideA, Cfg::kBlockK, Cfg::kBlockK, kWide);
-  if (!ok) return cudaErrorInvalidValue;
-  if (!kBMN) ok = make_operand_map(&tmB, g.in_dtype, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, Cfg::kBlockK, kLocalN, false);
-  else       ok = make_operand_map(&tmB, g.in_dtype, g.B, g.N, g.K, g.ldb, g.batch, g.strideB, Cfg::kBlockK, Cfg::kBlockK, kWide);
-  if (!ok) return cudaErrorInvalidValue;
-
-  // Outputs as tensor maps for the epilogue's bulk stores (when base, pitch and batch stride allow).
-  CUtensorMap tmD = tmA, tmZ = tmA;
-  p.store_wide = (p.d_vec && g.epi.Z == nullptr && g.epi.d_dtype != kF32) ? 1 : 0;
-  if (p.d_vec && !make_output_map(&tmD, g.epi.d_dtype, g.epi.D, g.N, g.M, g.epi.ldd, p.batch, g.epi.strideD,
-                                  p.store_wide != 0)) {
-    p.d_vec = 0;
-    p.store_wide = 0;
-  }
-  if (p.z_vec && !make_output_map(&tmZ, g.epi.z_dtype, g.epi.Z, g.N, g.M, g.epi.ldz, p.batch, g.epi.strideZ, false))
-    p.z_vec = 0;
-  p.store_dbl = (g.epi.d_dtype != kF32 && (g.epi.Z == nullptr || g.epi.z_dtype != kF32)) ? 1 : 0;
+  ProblemMaps pm;
+  if (!prepare_problem<kElemBytes, kAMN, kBMN, kBlockN, kStages, kCG>(g, p, pm)) return cudaErrorInvalidValue;
+  const CUtensorMap &tmA = pm.tmA, &tmB = pm.tmB, &tmD = pm.tmD, &tmZ = pm.tmZ;
+  CUtensorMap tmBh;
 
   const long long tiles = static_cast<long long>(p.batch) * p.m_blocks * p.n_blocks;
   const long long units = sm_budget() / kCG > 0 ? sm_budget() / kCG : 1;   // one CTA (or CTA pair) per SM (pair of SMs)
 
   // Split-K: a problem whose tiles fill at most half of the machine is cut along the reduction as well.
-  p.main_tiles = static_cast<int>(tiles);
-  p.tail_tiles = 0;
-  p.split = 1;
   const long long rem = tiles % units;
   static const bool split_off = [] { const char* e = getenv("GE2B_SPLITK"); return e && atoi(e) == 0; }();
   // Only problems smaller than one wave are split: with several waves the measured gain of splitting just the last
@@ -894,7 +949,7 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (p.split > 1 && !narrow_tail) {
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel_split, tmA, tmB, tmBh, tmD, tmZ, p);
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel_split, tmA, tmB, tmBh, tmD, tmZ, p, no_second_problem());
     if (e != cudaSuccess || p.fin_in_kernel) return e;
     const int quads = kBlockN / 4, rows_per_pass = 256 / quads;
     int gy = kTileM / rows_per_pass;                    // one pass per block when the grid is small ...
@@ -902,7 +957,45 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
     splitk_finalize_kernel<<<dim3(p.tail_tiles, gy), 256, 0, s>>>(p, kTileM, kBlockN);
     return cudaGetLastError();
   }
-  return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmBh, tmD, tmZ, p);
+  return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmBh, tmD, tmZ, p, no_second_problem());
+}
+
+// Two independent problems in one persistent launch (CTA pairs, 256 x 256 tiles, no split-K, no narrow tail): the
+// tiles of the second follow those of the first in one list.  Both must be 16-bit or both 32-bit, and both must leave
+// through the same kind of store (checked by the caller through the filled TcParams).
+template <int kElemBytes, bool kAMN1, bool kBMN1, bool kAMN2, bool kBMN2>
+cudaError_t launch_dual_cfg(const GemmProblem& g1, TcParams& p1, const GemmProblem& g2, TcParams& p2, cudaStream_t s) {
+  constexpr int kBlockN = 256, kStages = 6, kCG = 2;
+  using Cfg = TcCfg<kElemBytes, kBlockN, kStages, kCG>;
+  auto kernel = gemm_tc_kernel<kElemBytes, kAMN1, kBMN1, kBlockN, kStages, kCG, false, true, kAMN2, kBMN2>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [&] {
+    attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  ProblemMaps m1, m2;
+  if (!prepare_problem<kElemBytes, kAMN1, kBMN1, kBlockN, kStages, kCG>(g1, p1, m1)) return cudaErrorInvalidValue;
+  if (!prepare_problem<kElemBytes, kAMN2, kBMN2, kBlockN, kStages, kCG>(g2, p2, m2)) return cudaErrorInvalidValue;
+  if (p1.store_wide != p2.store_wide || p1.store_dbl != p2.store_dbl || g2.epi.Z != nullptr) return cudaErrorNotSupported;
+  DualParams d2;
+  d2.tmA = m2.tmA; d2.tmB = m2.tmB; d2.tmD = m2.tmD;
+  d2.p = p2;
+  const long long items = static_cast<long long>(p1.main_tiles) + p2.main_tiles;
+  const long long units = sm_budget() / kCG > 0 ? sm_budget() / kCG : 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>((items < units ? items : units) * kCG), 1, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, m1.tmA, m1.tmB, m1.tmB, m1.tmD, m1.tmZ, p1, d2);
 }
 
 struct TileChoice { int block_n, cta_group; };
@@ -920,6 +1013,10 @@ cudaError_t launch_bn(const GemmProblem& g, TcParams& p, TileChoice t, cudaStrea
 GE2B_TC_DECLARE(2, false, false) GE2B_TC_DECLARE(2, false, true) GE2B_TC_DECLARE(2, true, false) GE2B_TC_DECLARE(2, true, true)
 GE2B_TC_DECLARE(4, false, false) GE2B_TC_DECLARE(4, false, true) GE2B_TC_DECLARE(4, true, false) GE2B_TC_DECLARE(4, true, true)
 #undef GE2B_TC_DECLARE
+extern template cudaError_t launch_dual_cfg<2, false, false, true, true>(const GemmProblem&, TcParams&, const GemmProblem&,
+                                                                          TcParams&, cudaStream_t);
+extern template cudaError_t launch_dual_cfg<4, false, false, true, true>(const GemmProblem&, TcParams&, const GemmProblem&,
+                                                                          TcParams&, cudaStream_t);
 
 }  // namespace tc
 }  // namespace ge2b

@@ -449,3 +449,49 @@ def test_narrow_tail_batched(pkg, lib, oracle):
     torch.cuda.synchronize()
     S64 = 0.125 * np.einsum("bld,bmd->blm", Q.astype(np.float64), Kx.astype(np.float64))
     assert oracle.rel_fro(host(S), S64) <= FRO_TOL
+
+
+# --------------------------------------------------------------------------- dX and dW in one launch
+@pytest.mark.parametrize("dtype,math", [(torch.bfloat16, "fp32"), (torch.float32, "tf32")])
+@pytest.mark.parametrize("shape", [(4096, 4096, 4096, 1), (2304, 2304, 2304, 1), (2300, 2056, 2200, 1), (2048, 1536, 2560, 0),
+                                   (1100, 1032, 1416, 0)])
+def test_backward_pair_in_one_launch(pkg, lib, oracle, dtype, math, shape):
+    """When both gradients are wanted and their combined tile list fills the machine better than the two lists do
+    one after the other, dX = gZ.W^T and dW = X^T.gZ run as ONE persistent launch (two problems with different
+    operand orders in one tile list).  The launch counter tells which form ran; results are checked on sampled rows
+    against float64 either way."""
+    M, K, N, expect_dual = shape
+    rng = np.random.default_rng(21)
+    X = rng.standard_normal((M, K), dtype=np.float32)
+    W = (rng.standard_normal((K, N), dtype=np.float32) / np.sqrt(K)).astype(np.float32)
+    dY = rng.standard_normal((M, N), dtype=np.float32)
+    Zh = rng.standard_normal((M, N), dtype=np.float32)
+    if dtype == torch.bfloat16:
+        X, W, dY, Zh = (oracle.bf16_round(a) for a in (X, W, dY, Zh))
+    tX, tW, tdY, tZ = dev(X, dtype), dev(W, dtype), dev(dY, dtype), dev(Zh, dtype)
+    work = torch.empty_like(tdY)
+    gA, gB, gb = torch.empty_like(tX), torch.empty_like(tW), torch.empty(N, device="cuda")
+    kw = dict(act="gelu", gA_out=gA, gB_out=gB, gBias_out=gb, work_dZ=work, math=math)
+    pkg.ops_gemm.backward_into(tX, tW, tdY, tZ, **kw)           # warm (first-use setup)
+    l0 = lib.ge2b_launches_total()
+    pkg.ops_gemm.backward_into(tX, tW, tdY, tZ, **kw)
+    launches = lib.ge2b_launches_total() - l0
+    torch.cuda.synchronize()
+    units = lib.ge2b_sm_count() // 2
+    tiles = lambda r, c: -(-r // 256) * -(-c // 256)              # noqa: E731
+    waves = lambda t: -(-t // units)                              # noqa: E731
+    dual = (tiles(M, K) + tiles(K, N) >= units and
+            waves(tiles(M, K) + tiles(K, N)) < waves(tiles(M, K)) + waves(tiles(K, N)))
+    assert dual == bool(expect_dual) or units != 74
+    assert launches == (2 if dual else 3)                         # prologue + one or two GEMM launches
+    gZ = dY.astype(np.float64) * oracle.act_deriv_f64("gelu", Zh.astype(np.float64))
+    gZ = host(work).astype(np.float64) if dtype == torch.bfloat16 else gZ
+    rows = np.sort(rng.choice(M, min(M, 64), replace=False))
+    cols = np.sort(rng.choice(K, min(K, 64), replace=False))
+    assert oracle.rel_fro(host(gA[rows]), gZ[rows] @ W.astype(np.float64).T) <= FRO_TOL
+    assert oracle.rel_fro(host(gB[cols]), X[:, cols].astype(np.float64).T @ gZ) <= FRO_TOL
+    # the same call twice gives the same bits
+    gA2, gB2 = gA.clone(), gB.clone()
+    pkg.ops_gemm.backward_into(tX, tW, tdY, tZ, **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(gA, gA2) and torch.equal(gB, gB2)
