@@ -164,6 +164,86 @@ bwd_prologue_kernel(const ProParams pp) {
   }
 }
 
+// Fast form for the common call: gY, Z and gZ all 16-bit of one type, every row 16-byte aligned, N a multiple of
+// 8, no gC, bias gradient per column or none.  Same arithmetic as the general kernel (fp32 derivative, fp32 column
+// sums taken before gZ is rounded), but the dtype is a template parameter, a thread's 8 rows x 8 columns are loaded
+// four rows at a time before any of them is used (8 independent 16-byte loads in flight per thread), and all index
+// arithmetic is hoisted out of the row loop.
+template <int ACT, bool kBf16>
+__global__ void __launch_bounds__(kTX * kTY)
+bwd_prologue_fast_kernel(const ProParams pp) {
+  const BwdPrologueArgs& a = pp.a;
+  __shared__ float red[kTY][kTileCols + 1];
+  const int col0 = blockIdx.x * kTileCols + threadIdx.x * kColsPerThread;
+  const int row0 = blockIdx.y * kTileRows + threadIdx.y;
+  const bool col_ok = col0 < a.N;
+  const bool want_bias = a.gBias != nullptr;
+
+  float colsum[kColsPerThread];
+#pragma unroll
+  for (int j = 0; j < kColsPerThread; ++j) colsum[j] = 0.f;
+
+  if (col_ok) {
+    const unsigned short* gy_p = static_cast<const unsigned short*>(a.gY) + static_cast<long long>(row0) * a.ldgY + col0;
+    const unsigned short* z_p = static_cast<const unsigned short*>(a.Z) + static_cast<long long>(row0) * a.ldZ + col0;
+    unsigned short* gz_p = static_cast<unsigned short*>(a.gZ) + static_cast<long long>(row0) * a.ldgZ + col0;
+    const long long gy_step = static_cast<long long>(kTY) * a.ldgY, z_step = static_cast<long long>(kTY) * a.ldZ,
+                    gz_step = static_cast<long long>(kTY) * a.ldgZ;
+    constexpr int kBatch = 4;
+#pragma unroll
+    for (int r0 = 0; r0 < kTileRows / kTY; r0 += kBatch) {
+      uint4 gy[kBatch], z[kBatch];
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        const bool ok = row0 + (r0 + i) * kTY < a.M;
+        gy[i] = ok ? __ldg(reinterpret_cast<const uint4*>(gy_p + (r0 + i) * gy_step)) : make_uint4(0, 0, 0, 0);
+        z[i]  = ok ? __ldg(reinterpret_cast<const uint4*>(z_p + (r0 + i) * z_step)) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < kBatch; ++i) {
+        const unsigned gw[4] = {gy[i].x, gy[i].y, gy[i].z, gy[i].w};
+        const unsigned zw[4] = {z[i].x, z[i].y, z[i].z, z[i].w};
+        unsigned ow[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          float g0, g1, z0, z1;
+          if constexpr (kBf16) {
+            g0 = __uint_as_float(gw[t] << 16); g1 = __uint_as_float(gw[t] & 0xffff0000u);
+            z0 = __uint_as_float(zw[t] << 16); z1 = __uint_as_float(zw[t] & 0xffff0000u);
+          } else {
+            const __half2 gh = *reinterpret_cast<const __half2*>(&gw[t]);
+            const __half2 zh = *reinterpret_cast<const __half2*>(&zw[t]);
+            g0 = __low2float(gh); g1 = __high2float(gh); z0 = __low2float(zh); z1 = __high2float(zh);
+          }
+          const float r0v = g0 * act_bwd<ACT, true>(z0, a.leaky);
+          const float r1v = g1 * act_bwd<ACT, true>(z1, a.leaky);
+          colsum[2 * t] += r0v;          // rows past M were loaded as zeros: they add nothing
+          colsum[2 * t + 1] += r1v;
+          if constexpr (kBf16) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(r0v, r1v);
+            ow[t] = *reinterpret_cast<const unsigned*>(&h);
+          } else {
+            const __half2 h = __floats2half2_rn(r0v, r1v);
+            ow[t] = *reinterpret_cast<const unsigned*>(&h);
+          }
+        }
+        if (row0 + (r0 + i) * kTY < a.M)
+          *reinterpret_cast<uint4*>(gz_p + (r0 + i) * gz_step) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      }
+    }
+  }
+  if (!want_bias) return;
+#pragma unroll
+  for (int j = 0; j < kColsPerThread; ++j) red[threadIdx.y][threadIdx.x * kColsPerThread + j] = colsum[j];
+  __syncthreads();
+  const int c = threadIdx.y * kTX + threadIdx.x;     // 0..255: one column each
+  float s = 0.f;
+#pragma unroll
+  for (int y = 0; y < kTY; ++y) s += red[y][c];
+  const int gc = blockIdx.x * kTileCols + c;
+  if (gc < a.N) atomicAdd(a.gBias + gc, s);
+}
+
 bool vec_ok(const void* p, long long ld, int dt) {
   if (!p) return false;
   return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && (ld * dtype_bytes(dt)) % 16 == 0;
@@ -181,6 +261,28 @@ cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s) {
   pp.gc_vec = vec_ok(a.gC, a.ldgC, a.gc_dtype);
   dim3 block(kTX, kTY), grid((a.N + kTileCols - 1) / kTileCols, (a.M + kTileRows - 1) / kTileRows);
   // gZ stored in 16 bits: the exp-based derivative forms are accurate enough (see epilogue_math.cuh)
+  // the common 16-bit call takes the specialised kernel
+  const bool same16 = a.gy_dtype != kF32 && a.gy_dtype == a.z_dtype && a.gy_dtype == a.gz_dtype;
+  const bool col_bias_or_none = a.gBias == nullptr || a.bias_kind == kBiasPerN || a.bias_kind == kBiasNone;
+  if (same16 && pp.gy_vec && pp.z_vec && pp.gz_vec && a.N % 8 == 0 && a.gC == nullptr && col_bias_or_none) {
+    if (a.gBias != nullptr && a.bias_kind == kBiasNone) pp.a.gBias = nullptr;
+    const bool bf = a.gy_dtype == kBF16;
+#define GE2B_LAUNCH_FAST(ACT_)                                                                \
+    do {                                                                                      \
+      if (bf) bwd_prologue_fast_kernel<ACT_, true><<<grid, block, 0, s>>>(pp);                \
+      else    bwd_prologue_fast_kernel<ACT_, false><<<grid, block, 0, s>>>(pp);               \
+    } while (0)
+    switch (a.act) {
+      case kActReLU:    GE2B_LAUNCH_FAST(kActReLU); break;
+      case kActLeaky:   GE2B_LAUNCH_FAST(kActLeaky); break;
+      case kActGELU:    GE2B_LAUNCH_FAST(kActGELU); break;
+      case kActSigmoid: GE2B_LAUNCH_FAST(kActSigmoid); break;
+      case kActTanh:    GE2B_LAUNCH_FAST(kActTanh); break;
+      default:          GE2B_LAUNCH_FAST(kActNone); break;
+    }
+#undef GE2B_LAUNCH_FAST
+    return cudaGetLastError();
+  }
   const bool fast = a.gz_dtype != kF32;
   const bool rowsum = a.gBias != nullptr && (a.bias_kind == kBiasPerM || a.bias_kind == kBiasScalar);
 #define GE2B_LAUNCH_PRO(ACT_)                                                                   \
