@@ -16,6 +16,7 @@
 // bit-identical) unless math = tensor asks for TF32; bf16 / f16 tensors run on the tcgen05 kernel.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 
 #include "../../include/ge2_b200.h"
@@ -32,24 +33,25 @@ struct ConvGeom {
   int Ho, Wo, HWo, HWp, K;      // HWp: HWo rounded up so that every Col / gZ row starts on a 32-byte boundary
 };
 
-constexpr int kColThreads = 128;
+constexpr int kColRows = 4;      // (k, n) rows per block: one warp each
 
 // Col[k][n][hw] = X[n][c][ho*sh - ph + kh*dh][wo*sw - pw + kw*dw] (zero outside the image and in the padding columns
-// hw >= HWo).  One block per (k, n) row; a thread gathers 16 bytes' worth of consecutive output positions and
-// writes them with one store.  T is the element's storage type: values are copied bit for bit.
+// hw >= HWo).  One warp per (k, n) row; a lane gathers 16 bytes' worth of consecutive output positions and writes
+// them with one store.  T is the element's storage type: values are copied bit for bit.
 template <typename T>
-__global__ void __launch_bounds__(kColThreads)
-im2col_batched_kernel(const T* __restrict__ X, T* __restrict__ Col, const ConvGeom g) {
+__global__ void __launch_bounds__(32 * kColRows)
+im2col_batched_kernel(const T* __restrict__ X, T* __restrict__ Col, const ConvGeom g, const long long rows) {
   constexpr int V = 16 / sizeof(T);
-  const int kn = blockIdx.x;
-  const int k = kn / g.N, n = kn - k * g.N;
+  const long long kn = static_cast<long long>(blockIdx.x) * kColRows + threadIdx.y;
+  if (kn >= rows) return;
+  const int k = static_cast<int>(kn / g.N), n = static_cast<int>(kn - static_cast<long long>(k) * g.N);
   const int kw = k % g.Kw;
   const int t = k / g.Kw;
   const int kh = t % g.Kh, c = t / g.Kh;
   const T* __restrict__ xc = X + (static_cast<long long>(n) * g.Cin + c) * g.H * g.W;
-  T* __restrict__ col = Col + static_cast<long long>(kn) * g.HWp;
+  T* __restrict__ col = Col + kn * g.HWp;
   const int h_off = kh * g.dh - g.ph, w_off = kw * g.dw - g.pw;
-  for (int v = threadIdx.x; v < g.HWp / V; v += kColThreads) {
+  for (int v = threadIdx.x; v < g.HWp / V; v += 32) {
     const int hw0 = v * V;
     int ho = hw0 / g.Wo, wo = hw0 - ho * g.Wo;
     alignas(16) T vals[V];
@@ -100,6 +102,17 @@ col2im_batched_kernel(const void* __restrict__ dCol, void* __restrict__ dX, cons
   }
 }
 
+// out[i] = sum_n part[n][i] in image order (the exact-fp32 route of the weight gradient: per-image products first,
+// then this fixed-order sum).
+__global__ void sum_images_kernel(const float* __restrict__ part, float* __restrict__ out, long long elems, int n_img,
+                                  int first) {
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < elems; i += gridDim.x * 256ll) {
+    float acc = first ? 0.f : out[i];
+    for (int n = 0; n < n_img; ++n) acc += part[static_cast<long long>(n) * elems + i];
+    out[i] = acc;
+  }
+}
+
 // dB[co] = sum_n rows[n * Cout + co]  (rows: per-(image, channel) sums of gZ left by the prologue kernel)
 __global__ void fold_db_kernel(const float* __restrict__ rows, float* __restrict__ dB, int N, int Cout) {
   const int co = blockIdx.x * blockDim.x + threadIdx.x;
@@ -137,13 +150,15 @@ bool pointwise(const ConvGeom& g, int esz) {
 
 cudaError_t launch_im2col(const void* X, void* Col, const ConvGeom& g, int dt, cudaStream_t s) {
   const long long rows = static_cast<long long>(g.K) * g.N;
-  if (rows > 0x7fffffffll) return cudaErrorInvalidValue;
+  const long long blocks = (rows + kColRows - 1) / kColRows;
+  if (blocks > 0x7fffffffll) return cudaErrorInvalidValue;
+  const dim3 block(32, kColRows);
   if (dtype_bytes(dt) == 4)
-    im2col_batched_kernel<float><<<static_cast<unsigned>(rows), kColThreads, 0, s>>>(
-        static_cast<const float*>(X), static_cast<float*>(Col), g);
+    im2col_batched_kernel<float><<<static_cast<unsigned>(blocks), block, 0, s>>>(
+        static_cast<const float*>(X), static_cast<float*>(Col), g, rows);
   else
-    im2col_batched_kernel<unsigned short><<<static_cast<unsigned>(rows), kColThreads, 0, s>>>(
-        static_cast<const unsigned short*>(X), static_cast<unsigned short*>(Col), g);
+    im2col_batched_kernel<unsigned short><<<static_cast<unsigned>(blocks), block, 0, s>>>(
+        static_cast<const unsigned short*>(X), static_cast<unsigned short*>(Col), g, rows);
   return cudaGetLastError();
 }
 
@@ -167,6 +182,28 @@ struct AsyncBuf {
   AsyncBuf& operator=(const AsyncBuf&) = delete;
 };
 
+// The OIHW weight is the row-major Cout x K matrix of the GEMMs.  When its rows do not start on 16-byte boundaries
+// (K * element size not a multiple of 16, e.g. a 7x7 stem on 3 channels) the tensor-core path could not address it:
+// a copy with padded pitch (a few hundred KB at most) keeps those layers on it.  Returns the matrix to use and its
+// pitch in elements.
+const void* aligned_weight(AsyncBuf& buf, const void* W, const ConvGeom& g, int dtype, int math, long long& ld,
+                           cudaStream_t s, bool& failed) {
+  const int esz = dtype_bytes(dtype);
+  ld = g.K;
+  failed = false;
+  const bool tensor_path = dtype != kF32 || math == 1;
+  if (!tensor_path || (static_cast<long long>(g.K) * esz) % 16 == 0) return W;
+  const long long kp = (g.K + 7) / 8 * 8;
+  if (!buf.alloc(static_cast<size_t>(g.Cout) * kp * esz) ||
+      cudaMemcpy2DAsync(buf.p, kp * esz, W, static_cast<size_t>(g.K) * esz, static_cast<size_t>(g.K) * esz, g.Cout,
+                        cudaMemcpyDeviceToDevice, s) != cudaSuccess) {
+    failed = true;
+    return W;
+  }
+  ld = kp;
+  return buf.p;
+}
+
 }  // namespace
 
 int conv2d_forward(const ge2b_conv2d_params_t& p, const void* X, const void* W, const float* bias, void* Y, void* Z,
@@ -186,10 +223,15 @@ int conv2d_forward(const ge2b_conv2d_params_t& p, const void* X, const void* W, 
     if (launch_im2col(X, col.p, g, p.dtype, s) != cudaSuccess) return kCudaError;
     B = col.p; ldb = static_cast<long long>(g.N) * g.HWp; strideB = g.HWp;
   }
+  AsyncBuf wpad(s);
+  long long ldw = g.K;
+  bool failed = false;
+  const void* Wm = aligned_weight(wpad, W, g, p.dtype, p.math, ldw, s, failed);
+  if (failed) return kCudaError;
   DenseForward f;
   f.M = g.Cout; f.N = g.HWo; f.K = g.K; f.batch = g.N;
   f.dtype = p.dtype; f.z_dtype = zdt; f.math = p.math;
-  f.A = W; f.lda = g.K; f.strideA = 0;                       // the weight is shared by every image
+  f.A = Wm; f.lda = ldw; f.strideA = 0;                      // the weight is shared by every image
   f.B = B; f.ldb = ldb; f.strideB = strideB;
   f.D = Y; f.ldd = g.HWo; f.strideD = static_cast<long long>(g.Cout) * g.HWo;
   f.Z = Z; f.ldz = g.HWo; f.strideZ = f.strideD;
@@ -254,7 +296,35 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
     q.epi.alpha = 1.f; q.epi.act = kActNone; q.epi.bias_kind = kBiasNone;
     int rc = run_gemm_problem(q, s);
     if (rc == kUnimplemented) {
-      // exact-fp32 route: one launch per image, accumulating into dW (beta = 1 from the second image on)
+      // Route without the batch-reducing kernel (exact fp32, or a pitch TMA cannot address): the images' products
+      // as ONE batched launch into a scratch [group][Cout][K], then a sum over the group in image order; groups keep
+      // the scratch under 256 MiB.  fp32 tensors only (a 16-bit scratch would round the partial sums).
+      if (p.dtype == kF32) {
+        const long long elems = static_cast<long long>(g.Cout) * g.K;
+        long long group = (256ll << 20) / (elems * 4);
+        if (group < 1) group = 1;
+        if (group > g.N) group = g.N;
+        AsyncBuf part(s);
+        if (!part.alloc(static_cast<size_t>(group) * elems * 4)) return kCudaError;
+        for (int n0 = 0; n0 < g.N; n0 += static_cast<int>(group)) {
+          const int cnt = static_cast<int>(std::min<long long>(group, g.N - n0));
+          DenseForward f;
+          f.M = g.Cout; f.N = g.K; f.K = g.HWo; f.batch = cnt;
+          f.dtype = p.dtype; f.z_dtype = p.dtype; f.math = p.math;
+          f.trans_b = true;
+          f.A = static_cast<const uint8_t*>(gz.p) + static_cast<size_t>(n0) * gz_stride * esz; f.lda = g.HWp; f.strideA = gz_stride;
+          f.B = static_cast<const uint8_t*>(B) + static_cast<size_t>(n0) * strideB * esz; f.ldb = ldb; f.strideB = strideB;
+          f.D = part.p; f.ldd = g.K; f.strideD = elems;
+          rc = dense_forward(f, s);
+          if (rc != kOk) return rc;
+          long long blocks = (elems + 255) / 256;
+          if (blocks > 4096) blocks = 4096;
+          sum_images_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const float*>(part.p),
+                                                                        static_cast<float*>(dW), elems, cnt, n0 == 0);
+          if (cudaGetLastError() != cudaSuccess) return kCudaError;
+        }
+      } else {
+      // 16-bit tensors whose pitch TMA cannot address: one launch per image, accumulating into dW
       for (int n = 0; n < g.N; ++n) {
         DenseForward f;
         f.M = g.Cout; f.N = g.K; f.K = g.HWo; f.batch = 1;
@@ -267,6 +337,7 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
         rc = dense_forward(f, s);
         if (rc != kOk) return rc;
       }
+      }
     } else if (rc != kOk) {
       return rc;
     }
@@ -278,7 +349,12 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
     f.M = g.K; f.N = g.HWo; f.K = g.Cout; f.batch = g.N;
     f.dtype = p.dtype; f.z_dtype = p.dtype; f.math = p.math;
     f.trans_a = true;                                          // W is stored Cout x K: reduction index outermost
-    f.A = W; f.lda = g.K; f.strideA = 0;
+    AsyncBuf wpad(s);
+    long long ldw = g.K;
+    bool failed = false;
+    f.A = aligned_weight(wpad, W, g, p.dtype, p.math, ldw, s, failed);
+    if (failed) return kCudaError;
+    f.lda = ldw; f.strideA = 0;
     f.B = gz.p; f.ldb = g.HWp; f.strideB = gz_stride;
     if (pw) { f.D = dX; f.ldd = g.HWo; f.strideD = static_cast<long long>(g.Cin) * g.HWo; }
     else    { f.D = col.p; f.ldd = static_cast<long long>(g.N) * g.HWp; f.strideD = g.HWp; }
