@@ -218,6 +218,27 @@ __device__ __forceinline__ void store_frag_tma(EpiStage& st, bool dbl, const CUt
   if (dbl) st.slot ^= 1;
 }
 
+// Store for outputs whose base or pitch is not 16-byte aligned (no TMA store possible): the fragment goes through the
+// warp's staging buffer as fp32, element (r, j) at word r * 32 + (j ^ r) (conflict-free both ways), and leaves one row per instruction
+// with consecutive lanes on consecutive columns, so that each store covers one contiguous run of a row instead of
+// 32 different rows.  Waits for any bulk store that may still be reading the buffer first.
+__device__ __forceinline__ void store_frag_rows(EpiStage& st, void* base, long long off0, long long ld, int dt,
+                                                const float (&v)[32], int row0, int col0, int M, int N, int lane) {
+  if (lane == 0) ptx::bulk_wait_group_read<0>();
+  __syncwarp();
+  float* buf = reinterpret_cast<float*>(st.buf);
+#pragma unroll
+  for (int j = 0; j < 32; ++j) buf[lane * 32 + (j ^ lane)] = v[j];
+  __syncwarp();
+  const bool col_ok = col0 + lane < N;
+  const int rows = min(32, M - row0);
+  for (int r = 0; r < rows; ++r) {
+    const float x = buf[r * 32 + (lane ^ r)];
+    if (col_ok) store_from_f32(base, off0 + static_cast<long long>(row0 + r) * ld + col0 + lane, dt, x);
+  }
+  __syncwarp();
+}
+
 // 16-bit, single output: fragments of two neighbouring 32-column chunks share one buffer of 128-byte rows
 // (chunk index XOR row & 7) and leave together, halving the number of bulk stores, proxy fences and waits.
 // `second` is the odd chunk of the pair, `flush` says that no further chunk follows (a ragged last pair: the
@@ -310,9 +331,9 @@ __device__ __forceinline__ void epilogue_frag(const TcParams& p, const CUtensorM
   if (e.Z != nullptr) {
     if (p.z_vec)
       store_frag_tma(stage, p.store_dbl != 0, tmZ, e.z_dtype, v, row - lane, col0, b, lane);
-    else if (row_ok)
-      store_row_frag(e.Z, static_cast<long long>(b) * e.strideZ + static_cast<long long>(row) * e.ldz + col0,
-                     e.z_dtype, v, ncols, false);
+    else
+      store_frag_rows(stage, e.Z, static_cast<long long>(b) * e.strideZ, e.ldz, e.z_dtype, v, row - lane, col0, p.M, p.N,
+                      lane);
   }
   const bool fast = e.d_dtype != kF32;       // the result is rounded to 16 bits: exp-based tanh / sigmoid suffice
   switch (e.act) {
@@ -327,9 +348,9 @@ __device__ __forceinline__ void epilogue_frag(const TcParams& p, const CUtensorM
     store_frag_tma_wide(stage, tmD, e.d_dtype, v, row - lane, col0, b, lane, second, last);
   else if (p.d_vec)
     store_frag_tma(stage, p.store_dbl != 0, tmD, e.d_dtype, v, row - lane, col0, b, lane);
-  else if (row_ok)
-    store_row_frag(e.D, static_cast<long long>(b) * e.strideD + static_cast<long long>(row) * e.ldd + col0, e.d_dtype,
-                   v, ncols, false);
+  else
+    store_frag_rows(stage, e.D, static_cast<long long>(b) * e.strideD, e.ldd, e.d_dtype, v, row - lane, col0, p.M, p.N,
+                    lane);
 }
 
 // Persistent tile order: within a batch slice, groups of kGroupM row-blocks sweep all column-blocks,
