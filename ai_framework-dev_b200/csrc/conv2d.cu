@@ -72,30 +72,48 @@ im2col_batched_kernel(const T* __restrict__ X, T* __restrict__ Col, const ConvGe
 // dX[n][c][h][w] = sum over the (kh, kw) taps whose output position exists of dCol[(c,kh,kw)][n][ho*Wo + wo];
 // fp32 accumulation in tap order (kh outer, kw inner), one thread per input pixel, plain store (no atomics).
 // grid.x = (n, c) plane, grid.y covers the plane's pixels.  kUnit: stride 1 in both directions (no divisions per tap).
-template <bool kUnit>
+// KS: compile-time square kernel size (0: taken from the geometry).  With unit stride every tap's load is issued
+// whether or not the tap exists (from a clamped address, its value then dropped), so that the loads of one pixel do
+// not wait for one another: with a branch around each load the kernel ran at the latency of Kh*Kw dependent loads.
+template <bool kUnit, int KS>
 __global__ void __launch_bounds__(256)
 col2im_batched_kernel(const void* __restrict__ dCol, void* __restrict__ dX, const ConvGeom g, const int dt) {
   const int plane = blockIdx.x;
   const int n = plane / g.Cin, c = plane - n * g.Cin;
   const int HW = g.H * g.W;
+  const int Kh = KS ? KS : g.Kh, Kw = KS ? KS : g.Kw;
   const long long out_base = static_cast<long long>(plane) * HW;
+  const long long row_stride = static_cast<long long>(g.N) * g.HWp;          // from tap k to tap k + 1
+  const long long tap0 = (static_cast<long long>(c) * Kh * Kw * g.N + n) * g.HWp;
   for (int pix = blockIdx.y * 256 + threadIdx.x; pix < HW; pix += gridDim.y * 256) {
     const int h = pix / g.W, w = pix - h * g.W;
     float acc = 0.f;
-    for (int kh = 0; kh < g.Kh; ++kh) {
+#pragma unroll
+    for (int kh = 0; kh < Kh; ++kh) {
       const int hn = h + g.ph - kh * g.dh;
-      int ho;
-      if constexpr (kUnit) { ho = hn; }
-      else { if (hn < 0 || hn % g.sh) continue; ho = hn / g.sh; }
-      if (static_cast<unsigned>(ho) >= static_cast<unsigned>(g.Ho)) continue;
-      for (int kw = 0; kw < g.Kw; ++kw) {
-        const int wn = w + g.pw - kw * g.dw;
-        int wo;
-        if constexpr (kUnit) { wo = wn; }
-        else { if (wn < 0 || wn % g.sw) continue; wo = wn / g.sw; }
-        if (static_cast<unsigned>(wo) >= static_cast<unsigned>(g.Wo)) continue;
-        const int k = (c * g.Kh + kh) * g.Kw + kw;
-        acc += load_as_f32(dCol, (static_cast<long long>(k) * g.N + n) * g.HWp + ho * g.Wo + wo, dt);
+      if constexpr (kUnit) {
+        const int ho = hn;
+        const bool hok = static_cast<unsigned>(ho) < static_cast<unsigned>(g.Ho);
+#pragma unroll 4
+        for (int kw = 0; kw < Kw; ++kw) {
+          const int wo = w + g.pw - kw * g.dw;
+          const bool ok = hok && static_cast<unsigned>(wo) < static_cast<unsigned>(g.Wo);
+          const long long idx = ok ? tap0 + (kh * Kw + kw) * row_stride + ho * g.Wo + wo : tap0;
+          const float x = load_as_f32(dCol, idx, dt);
+          acc += ok ? x : 0.f;
+        }
+      } else {
+        // strided: most taps have no output position for a given pixel (1 in sh*sw does), so they are skipped
+        if (hn < 0 || hn % g.sh) continue;
+        const int ho = hn / g.sh;
+        if (ho >= g.Ho) continue;
+        for (int kw = 0; kw < Kw; ++kw) {
+          const int wn = w + g.pw - kw * g.dw;
+          if (wn < 0 || wn % g.sw) continue;
+          const int wo = wn / g.sw;
+          if (wo >= g.Wo) continue;
+          acc += load_as_f32(dCol, tap0 + (kh * Kw + kw) * row_stride + ho * g.Wo + wo, dt);
+        }
       }
     }
     store_from_f32(dX, out_base + pix, dt, acc);
@@ -366,8 +384,20 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
       int gy = (g.H * g.W + 255) / 256;
       if (gy > 4096) gy = 4096;
       const dim3 grid(static_cast<unsigned>(planes), gy);
-      if (g.sh == 1 && g.sw == 1) col2im_batched_kernel<true><<<grid, 256, 0, s>>>(col.p, dX, g, p.dtype);
-      else                        col2im_batched_kernel<false><<<grid, 256, 0, s>>>(col.p, dX, g, p.dtype);
+      const bool unit = g.sh == 1 && g.sw == 1;
+      const int ks = (g.Kh == g.Kw && (g.Kh == 3 || g.Kh == 5 || g.Kh == 7)) ? g.Kh : 0;
+#define GE2B_COL2IM(KS_)                                                                              \
+      do {                                                                                            \
+        if (unit) col2im_batched_kernel<true, KS_><<<grid, 256, 0, s>>>(col.p, dX, g, p.dtype);       \
+        else      col2im_batched_kernel<false, KS_><<<grid, 256, 0, s>>>(col.p, dX, g, p.dtype);      \
+      } while (0)
+      switch (ks) {
+        case 3:  GE2B_COL2IM(3); break;
+        case 5:  GE2B_COL2IM(5); break;
+        case 7:  GE2B_COL2IM(7); break;
+        default: GE2B_COL2IM(0); break;
+      }
+#undef GE2B_COL2IM
       if (cudaGetLastError() != cudaSuccess) return kCudaError;
     }
   }
