@@ -385,7 +385,8 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
       if (gy > 4096) gy = 4096;
       const dim3 grid(static_cast<unsigned>(planes), gy);
       const bool unit = g.sh == 1 && g.sw == 1;
-      const int ks = (g.Kh == g.Kw && (g.Kh == 3 || g.Kh == 5 || g.Kh == 7)) ? g.Kh : 0;
+      // compile-time kernel sizes pay off only in the unit-stride form (all taps unrolled, loads in flight together)
+      const int ks = (unit && g.Kh == g.Kw && (g.Kh == 3 || g.Kh == 5 || g.Kh == 7)) ? g.Kh : 0;
 #define GE2B_COL2IM(KS_)                                                                              \
       do {                                                                                            \
         if (unit) col2im_batched_kernel<true, KS_><<<grid, 256, 0, s>>>(col.p, dX, g, p.dtype);       \
