@@ -50,6 +50,7 @@ struct TcParams {
   EpilogueArgs epi;
   int d_vec, z_vec, c_vec, bias_vec;   // base, pitch and batch stride 16-byte aligned: D / Z leave through TMA stores,
                                        // C and bias are read with 16-byte loads
+  int plain;                           // no C, no bias, no Z, no activation: the epilogue only scales and stores
   int store_dbl;                       // every stored tensor is 16-bit: the staging buffer is used as two halves
   int store_wide;                      // D is the only output and 16-bit: two 32-column fragments leave as one
                                        // 64-column (128-byte rows) bulk store; tmD then has a 64 x 32 box
@@ -297,6 +298,17 @@ __device__ __forceinline__ void epilogue_frag(const TcParams& p, const CUtensorM
   if (e.alpha != 1.f) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] *= e.alpha;
+  }
+  if (p.plain) {
+    // nothing but the scaled product to store (dX, dW, the attention GEMMs): skip the rest of the epilogue's tests
+    if (p.store_wide)
+      store_frag_tma_wide(stage, tmD, e.d_dtype, v, row - lane, col0, b, lane, second, last);
+    else if (p.d_vec)
+      store_frag_tma(stage, p.store_dbl != 0, tmD, e.d_dtype, v, row - lane, col0, b, lane);
+    else
+      store_frag_rows(stage, e.D, static_cast<long long>(b) * e.strideD, e.ldd, e.d_dtype, v, row - lane, col0, p.M, p.N,
+                      lane);
+    return;
   }
   if (e.C != nullptr && e.beta != 0.f && row_ok) {
     float c[32];
@@ -882,6 +894,7 @@ bool prepare_problem(const GemmProblem& g, TcParams& p, ProblemMaps& m) {
   if (p.z_vec && !make_output_map(&m.tmZ, g.epi.z_dtype, g.epi.Z, g.N, g.M, g.epi.ldz, p.batch, g.epi.strideZ, false))
     p.z_vec = 0;
   p.store_dbl = (g.epi.d_dtype != kF32 && (g.epi.Z == nullptr || g.epi.z_dtype != kF32)) ? 1 : 0;
+  p.plain = (g.epi.C == nullptr && g.epi.bias == nullptr && g.epi.Z == nullptr && g.epi.act == kActNone) ? 1 : 0;
   p.main_tiles = static_cast<int>(static_cast<long long>(p.batch) * p.m_blocks * p.n_blocks);
   p.tail_tiles = 0;
   p.split = 1;
