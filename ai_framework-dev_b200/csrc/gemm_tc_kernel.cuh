@@ -100,50 +100,7 @@ struct TcCfg {
   static_assert(8 * (2 * kStages + 4) + 16 <= kBarBytes, "barrier block too small");
 };
 
-// ---- row-fragment stores: one thread owns `n` (<= 32) consecutive columns of one output row ----
-__device__ __forceinline__ void store_row_frag(void* base, long long off, int dt, const float (&v)[32], int n,
-                                               bool vec) {
-  if (dt == kF32) {
-    float* p = reinterpret_cast<float*>(base) + off;
-    if (vec && n == 32) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        reinterpret_cast<float4*>(p)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < n) p[j] = v[j];
-    }
-  } else {
-    unsigned short* p = reinterpret_cast<unsigned short*>(base) + off;
-    if (vec && n == 32) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t w[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float lo = v[8 * j + 2 * t], hi = v[8 * j + 2 * t + 1];
-          if (dt == kBF16) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-            w[t] = *reinterpret_cast<uint32_t*>(&h);
-          } else {
-            __half2 h = __floats2half2_rn(lo, hi);
-            w[t] = *reinterpret_cast<uint32_t*>(&h);
-          }
-        }
-        reinterpret_cast<uint4*>(p)[j] = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < n) {
-          if (dt == kBF16) p[j] = f32_to_bf16_bits(v[j]);
-          else             reinterpret_cast<__half*>(p)[j] = __float2half_rn(v[j]);
-        }
-    }
-  }
-}
-
+// ---- row-fragment load: one thread owns `n` (<= 32) consecutive columns of one row of C ----
 __device__ __forceinline__ void load_row_frag(const void* base, long long off, int dt, float (&v)[32], int n,
                                               bool vec) {
   if (dt == kF32) {

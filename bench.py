@@ -207,8 +207,9 @@ def run_ours(args):
     fwd_events = []
 
     # row blocks of dW whose all-reduce starts as each finishes; a single GPU has nothing to overlap and uses one
-    dw_chunks = max(1, int(os.environ.get("GE2B_BENCH_DW_CHUNKS", "2" if world > 1 else "1")))
-    rows_per_chunk = K // dw_chunks
+    # 0: no overlap - the backward runs as on one GPU (dX and dW in one launch) and the all-reduce follows it
+    dw_chunks = max(0, int(os.environ.get("GE2B_BENCH_DW_CHUNKS", "2" if world > 1 else "1")))
+    rows_per_chunk = K // max(1, dw_chunks)
 
     def step(timed):
         if timed:
@@ -226,10 +227,13 @@ def run_ours(args):
                 with torch.cuda.stream(comm):
                     dist.all_reduce(t)          # asynchronous on the device: ordered on the side stream
 
-        if world == 1:
+        if world == 1 or dw_chunks == 0:
             # the whole backward in one call: gZ = dY * gelu'(Z) with db, then dX and dW (one launch for both: their
             # tiles form one list, so only the combined list's last wave is partly filled)
             og.backward_into(X, W, dY, Z, act=ACT, with_bias=True, gA_out=dX, gB_out=dW, gBias_out=db, work_dZ=work)
+            if world > 1:
+                dist.all_reduce(dW)
+                dist.all_reduce(db)
             return
         # gZ = dY * gelu'(Z) and db in one pass; gZ stays in `work` for the two GEMMs
         og.backward_into(X, W, dY, Z, act=ACT, with_bias=True, gBias_out=db, work_dZ=work)
@@ -430,7 +434,9 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": dict(CONFIG, parallelism=f"dp{world} (rows of the batch; all-reduce of dW row blocks + db overlapped with backward GEMMs)"
+            "config": dict(CONFIG, parallelism=(f"dp{world} (rows of the batch; all-reduce of dW row blocks + db overlapped with backward GEMMs)"
+                                        if dw_chunks > 0 else
+                                        f"dp{world} (rows of the batch; dX and dW in one launch, all-reduce of dW + db after it)")
                            if world > 1 else "single GPU"),
             "clocks": clk.summary(),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
