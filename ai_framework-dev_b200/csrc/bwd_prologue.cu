@@ -21,6 +21,7 @@ constexpr int kColsPerThread = 8;
 constexpr int kTX = 32, kTY = 8;
 constexpr int kTileCols = kTX * kColsPerThread;   // 256
 constexpr int kTileRows = 64;
+constexpr int kFastRows = 32;   // rows per CTA of the specialised kernel: more, smaller CTAs fill the last wave better
 
 struct ProParams {
   BwdPrologueArgs a;
@@ -175,7 +176,7 @@ bwd_prologue_fast_kernel(const ProParams pp) {
   const BwdPrologueArgs& a = pp.a;
   __shared__ float red[kTY][kTileCols + 1];
   const int col0 = blockIdx.x * kTileCols + threadIdx.x * kColsPerThread;
-  const int row0 = blockIdx.y * kTileRows + threadIdx.y;
+  const int row0 = blockIdx.y * kFastRows + threadIdx.y;
   const bool col_ok = col0 < a.N;
   const bool want_bias = a.gBias != nullptr;
 
@@ -191,7 +192,7 @@ bwd_prologue_fast_kernel(const ProParams pp) {
                     gz_step = static_cast<long long>(kTY) * a.ldgZ;
     constexpr int kBatch = 4;
 #pragma unroll
-    for (int r0 = 0; r0 < kTileRows / kTY; r0 += kBatch) {
+    for (int r0 = 0; r0 < kFastRows / kTY; r0 += kBatch) {
       uint4 gy[kBatch], z[kBatch];
 #pragma unroll
       for (int i = 0; i < kBatch; ++i) {
@@ -267,10 +268,11 @@ cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s) {
   if (same16 && pp.gy_vec && pp.z_vec && pp.gz_vec && a.N % 8 == 0 && a.gC == nullptr && col_bias_or_none) {
     if (a.gBias != nullptr && a.bias_kind == kBiasNone) pp.a.gBias = nullptr;
     const bool bf = a.gy_dtype == kBF16;
+    const dim3 fgrid((a.N + kTileCols - 1) / kTileCols, (a.M + kFastRows - 1) / kFastRows);
 #define GE2B_LAUNCH_FAST(ACT_)                                                                \
     do {                                                                                      \
-      if (bf) bwd_prologue_fast_kernel<ACT_, true><<<grid, block, 0, s>>>(pp);                \
-      else    bwd_prologue_fast_kernel<ACT_, false><<<grid, block, 0, s>>>(pp);               \
+      if (bf) bwd_prologue_fast_kernel<ACT_, true><<<fgrid, block, 0, s>>>(pp);               \
+      else    bwd_prologue_fast_kernel<ACT_, false><<<fgrid, block, 0, s>>>(pp);              \
     } while (0)
     switch (a.act) {
       case kActReLU:    GE2B_LAUNCH_FAST(kActReLU); break;
