@@ -480,10 +480,12 @@ Status Conv2DCudaLaunch(const Tensor& X, const Tensor& W, const Tensor* B, Tenso
   if (W.desc.shape[1] != X.desc.shape[1]) return Status::ShapeMismatch;
   ge2b_conv2d_params_t p{};
   if (!fill_params(X, W, a, p)) return Status::Invalid;
-  int Ho = 0, Wo = 0;
-  const bool geom_ok = ge2b_conv2d_output_size(&p, &Ho, &Wo) == 0;
-  if (geom_ok && !shape_is(Y, p.N, p.Cout, Ho, Wo)) return Status::ShapeMismatch;
-  if (!geom_ok) return Status::Invalid;
+  if (a.stride_h <= 0 || a.stride_w <= 0) return Status::Invalid;
+  // output size and the order of the two checks as in conv2d/launcher.cu:137-146
+  const int Ho = (p.H + 2 * p.pad_h - p.dil_h * (p.Kh - 1) - 1) / p.stride_h + 1;
+  const int Wo = (p.W + 2 * p.pad_w - p.dil_w * (p.Kw - 1) - 1) / p.stride_w + 1;
+  if (!shape_is(Y, p.N, p.Cout, Ho, Wo)) return Status::ShapeMismatch;
+  if (Ho <= 0 || Wo <= 0 || ge2b_conv2d_output_size(&p, nullptr, nullptr) != 0) return Status::Invalid;
   const bool want_z = a.save_z && Z_saved != nullptr;
   if (want_z) {
     const shim::DType zdt = Z_saved->desc.dtype;
@@ -511,9 +513,11 @@ Status Conv2DCudaBackwardLaunch(const Tensor& X, const Tensor& W, const Tensor& 
   ge2b_conv2d_params_t p{};
   if (!fill_params(X, W, a, p)) return Status::Invalid;
   p.z_dtype = static_cast<int>(zdt);
-  int Ho = 0, Wo = 0;
-  const bool geom_ok = ge2b_conv2d_output_size(&p, &Ho, &Wo) == 0;
-  if (geom_ok && (!shape_is(dY, p.N, p.Cout, Ho, Wo) || !shape_is(Z, p.N, p.Cout, Ho, Wo))) return Status::ShapeMismatch;
+  if (a.stride_h <= 0 || a.stride_w <= 0) return Status::Invalid;
+  const int Ho = (p.H + 2 * p.pad_h - p.dil_h * (p.Kh - 1) - 1) / p.stride_h + 1;
+  const int Wo = (p.W + 2 * p.pad_w - p.dil_w * (p.Kw - 1) - 1) / p.stride_w + 1;
+  const bool geom_ok = Ho > 0 && Wo > 0 && ge2b_conv2d_output_size(&p, nullptr, nullptr) == 0;
+  if (!shape_is(dY, p.N, p.Cout, Ho, Wo) || !shape_is(Z, p.N, p.Cout, Ho, Wo)) return Status::ShapeMismatch;
   if (dW && (!is4(*dW, dt) || !shape_is(*dW, p.Cout, p.Cin, p.Kh, p.Kw))) return Status::ShapeMismatch;
   if (dB && !(dB->device == shim::Device::CUDA && dB->desc.dtype == shim::DType::F32 && dB->desc.shape.size() == 1 &&
               dB->desc.shape[0] == p.Cout))

@@ -1,8 +1,9 @@
 // Host-only check of the registry / run layer: argument errors come back with the reference's codes before any
 // CUDA call, find_best falls back from the activation-specific key to the act = None entry, and an empty registry
-// yields -100.  Prints "ok" or the first failing line; exit code 0 / 1.
+// yields -100; the convolution's operator API rejects bad tensors with the reference's Status values.  Prints "ok" or the first failing line; exit code 0 / 1.
 #include <cstdio>
 
+#include "ge2_conv2d_api.hpp"
 #include "ge2_dispatch.hpp"
 
 using namespace ai;
@@ -55,6 +56,33 @@ int main() {
   CHECK(shim::GemmCudaLaunch(A, B, nullptr, Y, at, nullptr, nullptr, &ws) == shim::Status::Invalid);
   Tensor gC = Y;
   CHECK(shim::GemmCudaBackward(A, B, nullptr, Y, Y, nullptr, nullptr, &gC, nullptr, at, nullptr) == shim::Status::MissingInput);
+  // the convolution's operator API: validation order of conv2d/launcher.cu (no CUDA call is reached)
+  {
+    auto t4 = [&](std::int64_t a, std::int64_t b, std::int64_t c, std::int64_t d) {
+      Tensor t; t.data = &dummy; t.desc.shape = {a, b, c, d}; t.desc.stride = {b * c * d, c * d, d, 1}; return t;
+    };
+    Tensor X = t4(2, 3, 8, 8), W = t4(4, 3, 3, 3), Yc = t4(2, 4, 6, 6);
+    Conv2DAttrs ca{};
+    Tensor Xi = X; Xi.desc.dtype = shim::DType::I32;
+    CHECK(Conv2DCudaLaunch(Xi, W, nullptr, Yc, ca, nullptr) == shim::Status::Invalid);
+    Tensor X3 = X; X3.desc.shape = {2, 3, 64};
+    CHECK(Conv2DCudaLaunch(X3, W, nullptr, Yc, ca, nullptr) == shim::Status::Invalid);
+    ca.groups = 2;
+    CHECK(Conv2DCudaLaunch(X, W, nullptr, Yc, ca, nullptr) == shim::Status::Unimplemented);
+    ca.groups = 1;
+    Tensor W2 = t4(4, 5, 3, 3);
+    CHECK(Conv2DCudaLaunch(X, W2, nullptr, Yc, ca, nullptr) == shim::Status::ShapeMismatch);
+    Tensor Ybad = t4(2, 4, 8, 8);                       // no padding: the output is 6 x 6
+    CHECK(Conv2DCudaLaunch(X, W, nullptr, Ybad, ca, nullptr) == shim::Status::ShapeMismatch);
+    Tensor Wbig = t4(4, 3, 9, 9), Y1 = t4(2, 4, 1, 1);   // kernel larger than the image: computed size 0 x 0
+    CHECK(Conv2DCudaLaunch(X, Wbig, nullptr, Y1, ca, nullptr) == shim::Status::ShapeMismatch);
+    Tensor Y0 = t4(2, 4, 0, 0);
+    CHECK(Conv2DCudaLaunch(X, Wbig, nullptr, Y0, ca, nullptr) == shim::Status::Invalid);
+    Tensor dWbad = t4(4, 3, 5, 5);
+    CHECK(Conv2DCudaBackwardLaunch(X, W, Yc, Yc, &dWbad, nullptr, nullptr, ca, nullptr) == shim::Status::ShapeMismatch);
+    Tensor dXbad = t4(2, 3, 8, 9);
+    CHECK(Conv2DCudaBackwardLaunch(X, W, Yc, Yc, nullptr, nullptr, &dXbad, ca, nullptr) == shim::Status::ShapeMismatch);
+  }
   std::printf("ok\n");
   return 0;
 }
