@@ -208,10 +208,9 @@ def run_ours(args):
 
     # row blocks of dW whose all-reduce starts as each finishes; a single GPU has nothing to overlap and uses one
     # 0: no overlap - the backward runs as on one GPU (dX and dW in one launch) and the all-reduce follows it
-    # (the default at N > 1: beside a GEMM the all-reduce and the GEMM slow each other down by more than the overlap
-    # saves, and the one-launch backward is 0.023 ms faster than dW and dX apart; >= 1 selects the overlapped form
-    # with that many row blocks of dW)
-    dw_chunks = max(0, int(os.environ.get("GE2B_BENCH_DW_CHUNKS", "0" if world > 1 else "1")))
+    # Default: overlapped with 2 row blocks up to 4 GPUs (measured: N = 2 0.402 ms overlapped / 0.396 sequential, N = 4
+    # 0.413 / 0.474), sequential beyond (at N = 8 the overlapped form left 0.2 ms of a slowed-down all-reduce exposed).
+    dw_chunks = max(0, int(os.environ.get("GE2B_BENCH_DW_CHUNKS", "1" if world == 1 else ("2" if world <= 4 else "0"))))
     rows_per_chunk = K // max(1, dw_chunks)
 
     def step(timed):
