@@ -85,6 +85,7 @@ EXPORTS = [
     "ge2_launch_gemm_bias_act_typed", "ge2_launch_gemm_bias_act_bwd_typed",
     "ge2b_backward_scratch_bytes", "ge2b_device_status", "ge2b_sm_count", "ge2b_set_sm_limit", "ge2b_version",
     "ge2b_last_route", "ge2b_launches_total", "ge2b_register_gemm_kernels",
+    "ge2b_split_unavailable_total", "ge2b_release_scratch",
     "ge2b_dense_plan_create", "ge2b_dense_plan_step", "ge2b_dense_plan_destroy",
     "ge2b_dense_plan_submit", "ge2b_dense_plan_wait",
     "ge2_launch_gemm_bias_act_bwd_noalloc",
@@ -124,6 +125,8 @@ def load_library() -> C.CDLL:
     lib.ge2b_version.restype = C.c_char_p
     lib.ge2b_last_route.restype = C.c_int
     lib.ge2b_launches_total.restype = C.c_longlong
+    lib.ge2b_split_unavailable_total.restype = C.c_longlong
+    lib.ge2b_release_scratch.restype = None
     lib.ge2b_dense_plan_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                            C.c_float, C.c_int, C.c_int]
     lib.ge2b_dense_plan_create.restype = C.c_int

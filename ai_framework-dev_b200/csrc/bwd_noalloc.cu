@@ -12,11 +12,17 @@
 //     process exits, used or not;
 //   * a call is refused (-1) when M * N * sizeof(element) exceeds that size;
 //   * all calls share the one array per GPU and it keeps whatever the previous call left there.  Nothing in it
-//     has to start at zero, because the prologue kernel overwrites the M x N region before the GEMMs read it;
-//     gBias / gC are zeroed by cudaMemsetAsync as in the ordinary path.  Two calls whose kernels overlap on the
-//     GPU (different streams without ordering) race on the array: order them;
+//     has to start at zero except the split-K arrival counters, which every launch that uses them clears on the
+//     stream first; the prologue kernel overwrites the M x N region before the GEMMs read it; gBias / gC are zeroed
+//     by cudaMemsetAsync as in the ordinary path.  Two calls whose kernels overlap on the GPU (different streams
+//     without ordering) race on the array: order them;
+//   * what the array has left after gZ is lent to the GEMM launches for their split-K partial sums (problems smaller
+//     than one wave of the machine); when that is too little for a split the launch runs unsplit.  While the call
+//     is running the launch layer is forbidden to create scratch of its own (ScopedLease with no_alloc);
 //   * the first call on each device looks up the array's device address (cudaGetSymbolAddress) and, inside the
-//     GEMM launcher, sets a function attribute; make that first call before starting any stream capture.
+//     GEMM launcher, sets a function attribute; make that first call before starting any stream capture.  With
+//     lazy module loading that first call is also the moment the driver reserves the 16 MiB for the array: under a
+//     pool that has already taken every byte of the GPU it fails with -2; load the library before the pool grows.
 // The entry point calls no cudaMalloc / cudaFree / cudaMallocAsync and no allocating library routine.
 #include <cuda_runtime.h>
 
@@ -98,5 +104,9 @@ extern "C" int ge2_launch_gemm_bias_act_bwd_noalloc(const ge2_uintptr* bufs, int
   b.scratch = scratch;
   b.scratch_bytes = GE2B_NOALLOC_SCRATCH_BYTES;
   b.reuse_gz = false;
+  // the rest of the array serves the GEMM launches' split-K partial sums; nothing may be allocated meanwhile
+  const size_t used = (need + 255u) & ~static_cast<size_t>(255u);
+  ScopedLease lease(static_cast<unsigned char*>(scratch) + used,
+                    used < static_cast<size_t>(GE2B_NOALLOC_SCRATCH_BYTES) ? GE2B_NOALLOC_SCRATCH_BYTES - used : 0, true);
   return dense_backward(b, reinterpret_cast<cudaStream_t>(stream));
 }

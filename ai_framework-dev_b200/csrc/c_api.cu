@@ -195,5 +195,7 @@ const char* ge2b_version(void) { return "ge2_b200 0.1 (sm_100a)"; }
 // Not part of the public header: introspection used by the test-suite and the benchmark.
 int ge2b_last_route(void) { return last_route(); }
 long long ge2b_launches_total(void) { return launches_total(); }
+long long ge2b_split_unavailable_total(void) { return split_unavailable_total(); }
+void ge2b_release_scratch(void) { release_library_scratch(); }
 
 }  // extern "C"

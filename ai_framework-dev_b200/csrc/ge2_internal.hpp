@@ -5,6 +5,7 @@
 // (backends/cuda/ops/_common/shim/enums.hpp:10-24, ai_device.hpp:14-16) so that values
 // can be passed through unchanged from the operator API.
 #pragma once
+#include <atomic>
 #include <cstddef>
 #include <cstdint>
 #include <cuda_runtime.h>
@@ -80,6 +81,29 @@ cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s);
 // Reads (and optionally clears) the device status word of the current device. Synchronises.
 int  device_status_word(bool clear);
 int* device_status_ptr();   // device address of the status word for the current device
+
+// Device memory a caller lends to the launch layer for the duration of one call on this thread (split-K partial tiles
+// and arrival counters are placed in it).  `no_alloc`: the launch layer must not create scratch of its own during the
+// call; what does not fit the lent memory runs unsplit.  Set through ScopedLease.
+struct ScratchLease { void* base = nullptr; size_t bytes = 0; bool no_alloc = false; };
+ScratchLease& scratch_lease();                       // thread-local
+struct ScopedLease {
+  ScratchLease saved;
+  ScopedLease(void* base, size_t bytes, bool no_alloc) : saved(scratch_lease()) {
+    // the launch layer wants a 256-byte aligned base
+    uintptr_t a = reinterpret_cast<uintptr_t>(base);
+    const uintptr_t up = (a + 255u) & ~static_cast<uintptr_t>(255u);
+    if (base && bytes > up - a) { scratch_lease().base = reinterpret_cast<void*>(up); scratch_lease().bytes = bytes - (up - a); }
+    else { scratch_lease().base = nullptr; scratch_lease().bytes = 0; }
+    scratch_lease().no_alloc = no_alloc;
+  }
+  ~ScopedLease() { scratch_lease() = saved; }
+  ScopedLease(const ScopedLease&) = delete;
+  ScopedLease& operator=(const ScopedLease&) = delete;
+};
+long long split_unavailable_total();   // split-K launches that ran unsplit because no scratch could be had (capture, no_alloc)
+void release_library_scratch();        // synchronises the device and frees every split-K scratch the library created
+std::atomic<unsigned long long>& plan_cache_generation();   // bumping it invalidates every thread's cached launches
 
 int  sm_count();            // cached multiprocessor count of the current device
 int  sm_budget();           // SMs the persistent GEMM may occupy: sm_count() unless lowered by set_sm_limit()

@@ -1,7 +1,10 @@
 // Tensor-core GEMM: host-side helpers (tensor maps, split-K scratch), tile choice and dispatch.  The kernel template
 // lives in gemm_tc_kernel.cuh and is instantiated by the gemm_tc_inst_*.cu files.
+#include <atomic>
+#include <cstring>
 #include <map>
 #include <utility>
+#include <vector>
 
 #include "gemm_tc_kernel.cuh"
 
@@ -80,53 +83,210 @@ bool tensor_vec_ok(const void* p, long long ld, long long batch_stride, int dt) 
   return aligned16(p) && (ld * esz) % 16 == 0 && (batch_stride * esz) % 16 == 0;
 }
 
-// Scratch of split-K launches (fp32 partial tiles + one arrival counter per tile and epilogue-warp slot).  One buffer per
-// (device, stream), created the first time a launch on that stream needs it and kept for the life of the process:
-// launches on one stream are ordered, launches on different streams get different buffers.  Creating it allocates
-// device memory, so the first split launch on a stream must happen outside stream capture (warm the shape up once).
+// Scratch of split-K launches (fp32 partial tiles + one arrival counter per tile and epilogue-warp slot).
+//
+// Where it comes from, in this order:
+//   1. memory the caller lent for the duration of the call (scratch_lease(): the operator API's lt_workspace, the tail
+//      of the fixed array of the allocation-free backward entry); nothing is allocated;
+//   2. the library's own buffer, one per (device, stream): launches on one stream are ordered, launches on different
+//      streams get different buffers.  It is created (cudaMalloc) the first time a split launch arrives on that
+//      stream, which cannot happen while the stream is being captured or when the lease forbids allocation; the launch
+//      then runs unsplit and `split_unavailable_total()` counts it.  Warm a shape up once, on the stream that will
+//      be captured, before capturing it.  release_library_scratch() frees all of them.
+namespace {
+struct OwnedScratch { float* ws = nullptr; int* flags = nullptr; };
+std::mutex g_scratch_mu;
+std::map<std::pair<int, cudaStream_t>, OwnedScratch> g_scratch_table;
+std::atomic<long long> g_split_unavailable{0};
+}  // namespace
 
-SplitScratch* split_scratch(cudaStream_t s) {
-  static std::mutex mu;
-  static std::map<std::pair<int, cudaStream_t>, SplitScratch> table;
+bool split_scratch(cudaStream_t s, SplitScratch* out) {
+  const ScratchLease& lease = scratch_lease();
+  if (lease.base && lease.bytes >= kSplitFlagBytes + (1u << 20)) {
+    // flags first (256-byte aligned base), partial tiles after them
+    out->flags = static_cast<int*>(lease.base);
+    out->ws = reinterpret_cast<float*>(static_cast<unsigned char*>(lease.base) + kSplitFlagBytes);
+    out->ws_bytes = lease.bytes - kSplitFlagBytes;
+    return true;
+  }
+  if (lease.no_alloc) { g_split_unavailable.fetch_add(1, std::memory_order_relaxed); return false; }
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
-  std::lock_guard<std::mutex> lk(mu);
-  SplitScratch& sc = table[{dev, s}];
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  std::lock_guard<std::mutex> lk(g_scratch_mu);
+  OwnedScratch& sc = g_scratch_table[{dev, s}];
   if (!sc.ws) {
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return nullptr;
-    if (cudaMalloc(reinterpret_cast<void**>(&sc.ws), kSplitWsBytes) != cudaSuccess) { sc.ws = nullptr; return nullptr; }
-    if (cudaMalloc(reinterpret_cast<void**>(&sc.flags), kSplitMaxTail * kEpiWarps * 2 * sizeof(int)) != cudaSuccess) {
-      cudaFree(sc.ws); sc.ws = nullptr; return nullptr;
+    if (cudaStreamIsCapturing(s, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+      g_split_unavailable.fetch_add(1, std::memory_order_relaxed);
+      return false;
     }
-    sc.ws_bytes = kSplitWsBytes;
+    if (cudaMalloc(reinterpret_cast<void**>(&sc.ws), kSplitWsBytes) != cudaSuccess) {
+      cudaGetLastError();        // the failed allocation must not surface as the next launch's error
+      sc.ws = nullptr;
+      g_split_unavailable.fetch_add(1, std::memory_order_relaxed);
+      return false;
+    }
+    if (cudaMalloc(reinterpret_cast<void**>(&sc.flags), kSplitFlagBytes) != cudaSuccess) {
+      cudaGetLastError();
+      cudaFree(sc.ws); sc.ws = nullptr;
+      g_split_unavailable.fetch_add(1, std::memory_order_relaxed);
+      return false;
+    }
   }
-  return &sc;
+  out->ws = sc.ws; out->flags = sc.flags; out->ws_bytes = kSplitWsBytes;
+  return true;
 }
 
-
 bool driver_has_tensor_maps() { return encode_tiled_fn_impl() != nullptr; }
+
+}  // namespace tc
+
+long long split_unavailable_total() { return tc::g_split_unavailable.load(std::memory_order_relaxed); }
+
+void release_library_scratch() {
+  cudaDeviceSynchronize();
+  std::lock_guard<std::mutex> lk(tc::g_scratch_mu);
+  int cur = 0;
+  cudaGetDevice(&cur);
+  for (auto& kv : tc::g_scratch_table) {
+    if (!kv.second.ws) continue;
+    cudaSetDevice(kv.first.first);
+    cudaFree(kv.second.ws);
+    cudaFree(kv.second.flags);
+  }
+  tc::g_scratch_table.clear();
+  cudaSetDevice(cur);
+  plan_cache_generation().fetch_add(1, std::memory_order_relaxed);   // cached launches may point into freed scratch
+}
+
+ScratchLease& scratch_lease() {
+  thread_local ScratchLease lease;
+  return lease;
+}
+
+std::atomic<unsigned long long>& plan_cache_generation() {
+  static std::atomic<unsigned long long> gen{1};
+  return gen;
+}
+
+namespace tc {
+
+cudaError_t run_prepared(const PreparedLaunch& L, cudaStream_t s) {
+  if (L.flag_bytes && cudaMemsetAsync(L.p.flags, 0, L.flag_bytes, s) != cudaSuccess) return cudaErrorUnknown;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(L.grid, 1, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = static_cast<size_t>(L.smem);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(L.cluster);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  void* args[] = {const_cast<CUtensorMap*>(&L.tmA), const_cast<CUtensorMap*>(&L.tmB), const_cast<CUtensorMap*>(&L.tmBh),
+                  const_cast<CUtensorMap*>(&L.tmD), const_cast<CUtensorMap*>(&L.tmZ), const_cast<TcParams*>(&L.p),
+                  const_cast<DualParams*>(&L.d2)};
+  const cudaError_t e = cudaLaunchKernelExC(&cfg, L.kernel, args);
+  if (e != cudaSuccess || L.fin_gy == 0) return e;
+  splitk_finalize_kernel<<<dim3(L.p.tail_tiles, L.fin_gy), 256, 0, s>>>(L.p, L.fin_tile_m, L.fin_tile_n);
+  return cudaGetLastError();
+}
 
 }  // namespace tc
 
 namespace {
 using namespace tc;
 
+// ---- per-thread cache of prepared launches ----
+// A launch is fully determined by the problem description (pointers, shapes, pitches, epilogue), the stream (whose
+// split-K scratch it may use), the lent scratch, the device and the SM budget.  Encoding tensor maps costs several
+// microseconds per map; a training step repeats the same few launches, so they are kept ready.  Tensor maps hold
+// addresses and shapes only, so an entry stays valid even if the buffers behind the pointers are freed and given out
+// again: the key then simply matches a problem with the same geometry at the same addresses.
+struct PlanKey {
+  static constexpr int kWords = 80;
+  unsigned long long w[kWords];
+  int n = 0;
+  void add(unsigned long long v) { if (n < kWords) w[n++] = v; }
+  void add_ptr(const void* p) { add(reinterpret_cast<unsigned long long>(p)); }
+  void add_f(float f) { unsigned u; std::memcpy(&u, &f, 4); add(u); }
+  unsigned long long hash() const {
+    unsigned long long h = 1469598103934665603ull;
+    for (int i = 0; i < n; ++i) { h ^= w[i]; h *= 1099511628211ull; }
+    return h;
+  }
+  bool same(const PlanKey& o) const { return n == o.n && std::memcmp(w, o.w, sizeof(unsigned long long) * n) == 0; }
+};
+
+void key_problem(PlanKey& k, const GemmProblem& g) {
+  k.add((static_cast<unsigned long long>(static_cast<unsigned>(g.M)) << 32) | static_cast<unsigned>(g.N));
+  k.add((static_cast<unsigned long long>(static_cast<unsigned>(g.K)) << 32) | static_cast<unsigned>(g.batch));
+  k.add(static_cast<unsigned long long>(g.in_dtype) | (static_cast<unsigned long long>(g.math) << 8) |
+        (static_cast<unsigned long long>(g.a_mn) << 16) | (static_cast<unsigned long long>(g.b_mn) << 17) |
+        (static_cast<unsigned long long>(g.reduce_batch) << 18) | (static_cast<unsigned long long>(g.epi.bias_kind) << 24) |
+        (static_cast<unsigned long long>(g.epi.act) << 32) | (static_cast<unsigned long long>(g.epi.d_dtype) << 40) |
+        (static_cast<unsigned long long>(g.epi.z_dtype) << 48));
+  k.add_ptr(g.A); k.add(g.lda); k.add(g.strideA);
+  k.add_ptr(g.B); k.add(g.ldb); k.add(g.strideB);
+  k.add_ptr(g.epi.D); k.add(g.epi.ldd); k.add(g.epi.strideD);
+  k.add_ptr(g.epi.Z); k.add(g.epi.ldz); k.add(g.epi.strideZ);
+  k.add_ptr(g.epi.C); k.add(g.epi.ldc); k.add(g.epi.strideC);
+  k.add_ptr(g.epi.bias);
+  k.add_f(g.epi.leaky); k.add_f(g.epi.alpha); k.add_f(g.epi.beta);
+}
+
+void key_context(PlanKey& k, cudaStream_t s, int extra) {
+  int dev = -1;
+  cudaGetDevice(&dev);
+  const ScratchLease& lease = scratch_lease();
+  k.add_ptr(s); k.add_ptr(lease.base); k.add(lease.bytes);
+  k.add(static_cast<unsigned long long>(dev + 1) | (static_cast<unsigned long long>(lease.no_alloc) << 16) |
+        (static_cast<unsigned long long>(sm_budget()) << 32));
+  k.add(static_cast<unsigned long long>(extra));
+  k.add(plan_cache_generation().load(std::memory_order_relaxed));
+}
+
+struct PlanEntry { unsigned long long hash = 0, stamp = 0; PlanKey key; PreparedLaunch L; bool used = false; };
+constexpr int kPlanEntries = 64;
+
+struct PlanCache {
+  std::vector<PlanEntry> e;
+  unsigned long long clock = 0;
+  PlanEntry* find(const PlanKey& k, unsigned long long h) {
+    for (auto& x : e)
+      if (x.used && x.hash == h && x.key.same(k)) { x.stamp = ++clock; return &x; }
+    return nullptr;
+  }
+  PlanEntry* slot() {
+    if (e.empty()) e.resize(kPlanEntries);
+    PlanEntry* best = &e[0];
+    for (auto& x : e) {
+      if (!x.used) { best = &x; break; }
+      if (x.stamp < best->stamp) best = &x;
+    }
+    return best;
+  }
+};
+PlanCache& plan_cache() { thread_local PlanCache c; return c; }
+const bool g_plan_cache_off = [] { const char* e = getenv("GE2B_PLAN_CACHE"); return e && atoi(e) == 0; }();
+
 template <int kElemBytes>
-cudaError_t launch_major(const GemmProblem& g, TcParams& p, TileChoice t, cudaStream_t s) {
-  if (g.a_mn) return g.b_mn ? launch_bn<kElemBytes, true, true>(g, p, t, s)
-                            : launch_bn<kElemBytes, true, false>(g, p, t, s);
-  return g.b_mn ? launch_bn<kElemBytes, false, true>(g, p, t, s)
-                : launch_bn<kElemBytes, false, false>(g, p, t, s);
+cudaError_t prepare_major(const GemmProblem& g, TcParams& p, TileChoice t, cudaStream_t s, PreparedLaunch& L) {
+  if (g.a_mn) return g.b_mn ? prepare_bn<kElemBytes, true, true>(g, p, t, s, L)
+                            : prepare_bn<kElemBytes, true, false>(g, p, t, s, L);
+  return g.b_mn ? prepare_bn<kElemBytes, false, true>(g, p, t, s, L)
+                : prepare_bn<kElemBytes, false, false>(g, p, t, s, L);
 }
 
 // Tile choice.  Wide (256) tiles run the tensor pipe at full rate; narrow (128) tiles quantise better onto the
-// SMs.  CTA pairs need at least two row blocks to be worth their while.  GE2B_BLOCK_N / GE2B_CTA_GROUP override.
+// SMs.  CTA pairs need at least two row blocks to be worth their while.  GE2B_BLOCK_N / GE2B_CTA_GROUP (read once)
+// override.
 TileChoice choose_tile(const GemmProblem& g) {
   TileChoice t{256, 1};
-  int force_bn = 0, force_cg = 0;
-  if (const char* e = getenv("GE2B_BLOCK_N")) { const int v = atoi(e); if (v == 128 || v == 256) force_bn = v; }
-  if (const char* e = getenv("GE2B_CTA_GROUP")) { const int v = atoi(e); if (v == 1 || v == 2) force_cg = v; }
+  static const int force_bn = [] { const char* e = getenv("GE2B_BLOCK_N"); const int v = e ? atoi(e) : 0; return (v == 128 || v == 256) ? v : 0; }();
+  static const int force_cg = [] { const char* e = getenv("GE2B_CTA_GROUP"); const int v = e ? atoi(e) : 0; return (v == 1 || v == 2) ? v : 0; }();
   // A CTA pair (256 rows per tile, half of B per CTA, deeper ring) is the faster form whenever the problem has at
   // least two 128-row blocks; below that the second CTA of a pair would only compute padding.
   t.cta_group = force_cg ? force_cg : (g.M > 128 ? 2 : 1);
@@ -146,6 +306,18 @@ TileChoice choose_tile(const GemmProblem& g) {
   return t;
 }
 
+void fill_common(const GemmProblem& g, tc::TcParams& p) {
+  p.M = g.M; p.N = g.N; p.K = g.K; p.batch = g.reduce_batch ? 1 : g.batch;
+  p.a_bcast = (g.batch > 1 && g.strideA == 0) ? 1 : 0;
+  p.b_bcast = (g.batch > 1 && g.strideB == 0) ? 1 : 0;
+  p.epi = g.epi;
+  p.d_vec = tensor_vec_ok(g.epi.D, g.epi.ldd, g.epi.strideD, g.epi.d_dtype);
+  p.z_vec = tensor_vec_ok(g.epi.Z, g.epi.ldz, g.epi.strideZ, g.epi.z_dtype);
+  p.c_vec = tensor_vec_ok(g.epi.C, g.epi.ldc, g.epi.strideC, g.epi.d_dtype);
+  p.bias_vec = g.epi.bias && aligned16(g.epi.bias);
+  p.status = device_status_ptr();
+}
+
 }  // namespace
 
 bool gemm_tc_supported(const GemmProblem& g, const char** why) {
@@ -162,20 +334,6 @@ bool gemm_tc_supported(const GemmProblem& g, const char** why) {
   return true;
 }
 
-namespace {
-void fill_common(const GemmProblem& g, tc::TcParams& p) {
-  p.M = g.M; p.N = g.N; p.K = g.K; p.batch = g.reduce_batch ? 1 : g.batch;
-  p.a_bcast = (g.batch > 1 && g.strideA == 0) ? 1 : 0;
-  p.b_bcast = (g.batch > 1 && g.strideB == 0) ? 1 : 0;
-  p.epi = g.epi;
-  p.d_vec = tensor_vec_ok(g.epi.D, g.epi.ldd, g.epi.strideD, g.epi.d_dtype);
-  p.z_vec = tensor_vec_ok(g.epi.Z, g.epi.ldz, g.epi.strideZ, g.epi.z_dtype);
-  p.c_vec = tensor_vec_ok(g.epi.C, g.epi.ldc, g.epi.strideC, g.epi.d_dtype);
-  p.bias_vec = g.epi.bias && aligned16(g.epi.bias);
-  p.status = device_status_ptr();
-}
-}  // namespace
-
 cudaError_t launch_gemm_tc_dual(const GemmProblem& dx, const GemmProblem& dw, cudaStream_t s) {
   static const bool off = [] { const char* e = getenv("GE2B_DUAL_BWD"); return e && atoi(e) == 0; }();
   if (off) return cudaErrorNotSupported;
@@ -184,36 +342,59 @@ cudaError_t launch_gemm_tc_dual(const GemmProblem& dx, const GemmProblem& dw, cu
   if (dx.batch != 1 || dw.batch != 1 || dx.in_dtype != dw.in_dtype) return cudaErrorNotSupported;
   if (dx.a_mn || dx.b_mn || !dw.a_mn || !dw.b_mn) return cudaErrorNotSupported;
   if (dx.M <= 128 || dw.M <= 128 || dx.N <= 128 || dw.N <= 128) return cudaErrorNotSupported;
-  if (!gemm_tc_supported(dx, nullptr) || !gemm_tc_supported(dw, nullptr)) return cudaErrorNotSupported;
-  if (dx.epi.Z || dw.epi.Z || dx.epi.d_dtype != dw.epi.d_dtype) return cudaErrorNotSupported;
-  TcParams p1{}, p2{};
-  fill_common(dx, p1);
-  fill_common(dw, p2);
-  if (!p1.status || !p1.d_vec || !p2.d_vec) return cudaErrorNotSupported;
   // worth it only when the combined list quantises better than the two lists do separately
   const long long units = sm_budget() / 2 > 0 ? sm_budget() / 2 : 1;
   auto tiles = [](const GemmProblem& g) { return static_cast<long long>((g.M + 255) / 256) * ((g.N + 255) / 256); };
   auto waves = [&](long long t) { return (t + units - 1) / units; };
   if (tiles(dx) + tiles(dw) < units) return cudaErrorNotSupported;   // small problems are better off with split-K each
   if (waves(tiles(dx) + tiles(dw)) >= waves(tiles(dx)) + waves(tiles(dw))) return cudaErrorNotSupported;
-  return dx.in_dtype == kF32 ? tc::launch_dual_cfg<4, false, false, true, true>(dx, p1, dw, p2, s)
-                             : tc::launch_dual_cfg<2, false, false, true, true>(dx, p1, dw, p2, s);
+
+  PlanKey key;
+  PlanEntry* hit = nullptr;
+  unsigned long long h = 0;
+  if (!g_plan_cache_off) {
+    key_problem(key, dx); key_problem(key, dw); key_context(key, s, 2);
+    h = key.hash();
+    hit = plan_cache().find(key, h);
+    if (hit) return run_prepared(hit->L, s);
+  }
+  if (!gemm_tc_supported(dx, nullptr) || !gemm_tc_supported(dw, nullptr)) return cudaErrorNotSupported;
+  if (dx.epi.Z || dw.epi.Z || dx.epi.d_dtype != dw.epi.d_dtype) return cudaErrorNotSupported;
+  TcParams p1{}, p2{};
+  fill_common(dx, p1);
+  fill_common(dw, p2);
+  if (!p1.status || !p1.d_vec || !p2.d_vec) return cudaErrorNotSupported;
+  PreparedLaunch L;
+  const cudaError_t e = dx.in_dtype == kF32 ? tc::prepare_dual_cfg<4, false, false, true, true>(dx, p1, dw, p2, L)
+                                            : tc::prepare_dual_cfg<2, false, false, true, true>(dx, p1, dw, p2, L);
+  if (e != cudaSuccess) return e;
+  if (!g_plan_cache_off && L.cacheable) {
+    PlanEntry* slot = plan_cache().slot();
+    slot->key = key; slot->hash = h; slot->L = L; slot->used = true; slot->stamp = ++plan_cache().clock;
+  }
+  return run_prepared(L, s);
 }
 
 cudaError_t launch_gemm_tc(const GemmProblem& g, cudaStream_t s) {
+  PlanKey key;
+  unsigned long long h = 0;
+  if (!g_plan_cache_off) {
+    key_problem(key, g); key_context(key, s, 1);
+    h = key.hash();
+    if (PlanEntry* hit = plan_cache().find(key, h)) return run_prepared(hit->L, s);
+  }
   TcParams p{};
-  p.M = g.M; p.N = g.N; p.K = g.K; p.batch = g.reduce_batch ? 1 : g.batch;
-  p.a_bcast = (g.batch > 1 && g.strideA == 0) ? 1 : 0;
-  p.b_bcast = (g.batch > 1 && g.strideB == 0) ? 1 : 0;
-  p.epi = g.epi;
-  p.d_vec = tensor_vec_ok(g.epi.D, g.epi.ldd, g.epi.strideD, g.epi.d_dtype);
-  p.z_vec = tensor_vec_ok(g.epi.Z, g.epi.ldz, g.epi.strideZ, g.epi.z_dtype);
-  p.c_vec = tensor_vec_ok(g.epi.C, g.epi.ldc, g.epi.strideC, g.epi.d_dtype);
-  p.bias_vec = g.epi.bias && aligned16(g.epi.bias);
-  p.status = device_status_ptr();
+  fill_common(g, p);
   if (!p.status) return cudaErrorInvalidDevice;
   const TileChoice t = choose_tile(g);
-  return g.in_dtype == kF32 ? launch_major<4>(g, p, t, s) : launch_major<2>(g, p, t, s);
+  PreparedLaunch L;
+  const cudaError_t e = g.in_dtype == kF32 ? prepare_major<4>(g, p, t, s, L) : prepare_major<2>(g, p, t, s, L);
+  if (e != cudaSuccess) return e;
+  if (!g_plan_cache_off && L.cacheable) {
+    PlanEntry* slot = plan_cache().slot();
+    slot->key = key; slot->hash = h; slot->L = L; slot->used = true; slot->stamp = ++plan_cache().clock;
+  }
+  return run_prepared(L, s);
 }
 
 }  // namespace ge2b

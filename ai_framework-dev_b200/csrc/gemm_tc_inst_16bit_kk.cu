@@ -4,9 +4,9 @@
 
 namespace ge2b {
 namespace tc {
-template cudaError_t launch_bn<2, false, false>(const GemmProblem&, TcParams&, TileChoice, cudaStream_t);
+template cudaError_t prepare_bn<2, false, false>(const GemmProblem&, TcParams&, TileChoice, cudaStream_t, PreparedLaunch&);
 // the dense layer's backward pair: dX = gZ.W^T (both operands reduction-contiguous) and dW = X^T.gZ (both M/N-contiguous)
-template cudaError_t launch_dual_cfg<2, false, false, true, true>(const GemmProblem&, TcParams&, const GemmProblem&, TcParams&,
-                                                                   cudaStream_t);
+template cudaError_t prepare_dual_cfg<2, false, false, true, true>(const GemmProblem&, TcParams&, const GemmProblem&, TcParams&,
+                                                                    PreparedLaunch&);
 }  // namespace tc
 }  // namespace ge2b

@@ -4,6 +4,6 @@
 
 namespace ge2b {
 namespace tc {
-template cudaError_t launch_bn<4, true, false>(const GemmProblem&, TcParams&, TileChoice, cudaStream_t);
+template cudaError_t prepare_bn<4, true, false>(const GemmProblem&, TcParams&, TileChoice, cudaStream_t, PreparedLaunch&);
 }  // namespace tc
 }  // namespace ge2b

@@ -810,7 +810,26 @@ struct SplitScratch { float* ws = nullptr; int* flags = nullptr; size_t ws_bytes
 constexpr size_t kSplitWsBytes = 64u << 20;
 constexpr int kSplitMaxTail = 256;
 constexpr int kSplitInKernelMax = 8;   // more slices than this: the second kernel adds them up
-SplitScratch* split_scratch(cudaStream_t s);
+constexpr size_t kSplitFlagBytes = static_cast<size_t>(kSplitMaxTail) * kEpiWarps * 2 * sizeof(int);
+// Split-K scratch for a launch on stream `s`: the memory the caller lent for this call (scratch_lease()) when there is
+// one, else the library's own per-(device, stream) buffer, created on first use unless the lease forbids it or the
+// stream is being captured.  Returns false when there is none; the launch then runs unsplit.
+bool split_scratch(cudaStream_t s, SplitScratch* out);
+
+// Everything one launch of gemm_tc_kernel needs, ready to be handed to the driver: built once per distinct problem
+// (tensor maps are the expensive part) and replayed from a per-thread cache on later calls with the same arguments.
+struct PreparedLaunch {
+  const void* kernel = nullptr;
+  unsigned grid = 0;
+  int cluster = 1, smem = 0;
+  CUtensorMap tmA, tmB, tmBh, tmD, tmZ;
+  TcParams p;
+  DualParams d2;
+  size_t flag_bytes = 0;              // > 0: p.flags is zeroed on the stream before the launch
+  int fin_gy = 0, fin_tile_m = 0, fin_tile_n = 0;   // fin_gy > 0: splitk_finalize_kernel follows
+  bool cacheable = true;              // false: the launch ran unsplit only because no scratch could be had right now
+};
+cudaError_t run_prepared(const PreparedLaunch& L, cudaStream_t s);
 
 struct ProblemMaps { CUtensorMap tmA, tmB, tmD, tmZ; };
 
@@ -862,13 +881,8 @@ bool prepare_problem(const GemmProblem& g, TcParams& p, ProblemMaps& m) {
   return true;
 }
 
-inline const DualParams& no_second_problem() {
-  static const DualParams none{};
-  return none;
-}
-
 template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG>
-cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
+cudaError_t prepare_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s, PreparedLaunch& L) {
   using Cfg = TcCfg<kElemBytes, kBlockN, kStages, kCG>;
   auto kernel = gemm_tc_kernel<kElemBytes, kAMN, kBMN, kBlockN, kStages, kCG, false>;
   auto kernel_split = gemm_tc_kernel<kElemBytes, kAMN, kBMN, kBlockN, kStages, kCG, true>;
@@ -885,8 +899,7 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
   constexpr int kLocalN = kBlockN / kCG;
   ProblemMaps pm;
   if (!prepare_problem<kElemBytes, kAMN, kBMN, kBlockN, kStages, kCG>(g, p, pm)) return cudaErrorInvalidValue;
-  const CUtensorMap &tmA = pm.tmA, &tmB = pm.tmB, &tmD = pm.tmD, &tmZ = pm.tmZ;
-  CUtensorMap tmBh;
+  L.tmA = pm.tmA; L.tmB = pm.tmB; L.tmD = pm.tmD; L.tmZ = pm.tmZ;
 
   const long long tiles = static_cast<long long>(p.batch) * p.m_blocks * p.n_blocks;
   const long long units = sm_budget() / kCG > 0 ? sm_budget() / kCG : 1;   // one CTA (or CTA pair) per SM (pair of SMs)
@@ -900,18 +913,21 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
     long long sp = units / rem;
     if (sp > 32) sp = 32;
     if (sp > p.k_blocks / 8) sp = p.k_blocks / 8;               // keep at least 8 k-blocks per slice
-    while (sp >= 2 && static_cast<size_t>(sp) * rem * kTileM * kBlockN * sizeof(float) > kSplitWsBytes) --sp;
     if (sp >= 2) {
-      if (SplitScratch* sc = split_scratch(s)) {
-        p.main_tiles = static_cast<int>(tiles - rem);
-        p.tail_tiles = static_cast<int>(rem);
-        p.split = static_cast<int>(sp);
-        p.ws = sc->ws;
-        p.flags = sc->flags;
-        p.fin_in_kernel = sp <= kSplitInKernelMax ? 1 : 0;
-        if (p.fin_in_kernel &&
-            cudaMemsetAsync(sc->flags, 0, static_cast<size_t>(rem) * kEpiWarps * kCG * sizeof(int), s) != cudaSuccess)
-          return cudaErrorUnknown;
+      SplitScratch sc;
+      if (split_scratch(s, &sc)) {
+        while (sp >= 2 && static_cast<size_t>(sp) * rem * kTileM * kBlockN * sizeof(float) > sc.ws_bytes) --sp;
+        if (sp >= 2) {
+          p.main_tiles = static_cast<int>(tiles - rem);
+          p.tail_tiles = static_cast<int>(rem);
+          p.split = static_cast<int>(sp);
+          p.ws = sc.ws;
+          p.flags = sc.flags;
+          p.fin_in_kernel = sp <= kSplitInKernelMax ? 1 : 0;
+          if (p.fin_in_kernel) L.flag_bytes = static_cast<size_t>(rem) * kEpiWarps * kCG * sizeof(int);
+        }
+      } else {
+        L.cacheable = false;
       }
     }
   }
@@ -924,42 +940,33 @@ cudaError_t launch_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s) {
     p.tail_tiles = static_cast<int>(rem);
     p.split = 2;
   }
-  tmBh = tmB;
+  L.tmBh = L.tmB;
   if (narrow_tail && !kBMN &&
-      !make_operand_map(&tmBh, g.in_dtype, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, Cfg::kBlockK, kLocalN / 2, false))
+      !make_operand_map(&L.tmBh, g.in_dtype, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, Cfg::kBlockK, kLocalN / 2, false))
     return cudaErrorInvalidValue;
   const long long items = static_cast<long long>(p.main_tiles) + static_cast<long long>(p.tail_tiles) * p.split;
-  const int grid = static_cast<int>((items < units ? items : units) * kCG);
-
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid, 1, 1);
-  cfg.blockDim = dim3(kNumThreads, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = kCG;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  L.grid = static_cast<unsigned>((items < units ? items : units) * kCG);
+  L.cluster = kCG;
+  L.smem = Cfg::kSmemBytes;
+  L.kernel = reinterpret_cast<const void*>(kernel);
   if (p.split > 1 && !narrow_tail) {
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel_split, tmA, tmB, tmBh, tmD, tmZ, p, no_second_problem());
-    if (e != cudaSuccess || p.fin_in_kernel) return e;
-    const int quads = kBlockN / 4, rows_per_pass = 256 / quads;
-    int gy = kTileM / rows_per_pass;                    // one pass per block when the grid is small ...
-    while (gy > 1 && static_cast<long long>(p.tail_tiles) * gy > 8ll * units) gy >>= 1;   // ... fewer blocks when it is not
-    splitk_finalize_kernel<<<dim3(p.tail_tiles, gy), 256, 0, s>>>(p, kTileM, kBlockN);
-    return cudaGetLastError();
+    L.kernel = reinterpret_cast<const void*>(kernel_split);
+    if (!p.fin_in_kernel) {
+      const int quads = kBlockN / 4, rows_per_pass = 256 / quads;
+      int gy = kTileM / rows_per_pass;                    // one pass per block when the grid is small ...
+      while (gy > 1 && static_cast<long long>(p.tail_tiles) * gy > 8ll * units) gy >>= 1;   // ... fewer blocks when it is not
+      L.fin_gy = gy; L.fin_tile_m = kTileM; L.fin_tile_n = kBlockN;
+    }
   }
-  return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmBh, tmD, tmZ, p, no_second_problem());
+  L.p = p;
+  return cudaSuccess;
 }
 
 // Two independent problems in one persistent launch (CTA pairs, 256 x 256 tiles, no split-K, no narrow tail): the
 // tiles of the second follow those of the first in one list.  Both must be 16-bit or both 32-bit, and both must leave
 // through the same kind of store (checked by the caller through the filled TcParams).
 template <int kElemBytes, bool kAMN1, bool kBMN1, bool kAMN2, bool kBMN2>
-cudaError_t launch_dual_cfg(const GemmProblem& g1, TcParams& p1, const GemmProblem& g2, TcParams& p2, cudaStream_t s) {
+cudaError_t prepare_dual_cfg(const GemmProblem& g1, TcParams& p1, const GemmProblem& g2, TcParams& p2, PreparedLaunch& L) {
   constexpr int kBlockN = 256, kStages = 6, kCG = 2;
   using Cfg = TcCfg<kElemBytes, kBlockN, kStages, kCG>;
   auto kernel = gemm_tc_kernel<kElemBytes, kAMN1, kBMN1, kBlockN, kStages, kCG, false, true, kAMN2, kBMN2>;
@@ -973,45 +980,38 @@ cudaError_t launch_dual_cfg(const GemmProblem& g1, TcParams& p1, const GemmProbl
   if (!prepare_problem<kElemBytes, kAMN1, kBMN1, kBlockN, kStages, kCG>(g1, p1, m1)) return cudaErrorInvalidValue;
   if (!prepare_problem<kElemBytes, kAMN2, kBMN2, kBlockN, kStages, kCG>(g2, p2, m2)) return cudaErrorInvalidValue;
   if (p1.store_wide != p2.store_wide || p1.store_dbl != p2.store_dbl || g2.epi.Z != nullptr) return cudaErrorNotSupported;
-  DualParams d2;
-  d2.tmA = m2.tmA; d2.tmB = m2.tmB; d2.tmD = m2.tmD;
-  d2.p = p2;
+  L.d2.tmA = m2.tmA; L.d2.tmB = m2.tmB; L.d2.tmD = m2.tmD;
+  L.d2.p = p2;
   const long long items = static_cast<long long>(p1.main_tiles) + p2.main_tiles;
   const long long units = sm_budget() / kCG > 0 ? sm_budget() / kCG : 1;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>((items < units ? items : units) * kCG), 1, 1);
-  cfg.blockDim = dim3(kNumThreads, 1, 1);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = kCG;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kernel, m1.tmA, m1.tmB, m1.tmB, m1.tmD, m1.tmZ, p1, d2);
+  L.tmA = m1.tmA; L.tmB = m1.tmB; L.tmBh = m1.tmB; L.tmD = m1.tmD; L.tmZ = m1.tmZ;
+  L.p = p1;
+  L.grid = static_cast<unsigned>((items < units ? items : units) * kCG);
+  L.cluster = kCG;
+  L.smem = Cfg::kSmemBytes;
+  L.kernel = reinterpret_cast<const void*>(kernel);
+  return cudaSuccess;
 }
 
 struct TileChoice { int block_n, cta_group; };
 
 template <int kElemBytes, bool kAMN, bool kBMN>
-cudaError_t launch_bn(const GemmProblem& g, TcParams& p, TileChoice t, cudaStream_t s) {
-  if (t.cta_group == 2 && t.block_n == 256) return launch_cfg<kElemBytes, kAMN, kBMN, 256, 6, 2>(g, p, s);
-  if (t.block_n == 128) return launch_cfg<kElemBytes, kAMN, kBMN, 128, 6, 1>(g, p, s);
-  return launch_cfg<kElemBytes, kAMN, kBMN, 256, 4, 1>(g, p, s);
+cudaError_t prepare_bn(const GemmProblem& g, TcParams& p, TileChoice t, cudaStream_t s, PreparedLaunch& L) {
+  if (t.cta_group == 2 && t.block_n == 256) return prepare_cfg<kElemBytes, kAMN, kBMN, 256, 6, 2>(g, p, s, L);
+  if (t.block_n == 128) return prepare_cfg<kElemBytes, kAMN, kBMN, 128, 6, 1>(g, p, s, L);
+  return prepare_cfg<kElemBytes, kAMN, kBMN, 256, 4, 1>(g, p, s, L);
 }
 
 // Defined (explicitly instantiated) in the gemm_tc_inst_*.cu files.
 #define GE2B_TC_DECLARE(E, A, B) \
-  extern template cudaError_t launch_bn<E, A, B>(const GemmProblem&, TcParams&, TileChoice, cudaStream_t);
+  extern template cudaError_t prepare_bn<E, A, B>(const GemmProblem&, TcParams&, TileChoice, cudaStream_t, PreparedLaunch&);
 GE2B_TC_DECLARE(2, false, false) GE2B_TC_DECLARE(2, false, true) GE2B_TC_DECLARE(2, true, false) GE2B_TC_DECLARE(2, true, true)
 GE2B_TC_DECLARE(4, false, false) GE2B_TC_DECLARE(4, false, true) GE2B_TC_DECLARE(4, true, false) GE2B_TC_DECLARE(4, true, true)
 #undef GE2B_TC_DECLARE
-extern template cudaError_t launch_dual_cfg<2, false, false, true, true>(const GemmProblem&, TcParams&, const GemmProblem&,
-                                                                          TcParams&, cudaStream_t);
-extern template cudaError_t launch_dual_cfg<4, false, false, true, true>(const GemmProblem&, TcParams&, const GemmProblem&,
-                                                                          TcParams&, cudaStream_t);
+extern template cudaError_t prepare_dual_cfg<2, false, false, true, true>(const GemmProblem&, TcParams&, const GemmProblem&,
+                                                                           TcParams&, PreparedLaunch&);
+extern template cudaError_t prepare_dual_cfg<4, false, false, true, true>(const GemmProblem&, TcParams&, const GemmProblem&,
+                                                                           TcParams&, PreparedLaunch&);
 
 }  // namespace tc
 }  // namespace ge2b

@@ -128,6 +128,8 @@ Status GemmCudaLaunch(const Tensor& A, const Tensor& B, const Tensor* Bias, Tens
   f.act = static_cast<int>(attrs.act);
   f.leaky = attrs.leaky_slope;
   f.alpha = 1.f; f.beta = 0.f;
+  // the caller's lt_workspace (which the reference plumbs through and never reads) holds split-K partial sums
+  ge2b::ScopedLease lease(ws ? ws->lt_workspace : nullptr, ws ? ws->lt_workspace_bytes : 0, false);
   return from_rc(ge2b::dense_forward(f, reinterpret_cast<cudaStream_t>(stream)));
 }
 
@@ -198,6 +200,7 @@ Status GemmCudaBackward(const Tensor& A, const Tensor& B, const Tensor* C, const
   b.beta = (C && gC) ? 1.f : 0.f;
   b.scratch = ws ? ws->scratch : nullptr;
   b.scratch_bytes = ws ? ws->scratch_bytes : 0;
+  ge2b::ScopedLease lease(ws ? ws->lt_workspace : nullptr, ws ? ws->lt_workspace_bytes : 0, false);
   return from_rc(ge2b::dense_backward(b, reinterpret_cast<cudaStream_t>(stream)));
 }
 

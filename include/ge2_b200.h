@@ -191,7 +191,11 @@ int ge2_launch_sgd_update(const ge2_uintptr* bufs, int n, void* stream);
  * bufs = [A, B, C|0, gY, Z, gA|0, gB|0, gC|0, gBias|0, &ge2_gemm_bwd_typed_params_t]  (10 slots; scratch_bytes and
  * reuse_gz of the struct are ignored).  Returns -1 when M*N*sizeof(element) > GE2B_NOALLOC_SCRATCH_BYTES.
  * All calls on one GPU share the array: calls whose kernels may overlap on the GPU must be ordered by the caller.
- * The first call on a device performs a one-time address lookup; make it before any stream capture begins. */
+ * What the array has left after gZ holds the GEMMs' split-K partial sums; the library creates no scratch of its own
+ * during the call (a problem whose split does not fit runs unsplit).
+ * The first call on a device performs a one-time address lookup, and with lazy module loading it is also when the
+ * driver reserves the array's 16 MiB; make it before any stream capture begins and before a pool takes the
+ * whole GPU. */
 #define GE2B_NOALLOC_SCRATCH_BYTES (16u << 20)
 int ge2_launch_gemm_bias_act_bwd_noalloc(const ge2_uintptr* bufs, int n, void* stream);
 
@@ -248,6 +252,13 @@ int ge2b_conv2d_output_size(const ge2b_conv2d_params_t* p, int* Ho, int* Wo);
  * has launched in the process. */
 int ge2b_last_route(void);
 long long ge2b_launches_total(void);
+/* Split-K launches that ran unsplit because no scratch could be had: the stream was being captured before any split
+ * launch had warmed it up, or the call was one that must not allocate and lent too little.  A step whose captured
+ * form differs from its eager form shows up here. */
+long long ge2b_split_unavailable_total(void);
+/* Synchronises the current device and frees every split-K scratch buffer the library created (64 MiB per
+ * (device, stream) that ever ran a split launch).  The buffers come back on demand. */
+void ge2b_release_scratch(void);
 
 #ifdef __cplusplus
 }

@@ -70,7 +70,7 @@ struct GemmAttrs {
 };
 
 struct alignas(256) GemmWorkspace {
-  void* lt_workspace = nullptr;          // validated for 256-byte alignment, otherwise unused
+  void* lt_workspace = nullptr;          // 256-byte aligned; lent to the launch for split-K partial sums when >= 2 MiB
   std::size_t lt_workspace_bytes = 0;
   void* scratch = nullptr;               // gZ of the backward pass, row-major with ld = N
   std::size_t scratch_bytes = 0;         // 0 = not stated

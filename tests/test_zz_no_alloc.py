@@ -7,11 +7,23 @@ through the C ABI twice in a row, with different inputs, and compares each resul
 given an explicit scratch buffer: gA and gB must be bit-identical (same kernels, same order), gBias within the
 tolerance the other GPU tests use for it (it is summed with fp32 atomics).  The file name sorts last so that
 the test runs after every other one; it also passes alone in a fresh process.
+
+`test_noalloc_first_call_in_fresh_process_allocates_nothing` starts a new interpreter, makes the allocation-free
+call the FIRST thing the library does there (at a shape whose dX and dW launches are split along the reduction, which
+is where the ordinary entry creates a 64 MiB scratch): the first call may cost at most the driver's code loading (far
+below that scratch), every later call must leave the device's free memory exactly as it was.
 """
+import os
+import subprocess
+import sys
+import textwrap
+from pathlib import Path
+
 import numpy as np
 import pytest
 
 torch = pytest.importorskip("torch")
+ROOT = Path(__file__).resolve().parent.parent
 
 
 def _call(pkg, lib, entry, A, W, gY, Z, act, scratch):
@@ -54,6 +66,62 @@ def test_noalloc_backward_matches_ordinary_entry_twice(pkg, lib, dtype):
         assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
         np.testing.assert_allclose(got[2].cpu().numpy(), want[2].cpu().numpy(), rtol=1e-4, atol=3e-4)
     assert lib.ge2b_device_status(1) == 0
+
+
+_FRESH = textwrap.dedent('''
+    import importlib, sys
+    sys.path.insert(0, {root!r})
+    import torch
+    pkg = importlib.import_module("ai_framework-dev_b200")
+    lib = pkg.load_library()
+    L = pkg._lib
+    torch.cuda.set_device(0)
+    first_delta = []
+    for dtype, code in ((torch.float32, L.DT_F32), (torch.bfloat16, L.DT_BF16)):
+        # fp32 (TF32 math): K = N = 512 gives 16 k-blocks of 32, bf16: K = N = 1024 gives 16 k-blocks of 64; with 6 + 4
+        # tiles on 74 CTA pairs both dX and dW qualify for a split along the reduction
+        M, K, N = (640, 384, 512) if dtype == torch.float32 else (640, 1024, 1024)
+        g = torch.Generator(device="cuda").manual_seed(3)
+        A = torch.randn((M, K), device="cuda", generator=g).to(dtype)
+        W = (torch.randn((K, N), device="cuda", generator=g) / 16).to(dtype)
+        gY = torch.randn((M, N), device="cuda", generator=g).to(dtype)
+        Z = torch.randn((M, N), device="cuda", generator=g).to(dtype)
+        gA, gB = torch.empty_like(A), torch.empty_like(W)
+        gBias = torch.empty((N,), device="cuda")
+        p = L.ParamsBwdTyped()
+        p.base.M, p.base.N, p.base.K = M, N, K
+        p.base.alpha, p.base.beta = 1.0, 0.0
+        p.base.bias_kind, p.base.act_kind, p.base.leaky_slope = L.BIAS_PER_N, L.ACT["gelu"], 0.01
+        p.dtype, p.z_dtype, p.math = code, code, L.MATH_TENSOR
+        bufs = L.make_bufs([A.data_ptr(), W.data_ptr(), 0, gY.data_ptr(), Z.data_ptr(), gA.data_ptr(), gB.data_ptr(), 0,
+                            gBias.data_ptr()], p)
+        s = torch.cuda.current_stream().cuda_stream
+        torch.cuda.synchronize()
+        # First call of this kernel family in the process: the driver may load code now (a few MiB at most, none
+        # with eager module loading), but the 64 MiB split-K scratch the ordinary entry would create must not appear.
+        free0 = torch.cuda.mem_get_info()[0]
+        assert lib.ge2_launch_gemm_bias_act_bwd_noalloc(bufs, len(bufs), s) == 0
+        torch.cuda.synchronize()
+        free1 = torch.cuda.mem_get_info()[0]
+        assert free0 - free1 < (32 << 20), ("the first allocation-free call took device memory", dtype, free0 - free1)
+        first_delta.append(free0 - free1)
+        for _ in range(2):                             # later calls: not a byte
+            assert lib.ge2_launch_gemm_bias_act_bwd_noalloc(bufs, len(bufs), s) == 0
+        torch.cuda.synchronize()
+        free2 = torch.cuda.mem_get_info()[0]
+        assert free2 == free1, ("device memory changed across the allocation-free call", dtype, free1 - free2)
+        assert torch.isfinite(gA.float()).all() and torch.isfinite(gB.float()).all()
+    assert lib.ge2b_device_status(1) == 0
+    print("NOALLOC_OK", lib.ge2b_split_unavailable_total(), first_delta)
+''')
+
+
+@pytest.mark.gpu
+def test_noalloc_first_call_in_fresh_process_allocates_nothing(lib):
+    env = dict(os.environ, CUDA_MODULE_LOADING="EAGER")      # code is loaded with the library, not at first launch
+    r = subprocess.run([sys.executable, "-c", _FRESH.format(root=str(ROOT))], capture_output=True, text=True, timeout=600,
+                       env=env)
+    assert r.returncode == 0 and "NOALLOC_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
 def test_noalloc_backward_rejects_oversize(pkg, lib):
