@@ -15,7 +15,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from . import _lib
-from .ops_gemm import _act_code, _dt, _math_code, _stream_ptr
+from .ops_gemm import _act_code, _dt, _math_code, _one_device, _stream_ptr
 
 
 def _check_4d(t: torch.Tensor, name: str) -> Tuple[int, int, int, int]:
@@ -82,9 +82,11 @@ def forward_into(X, W, *, out, B=None, stride=(1, 1), padding=(0, 0), dilation=(
             raise ValueError(f"Z_saved must be a contiguous tensor of shape {oshape}")
     if p.with_bias and (B.dtype != torch.float32 or B.numel() != p.Cout):
         raise ValueError("B must be float32 with Cout elements")
-    _rc(lib.ge2b_conv2d_forward(C.byref(p), X.data_ptr(), W.data_ptr(), B.data_ptr() if p.with_bias else None,
-                                out.data_ptr(), Z_saved.data_ptr() if save_z else None, _stream_ptr(stream)),
-        "ge2b_conv2d_forward")
+    device = _one_device(X, W, out, B if p.with_bias else None, Z_saved if save_z else None)
+    with torch.cuda.device(device):
+        _rc(lib.ge2b_conv2d_forward(C.byref(p), X.data_ptr(), W.data_ptr(), B.data_ptr() if p.with_bias else None,
+                                    out.data_ptr(), Z_saved.data_ptr() if save_z else None, _stream_ptr(stream, device)),
+            "ge2b_conv2d_forward")
 
 
 def forward(X, W, B=None, *, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1, with_bias=False, act="none",
@@ -121,8 +123,10 @@ def backward_into(X, W, gY, Z, *, stride=(1, 1), padding=(0, 0), dilation=(1, 1)
     if gB_out is not None and (gB_out.dtype != torch.float32 or gB_out.numel() != p.Cout):
         raise ValueError("gB_out must be float32 with Cout elements")
     ptr = lambda t: t.data_ptr() if t is not None else None   # noqa: E731
-    _rc(lib.ge2b_conv2d_backward(C.byref(p), X.data_ptr(), W.data_ptr(), gY.data_ptr(), Z.data_ptr(), ptr(gW_out),
-                                 ptr(gB_out), ptr(gX_out), _stream_ptr(stream)), "ge2b_conv2d_backward")
+    device = _one_device(X, W, gY, Z, gX_out, gW_out, gB_out)
+    with torch.cuda.device(device):
+        _rc(lib.ge2b_conv2d_backward(C.byref(p), X.data_ptr(), W.data_ptr(), gY.data_ptr(), Z.data_ptr(), ptr(gW_out),
+                                     ptr(gB_out), ptr(gX_out), _stream_ptr(stream, device)), "ge2b_conv2d_backward")
 
 
 def backward(X, W, gY, Z, *, stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1, with_bias=False, act="none",

@@ -48,12 +48,28 @@ def _math_code(math: str) -> int:
     return MATH_TENSOR if math == "tf32" else MATH_FP32
 
 
-def _stream_ptr(stream) -> int:
+def _stream_ptr(stream, device=None) -> int:
     if stream is None:
-        return int(torch.cuda.current_stream().cuda_stream)
+        return int(torch.cuda.current_stream(device).cuda_stream)
     if isinstance(stream, torch.cuda.Stream):
         return int(stream.cuda_stream)
     return int(stream)
+
+
+def _one_device(*tensors) -> torch.device:
+    """All tensors of a call must live on ONE GPU: the launch layer builds tensor maps over their addresses and
+    launches on that device.  Raises before anything is launched."""
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise ValueError("expected CUDA tensors")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError(f"tensors of one call are on different devices: {dev} and {t.device}")
+    return dev
 
 
 def _bias_kind(bias: torch.Tensor, M: int, N: int) -> int:
@@ -122,6 +138,7 @@ def forward_into(A, B, *, out, bias=None, act="none", with_bias=False, leaky_slo
     if z_out is not None and _check_2d(z_out, "z_out") != (M, N):
         raise ValueError(f"z_out must be [{M},{N}]")
 
+    device = _one_device(A, B, out, bias, z_out)
     lib = _lib.load_library()
     p = _lib.ParamsTyped()
     b = p.base
@@ -146,7 +163,8 @@ def forward_into(A, B, *, out, bias=None, act="none", with_bias=False, leaky_slo
     if b.save_preact:
         ptrs.append(z_out.data_ptr())
     bufs = _lib.make_bufs(ptrs, p)
-    _lib.check(lib.ge2_launch_gemm_bias_act_typed(bufs, len(bufs), _stream_ptr(stream)), "forward")
+    with torch.cuda.device(device):
+        _lib.check(lib.ge2_launch_gemm_bias_act_typed(bufs, len(bufs), _stream_ptr(stream, device)), "forward")
 
 
 def forward(A, B, bias=None, *, act="none", with_bias=False, leaky_slope=0.01, stream=None, out=None, save_z=False,
@@ -206,6 +224,7 @@ def backward_into(A, B, gY, Z, *, act="none", with_bias=False, leaky_slope=0.01,
     if work_dZ is not None and work_dZ.numel() * work_dZ.element_size() < need:
         raise ValueError(f"work_dZ too small: need {need} bytes")
 
+    device = _one_device(A, B, gY, Z, C, gA_out, gB_out, gC_out, gBias_out, work_dZ)
     lib = _lib.load_library()
     p = _lib.ParamsBwdTyped()
     b = p.base
@@ -229,7 +248,8 @@ def backward_into(A, B, gY, Z, *, act="none", with_bias=False, leaky_slope=0.01,
     ptr = lambda t: t.data_ptr() if t is not None else 0   # noqa: E731
     bufs = _lib.make_bufs([ptr(A), ptr(B), ptr(C), ptr(gY), ptr(Z), ptr(gA_out), ptr(gB_out), ptr(gC_out),
                            ptr(gBias_out), ptr(work_dZ)], p)
-    _lib.check(lib.ge2_launch_gemm_bias_act_bwd_typed(bufs, len(bufs), _stream_ptr(stream)), "backward")
+    with torch.cuda.device(device):
+        _lib.check(lib.ge2_launch_gemm_bias_act_bwd_typed(bufs, len(bufs), _stream_ptr(stream, device)), "backward")
 
 
 def backward(A, B, gY, Z, *, act="none", with_bias=False, leaky_slope=0.01, C=None, want_gA=True, want_gB=True,
@@ -264,9 +284,16 @@ def forward_batched(A, B, *, out, trans_b=False, alpha=1.0, bias=None, act="none
     def flat(t, name):
         if t.dim() < 2 or t.stride(-1) != 1:
             raise ValueError(f"{name}: need [..., rows, cols] with unit inner stride")
-        t3 = t.reshape(-1, t.shape[-2], t.shape[-1]) if t.dim() != 3 else t
-        return t3
+        if t.dim() == 3:
+            return t
+        try:
+            # a view or nothing: a silent copy would hide an allocation and, for `out`, lose the result
+            return t.view(-1, t.shape[-2], t.shape[-1])
+        except RuntimeError:
+            raise ValueError(f"{name}: the leading dimensions do not flatten to one batch index with a constant "
+                             "stride (pass a contiguous or 3-D tensor)") from None
     A3, B3, O3 = flat(A, "A"), flat(B, "B"), flat(out, "out")
+    device = _one_device(A, B, out, bias if isinstance(bias, torch.Tensor) else None)
     batch = O3.shape[0]
     M, K = int(A3.shape[1]), int(A3.shape[2])
     N = int(B3.shape[1] if trans_b else B3.shape[2])
@@ -300,4 +327,5 @@ def forward_batched(A, B, *, out, trans_b=False, alpha=1.0, bias=None, act="none
     p.strideA, p.strideB, p.strideD = bstride(A3), bstride(B3), O3.stride(0) if batch > 1 else M * N
     ptrs = [A3.data_ptr(), B3.data_ptr(), O3.data_ptr()] + ([bias_t.data_ptr()] if bias_t is not None else [])
     bufs = _lib.make_bufs(ptrs, p)
-    _lib.check(lib.ge2_launch_gemm_bias_act_typed(bufs, len(bufs), _stream_ptr(stream)), "forward_batched")
+    with torch.cuda.device(device):
+        _lib.check(lib.ge2_launch_gemm_bias_act_typed(bufs, len(bufs), _stream_ptr(stream, device)), "forward_batched")

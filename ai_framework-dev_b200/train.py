@@ -23,10 +23,8 @@ _DT = {torch.float32: DT_F32, torch.float16: DT_F16, torch.bfloat16: DT_BF16}
 _RED = {"none": 0, "mean": 1, "sum": 2}
 
 
-def _stream_ptr(stream) -> int:
-    if stream is None:
-        return int(torch.cuda.current_stream().cuda_stream)
-    return int(stream.cuda_stream) if isinstance(stream, torch.cuda.Stream) else int(stream)
+_stream_ptr = ops_gemm._stream_ptr
+_one_device = ops_gemm._one_device
 
 
 def softmax_ce_fused(logits: torch.Tensor, labels: torch.Tensor, *, dlogits: torch.Tensor,
@@ -53,7 +51,10 @@ def softmax_ce_fused(logits: torch.Tensor, labels: torch.Tensor, *, dlogits: tor
     p.mean_denominator = mean_denominator
     bufs = _lib.make_bufs([logits.data_ptr(), labels.data_ptr(), dlogits.data_ptr(),
                            loss.data_ptr() if loss is not None else 0], p)
-    _lib.check(_lib.load_library().ge2_launch_softmax_ce_fused(bufs, len(bufs), _stream_ptr(stream)), "softmax_ce")
+    device = _one_device(logits, labels, dlogits, loss)
+    with torch.cuda.device(device):
+        _lib.check(_lib.load_library().ge2_launch_softmax_ce_fused(bufs, len(bufs), _stream_ptr(stream, device)),
+                   "softmax_ce")
 
 
 def sgd_update(param: torch.Tensor, grad: torch.Tensor, *, lr: float, velocity: Optional[torch.Tensor] = None,
@@ -76,7 +77,9 @@ def sgd_update(param: torch.Tensor, grad: torch.Tensor, *, lr: float, velocity: 
     p.grad_scale = float(grad_scale)
     bufs = _lib.make_bufs([param.data_ptr(), grad.data_ptr(), velocity.data_ptr() if velocity is not None else 0,
                            low.data_ptr() if low is not None else 0], p)
-    _lib.check(_lib.load_library().ge2_launch_sgd_update(bufs, len(bufs), _stream_ptr(stream)), "sgd_update")
+    device = _one_device(param, grad, velocity, low)
+    with torch.cuda.device(device):
+        _lib.check(_lib.load_library().ge2_launch_sgd_update(bufs, len(bufs), _stream_ptr(stream, device)), "sgd_update")
 
 
 def shard_rows(global_batch: int, world: int, rank: int):
@@ -145,11 +148,24 @@ class DenseStackTrainer:
         self.loss = torch.zeros((1,), device=dev, dtype=torch.float32)
         self.comm = torch.cuda.Stream(device=dev) if self.world > 1 else None
         self.compiled = True
-        for _ in range(2):            # warm-up outside capture: function attributes, lazy scratch, NCCL channels
+        # Warm-up outside capture (function attributes, per-stream split-K scratch, NCCL channels).  A step updates
+        # the parameters, so they are saved and put back: training starts from the initial weights.
+        saved = [t.clone() for t in (*self.W32, *self.W, *self.b)]
+        want_graph = bool(capture) and (self.world == 1 or capture == "with_collectives")
+        cap = torch.cuda.Stream(device=dev) if want_graph else None
+        self.run_step()
+        if cap is not None:           # the stream that will be captured must have run the step once itself
+            cap.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(cap):
+                self.run_step()
+            torch.cuda.current_stream().wait_stream(cap)
+        else:
             self.run_step()
         torch.cuda.synchronize()
-        if capture and (self.world == 1 or capture == "with_collectives"):
-            cap = torch.cuda.Stream(device=dev)
+        for t, s0 in zip((*self.W32, *self.W, *self.b), saved):
+            t.copy_(s0)
+        torch.cuda.synchronize()
+        if want_graph:
             cap.wait_stream(torch.cuda.current_stream())
             self.graph = torch.cuda.CUDAGraph()
             # thread-local capture mode: the collective library's watchdog thread may touch the CUDA API meanwhile
@@ -195,13 +211,22 @@ class DenseStackTrainer:
             self.run_step()
 
     def one_step(self, X: torch.Tensor, labels: torch.Tensor) -> float:
-        """Copies the batch into the static buffers, runs one step and returns the (local-shard) mean loss."""
+        """Copies the batch into the static buffers, runs one step and returns this replica's share of the mean loss
+        (see global_loss)."""
         if not self.compiled:
             self.compile()
         self.X.copy_(X, non_blocking=True)
         self.labels.copy_(labels, non_blocking=True)
         self.launch()
         return float(self.loss.item())
+
+    def global_loss(self) -> float:
+        """Mean loss over the GLOBAL batch: every replica holds its rows' sum over the global denominator, so the
+        replicas' values add up to the loss (the same number whatever the number of replicas)."""
+        t = self.loss.clone()
+        if self.world > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+        return float(t.item())
 
     def flop_per_step(self) -> float:
         """2*B*sum(d_i*d_{i+1}) forward, twice that backward (dX is computed for the first layer too)."""

@@ -80,3 +80,20 @@ def test_cpp_parameter_block_and_registry_on_gpu(pkg, lib, tmp_path):
                     f"-Wl,-rpath,{libdir}"], check=True)
     r = subprocess.run([str(exe)], capture_output=True, text=True)
     assert r.returncode == 0 and r.stdout.strip() == "ok", r.stdout + r.stderr
+
+
+def test_mixed_device_call_is_refused_before_any_launch(pkg):
+    """All tensors of one call must be on one GPU; checked in Python before the C ABI is reached (no GPU needed:
+    the tensors are stand-ins that only carry a device)."""
+    from unittest import mock
+    import torch
+    a, b = mock.Mock(spec=torch.Tensor), mock.Mock(spec=torch.Tensor)
+    a.is_cuda = b.is_cuda = True
+    a.device, b.device = torch.device("cuda", 0), torch.device("cuda", 1)
+    with pytest.raises(ValueError, match="different devices"):
+        pkg.ops_gemm._one_device(a, None, b)
+    assert pkg.ops_gemm._one_device(a, None, a) == torch.device("cuda", 0)
+    with pytest.raises(ValueError):
+        pkg.ops_gemm._one_device(torch.zeros(2))            # a CPU tensor
+    with pytest.raises(ValueError):
+        pkg.ops_gemm.forward_into(torch.zeros(2, 2), torch.zeros(2, 2), out=torch.zeros(2, 2))

@@ -71,9 +71,11 @@ def test_dense_stack_training_steps_match_float64(pkg, lib, oracle, capture):
     W = [w.cpu().numpy().astype(np.float64) for w in tr.W32]
     b = [x.cpu().numpy().astype(np.float64) for x in tr.b]
     tr.compile(capture=capture)
-    # compile() ran warm-up steps on zero inputs: start both sides from the trainer's current state
-    W = [w.cpu().numpy().astype(np.float64) for w in tr.W32]
-    b = [x.cpu().numpy().astype(np.float64) for x in tr.b]
+    # compile() warms the step up and must leave the parameters as they were initialised
+    for w0, w in zip(W, tr.W32):
+        assert np.array_equal(w0, w.cpu().numpy().astype(np.float64)), "compile() changed the weights"
+    for b0, x in zip(b, tr.b):
+        assert np.array_equal(b0, x.cpu().numpy().astype(np.float64)), "compile() changed the biases"
     W_start = [w.copy() for w in W]
     rng = np.random.default_rng(0)
     for step in range(3):
