@@ -47,7 +47,7 @@ class ParamsTyped(C.Structure):
 class ParamsSoftmaxCE(C.Structure):
     _fields_ = [("M", C.c_int), ("C", C.c_int), ("ld_logits", C.c_int), ("ld_dlogits", C.c_int),
                 ("dtype", C.c_int), ("grad_dtype", C.c_int), ("reduction", C.c_int), ("ignore_index", C.c_int),
-                ("grad_scale", C.c_float), ("mean_denominator", C.c_int)]
+                ("grad_scale", C.c_float), ("mean_denominator", C.c_int), ("label_smoothing", C.c_float)]
 
 
 class ParamsSGD(C.Structure):
@@ -85,7 +85,7 @@ EXPORTS = [
     "ge2_launch_gemm_bias_act_typed", "ge2_launch_gemm_bias_act_bwd_typed",
     "ge2b_backward_scratch_bytes", "ge2b_device_status", "ge2b_sm_count", "ge2b_set_sm_limit", "ge2b_version",
     "ge2b_last_route", "ge2b_launches_total", "ge2b_register_gemm_kernels",
-    "ge2b_split_unavailable_total", "ge2b_release_scratch",
+    "ge2b_split_unavailable_total", "ge2b_release_scratch", "ge2b_selftest_wait_expiry",
     "ge2b_dense_plan_create", "ge2b_dense_plan_step", "ge2b_dense_plan_destroy",
     "ge2b_dense_plan_submit", "ge2b_dense_plan_wait",
     "ge2_launch_gemm_bias_act_bwd_noalloc",
@@ -127,6 +127,8 @@ def load_library() -> C.CDLL:
     lib.ge2b_launches_total.restype = C.c_longlong
     lib.ge2b_split_unavailable_total.restype = C.c_longlong
     lib.ge2b_release_scratch.restype = None
+    lib.ge2b_selftest_wait_expiry.argtypes = [C.c_longlong, C.POINTER(C.c_int), C.c_void_p]
+    lib.ge2b_selftest_wait_expiry.restype = C.c_int
     lib.ge2b_dense_plan_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                            C.c_float, C.c_int, C.c_int]
     lib.ge2b_dense_plan_create.restype = C.c_int

@@ -51,6 +51,7 @@ int default_fp32_math() {
 }
 
 int dense_forward(const DenseForward& f, cudaStream_t s) {
+  NvtxRange range("gemm.fwd");
   if (f.M <= 0 || f.N <= 0 || f.K <= 0 || !f.A || !f.B || !f.D) return kBadArgs;
   if (f.dtype != kF32 && f.dtype != kF16 && f.dtype != kBF16) return kBadArgs;
   const int batch = f.batch < 1 ? 1 : f.batch;
@@ -76,6 +77,7 @@ int dense_forward(const DenseForward& f, cudaStream_t s) {
 }
 
 int dense_backward(const DenseBackward& b, cudaStream_t s) {
+  NvtxRange range("gemm.bwd");
   if (b.M <= 0 || b.N <= 0 || b.K <= 0 || !b.gY || !b.Z) return kBadArgs;
   if ((b.gA && !b.B) || (b.gB && !b.A)) return kBadArgs;
   if (b.ldgY < b.N || b.ldZ < b.N) return kBadArgs;
@@ -122,7 +124,10 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
   pa.gC = fuse_gc ? b.gC : nullptr; pa.ldgC = b.ldgC; pa.gc_dtype = b.dtype; pa.beta = b.beta;
   pa.gBias = want_bias ? b.gBias : nullptr; pa.bias_kind = want_bias ? b.bias_kind : kBiasNone;
   pa.act = b.act; pa.leaky = b.leaky;
-  if (launch_bwd_prologue(pa, s) != cudaSuccess) return finish(kCudaError);
+  {
+    NvtxRange epi_range("bwd.epilogue");
+    if (launch_bwd_prologue(pa, s) != cudaSuccess) return finish(kCudaError);
+  }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   }
 
@@ -133,6 +138,7 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
     return e;
   };
 
+  NvtxRange gemms_range("bwd.gemms");
   GemmProblem ga{}, gb{};
   if (b.gA) {   // gA[M,K] = alpha * gZ[M,N] . B[K,N]^T : reduction over N, contiguous in both operands
     if (b.ldb < b.N || b.ldgA < b.K) return finish(kBadArgs);

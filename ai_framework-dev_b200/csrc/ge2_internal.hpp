@@ -10,6 +10,26 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 
+// Profiler ranges with the reference's names ("gemm.fwd", "gemm.bwd", "bwd.epilogue", "bwd.gemms":
+// backends/cuda/ops/gemm/launcher.cu:154,287, kernels/regemm_backward.cu:201,262), compiled in under the reference's
+// own switch AI_USE_NVTX (backends/cuda/ops/_common/shim/ai_nvtx.hpp:8-16).  Header-only NVTX: without a profiler
+// attached a range costs a few nanoseconds.
+#if defined(AI_USE_NVTX) || defined(USE_NVTX) || defined(AI_ENABLE_NVTX)
+#include <nvtx3/nvToolsExt.h>
+namespace ge2b {
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+  NvtxRange(const NvtxRange&) = delete;
+  NvtxRange& operator=(const NvtxRange&) = delete;
+};
+}  // namespace ge2b
+#else
+namespace ge2b {
+struct NvtxRange { explicit NvtxRange(const char*) {} };
+}  // namespace ge2b
+#endif
+
 namespace ge2b {
 
 enum : int { kActNone = 0, kActReLU = 1, kActLeaky = 2, kActGELU = 3, kActSigmoid = 4, kActTanh = 5 };

@@ -44,14 +44,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // false so that all roles leave their loops.  Budget is in SM clock cycles.
 constexpr long long kWaitBudgetCycles = 4000000000ll;   // about 2 s at 1.9 GHz
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long budget_cycles = kWaitBudgetCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0x3ffu) == 0u) {
       if (*abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) { *abort_flag = 1; return false; }
+      if (clock64() - t0 > budget_cycles) { *abort_flag = 1; return false; }
     }
   }
   return true;

@@ -6,7 +6,9 @@
 //     word (Mean divides by the number of rows, ignored rows included, as the native op does:
 //     cross_entropy/launcher.cu:114-115).  Additions: 16-bit logits / gradients, a row is read once into registers
 //     when it has at most 2048 classes, `grad_scale` folds the 1/batch of a mean loss (or 1/global batch under data
-//     parallelism) into the gradient, and an ignore_index row yields zero loss and zero gradient.
+//     parallelism) into the gradient, an ignore_index row yields zero loss and zero gradient, and label smoothing
+//     follows the reference's separate forward / backward ops (kernels.cu:96-101, 188-195):
+//     loss_row = (1-ls)(logZ - x_t) + ls (logZ - mean(x)),  target = (1-ls) onehot + ls / C.
 //   * SGD update on fp32 master weights with an optional low-precision copy for the next forward:
 //       g' = grad_scale * g (+ wd * p when decay is L2);  v = mu * v + (1 - damp) * g';  step = nesterov ? g' + mu * v : v
 //       p -= lr * step (+ lr * wd * p when decay is decoupled)
@@ -44,6 +46,7 @@ struct CeParams {
   float* loss;                 // null, [M] (reduction none) or [1]
   int M, C, reduction, ignore_index;
   float grad_scale, loss_scale;
+  float ls;                    // label smoothing: target = (1 - ls) * onehot + ls / C
 };
 
 // kCache > 0: a lane keeps kCache values of its row in registers (rows of up to 32*kCache classes are read once);
@@ -62,17 +65,24 @@ softmax_ce_fused_kernel(const CeParams p) {
 
   float cache[kMaxCached];
   float m = -CUDART_INF_F;
+  float sumx = 0.f;            // sum of the row's logits, for the smoothed target's uniform part
   if constexpr (kCached) {
 #pragma unroll
     for (int i = 0; i < kMaxCached; ++i) {
       const int c = lane + 32 * i;
       cache[i] = (c < p.C) ? load_as_f32(p.logits, xo + c, p.x_dtype) : -CUDART_INF_F;
       m = fmaxf(m, cache[i]);
+      if (c < p.C) sumx += cache[i];
     }
   } else {
-    for (int c = lane; c < p.C; c += 32) m = fmaxf(m, load_as_f32(p.logits, xo + c, p.x_dtype));
+    for (int c = lane; c < p.C; c += 32) {
+      const float x = load_as_f32(p.logits, xo + c, p.x_dtype);
+      m = fmaxf(m, x);
+      sumx += x;
+    }
   }
   m = warp_max(m);
+  if (p.ls != 0.f) sumx = warp_sum(sumx);
 
   float s = 0.f;
   if constexpr (kCached) {
@@ -87,23 +97,29 @@ softmax_ce_fused_kernel(const CeParams p) {
   s = warp_sum(s);
 
   if (lane == 0 && p.loss != nullptr) {
-    const float loss_row = ignored ? 0.f : (m + logf(s)) - load_as_f32(p.logits, xo + t, p.x_dtype);
+    float loss_row = 0.f;
+    if (!ignored) {
+      const float logZ = m + logf(s);
+      loss_row = logZ - load_as_f32(p.logits, xo + t, p.x_dtype);
+      if (p.ls != 0.f) loss_row = (1.f - p.ls) * loss_row + p.ls * (logZ - sumx / static_cast<float>(p.C));
+    }
     if (p.reduction == 0) p.loss[row] = loss_row;
     else if (!ignored)    atomicAdd(p.loss, loss_row * p.loss_scale);
   }
 
   const float inv = ignored ? 0.f : p.grad_scale / s;
-  const float hot = ignored ? 0.f : p.grad_scale;
+  const float hot = ignored ? 0.f : p.grad_scale * (1.f - p.ls);
+  const float uni = ignored ? 0.f : p.grad_scale * p.ls / static_cast<float>(p.C);
   if constexpr (kCached) {
 #pragma unroll
     for (int i = 0; i < kMaxCached; ++i) {
       const int c = lane + 32 * i;
-      if (c < p.C) store_from_f32(p.dlogits, dox + c, p.d_dtype, cache[i] * inv - (c == t ? hot : 0.f));
+      if (c < p.C) store_from_f32(p.dlogits, dox + c, p.d_dtype, cache[i] * inv - (c == t ? hot : 0.f) - uni);
     }
   } else {
     for (int c = lane; c < p.C; c += 32) {
       const float e = __expf(load_as_f32(p.logits, xo + c, p.x_dtype) - m);
-      store_from_f32(p.dlogits, dox + c, p.d_dtype, e * inv - (c == t ? hot : 0.f));
+      store_from_f32(p.dlogits, dox + c, p.d_dtype, e * inv - (c == t ? hot : 0.f) - uni);
     }
   }
 }
@@ -154,6 +170,8 @@ int ge2_launch_softmax_ce_fused(const ge2_uintptr* bufs, int n, void* stream) {
   p.loss = reinterpret_cast<float*>(bufs[3]);
   p.M = q->M; p.C = q->C; p.reduction = q->reduction; p.ignore_index = q->ignore_index;
   p.grad_scale = q->grad_scale;
+  p.ls = q->label_smoothing;
+  if (!(p.ls >= 0.f && p.ls < 1.f)) return kBadArgs;
   // Mean: divide by the stated denominator (the global batch under data parallelism), default the row count
   p.loss_scale = q->reduction == 1 ? 1.f / static_cast<float>(q->mean_denominator > 0 ? q->mean_denominator : q->M) : 1.f;
   if (p.loss && q->reduction != 0 && cudaMemsetAsync(p.loss, 0, sizeof(float), s) != cudaSuccess) return kCudaError;

@@ -29,7 +29,8 @@ _one_device = ops_gemm._one_device
 
 def softmax_ce_fused(logits: torch.Tensor, labels: torch.Tensor, *, dlogits: torch.Tensor,
                      loss: Optional[torch.Tensor] = None, reduction: str = "mean", ignore_index: int = -1,
-                     grad_scale: Optional[float] = None, mean_denominator: int = 0, stream=None) -> None:
+                     grad_scale: Optional[float] = None, mean_denominator: int = 0, label_smoothing: float = 0.0,
+                     stream=None) -> None:
     """loss = CE(softmax(logits), labels) and dlogits = (softmax - onehot) * grad_scale in one pass.
     labels are int32.  grad_scale defaults to 1/rows for "mean" and 1 otherwise; pass 1/global_batch (and
     mean_denominator = global_batch) when the rows are one shard of a data-parallel batch."""
@@ -49,6 +50,7 @@ def softmax_ce_fused(logits: torch.Tensor, labels: torch.Tensor, *, dlogits: tor
     denom = mean_denominator if mean_denominator > 0 else M
     p.grad_scale = float(grad_scale) if grad_scale is not None else (1.0 / denom if reduction == "mean" else 1.0)
     p.mean_denominator = mean_denominator
+    p.label_smoothing = float(label_smoothing)
     bufs = _lib.make_bufs([logits.data_ptr(), labels.data_ptr(), dlogits.data_ptr(),
                            loss.data_ptr() if loss is not None else 0], p)
     device = _one_device(logits, labels, dlogits, loss)

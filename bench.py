@@ -325,6 +325,15 @@ def run_ours(args):
         barrier()
         print(json.dumps({"profile": "conv", "status": lib.ge2b_device_status(0)}), flush=True)
         return
+    if args.profile == "qk":
+        # the batched attention GEMM S = (Q.K^T)/sqrt(d) at B*H = 128, L = 2048, d = 128, four launches
+        Q, Kt = (torch.randn((8, 16, 2048, 128), device=dev).bfloat16() for _ in range(2))
+        S = torch.empty((8, 16, 2048, 2048), device=dev, dtype=torch.bfloat16)
+        for _ in range(4):
+            og.forward_batched(Q, Kt, out=S, trans_b=True, alpha=1.0 / 128 ** 0.5)
+        barrier()
+        print(json.dumps({"profile": "qk", "status": lib.ge2b_device_status(0)}), flush=True)
+        return
     if args.profile:
         # a short, fixed launch sequence for a profiler capture: 2 warm-up steps, then 2 more
         for _ in range(4):
@@ -672,6 +681,36 @@ def run_sweep(args):
             ts.append(e0.elapsed_time(e1) / reps)
         return statistics.median(ts)
 
+    def timeit_graph(fn, iters, reps=16):
+        """the same launches captured once into a CUDA graph and replayed: no host work between the kernels"""
+        st = torch.cuda.Stream()
+        st.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(st):
+            fn()                                   # the capture stream's own first (un-captured) run
+        st.synchronize()
+        g_ = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_, stream=st, capture_error_mode="thread_local"):
+            for _ in range(reps):
+                fn()
+        torch.cuda.current_stream().wait_stream(st)
+        g_.replay()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g_.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) / reps)
+        return statistics.median(ts)
+
+    hbm_peak = 6547.2
+    try:
+        hbm_peak = float(json.loads((ROOT / "MEASURED_PEAKS.json").read_text())["hbm_gbs"])
+    except Exception:
+        pass
+
     def dense_point(Mx, Nx, Kx, dtype, math, act, iters, with_ref=False):
         tdt = torch.bfloat16 if dtype == "bf16" else torch.float32
         X = torch.randn((Mx, Kx), device="cuda").to(tdt)
@@ -686,10 +725,19 @@ def run_sweep(args):
         g = lambda: og.backward_into(X, W, dY, Z, act=act, with_bias=True, gA_out=dX, gB_out=dW, gBias_out=db,  # noqa: E731
                                      work_dZ=work, math=math)
         tf, tb = timeit(f, iters), timeit(g, iters)
+        small = Mx * Nx * Kx <= 4096 ** 3
+        tfg, tbg = (timeit_graph(f, iters), timeit_graph(g, iters)) if small else (tf, tb)
+        esz = 2 if dtype == "bf16" else 4
+        fwd_bytes = esz * (Mx * Kx + Kx * Nx + 2 * Mx * Nx) + 4 * Nx          # X, W, bias in; Y, Z out
         line = {"sweep": "dense", "M": Mx, "N": Nx, "K": Kx, "dtype": dtype, "math": math, "act": act,
                 "fwd_ms": round(tf, 4), "fwd_tflops": round(2.0 * Mx * Nx * Kx / tf / 1e9, 1),
                 "bwd_ms": round(tb, 4), "bwd_tflops": round(4.0 * Mx * Nx * Kx / tb / 1e9, 1),
                 "fwd_bwd_tflops": round(6.0 * Mx * Nx * Kx / (tf + tb) / 1e9, 1),
+                "graph": {"fwd_ms": round(tfg, 4), "bwd_ms": round(tbg, 4),
+                          "fwd_tflops": round(2.0 * Mx * Nx * Kx / tfg / 1e9, 1),
+                          "bwd_tflops": round(4.0 * Mx * Nx * Kx / tbg / 1e9, 1),
+                          "fwd_GBs": round(fwd_bytes / tfg / 1e6, 1),
+                          "fwd_frac_of_hbm": round(fwd_bytes / tfg / 1e6 / hbm_peak, 3)} if small else None,
                 "route": {1: "exact fp32 (CUDA cores)", 2: "tcgen05"}.get(lib.ge2b_last_route())}
         if with_ref and ref is not None and dtype == "fp32":
             scratch = torch.empty((Mx, Nx), device="cuda")
@@ -703,15 +751,19 @@ def run_sweep(args):
                                              "bwd_ms": round(trb, 4), "bwd_tflops": round(4.0 * Mx * Nx * Kx / trb / 1e9, 2)}
         print(json.dumps(line), flush=True)
 
+    quick = args.sweep_quick
     for n in (1024, 2048, 4096, 8192, 16384):
         for dtype, math in (("bf16", "fp32"), ("fp32", "tf32")):
-            for act in ("none", "relu", "gelu", "sigmoid"):
+            for act in (("gelu",) if quick else ("none", "relu", "gelu", "sigmoid")):
                 dense_point(n, n, n, dtype, math, act, 5 if n <= 8192 else 2)
     for m in (16, 32, 64, 128):
         for dtype, math in (("bf16", "fp32"), ("fp32", "tf32")):
             dense_point(m, 8192, 8192, dtype, math, "gelu", 7)
     for n in (256, 1024, 2048, 4096):          # the parity path and the reference's own kernels on the same box
         dense_point(n, n if n > 256 else 512, n if n > 256 else 512, "fp32", "fp32", "relu", 3, with_ref=True)
+    if quick:
+        assert lib.ge2b_device_status(0) == 0
+        return
 
     # batched attention GEMMs: B*H = 128 slices, L = 2048, d = 128, bf16, fp32 accumulate
     Bn, H, L, d = 8, 16, 2048, 128
@@ -786,12 +838,13 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile", default="", choices=["", "fwd", "step", "conv"],
+    ap.add_argument("--profile", default="", choices=["", "fwd", "step", "conv", "qk"],
                     help="run a short fixed launch sequence (for ncu) instead of the benchmark")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU-oracle leg (profiling runs)")
     ap.add_argument("--skip-mlp", action="store_true", help="omit the MLP training-step leg")
     ap.add_argument("--skip-target", action="store_true", help="omit the M=N=K=8192 block")
     ap.add_argument("--sweep", action="store_true", help="print the shape sweep (one JSON line per point) and exit")
+    ap.add_argument("--sweep-quick", action="store_true", help="with --sweep: GELU only, dense points only")
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)

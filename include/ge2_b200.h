@@ -159,6 +159,8 @@ typedef struct {
   int ignore_index;           /* rows with this label give zero loss and zero gradient; -1 disables */
   float grad_scale;           /* dlogits = (softmax - onehot) * grad_scale; pass 1/batch for a mean loss */
   int mean_denominator;       /* <= 0: M.  The global batch when the rows are one shard of it. */
+  float label_smoothing;      /* target = (1 - ls) * onehot + ls / C, as the reference's separate CE ops
+                                 (cross_entropy/kernels.cu:96-101,188-195); 0 = off */
 } ge2_softmax_ce_params_t;
 
 /* Fused softmax + cross-entropy from logits, forward and backward in one pass.
@@ -256,6 +258,12 @@ long long ge2b_launches_total(void);
  * launch had warmed it up, or the call was one that must not allocate and lent too little.  A step whose captured
  * form differs from its eager form shows up here. */
 long long ge2b_split_unavailable_total(void);
+/* Self-test of the kernels' bounded waits: launches a one-warp kernel that waits, with a budget of `budget_cycles` SM
+ * clocks (at most 2e8), on an mbarrier nothing arrives at.  The wait gives up, the kernel ORs the "wait timed out" bit
+ * (1) into the device status word and returns; report4 (host memory, 4 ints) receives {wait result (0 = gave up),
+ * abort flag, cycles waited, result of a second waiter that found the abort flag set}.  Synchronises the stream.
+ * Clear the status word with ge2b_device_status(1) afterwards. */
+int ge2b_selftest_wait_expiry(long long budget_cycles, int* report4, void* stream);
 /* Synchronises the current device and frees every split-K scratch buffer the library created (64 MiB per
  * (device, stream) that ever ran a split launch).  The buffers come back on demand. */
 void ge2b_release_scratch(void);

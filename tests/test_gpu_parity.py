@@ -497,3 +497,23 @@ def test_backward_pair_in_one_launch(pkg, lib, oracle, dtype, math, shape):
     pkg.ops_gemm.backward_into(tX, tW, tdY, tZ, **kw)
     torch.cuda.synchronize()
     assert torch.equal(gA, gA2) and torch.equal(gB, gB2)
+
+
+# --------------------------------------------------------------------------- the bounded wait, made to run out
+def test_bounded_wait_expires_and_reports(pkg, lib):
+    """Every mbarrier wait in the GEMM kernels is bounded; this runs the expiry path itself: a barrier nothing arrives
+    at, a budget of a million clocks.  The wait returns false, the status word gets its bit, the context lives on."""
+    rep = (C.c_int * 4)()
+    assert lib.ge2b_device_status(1) == 0
+    assert lib.ge2b_selftest_wait_expiry(1_000_000, rep, torch.cuda.current_stream().cuda_stream) == 0
+    gave_up, abort_flag, cycles, second = list(rep)
+    assert gave_up == 0 and abort_flag == 1 and second == 0
+    assert 1_000_000 <= cycles < 50_000_000                 # waited its budget, not forever
+    assert lib.ge2b_device_status(1) == 1                   # kErrWaitTimeout, read and cleared
+    assert lib.ge2b_device_status(0) == 0
+    # the context is still usable: an ordinary launch works and leaves the status clean
+    x = torch.randn(256, 256, device="cuda").bfloat16()
+    y = pkg.ops_gemm.forward(x, x)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y.float()).all() and lib.ge2b_device_status(0) == 0
+    assert lib.ge2b_selftest_wait_expiry(0, rep, None) == -1            # budget out of range

@@ -89,3 +89,94 @@ def test_dense_stack_training_steps_match_float64(pkg, lib, oracle, capture):
         want = W[i] - W_start[i]
         assert oracle.rel_fro(got, want) <= 5e-2, i
         assert torch.equal(tr.W[i], tr.W32[i].bfloat16())
+
+
+# --------------------------------------------------------------------------- the reference's own ops as the oracle
+def _ref_train():
+    import ctypes as C
+    from pathlib import Path
+    so = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "libref_train.so"
+    if not so.exists():
+        pytest.skip("oracle/_ref/libref_train.so was not built (needs the reference tree at build time)")
+    r = C.CDLL(str(so))
+    vp, i, f = C.c_void_p, C.c_int, C.c_float
+    r.ref_ce_fused.argtypes = [vp, vp, vp, vp, i, i, i, vp]
+    r.ref_ce_forward.argtypes = [vp, vp, vp, i, i, i, i, f, vp]
+    r.ref_ce_backward.argtypes = [vp, vp, vp, i, i, i, i, f, vp]
+    r.ref_sgd.argtypes = [vp, vp, vp, C.c_longlong, f, f, f, i, f, vp]
+    for fn in (r.ref_ce_fused, r.ref_ce_forward, r.ref_ce_backward, r.ref_sgd):
+        fn.restype = i
+    return r
+
+
+@pytest.mark.parametrize("C", [10, 1024, 1500, 3000])
+@pytest.mark.parametrize("red", ["none", "mean", "sum"])
+def test_softmax_ce_against_reference_fused_op(pkg, lib, C, red):
+    """SoftmaxCEFusedForwardBackwardCudaLaunch (cross_entropy/launcher.cu:238-306) compiled for sm_100a, on the same
+    device buffers.  Its gradient is softmax - onehot WITHOUT the 1/M of a mean loss (kernels.cu:365-369), which is
+    grad_scale = 1 here; its mean loss divides by every row (kernels.cu:356-358)."""
+    ref = _ref_train()
+    g = torch.Generator(device="cuda").manual_seed(C)
+    M = 300
+    x = torch.randn((M, C), device="cuda", generator=g) * 3
+    lab = torch.randint(0, C, (M,), device="cuda", generator=g, dtype=torch.int32)
+    code = {"none": 0, "mean": 1, "sum": 2}[red]
+    n_loss = M if red == "none" else 1
+    d_ref, l_ref = torch.empty_like(x), torch.full((n_loss,), 5.0, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    assert ref.ref_ce_fused(x.data_ptr(), lab.data_ptr(), d_ref.data_ptr(), l_ref.data_ptr(), M, C, code, s) == 0
+    d, loss = torch.empty_like(x), torch.full((n_loss,), 7.0, device="cuda")
+    pkg.softmax_ce_fused(x, lab, dlogits=d, loss=loss, reduction=red, grad_scale=1.0)
+    torch.cuda.synchronize()
+    assert float((d - d_ref).abs().max()) <= 1e-6
+    # scalar losses are atomic sums of M terms in both libraries: order differs
+    np.testing.assert_allclose(loss.cpu().numpy(), l_ref.cpu().numpy(), rtol=1e-6 if red == "none" else 2e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("ls", [0.0, 0.1])
+@pytest.mark.parametrize("red", ["none", "mean", "sum"])
+def test_softmax_ce_against_reference_separate_ops(pkg, lib, red, ls):
+    """CrossEntropyCudaLaunch / CrossEntropyCudaBackwardLaunch (from logits): ignore_index rows give zero loss and zero
+    gradient but still count in the mean's denominator (launcher.cu:114-115), label smoothing as kernels.cu:96-101."""
+    ref = _ref_train()
+    g = torch.Generator(device="cuda").manual_seed(7)
+    M, C, ign = 513, 777, 5
+    x = torch.randn((M, C), device="cuda", generator=g) * 2
+    lab = torch.randint(0, C, (M,), device="cuda", generator=g, dtype=torch.int32)
+    lab[::9] = ign                                         # about 11 % ignored rows
+    code = {"none": 0, "mean": 1, "sum": 2}[red]
+    n_loss = M if red == "none" else 1
+    d_ref, l_ref = torch.empty_like(x), torch.full((n_loss,), 5.0, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    assert ref.ref_ce_forward(x.data_ptr(), lab.data_ptr(), l_ref.data_ptr(), M, C, code, ign, ls, s) == 0
+    assert ref.ref_ce_backward(x.data_ptr(), lab.data_ptr(), d_ref.data_ptr(), M, C, code, ign, ls, s) == 0
+    d, loss = torch.empty_like(x), torch.full((n_loss,), 7.0, device="cuda")
+    pkg.softmax_ce_fused(x, lab, dlogits=d, loss=loss, reduction=red, ignore_index=ign, label_smoothing=ls)
+    torch.cuda.synchronize()
+    assert float((d - d_ref).abs().max()) <= 1e-6
+    assert torch.all(d[::9] == 0)
+    np.testing.assert_allclose(loss.cpu().numpy(), l_ref.cpu().numpy(), rtol=2e-6 if red == "none" else 2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("momentum,dampening,nesterov,wd", [(0.0, 0.0, False, 0.0), (0.9, 0.0, True, 0.0),
+                                                             (0.9, 0.1, False, 0.01), (0.0, 0.0, False, 0.01)])
+def test_sgd_against_reference_op(pkg, lib, momentum, dampening, nesterov, wd):
+    """SGDCudaUpdateLaunch (optimizer/kernels.cu:33-66): L2 decay added to the gradient, momentum / Nesterov."""
+    ref = _ref_train()
+    g = torch.Generator(device="cuda").manual_seed(2)
+    n = 100003
+    p0 = torch.randn(n, device="cuda", generator=g)
+    grad = torch.randn(n, device="cuda", generator=g)
+    v0 = torch.randn(n, device="cuda", generator=g)
+    p_ref, v_ref = p0.clone(), v0.clone()
+    s = torch.cuda.current_stream().cuda_stream
+    assert ref.ref_sgd(p_ref.data_ptr(), grad.data_ptr(), v_ref.data_ptr() if momentum else None, n, 0.05, momentum,
+                       dampening, int(nesterov), wd, s) == 0
+    p, v = p0.clone(), v0.clone()
+    pkg.sgd_update(p, grad, lr=0.05, velocity=v if momentum else None, momentum=momentum, dampening=dampening,
+                   nesterov=nesterov, weight_decay=wd, decay="l2")
+    torch.cuda.synchronize()
+    # the same fp32 operations, possibly contracted differently into FMAs by the two compilations
+    assert float(((p - p_ref).abs() / p_ref.abs().clamp_min(1.0)).max()) <= 1e-6
+    if momentum:
+        assert float(((v - v_ref).abs() / v_ref.abs().clamp_min(1.0)).max()) <= 1e-6
