@@ -326,9 +326,10 @@ def run_ours(args):
         print(json.dumps({"profile": "conv", "status": lib.ge2b_device_status(0)}), flush=True)
         return
     if args.profile == "qk":
-        # the batched attention GEMM S = (Q.K^T)/sqrt(d) at B*H = 128, L = 2048, d = 128, four launches
-        Q, Kt = (torch.randn((8, 16, 2048, 128), device=dev).bfloat16() for _ in range(2))
-        S = torch.empty((8, 16, 2048, 2048), device=dev, dtype=torch.bfloat16)
+        # the batched attention GEMM S = (Q.K^T)/sqrt(d) at L = 2048, d = 128 on 16 of the 128 (batch, head) slices
+        # (134 MB of output: larger than L2, small enough for a profiler's save / restore), four launches
+        Q, Kt = (torch.randn((2, 8, 2048, 128), device=dev).bfloat16() for _ in range(2))
+        S = torch.empty((2, 8, 2048, 2048), device=dev, dtype=torch.bfloat16)
         for _ in range(4):
             og.forward_batched(Q, Kt, out=S, trans_b=True, alpha=1.0 / 128 ** 0.5)
         barrier()
