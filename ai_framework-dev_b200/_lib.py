@@ -56,6 +56,15 @@ class ParamsSGD(C.Structure):
                 ("weight_decay", C.c_float), ("decay_mode", C.c_int), ("grad_scale", C.c_float)]
 
 
+class AllreduceSegment(C.Structure):
+    _fields_ = [("offset_bytes", C.c_ulonglong), ("bytes", C.c_ulonglong), ("dtype", C.c_int)]
+
+
+class AllreduceNvls(C.Structure):
+    _fields_ = [("multicast_base", C.c_void_p), ("signal_pads", C.POINTER(C.c_void_p)), ("world", C.c_int),
+                ("rank", C.c_int), ("n_segments", C.c_int), ("segments", AllreduceSegment * 2), ("blocks", C.c_int)]
+
+
 class ParamsBwdTyped(C.Structure):
     _fields_ = [("base", ParamsBwd),
                 ("dtype", C.c_int), ("z_dtype", C.c_int), ("math", C.c_int),
@@ -86,6 +95,7 @@ EXPORTS = [
     "ge2b_backward_scratch_bytes", "ge2b_device_status", "ge2b_sm_count", "ge2b_set_sm_limit", "ge2b_version",
     "ge2b_last_route", "ge2b_launches_total", "ge2b_register_gemm_kernels",
     "ge2b_split_unavailable_total", "ge2b_release_scratch", "ge2b_selftest_wait_expiry",
+    "ge2b_allreduce_nvls", "ge2b_allreduce_nvls_pad_bytes",
     "ge2b_dense_plan_create", "ge2b_dense_plan_step", "ge2b_dense_plan_destroy",
     "ge2b_dense_plan_submit", "ge2b_dense_plan_wait",
     "ge2_launch_gemm_bias_act_bwd_noalloc",
@@ -129,6 +139,9 @@ def load_library() -> C.CDLL:
     lib.ge2b_release_scratch.restype = None
     lib.ge2b_selftest_wait_expiry.argtypes = [C.c_longlong, C.POINTER(C.c_int), C.c_void_p]
     lib.ge2b_selftest_wait_expiry.restype = C.c_int
+    lib.ge2b_allreduce_nvls.argtypes = [C.POINTER(AllreduceNvls), C.c_void_p]
+    lib.ge2b_allreduce_nvls.restype = C.c_int
+    lib.ge2b_allreduce_nvls_pad_bytes.restype = C.c_int
     lib.ge2b_dense_plan_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                            C.c_float, C.c_int, C.c_int]
     lib.ge2b_dense_plan_create.restype = C.c_int

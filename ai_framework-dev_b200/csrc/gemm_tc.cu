@@ -107,6 +107,7 @@ bool split_scratch(cudaStream_t s, SplitScratch* out) {
     out->flags = static_cast<int*>(lease.base);
     out->ws = reinterpret_cast<float*>(static_cast<unsigned char*>(lease.base) + kSplitFlagBytes);
     out->ws_bytes = lease.bytes - kSplitFlagBytes;
+    out->lent = true;
     return true;
   }
   if (lease.no_alloc) { g_split_unavailable.fetch_add(1, std::memory_order_relaxed); return false; }
@@ -126,14 +127,16 @@ bool split_scratch(cudaStream_t s, SplitScratch* out) {
       g_split_unavailable.fetch_add(1, std::memory_order_relaxed);
       return false;
     }
-    if (cudaMalloc(reinterpret_cast<void**>(&sc.flags), kSplitFlagBytes) != cudaSuccess) {
+    if (cudaMalloc(reinterpret_cast<void**>(&sc.flags), kSplitFlagBytes) != cudaSuccess ||
+        cudaMemset(sc.flags, 0, kSplitFlagBytes) != cudaSuccess) {
       cudaGetLastError();
       cudaFree(sc.ws); sc.ws = nullptr;
+      if (sc.flags) { cudaFree(sc.flags); sc.flags = nullptr; }
       g_split_unavailable.fetch_add(1, std::memory_order_relaxed);
       return false;
     }
   }
-  out->ws = sc.ws; out->flags = sc.flags; out->ws_bytes = kSplitWsBytes;
+  out->ws = sc.ws; out->flags = sc.flags; out->ws_bytes = kSplitWsBytes; out->lent = false;
   return true;
 }
 

@@ -693,19 +693,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           arrived = __shfl_sync(0xffffffffu, arrived, 0);
           if (arrived == pp.split - 1) {
             __threadfence();
+            // last of the slices: put the counter back to zero for the next launch that uses these counters (launches
+            // on one stream are ordered, and every warp slot of every tile has exactly one last arriver)
+            if (lane == 0)
+              pp.flags[w.tail * (kEpiWarps * kCG) + static_cast<int>(cta_rank) * kEpiWarps + (warp - 2)] = 0;
             const float* sum_row = pp.ws + static_cast<size_t>(w.tail) * tile_elems +
                                    static_cast<size_t>(row_in_tile) * kBlockN + half * (kBlockN / 2);
+            const size_t slice_stride = static_cast<size_t>(pp.tail_tiles) * tile_elems;
 #pragma unroll 1
             for (int c = 0; c < n_chunks; ++c) {
               float v[32];
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = 0.f;
-              for (int sl = 0; row_ok && sl < pp.split; ++sl) {
-                const float* src = sum_row + static_cast<size_t>(sl) * pp.tail_tiles * tile_elems + c * 32;
+              // The partial sums come from L2, about a microsecond away: the loads of two slices are issued together
+              // and only then added (in slice order), so a tile cut into `split` slices pays ceil(split / 2) round
+              // trips per chunk instead of `split` (three or four at a time would spill registers).
+              for (int sl0 = 0; row_ok && sl0 < pp.split; sl0 += 2) {
+                const bool two = sl0 + 1 < pp.split;
+                const float4* s0 = reinterpret_cast<const float4*>(sum_row + sl0 * slice_stride + c * 32);
+                const float4* s1 = reinterpret_cast<const float4*>(sum_row + (two ? sl0 + 1 : sl0) * slice_stride + c * 32);
+                float4 f0[8], f1[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f0[j] = __ldcg(s0 + j);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f1[j] = __ldcg(s1 + j);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
-                  const float4 f = __ldcg(reinterpret_cast<const float4*>(src) + j);
-                  v[4 * j] += f.x; v[4 * j + 1] += f.y; v[4 * j + 2] += f.z; v[4 * j + 3] += f.w;
+                  v[4 * j] += f0[j].x; v[4 * j + 1] += f0[j].y; v[4 * j + 2] += f0[j].z; v[4 * j + 3] += f0[j].w;
+                }
+                if (two) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    v[4 * j] += f1[j].x; v[4 * j + 1] += f1[j].y; v[4 * j + 2] += f1[j].z; v[4 * j + 3] += f1[j].w;
+                  }
                 }
               }
               const int col0 = nh0 + c * 32;
@@ -806,7 +826,7 @@ bool make_operand_map(CUtensorMap* map, int dtype, const void* base, long long i
                       long long batch, long long batch_stride, int box_inner, int box_rows, bool swizzle_32b_units);
 bool make_output_map(CUtensorMap* map, int dtype, const void* base, long long cols, long long rows, long long ld,
                      long long batch, long long batch_stride, bool wide);
-struct SplitScratch { float* ws = nullptr; int* flags = nullptr; size_t ws_bytes = 0; };
+struct SplitScratch { float* ws = nullptr; int* flags = nullptr; size_t ws_bytes = 0; bool lent = false; };
 constexpr size_t kSplitWsBytes = 64u << 20;
 constexpr int kSplitMaxTail = 256;
 constexpr int kSplitInKernelMax = 8;   // more slices than this: the second kernel adds them up
@@ -924,7 +944,9 @@ cudaError_t prepare_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s, Prepa
           p.ws = sc.ws;
           p.flags = sc.flags;
           p.fin_in_kernel = sp <= kSplitInKernelMax ? 1 : 0;
-          if (p.fin_in_kernel) L.flag_bytes = static_cast<size_t>(rem) * kEpiWarps * kCG * sizeof(int);
+          // the library's own counters are zero when created and every launch leaves them zero; lent memory holds
+          // whatever the caller left there, so it is cleared on the stream first
+          if (p.fin_in_kernel && sc.lent) L.flag_bytes = static_cast<size_t>(rem) * kEpiWarps * kCG * sizeof(int);
         }
       } else {
         L.cacheable = false;

@@ -249,6 +249,35 @@ int ge2b_conv2d_backward(const ge2b_conv2d_params_t* p, const void* X, const voi
 /* Ho, Wo for the geometry in p (conv2d/launcher.cu:137-138). */
 int ge2b_conv2d_output_size(const ge2b_conv2d_params_t* p, int* Ho, int* Wo);
 
+/* ------------------------------------------------------------------------------------------------
+ * Data-parallel gradient exchange: sum all-reduce over NVLink / NVSwitch in one kernel per rank.
+ * No counterpart in the reference (it has no multi-GPU path); this is the "dW / db are combined across the GPUs"
+ * step of the sharded dense layer.  Every rank reduces its slice of a symmetric buffer inside the switch
+ * (multimem.ld_reduce) and writes the sums to every GPU (multimem.st).  bf16 values are summed in fp32.
+ * ------------------------------------------------------------------------------------------------ */
+typedef struct {
+  unsigned long long offset_bytes;   /* from the buffer base; multiple of 16 */
+  unsigned long long bytes;          /* multiple of 16 */
+  ge2_dtype_t dtype;                 /* GE2_DT_BF16 or GE2_DT_F32 */
+} ge2b_allreduce_segment_t;
+
+typedef struct {
+  void* multicast_base;              /* multicast address of the symmetric buffer (same offset layout on every rank) */
+  void* const* signal_pads;          /* [world] addresses, valid on this GPU, of every rank's signal pad: at least
+                                        ge2b_allreduce_nvls_pad_bytes() bytes each, zero before the first call */
+  int world, rank;                   /* 2..16 ranks, one per GPU */
+  int n_segments;                    /* 1 or 2 regions of the buffer (e.g. bf16 dW and fp32 db in one bucket) */
+  ge2b_allreduce_segment_t segments[2];
+  int blocks;                        /* thread blocks (SMs) to use; <= 0: 32 */
+} ge2b_allreduce_nvls_t;
+
+/* Launches the exchange on `stream`.  Every rank must call it with the same segments; the kernels of the ranks wait
+ * for each other (bounded: a wait that runs out sets bit 1 of ge2b_device_status and the kernel returns), so one rank
+ * per GPU.  The signal pads are left all-zero again, so the launch may be captured into a CUDA graph and replayed.
+ * Returns 0, -1 (bad arguments) or -2. */
+int ge2b_allreduce_nvls(const ge2b_allreduce_nvls_t* args, void* stream);
+int ge2b_allreduce_nvls_pad_bytes(void);
+
 /* Introspection for tests and benchmarks: which kernel family the calling thread's most recent GEMM went to
  * (0 none, 1 exact-fp32 CUDA-core kernel, 2 tcgen05 tensor-core kernel) and how many kernels this library
  * has launched in the process. */
