@@ -932,7 +932,12 @@ cudaError_t prepare_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s, Prepa
   if (!split_off && tiles < units && 2 * rem <= units && rem <= kSplitMaxTail) {
     long long sp = units / rem;
     if (sp > 32) sp = 32;
-    if (sp > p.k_blocks / 8) sp = p.k_blocks / 8;               // keep at least 8 k-blocks per slice
+    // Splitting costs a fixed 10 to 18 us (partial tiles out to L2, a fence and a counter per warp, the last warp's
+    // reads of every slice), measured on B200 against about 0.27 us per k-block of an unsplit tile: 1024^3 (16
+    // k-blocks) ran in 23 us split and 12 us unsplit, 1024 x 1024 x 4096 (64 k-blocks) in 30 and 25.  It pays only for
+    // long reductions, which are the HBM-bound skinny-M shapes (128 k-blocks at K = 8192: 32 us split, 42 unsplit).
+    if (p.k_blocks < 96) sp = 1;
+    if (sp > p.k_blocks / 24) sp = p.k_blocks / 24;             // keep at least 24 k-blocks per slice
     if (sp >= 2) {
       SplitScratch sc;
       if (split_scratch(s, &sc)) {

@@ -51,9 +51,12 @@ def _call(pkg, lib, entry, A, W, gY, Z, act, scratch):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(640, 384, 512), (256, 512, 6144)])      # the second: dX is split along its reduction
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_noalloc_backward_matches_ordinary_entry_twice(pkg, lib, dtype):
-    M, K, N = 640, 384, 512
+def test_noalloc_backward_matches_ordinary_entry_twice(pkg, lib, dtype, shape):
+    M, K, N = shape
+    if dtype == torch.float32 and M * N * 4 > pkg._lib.NOALLOC_SCRATCH_BYTES:
+        N //= 2
     for seed, act in ((0, "gelu"), (1, "relu")):        # two calls in a row share the fixed scratch
         g = torch.Generator(device="cuda").manual_seed(seed)
         A = torch.randn((M, K), device="cuda", generator=g).to(dtype)
@@ -78,9 +81,9 @@ _FRESH = textwrap.dedent('''
     torch.cuda.set_device(0)
     first_delta = []
     for dtype, code in ((torch.float32, L.DT_F32), (torch.bfloat16, L.DT_BF16)):
-        # fp32 (TF32 math): K = N = 512 gives 16 k-blocks of 32, bf16: K = N = 1024 gives 16 k-blocks of 64; with 6 + 4
-        # tiles on 74 CTA pairs both dX and dW qualify for a split along the reduction
-        M, K, N = (640, 384, 512) if dtype == torch.float32 else (640, 1024, 1024)
+        # dX = gZ.W^T reduces over N: 96 k-blocks (of 32 fp32 / 64 bf16 elements) on 2 output tiles, which the launch
+        # layer cuts into 4 slices along the reduction -- the case in which the ordinary entry creates its scratch
+        M, K, N = (256, 512, 3072) if dtype == torch.float32 else (256, 512, 6144)
         g = torch.Generator(device="cuda").manual_seed(3)
         A = torch.randn((M, K), device="cuda", generator=g).to(dtype)
         W = (torch.randn((K, N), device="cuda", generator=g) / 16).to(dtype)
