@@ -65,6 +65,17 @@ class AllreduceNvls(C.Structure):
                 ("rank", C.c_int), ("n_segments", C.c_int), ("segments", AllreduceSegment * 2), ("blocks", C.c_int)]
 
 
+MLP_MAX_LAYERS = 8
+
+
+class MlpConfig(C.Structure):
+    _fields_ = [("n_layers", C.c_int), ("dims", C.c_int * (MLP_MAX_LAYERS + 1)), ("acts", C.c_int * MLP_MAX_LAYERS),
+                ("batch", C.c_int), ("global_batch", C.c_int), ("dtype", C.c_int), ("lr", C.c_float),
+                ("world", C.c_int), ("rank", C.c_int), ("exchange", C.c_int),
+                ("grad_base", C.c_void_p), ("grad_multicast", C.c_void_p), ("peer_grad_bases", C.POINTER(C.c_void_p)),
+                ("nccl_unique_id", C.c_void_p), ("comm_blocks", C.c_int)]
+
+
 class ParamsBwdTyped(C.Structure):
     _fields_ = [("base", ParamsBwd),
                 ("dtype", C.c_int), ("z_dtype", C.c_int), ("math", C.c_int),
@@ -96,6 +107,10 @@ EXPORTS = [
     "ge2b_last_route", "ge2b_launches_total", "ge2b_register_gemm_kernels",
     "ge2b_split_unavailable_total", "ge2b_release_scratch", "ge2b_selftest_wait_expiry",
     "ge2b_allreduce_nvls", "ge2b_allreduce_nvls_pad_bytes",
+    "ge2b_mlp_plan_grad_bytes", "ge2b_nccl_unique_id", "ge2b_mlp_plan_create", "ge2b_mlp_plan_destroy",
+    "ge2b_mlp_plan_set_params", "ge2b_mlp_plan_get_params", "ge2b_mlp_plan_get_grads", "ge2b_mlp_plan_compile",
+    "ge2b_mlp_plan_launch", "ge2b_mlp_plan_step", "ge2b_mlp_plan_sync", "ge2b_mlp_plan_buffer",
+    "ge2b_mlp_plan_launches_per_step",
     "ge2b_dense_plan_create", "ge2b_dense_plan_step", "ge2b_dense_plan_destroy",
     "ge2b_dense_plan_submit", "ge2b_dense_plan_wait",
     "ge2_launch_gemm_bias_act_bwd_noalloc",
@@ -142,6 +157,28 @@ def load_library() -> C.CDLL:
     lib.ge2b_allreduce_nvls.argtypes = [C.POINTER(AllreduceNvls), C.c_void_p]
     lib.ge2b_allreduce_nvls.restype = C.c_int
     lib.ge2b_allreduce_nvls_pad_bytes.restype = C.c_int
+    vp = C.c_void_p
+    lib.ge2b_mlp_plan_grad_bytes.argtypes = [C.POINTER(MlpConfig)]
+    lib.ge2b_mlp_plan_grad_bytes.restype = C.c_size_t
+    lib.ge2b_nccl_unique_id.argtypes = [vp]
+    lib.ge2b_mlp_plan_create.argtypes = [C.POINTER(vp), C.POINTER(MlpConfig)]
+    lib.ge2b_mlp_plan_destroy.argtypes = [vp]
+    lib.ge2b_mlp_plan_destroy.restype = None
+    lib.ge2b_mlp_plan_set_params.argtypes = [vp, C.c_int, vp, vp]
+    lib.ge2b_mlp_plan_get_params.argtypes = [vp, C.c_int, vp, vp, vp]
+    lib.ge2b_mlp_plan_get_grads.argtypes = [vp, C.c_int, vp, vp]
+    lib.ge2b_mlp_plan_compile.argtypes = [vp, C.c_int]
+    lib.ge2b_mlp_plan_launch.argtypes = [vp]
+    lib.ge2b_mlp_plan_step.argtypes = [vp, vp, vp, vp]
+    lib.ge2b_mlp_plan_sync.argtypes = [vp]
+    lib.ge2b_mlp_plan_buffer.argtypes = [vp, C.c_int]
+    lib.ge2b_mlp_plan_buffer.restype = vp
+    lib.ge2b_mlp_plan_launches_per_step.argtypes = [vp]
+    lib.ge2b_mlp_plan_launches_per_step.restype = C.c_longlong
+    for name in ("ge2b_nccl_unique_id", "ge2b_mlp_plan_create", "ge2b_mlp_plan_set_params", "ge2b_mlp_plan_get_params",
+                 "ge2b_mlp_plan_get_grads", "ge2b_mlp_plan_compile", "ge2b_mlp_plan_launch", "ge2b_mlp_plan_step",
+                 "ge2b_mlp_plan_sync"):
+        getattr(lib, name).restype = C.c_int
     lib.ge2b_dense_plan_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                            C.c_float, C.c_int, C.c_int]
     lib.ge2b_dense_plan_create.restype = C.c_int

@@ -14,7 +14,7 @@
 // were written by earlier kernels of the same stream) and after writing (every rank's results have landed
 // everywhere).  A signal is a 32-bit word that the sender flips 0 -> 1 on the receiver and the receiver flips back
 // 1 -> 0, so the pads return to all-zero after every call and the same launch can be replayed from a CUDA graph.
-// Every wait is bounded (about one second of polling); on expiry the block records kErrWaitTimeout in the device
+// Every wait is bounded (two seconds of wall time); on expiry the block records kErrWaitTimeout in the device
 // status word and returns without touching the buffer again.
 //
 // One kernel per GPU and one rank per GPU: ranks never share a GPU (kernels that wait on each other must not).
@@ -35,7 +35,8 @@ constexpr int kArThreads = 512;
 constexpr int kArUnroll = 4;                   // 16-byte reductions in flight per thread
 constexpr int kArMaxBlocks = 64;
 constexpr int kArMaxWorld = 16;
-constexpr long long kSpinLimit = 20000000ll;   // polls; a poll of a remote word takes on the order of a microsecond
+constexpr int kArExclusiveSmem = 120 * 1024;   // more than half of an SM's shared memory: one block per SM
+constexpr unsigned long long kWaitNs = 2000000000ull;   // a rank that is two seconds late is not coming
 
 struct ArSegment {
   unsigned long long offset;    // bytes from the buffer base, 16-byte aligned
@@ -52,24 +53,39 @@ struct ArParams {
   int* status;
 };
 
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Both polls give up after kWaitNs of wall time (checked every 64 polls).
 __device__ __forceinline__ bool put_signal(uint32_t* addr) {
-  long long spins = 0;
-  uint32_t seen;
-  do {
+  unsigned long long t0 = 0;
+  uint32_t seen, spins = 0;
+  for (;;) {
     asm volatile("atom.global.release.sys.cas.b32 %0, [%1], 0, 1;" : "=r"(seen) : "l"(addr) : "memory");
     if (seen == 0u) return true;
-  } while (++spins < kSpinLimit);
-  return false;
+    if ((++spins & 63u) == 0u) {
+      const unsigned long long t = now_ns();
+      if (t0 == 0) t0 = t;
+      else if (t - t0 > kWaitNs) return false;
+    }
+  }
 }
 
 __device__ __forceinline__ bool wait_signal(uint32_t* addr) {
-  long long spins = 0;
-  uint32_t seen;
-  do {
+  unsigned long long t0 = 0;
+  uint32_t seen, spins = 0;
+  for (;;) {
     asm volatile("atom.global.acquire.sys.cas.b32 %0, [%1], 1, 0;" : "=r"(seen) : "l"(addr) : "memory");
     if (seen == 1u) return true;
-  } while (++spins < kSpinLimit);
-  return false;
+    if ((++spins & 63u) == 0u) {
+      const unsigned long long t = now_ns();
+      if (t0 == 0) t0 = t;
+      else if (t - t0 > kWaitNs) return false;
+    }
+  }
 }
 
 // All ranks' block `blockIdx.x` meet: thread p signals rank p's pad slot [block][my rank] and waits for its own
@@ -184,8 +200,27 @@ int ge2b_allreduce_nvls(const ge2b_allreduce_nvls_t* a, void* stream) {
   // small buffers: no more blocks than there are 16-byte units for
   const unsigned long long want = (total / 16 / a->world + kArThreads - 1) / kArThreads;
   if (static_cast<unsigned long long>(blocks) > want) blocks = want > 0 ? static_cast<int>(want) : 1;
-  allreduce_nvls_kernel<<<blocks, kArThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
-  return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
+  if (blocks > 1 && blocks % 2) --blocks;
+  // Placement.  The exchange usually runs beside a GEMM whose CTAs come in pairs that need both SMs of a TPC.  Blocks
+  // scattered one per TPC would break twice as many pairs as there are blocks, so the blocks are launched as clusters
+  // of two (co-scheduled on neighbouring SMs) and each asks for enough shared memory to have its SM to itself:
+  // `blocks` blocks then occupy exactly `blocks` SMs of blocks / 2 TPCs, whichever kernel is scheduled first.
+  static cudaError_t attr_err = cudaFuncSetAttribute(allreduce_nvls_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                     kArExclusiveSmem);
+  if (attr_err != cudaSuccess) return kCudaError;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks), 1, 1);
+  cfg.blockDim = dim3(kArThreads, 1, 1);
+  cfg.dynamicSmemBytes = kArExclusiveSmem;
+  cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (blocks % 2 == 0) ? 2u : 1u;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, allreduce_nvls_kernel, p) == cudaSuccess ? kOk : kCudaError;
 }
 
 }  // extern "C"

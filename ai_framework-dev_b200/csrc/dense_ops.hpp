@@ -55,6 +55,12 @@ int dense_forward(const DenseForward& f, cudaStream_t s);
 int run_gemm_problem(const GemmProblem& g, cudaStream_t s);
 int dense_backward(const DenseBackward& b, cudaStream_t s);
 
+// One tensor of a multi-tensor SGD launch: fp32 master `p`, gradient `g` of `g_dtype`, optional low-precision copy.
+struct SgdTensor {
+  float* p; const void* g; void* low; long long n; int g_dtype; int low_dtype;
+};
+constexpr int kSgdMaxTensors = 16;
+
 // fp32 tensors default to exact arithmetic; GE2B_FP32_MATH=tf32 in the environment opts the operator API
 // (which has no field for it) into TF32 tensor cores.
 int default_fp32_math();

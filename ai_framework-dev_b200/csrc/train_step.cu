@@ -153,7 +153,95 @@ sgd_update_kernel(const SgdParams a) {
 
 bool dtype_ok(int d) { return d == GE2_DT_F32 || d == GE2_DT_F16 || d == GE2_DT_BF16; }
 
+// Plain SGD (p -= lr * g) on up to 16 tensors in ONE launch: a training step updates every weight and bias of the
+// stack, and one launch per tensor costs more in launch gaps than the update itself once the tensors are small.
+// Block b works on a 4096-element chunk; `first_block[t]` says where tensor t's chunks begin.  Four elements per
+// thread and access (16-byte master loads / stores, 8- or 16-byte gradient loads) when the tensor's element count
+// and addresses allow, else scalar.
+constexpr int kSgdChunk = 4096;
+struct SgdMultiParams {
+  SgdTensor t[kSgdMaxTensors];
+  int first_block[kSgdMaxTensors + 1];
+  int n_tensors;
+  float lr;
+};
+
+__device__ __forceinline__ void load4(const void* g, long long i, int dt, float (&v)[4]) {
+  if (dt == kF32) {
+    const float4 f = *reinterpret_cast<const float4*>(static_cast<const float*>(g) + i);
+    v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+  } else {
+    const uint2 u = *reinterpret_cast<const uint2*>(static_cast<const unsigned short*>(g) + i);
+    if (dt == kBF16) {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+      v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    } else {
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+      v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) sgd_multi_kernel(const SgdMultiParams a) {
+  int ti = 0;
+  while (ti + 1 < a.n_tensors && static_cast<int>(blockIdx.x) >= a.first_block[ti + 1]) ++ti;
+  const SgdTensor t = a.t[ti];
+  const long long begin = static_cast<long long>(blockIdx.x - a.first_block[ti]) * kSgdChunk;
+  const long long end = begin + kSgdChunk < t.n ? begin + kSgdChunk : t.n;
+  const bool vec = (t.n % 4 == 0) && ((reinterpret_cast<uintptr_t>(t.p) | reinterpret_cast<uintptr_t>(t.g) |
+                                       reinterpret_cast<uintptr_t>(t.low)) % 16 == 0);
+  if (vec) {
+    for (long long i = begin + 4ll * threadIdx.x; i < end; i += 4 * 256) {
+      float4 p = *reinterpret_cast<float4*>(t.p + i);
+      float g[4];
+      load4(t.g, i, t.g_dtype, g);
+      p.x -= a.lr * g[0]; p.y -= a.lr * g[1]; p.z -= a.lr * g[2]; p.w -= a.lr * g[3];
+      *reinterpret_cast<float4*>(t.p + i) = p;
+      if (t.low != nullptr) {
+        if (t.low_dtype == kBF16) {
+          __nv_bfloat162 lo = __floats2bfloat162_rn(p.x, p.y), hi = __floats2bfloat162_rn(p.z, p.w);
+          *reinterpret_cast<uint2*>(static_cast<unsigned short*>(t.low) + i) =
+              make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
+        } else if (t.low_dtype == kF16) {
+          __half2 lo = __floats2half2_rn(p.x, p.y), hi = __floats2half2_rn(p.z, p.w);
+          *reinterpret_cast<uint2*>(static_cast<unsigned short*>(t.low) + i) =
+              make_uint2(*reinterpret_cast<unsigned*>(&lo), *reinterpret_cast<unsigned*>(&hi));
+        } else {
+          *reinterpret_cast<float4*>(static_cast<float*>(t.low) + i) = p;
+        }
+      }
+    }
+  } else {
+    for (long long i = begin + threadIdx.x; i < end; i += 256) {
+      const float p = t.p[i] - a.lr * load_as_f32(t.g, i, t.g_dtype);
+      t.p[i] = p;
+      if (t.low != nullptr) store_from_f32(t.low, i, t.low_dtype, p);
+    }
+  }
+}
+
 }  // namespace
+
+namespace ge2b {
+int launch_sgd_multi(const SgdTensor* t, int n, float lr, cudaStream_t s) {
+  if (!t || n < 1 || n > kSgdMaxTensors) return kBadArgs;
+  SgdMultiParams a{};
+  int blocks = 0;
+  for (int i = 0; i < n; ++i) {
+    if (!t[i].p || !t[i].g || t[i].n <= 0) return kBadArgs;
+    a.t[i] = t[i];
+    a.first_block[i] = blocks;
+    blocks += static_cast<int>((t[i].n + kSgdChunk - 1) / kSgdChunk);
+  }
+  a.first_block[n] = blocks;
+  a.n_tensors = n;
+  a.lr = lr;
+  sgd_multi_kernel<<<blocks, 256, 0, s>>>(a);
+  return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
+}
+}  // namespace ge2b
 
 extern "C" {
 

@@ -233,3 +233,170 @@ class DenseStackTrainer:
     def flop_per_step(self) -> float:
         """2*B*sum(d_i*d_{i+1}) forward, twice that backward (dX is computed for the first layer too)."""
         return 6.0 * self.batch * sum(self.dims[i] * self.dims[i + 1] for i in range(len(self.W)))
+
+
+class MlpPlan:
+    """The C++ step driver (csrc/mlp_plan.cu) behind its C ABI: Dense stack -> softmax cross-entropy -> SGD, buffers and
+    CUDA graph owned by the library.  This class only builds the configuration, draws the initial weights the way
+    `DenseStackTrainer` does (Kaiming-uniform from a seeded CPU generator) and, under data parallelism, obtains the
+    symmetric gradient buffer (or the collective library's unique id) from torch.distributed."""
+
+    def __init__(self, dims: Sequence[int], acts: Sequence[str], batch: int, *, dtype=torch.bfloat16, lr=1e-3, seed=0,
+                 device="cuda", group=None, global_batch: Optional[int] = None, bias_init_zero=True,
+                 exchange: str = "auto", comm_blocks: int = 16):
+        import ctypes as C
+        self._C = C
+        self.lib = _lib.load_library()
+        self.dims, self.acts, self.batch = [int(d) for d in dims], [a.lower() for a in acts], int(batch)
+        self.dtype, self.device = dtype, torch.device(device)
+        self.group = group
+        self.world = torch.distributed.get_world_size(group) if group is not None else 1
+        self.rank = torch.distributed.get_rank(group) if group is not None else 0
+        self.global_batch = int(global_batch) if global_batch else self.batch * self.world
+        cfg = _lib.MlpConfig()
+        cfg.n_layers = len(self.acts)
+        for i, d in enumerate(self.dims):
+            cfg.dims[i] = d
+        for i, a in enumerate(self.acts):
+            cfg.acts[i] = _lib.ACT[a]
+        cfg.batch, cfg.global_batch, cfg.dtype, cfg.lr = self.batch, self.global_batch, _DT[dtype], float(lr)
+        cfg.world, cfg.rank, cfg.comm_blocks = self.world, self.rank, int(comm_blocks)
+        self.exchange, self._keep = "none", []
+        with torch.cuda.device(self.device):
+            if self.world > 1:
+                nbytes = int(self.lib.ge2b_mlp_plan_grad_bytes(C.byref(cfg)))
+                handle = None
+                if exchange in ("auto", "nvls") and dtype in (torch.bfloat16, torch.float32):
+                    try:
+                        import torch.distributed._symmetric_memory as symm_mem
+                        buf = symm_mem.empty((nbytes,), dtype=torch.uint8, device=self.device)
+                        buf.zero_()
+                        torch.cuda.synchronize(self.device)
+                        handle = symm_mem.rendezvous(buf, group)
+                        if int(handle.multicast_ptr) == 0:
+                            handle = None
+                    except Exception:  # noqa: BLE001
+                        handle = None
+                    if handle is None and exchange == "nvls":
+                        raise RuntimeError("no symmetric memory with a multicast mapping for this process group")
+                if handle is not None:
+                    peers = (C.c_void_p * self.world)(*[int(p) for p in handle.buffer_ptrs])
+                    cfg.exchange, cfg.grad_base, cfg.grad_multicast = 1, buf.data_ptr(), int(handle.multicast_ptr)
+                    cfg.peer_grad_bases = C.cast(peers, C.POINTER(C.c_void_p))
+                    self._keep += [buf, handle, peers]
+                    self.exchange = "nvls kernel"
+                else:
+                    uid = torch.zeros(128, dtype=torch.uint8)
+                    if self.rank == 0:
+                        _lib.check(self.lib.ge2b_nccl_unique_id(uid.data_ptr()), "nccl_unique_id")
+                    dev_uid = uid.to(self.device)
+                    torch.distributed.broadcast(dev_uid, src=torch.distributed.get_global_rank(group, 0), group=group)
+                    uid = dev_uid.cpu()
+                    cfg.exchange, cfg.nccl_unique_id = 2, uid.data_ptr()
+                    self._keep.append(uid)
+                    self.exchange = "nccl"
+            self._plan = C.c_void_p()
+            _lib.check(self.lib.ge2b_mlp_plan_create(C.byref(self._plan), C.byref(cfg)), "mlp_plan_create")
+            gen = torch.Generator(device="cpu").manual_seed(seed)
+            for i in range(len(self.acts)):
+                lim = math.sqrt(6.0 / self.dims[i])
+                w = ((torch.rand((self.dims[i], self.dims[i + 1]), generator=gen) * 2 - 1) * lim).float().contiguous()
+                b = (torch.zeros(self.dims[i + 1]) if bias_init_zero
+                     else (torch.rand(self.dims[i + 1], generator=gen) * 0.2 - 0.1)).float().contiguous()
+                _lib.check(self.lib.ge2b_mlp_plan_set_params(self._plan, i, w.data_ptr(), b.data_ptr()), "mlp_set_params")
+        self.captured = False
+
+    def compile(self, capture: bool = True) -> None:
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.ge2b_mlp_plan_compile(self._plan, 1 if capture else 0), "mlp_plan_compile")
+        self.captured = bool(capture)
+
+    def stream(self) -> "torch.cuda.ExternalStream":
+        return torch.cuda.ExternalStream(int(self.lib.ge2b_mlp_plan_buffer(self._plan, 3)), device=self.device)
+
+    def launch(self) -> None:
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.ge2b_mlp_plan_launch(self._plan), "mlp_plan_launch")
+
+    def step_host(self, X: Optional[torch.Tensor], labels: Optional[torch.Tensor], want_loss=True) -> Optional[float]:
+        """One step from host tensors (X in the compute dtype, int32 labels; pinned memory copies asynchronously).
+        Returns this replica's share of the mean loss when asked to (that waits for the step)."""
+        C = self._C
+        loss = C.c_float(0.0)
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.ge2b_mlp_plan_step(self._plan, X.data_ptr() if X is not None else None,
+                                                   labels.data_ptr() if labels is not None else None,
+                                                   C.byref(loss) if want_loss else None), "mlp_plan_step")
+        return float(loss.value) if want_loss else None
+
+    def sync(self) -> None:
+        _lib.check(self.lib.ge2b_mlp_plan_sync(self._plan), "mlp_plan_sync")
+
+    def params(self, layer: int):
+        """(W fp32 master, b, W in the compute dtype) of one layer as CPU tensors."""
+        W = torch.empty((self.dims[layer], self.dims[layer + 1]), dtype=torch.float32)
+        b = torch.empty((self.dims[layer + 1],), dtype=torch.float32)
+        Wl = torch.empty((self.dims[layer], self.dims[layer + 1]), dtype=self.dtype)
+        _lib.check(self.lib.ge2b_mlp_plan_get_params(self._plan, layer, W.data_ptr(), b.data_ptr(), Wl.data_ptr()), "get_params")
+        return W, b, Wl
+
+    def grads(self, layer: int):
+        gW = torch.empty((self.dims[layer], self.dims[layer + 1]), dtype=self.dtype)
+        gb = torch.empty((self.dims[layer + 1],), dtype=torch.float32)
+        _lib.check(self.lib.ge2b_mlp_plan_get_grads(self._plan, layer, gW.data_ptr(), gb.data_ptr()), "get_grads")
+        return gW, gb
+
+    def launches_per_step(self) -> int:
+        return int(self.lib.ge2b_mlp_plan_launches_per_step(self._plan))
+
+    def flop_per_step(self) -> float:
+        return 6.0 * self.batch * sum(self.dims[i] * self.dims[i + 1] for i in range(len(self.acts)))
+
+    def global_loss(self) -> float:
+        """Mean loss over the global batch of the last step (the replicas' shares add up to it)."""
+        self.sync()
+        out = torch.zeros(1, device=self.device)
+        loss = self.step_loss_tensor()
+        out.copy_(loss)
+        if self.world > 1:
+            torch.distributed.all_reduce(out, group=self.group)
+        return float(out.item())
+
+    def step_loss_tensor(self) -> torch.Tensor:
+        """The plan's loss scalar as a 1-element CUDA tensor aliasing the library's buffer."""
+        ptr = int(self.lib.ge2b_mlp_plan_buffer(self._plan, 2))
+        return _alias_cuda(ptr, (1,), torch.float32, self.device)
+
+    def input_tensors(self):
+        """(X, labels) aliasing the plan's static device buffers, for filling a batch on the device."""
+        X = _alias_cuda(int(self.lib.ge2b_mlp_plan_buffer(self._plan, 0)), (self.batch, self.dims[0]), self.dtype, self.device)
+        y = _alias_cuda(int(self.lib.ge2b_mlp_plan_buffer(self._plan, 1)), (self.batch,), torch.int32, self.device)
+        return X, y
+
+    def close(self) -> None:
+        if getattr(self, "_plan", None) is not None and self._plan:
+            self.lib.ge2b_mlp_plan_destroy(self._plan)
+            self._plan = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+class _CudaArray:
+    """Minimal __cuda_array_interface__ carrier so that torch can alias memory the library owns."""
+
+    def __init__(self, ptr, shape, typestr):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(ptr), False), "version": 3,
+                                         "strides": None}
+
+
+def _alias_cuda(ptr: int, shape, dtype, device) -> torch.Tensor:
+    if dtype == torch.bfloat16:                     # no typestr for bf16: alias as int16 and reinterpret
+        with torch.cuda.device(device):
+            return torch.as_tensor(_CudaArray(ptr, shape, "<i2"), device=device).view(torch.bfloat16)
+    typestr = {torch.float32: "<f4", torch.int32: "<i4", torch.float16: "<f2"}[dtype]
+    with torch.cuda.device(device):
+        return torch.as_tensor(_CudaArray(ptr, shape, typestr), device=device)

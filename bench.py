@@ -248,19 +248,30 @@ def run_ours(args):
     Z = torch.empty_like(Y)
     work = torch.empty_like(Y)
     dX = torch.empty((M, K), device=dev, dtype=torch.bfloat16)
-    dW = torch.empty((K, N), device=dev, dtype=torch.bfloat16)
-    db = torch.empty((1, N), device=dev, dtype=torch.float32)
-    comm = torch.cuda.Stream(device=dev) if world > 1 else None
     sm_total = lib.ge2b_sm_count()
-    comm_sms = int(os.environ.get("GE2B_BENCH_COMM_SMS", "16"))   # SMs left free for NCCL during the overlapped GEMM
-    fwd_events = []
-
-    # row blocks of dW whose all-reduce starts as each finishes; a single GPU has nothing to overlap and uses one
-    # 0: no overlap - the backward runs as on one GPU (dX and dW in one launch) and the all-reduce follows it
-    # Default: overlapped with 2 row blocks up to 4 GPUs (measured: N = 2 0.402 ms overlapped / 0.396 sequential, N = 4
-    # 0.413 / 0.474), sequential beyond (at N = 8 the overlapped form left 0.2 ms of a slowed-down all-reduce exposed).
-    dw_chunks = max(0, int(os.environ.get("GE2B_BENCH_DW_CHUNKS", "1" if world == 1 else ("2" if world <= 4 else "0"))))
+    comm_sms = int(os.environ.get("GE2B_BENCH_COMM_SMS", "16"))   # SMs of the exchange kernel; GEMMs beside it leave them free
+    # Row blocks of dW whose exchange starts as each finishes (0: the backward runs as on one GPU, dX and dW in one
+    # launch, and the exchange follows it).
+    dw_chunks = max(0, int(os.environ.get("GE2B_BENCH_DW_CHUNKS", "1" if world == 1 else "2")))
     rows_per_chunk = K // max(1, dw_chunks)
+    n_reg = max(1, dw_chunks)
+    chunk_rows = [(c * rows_per_chunk, K if c == n_reg - 1 else (c + 1) * rows_per_chunk) for c in range(n_reg)]
+    # dW (in row blocks) and db share ONE gradient bucket: symmetric memory mapped into a multicast object, summed over
+    # the ranks by this library's NVLink kernel (multimem.ld_reduce / multimem.st), one launch per exchange; where the
+    # process group has no such mapping the bucket uses the collective library instead (reported in the JSON line)
+    bucket = None
+    if world > 1:
+        bucket = pkg.data_parallel.GradBucket([((r1 - r0, N), torch.bfloat16) for r0, r1 in chunk_rows] +
+                                              [((1, N), torch.float32)], dist.group.WORLD, dev, blocks=comm_sms,
+                                              force_nccl=os.environ.get("GE2B_BENCH_EXCHANGE", "") == "nccl")
+        flat = bucket.buffer[:K * N * 2].view(torch.bfloat16).view(K, N)     # the row blocks are contiguous: one dW
+        assert flat.data_ptr() == bucket.views[0].data_ptr() and (K * N * 2) % 256 == 0
+        dW, db = flat, bucket.views[-1]
+    else:
+        dW = torch.empty((K, N), device=dev, dtype=torch.bfloat16)
+        db = torch.empty((1, N), device=dev, dtype=torch.float32)
+    comm = torch.cuda.Stream(device=dev) if world > 1 else None
+    fwd_events = []
 
     def step(timed):
         if timed:
@@ -271,37 +282,29 @@ def run_ours(args):
             e1.record()
             fwd_events.append((e0, e1))
         cur = torch.cuda.current_stream()
-
-        def reduce_async(t):
-            if world > 1:
-                comm.wait_stream(cur)
-                with torch.cuda.stream(comm):
-                    dist.all_reduce(t)          # asynchronous on the device: ordered on the side stream
-
         if world == 1 or dw_chunks == 0:
             # the whole backward in one call: gZ = dY * gelu'(Z) with db, then dX and dW (one launch for both: their
             # tiles form one list, so only the combined list's last wave is partly filled)
             og.backward_into(X, W, dY, Z, act=ACT, with_bias=True, gA_out=dX, gB_out=dW, gBias_out=db, work_dZ=work)
             if world > 1:
-                dist.all_reduce(dW)
-                dist.all_reduce(db)
+                bucket.all_reduce()                     # dW and db in one exchange
             return
         # gZ = dY * gelu'(Z) and db in one pass; gZ stays in `work` for the two GEMMs
         og.backward_into(X, W, dY, Z, act=ACT, with_bias=True, gBias_out=db, work_dZ=work)
-        reduce_async(db)
-        # dW = X^T . gZ first, in row blocks, each block's all-reduce starting as soon as it is written,
-        # so that the exchange runs under the remaining dW blocks and the dX GEMM
-        for c in range(dw_chunks):
-            rows = slice(c * rows_per_chunk, K if c == dw_chunks - 1 else (c + 1) * rows_per_chunk)
-            og.forward_into(X[:, rows], work, out=dW[rows], trans_a=True)
-            reduce_async(dW[rows])
-        if world > 1 and comm_sms > 0:
-            lib.ge2b_set_sm_limit(sm_total - comm_sms)      # leave SMs to the all-reduce kernel running beside it
+        # dW = X^T . gZ first, in row blocks; each block's exchange starts on the side stream as soon as it is written
+        # and runs under the remaining dW blocks and the dX GEMM, which leave the exchange kernel its SMs
+        for c, (r0, r1) in enumerate(chunk_rows):
+            if c > 0 and comm_sms > 0:
+                lib.ge2b_set_sm_limit(sm_total - comm_sms)
+            og.forward_into(X[:, r0:r1], work, out=dW[r0:r1], trans_a=True)
+            comm.wait_stream(cur)
+            last = c == len(chunk_rows) - 1
+            bucket.all_reduce(c, c + 1 if last else c, stream=comm)      # the last exchange takes db along
+        if comm_sms > 0:
+            lib.ge2b_set_sm_limit(sm_total - comm_sms)
         og.backward_into(X, W, dY, Z, act=ACT, gA_out=dX, work_dZ=work, reuse_dZ=True)
-        if world > 1 and comm_sms > 0:
-            lib.ge2b_set_sm_limit(0)
-        if world > 1:
-            cur.wait_stream(comm)
+        lib.ge2b_set_sm_limit(0)
+        cur.wait_stream(comm)
 
     def barrier():
         torch.cuda.synchronize()
@@ -477,14 +480,11 @@ def run_ours(args):
         torch.cuda.empty_cache()
 
     # multi-GPU: the combined gradients are checked after the timed region.  One eager step; dW / db must equal the
-    # fp32 sum of every rank's own dW / db (gathered) on sampled rows, in both forms of the step.
+    # fp32 sum of every rank's own dW / db (gathered) on sampled rows.
     allreduce_check = None
     if world > 1:
         allreduce_check = "ok"
-        saved_chunks = dw_chunks
-        for form in (0, 2):
-            dw_chunks = form
-            rows_per_chunk = K // max(1, dw_chunks)
+        for form in ("step",):
             # this rank's own gradients (no exchange) ...
             og.backward_into(X, W, dY, Z, act=ACT, with_bias=True, gA_out=dX, gB_out=dW, gBias_out=db, work_dZ=work)
             rows_chk = torch.arange(0, K, 61, device=dev)
@@ -496,11 +496,11 @@ def run_ours(args):
             step(False)
             barrier()
             got = torch.cat([dW[rows_chk].float().reshape(-1), db.reshape(-1)])
-            err = float((got - want).norm() / want.norm())
+            err_t = ((got - want).norm() / want.norm()).reshape(1)
+            dist.all_reduce(err_t, op=dist.ReduceOp.MAX)              # the worst rank decides
+            err = float(err_t.item())
             if not err <= 1e-2:          # bf16 storage of the sum: 2^-9 relative per element
-                allreduce_check = f"MISMATCH form={form} rel_fro={err:.3e}"
-        dw_chunks = saved_chunks
-        rows_per_chunk = K // max(1, dw_chunks)
+                allreduce_check = f"MISMATCH rel_fro={err:.3e}"
     value = world * FLOP_PER_STEP * replays / (total_ms * 1e-3) / 1e12
     burst_value = world * FLOP_PER_STEP * args.steps / (burst_ms * 1e-3) / 1e12
     assert lib.ge2b_device_status(0) == 0, "a bounded wait inside a kernel timed out"
@@ -548,42 +548,65 @@ def run_ours(args):
     # plausibility of the plan's results against the device-resident run
     assert torch.equal(Y_o, Y.cpu()), "host-plan Y differs from the device-resident forward"
 
-    # ---- the 3-layer MLP training step: global batch 8192 sharded along M (strong scaling)
+    # ---- the 3-layer MLP training step: global batch 8192 sharded along M (strong scaling), driven by the C++ plan
+    # (ge2b_mlp_plan_*: buffers, warm-up, capture and replay inside the library; each layer's dW / db summed over the
+    # ranks under the rest of the backward pass)
     mlp = None
     if not args.skip_mlp and 8192 % world == 0:
-        tr = pkg.DenseStackTrainer([1024, 4096, 4096, 1024], ["relu", "gelu", "none"], 8192 // world, lr=1e-3, seed=0,
-                                   device=dev, group=dist.group.WORLD if world > 1 else None, global_batch=8192)
-        tr.compile(capture="with_collectives" if (world > 1 and nccl_graph) else True)
+        rows = 8192 // world
+        mp_ = pkg.MlpPlan([1024, 4096, 4096, 1024], ["relu", "gelu", "none"], rows, lr=1e-3, seed=0, device=dev,
+                          group=dist.group.WORLD if world > 1 else None, global_batch=8192, comm_blocks=comm_sms,
+                          exchange="nccl" if os.environ.get("GE2B_BENCH_EXCHANGE", "") == "nccl" else "auto")
+        mp_.compile(capture=True)
         gen.manual_seed(100 + rank)
-        tr.X.copy_(torch.randn((8192 // world, 1024), generator=gen).bfloat16())
-        tr.labels.copy_(torch.randint(0, 1024, (8192 // world,), generator=gen, dtype=torch.int32))
+        Xm_h = torch.randn((rows, 1024), generator=gen).bfloat16().pin_memory()
+        ym_h = torch.randint(0, 1024, (rows,), generator=gen, dtype=torch.int32).pin_memory()
+        mp_.step_host(Xm_h, ym_h)                       # the batch is now in the plan's device buffers
+        mst = mp_.stream()
         for _ in range(3):
-            tr.launch()
+            mp_.launch()
         barrier()
 
         def mlp_window(n):
             m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            tr.launch()
+            mp_.launch()
             barrier()                  # the ranks enter the window together
-            m0.record()
+            m0.record(mst)
             for _ in range(n):
-                tr.launch()
-            m1.record()
+                mp_.launch()
+            m1.record(mst)
             barrier()
             mms = torch.tensor([m0.elapsed_time(m1)], device=dev)
             if world > 1:
                 dist.all_reduce(mms, op=dist.ReduceOp.MAX)
             return float(mms.item())
 
-        probe = mlp_window(max(5, min(args.steps, 20))) / max(5, min(args.steps, 20))
+        probe_n = max(5, min(args.steps, 20))
+        probe = mlp_window(probe_n) / probe_n
         mlp_steps = max(20, int(500.0 / max(probe, 1e-3)) + 1)          # a window of at least half a second
         per = mlp_window(mlp_steps) / mlp_steps
+        # end to end: every step copies its batch up from pinned host memory and reads the loss back
+        e_n = max(5, min(args.steps, 30))
+        mp_.step_host(Xm_h, ym_h)
+        barrier()
+        w0 = time.perf_counter()
+        for _ in range(e_n):
+            mloss = mp_.step_host(Xm_h, ym_h)
+        w1 = time.perf_counter()
+        e_t = torch.tensor([(w1 - w0) / e_n], device=dev)
+        if world > 1:
+            dist.all_reduce(e_t, op=dist.ReduceOp.MAX)
         mlp = {"workload": "3-layer MLP training step, global batch 8192, 1024-4096-4096-1024, ReLU/GELU/none, bf16 weights "
                            "with fp32 master, softmax cross-entropy, SGD lr=1e-3; batch rows sharded over the GPUs",
-               "steps_per_s": 1e3 / per, "ms_per_step": per, "scaling": "strong", "steps_timed": mlp_steps,
-               "tflops": world * tr.flop_per_step() / (per * 1e-3) / 1e12,
-               "launch_mode": "cuda graph replay" if tr.graph is not None else "eager", "loss": tr.global_loss()}
+               "steps_per_s": 1e3 / per, "ms_per_step": per, "burst_steps_per_s": 1e3 / probe, "scaling": "strong",
+               "steps_timed": mlp_steps, "tflops": world * mp_.flop_per_step() / (per * 1e-3) / 1e12,
+               "driver": "ge2b_mlp_plan_* (C ABI): CUDA graph replay", "exchange": mp_.exchange,
+               "gpu_launches_per_step": mp_.launches_per_step(),
+               "e2e": {"steps_per_s": 1.0 / float(e_t.item()), "h2d_bytes_per_step": Xm_h.numel() * 2 + ym_h.numel() * 4,
+                       "d2h_bytes_per_step": 4, "api": "ge2b_mlp_plan_step (pinned host batch up, loss back, every step)"},
+               "loss": mp_.global_loss()}
         assert lib.ge2b_device_status(0) == 0
+        mp_.close()
 
     if rank == 0:
         peak, peak_kind = measured_peak("bf16_tflops")
@@ -596,9 +619,11 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": total_ms / replays, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": dict(CONFIG, parallelism=(f"dp{world} (rows of the batch; all-reduce of dW row blocks + db overlapped with backward GEMMs)"
-                                        if dw_chunks > 0 else
-                                        f"dp{world} (rows of the batch; dX and dW in one launch, all-reduce of dW + db after it)")
+            "config": dict(CONFIG, parallelism=(f"dp{world} (rows of the batch; dW in {dw_chunks} row block(s), each summed over the "
+                                                f"ranks under the rest of the backward; exchange: {bucket.impl})"
+                                                if dw_chunks > 0 else
+                                                f"dp{world} (rows of the batch; dX and dW in one launch, dW + db summed over the "
+                                                f"ranks after it; exchange: {bucket.impl})")
                            if world > 1 else "single GPU"),
             "replays_timed": replays, "timed_region_s": total_ms * 1e-3,
             "window": f"value: the step replayed {replays} times (a region of at least {MIN_WINDOW_S} s, the clock the "
@@ -629,6 +654,8 @@ def run_ours(args):
             line["target_8192"] = target
         if allreduce_check is not None:
             line["allreduce_check"] = allreduce_check
+            line["exchange"] = {"impl": bucket.impl, "fallback_reason": bucket.why or None, "sms": comm_sms,
+                                "dw_row_blocks": dw_chunks}
         if mlp is not None:
             line["mlp_step"] = mlp
         if world == 1 and not args.skip_cpu_baseline:

@@ -278,6 +278,57 @@ typedef struct {
 int ge2b_allreduce_nvls(const ge2b_allreduce_nvls_t* args, void* stream);
 int ge2b_allreduce_nvls_pad_bytes(void);
 
+/* ------------------------------------------------------------------------------------------------
+ * The captured training step around the dense layers: Dense stack -> softmax cross-entropy (mean) -> SGD.
+ * C++ counterpart of the reference's Python graph runtime for this path (graph/capture_plan.py:250-287 buffers per
+ * layer, graph/runtime.py:24-148 step order, graph/graph_exec.py:51-231 warm-up / capture / replay,
+ * layers/sequential.py:416-497 compile / one_step).  Buffers are allocated once; the step is replayed from a CUDA
+ * graph.  With world > 1 the rows are one shard of the global batch and every layer's dW / db are summed over the
+ * ranks on a side stream under the rest of the backward pass.
+ * ------------------------------------------------------------------------------------------------ */
+#define GE2B_MLP_MAX_LAYERS 8
+typedef struct ge2b_mlp_plan ge2b_mlp_plan;
+typedef struct {
+  int n_layers;                          /* 1..GE2B_MLP_MAX_LAYERS */
+  int dims[GE2B_MLP_MAX_LAYERS + 1];     /* dims[i] -> dims[i+1] is layer i */
+  int acts[GE2B_MLP_MAX_LAYERS];         /* GE2_ACT_* per layer */
+  int batch;                             /* rows on this rank */
+  int global_batch;                      /* rows over all ranks (<= 0: batch): denominator of the mean loss */
+  ge2_dtype_t dtype;                     /* compute dtype of weights / activations (fp32 master weights are kept) */
+  float lr;
+  int world, rank;                       /* data-parallel replicas; world 1 = single GPU */
+  int exchange;                          /* world > 1: 1 = ge2b_allreduce_nvls over the symmetric memory below,
+                                            2 = the collective library (NCCL), communicator built from nccl_unique_id */
+  void* grad_base;                       /* exchange 1: this rank's mapping of the symmetric gradient buffer of
+                                            ge2b_mlp_plan_grad_bytes() bytes, zero-filled ... */
+  void* grad_multicast;                  /* ... its multicast address ... */
+  void* const* peer_grad_bases;          /* ... and every rank's buffer as mapped on this GPU [world] */
+  const void* nccl_unique_id;            /* exchange 2: 128 bytes from ge2b_nccl_unique_id() on rank 0, sent to all */
+  int comm_blocks;                       /* exchange 1: thread blocks of the exchange kernel (<= 0: default) */
+} ge2b_mlp_config_t;
+
+size_t ge2b_mlp_plan_grad_bytes(const ge2b_mlp_config_t* cfg);
+int ge2b_nccl_unique_id(void* id128);
+int ge2b_mlp_plan_create(ge2b_mlp_plan** out, const ge2b_mlp_config_t* cfg);
+void ge2b_mlp_plan_destroy(ge2b_mlp_plan* plan);
+/* fp32 HOST arrays: W [dims[l], dims[l+1]] row-major and b [dims[l+1]]; null = leave unchanged. */
+int ge2b_mlp_plan_set_params(ge2b_mlp_plan* plan, int layer, const float* W, const float* b);
+/* Any of W (fp32 master), b, W_low (the compute-dtype copy) may be null. */
+int ge2b_mlp_plan_get_params(ge2b_mlp_plan* plan, int layer, float* W, float* b, void* W_low);
+/* Gradients of the last step, after the exchange: gW in the compute dtype, gb fp32. */
+int ge2b_mlp_plan_get_grads(ge2b_mlp_plan* plan, int layer, void* gW, float* gb);
+/* Warm-up (parameters are saved and restored around it) and, with capture != 0, graph capture + instantiation. */
+int ge2b_mlp_plan_compile(ge2b_mlp_plan* plan, int capture);
+/* One step on the batch already in the plan's device buffers (asynchronous). */
+int ge2b_mlp_plan_launch(ge2b_mlp_plan* plan);
+/* One step from HOST data (X in the compute dtype, int32 labels; null = keep the batch in place); with loss_out the
+ * call waits for the step and returns this rank's share of the mean loss. */
+int ge2b_mlp_plan_step(ge2b_mlp_plan* plan, const void* X_host, const int* labels_host, float* loss_out);
+int ge2b_mlp_plan_sync(ge2b_mlp_plan* plan);
+/* what: 0 input X, 1 labels (int32), 2 loss (fp32 scalar), 3 the plan's stream (cudaStream_t), 4 logits. */
+void* ge2b_mlp_plan_buffer(ge2b_mlp_plan* plan, int what);
+long long ge2b_mlp_plan_launches_per_step(ge2b_mlp_plan* plan);
+
 /* Introspection for tests and benchmarks: which kernel family the calling thread's most recent GEMM went to
  * (0 none, 1 exact-fp32 CUDA-core kernel, 2 tcgen05 tensor-core kernel) and how many kernels this library
  * has launched in the process. */

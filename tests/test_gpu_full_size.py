@@ -108,19 +108,36 @@ def test_attention_gemms_full_size(pkg, lib):
     assert torch.equal(S2, S)
 
 
-@pytest.mark.parametrize("capture", [True])
-def test_mlp_step_full_size(pkg, lib, oracle, capture):
-    """config 3: batch 8192, 1024 -> 4096 -> 4096 -> 1024, ReLU / GELU / none, softmax-CE (mean), SGD lr = 1e-3."""
+@pytest.mark.parametrize("driver", ["plan", "trainer"])
+def test_mlp_step_full_size(pkg, lib, oracle, driver):
+    """config 3: batch 8192, 1024 -> 4096 -> 4096 -> 1024, ReLU / GELU / none, softmax-CE (mean), SGD lr = 1e-3, one
+    captured step through the C++ plan (ge2b_mlp_plan_*) and through the torch-tensor trainer."""
     dims, acts, B, lr = [1024, 4096, 4096, 1024], ["relu", "gelu", "none"], 8192, 1e-3
-    tr = pkg.DenseStackTrainer(dims, acts, B, lr=lr, seed=0)
-    W0 = [w.cpu().numpy().astype(np.float64) for w in tr.W32]
-    b0 = [x.cpu().numpy().astype(np.float64) for x in tr.b]
-    tr.compile(capture=capture)
     rng = np.random.default_rng(3)
     X = oracle.bf16_round(rng.standard_normal((B, dims[0]), dtype=np.float32))
     y = rng.integers(0, dims[-1], B).astype(np.int32)
-    loss = tr.one_step(torch.from_numpy(X).cuda().bfloat16(), torch.from_numpy(y).cuda())
-    torch.cuda.synchronize()
+    if driver == "plan":
+        plan = pkg.MlpPlan(dims, acts, B, lr=lr, seed=0)
+        W0 = [plan.params(i)[0].numpy().astype(np.float64) for i in range(3)]
+        b0 = [plan.params(i)[1].numpy().astype(np.float64) for i in range(3)]
+        plan.compile(capture=True)
+        loss = plan.step_host(torch.from_numpy(X).bfloat16().pin_memory(), torch.from_numpy(y).pin_memory())
+        gWs = [plan.grads(i)[0].double().numpy() for i in range(3)]
+        gBs = [plan.grads(i)[1].double().numpy() for i in range(3)]
+        W32 = [plan.params(i)[0].double().numpy() for i in range(3)]
+        low_ok = all(torch.equal(plan.params(i)[2], plan.params(i)[0].bfloat16()) for i in range(3))
+        plan.close()
+    else:
+        tr = pkg.DenseStackTrainer(dims, acts, B, lr=lr, seed=0)
+        W0 = [w.cpu().numpy().astype(np.float64) for w in tr.W32]
+        b0 = [x.cpu().numpy().astype(np.float64) for x in tr.b]
+        tr.compile(capture=True)
+        loss = tr.one_step(torch.from_numpy(X).cuda().bfloat16(), torch.from_numpy(y).cuda())
+        torch.cuda.synchronize()
+        gWs = [t.double().cpu().numpy() for t in tr.gW]
+        gBs = [t.double().cpu().numpy().ravel() for t in tr.gB]
+        W32 = [t.double().cpu().numpy() for t in tr.W32]
+        low_ok = all(torch.equal(tr.W[i], tr.W32[i].bfloat16()) for i in range(3))
     assert lib.ge2b_device_status(1) == 0
     ref_loss, W1, b1, grads = oracle.mlp_step_f64(W0, b0, X, y, acts, lr, lowp=oracle.bf16_round)
     assert abs(loss - ref_loss) <= 5e-3 * abs(ref_loss), (loss, ref_loss)
@@ -128,10 +145,8 @@ def test_mlp_step_full_size(pkg, lib, oracle, capture):
         rows = _one_per_block(dims[i], rng)
         # gradients as the step left them (bf16 dW, fp32 db): intermediate activations and gradients are rounded to
         # bf16 between layers on the device and not in the float64 reference, hence the contract's 2e-2 here
-        gW = tr.gW[i].double().cpu().numpy()
-        assert rel_fro(gW[rows], grads[i][0][rows]) <= FRO_TOL, i
-        assert rel_fro(tr.gB[i].double().cpu().numpy().ravel(), grads[i][1]) <= FRO_TOL, i
+        assert rel_fro(gWs[i][rows], grads[i][0][rows]) <= FRO_TOL, i
+        assert rel_fro(gBs[i], grads[i][1]) <= FRO_TOL, i
         # the update itself: W1 - W0 = -lr * dW in fp32 on the rounded dW
-        got = tr.W32[i].double().cpu().numpy()[rows] - W0[i][rows]
-        assert rel_fro(got, W1[i][rows] - W0[i][rows]) <= 2.5e-2, i
-        assert torch.equal(tr.W[i], tr.W32[i].bfloat16())
+        assert rel_fro(W32[i][rows] - W0[i][rows], W1[i][rows] - W0[i][rows]) <= 2.5e-2, i
+    assert low_ok

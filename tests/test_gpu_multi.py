@@ -102,3 +102,61 @@ def test_gradient_bucket_all_reduce(tmp_path, force_nccl):
     impl = out.read_text()
     print("all-reduce implementation:", impl)
     assert impl.startswith("nccl") if force_nccl else True
+
+
+def _mlp_worker(rank, world, port, exchange, out):
+    import importlib
+    import numpy as np
+    import torch.distributed as dist
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    pkg = importlib.import_module("ai_framework-dev_b200")
+    oracle = importlib.import_module("oracle.dense_oracle")
+    lib = pkg.load_library()
+    dims, acts, B, lr = [256, 512, 384, 128], ["relu", "gelu", "none"], 512, 0.05
+    rows = B // world
+    plan = pkg.MlpPlan(dims, acts, rows, lr=lr, seed=5, device=torch.device("cuda", rank), group=dist.group.WORLD,
+                       global_batch=B, exchange=exchange, comm_blocks=8)
+    W = [plan.params(i)[0].numpy().astype(np.float64) for i in range(3)]
+    b = [plan.params(i)[1].numpy().astype(np.float64) for i in range(3)]
+    plan.compile(capture=True)
+    rng = np.random.default_rng(1)                         # every rank draws the same global batch
+    for step in range(3):
+        X = oracle.bf16_round(rng.standard_normal((B, dims[0]), dtype=np.float32))
+        y = rng.integers(0, dims[-1], B).astype(np.int32)
+        lo, hi = pkg.train.shard_rows(B, world, rank)
+        plan.step_host(torch.from_numpy(X[lo:hi]).bfloat16().pin_memory(), torch.from_numpy(y[lo:hi]).pin_memory())
+        loss = plan.global_loss()
+        ref_loss, W, b, _ = oracle.mlp_step_f64(W, b, X, y, acts, lr, lowp=oracle.bf16_round)   # the FULL batch
+        assert abs(loss - ref_loss) <= 2e-2 * abs(ref_loss), (rank, step, loss, ref_loss)
+    got = [plan.params(i)[0] for i in range(3)]
+    for i in range(3):
+        # every replica holds the same parameters, and they follow the full-batch reference
+        t = got[i].cuda()
+        ref = t.clone()
+        dist.broadcast(ref, src=0)
+        assert torch.equal(t, ref), ("replicas diverged", i)
+    assert lib.ge2b_device_status(1) == 0
+    if rank == 0:
+        Path(out).write_text(plan.exchange)
+    plan.close()
+    dist.barrier()
+    torch.cuda.synchronize()
+    os._exit(0)
+
+
+@pytest.mark.parametrize("exchange", ["auto", "nccl"])
+def test_mlp_plan_data_parallel(tmp_path, exchange):
+    """The C++ step driver on two replicas: each gets half of the rows, every layer's dW / db are summed over the
+    replicas inside the captured step, and the result follows the float64 reference of the FULL batch."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+    port = 29900 + os.getpid() % 90 + (5 if exchange == "nccl" else 0)
+    out = tmp_path / "x.txt"
+    mp.spawn(_mlp_worker, args=(2, port, exchange, str(out)), nprocs=2, join=True)
+    print("exchange:", out.read_text())
+    if exchange == "nccl":
+        assert out.read_text() == "nccl"

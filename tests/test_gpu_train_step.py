@@ -180,3 +180,53 @@ def test_sgd_against_reference_op(pkg, lib, momentum, dampening, nesterov, wd):
     assert float(((p - p_ref).abs() / p_ref.abs().clamp_min(1.0)).max()) <= 1e-6
     if momentum:
         assert float(((v - v_ref).abs() / v_ref.abs().clamp_min(1.0)).max()) <= 1e-6
+
+
+# --------------------------------------------------------------------------- the C++ step driver (ge2b_mlp_plan_*)
+@pytest.mark.parametrize("capture", [False, True])
+def test_mlp_plan_training_steps_match_float64(pkg, lib, oracle, capture):
+    """The library-owned plan (buffers, warm-up, capture, replay in C++) through its C ABI, host batches in."""
+    dims, acts, B, lr = [96, 256, 192, 64], ["relu", "gelu", "none"], 128, 0.05
+    plan = pkg.MlpPlan(dims, acts, B, lr=lr, seed=3)
+    W = [plan.params(i)[0].numpy().astype(np.float64) for i in range(3)]
+    b = [plan.params(i)[1].numpy().astype(np.float64) for i in range(3)]
+    plan.compile(capture=capture)
+    for i in range(3):                                       # the warm-up left the parameters alone
+        w1, b1, wl = plan.params(i)
+        assert np.array_equal(w1.numpy().astype(np.float64), W[i]) and np.array_equal(b1.numpy().astype(np.float64), b[i])
+        assert torch.equal(wl, w1.bfloat16())
+    W_start = [w.copy() for w in W]
+    rng = np.random.default_rng(0)
+    for step in range(3):
+        X = oracle.bf16_round(rng.standard_normal((B, dims[0]), dtype=np.float32))
+        y = rng.integers(0, dims[-1], B).astype(np.int32)
+        loss = plan.step_host(torch.from_numpy(X).bfloat16().pin_memory(), torch.from_numpy(y).pin_memory())
+        ref_loss, W, b, _ = oracle.mlp_step_f64(W, b, X, y, acts, lr, lowp=oracle.bf16_round)
+        assert abs(loss - ref_loss) <= 2e-2 * abs(ref_loss), (step, loss, ref_loss)
+    for i in range(3):
+        w1, b1, wl = plan.params(i)
+        assert oracle.rel_fro(w1.numpy().astype(np.float64) - W_start[i], W[i] - W_start[i]) <= 5e-2, i
+        assert torch.equal(wl, w1.bfloat16())
+    assert abs(plan.global_loss() - loss) <= 1e-6
+    assert lib.ge2b_device_status(1) == 0
+    plan.close()
+
+
+def test_mlp_plan_agrees_with_the_python_trainer(pkg, lib):
+    """Same seed, same batches: the C++ plan and the torch-tensor trainer launch the same kernels in the same order."""
+    dims, acts, B = [128, 320, 64], ["gelu", "none"], 256
+    tr = pkg.DenseStackTrainer(dims, acts, B, lr=0.02, seed=11)
+    plan = pkg.MlpPlan(dims, acts, B, lr=0.02, seed=11)
+    tr.compile(capture=True)
+    plan.compile(capture=True)
+    g = torch.Generator().manual_seed(1)
+    for _ in range(2):
+        X = torch.randn((B, dims[0]), generator=g).bfloat16()
+        y = torch.randint(0, dims[-1], (B,), generator=g, dtype=torch.int32)
+        l1 = tr.one_step(X.cuda(), y.cuda())
+        l2 = plan.step_host(X, y)
+        assert abs(l1 - l2) <= 1e-5 * max(1.0, abs(l1))
+    for i in range(2):
+        w, bb, _ = plan.params(i)
+        assert torch.allclose(w, tr.W32[i].cpu(), rtol=0, atol=1e-6) and torch.allclose(bb, tr.b[i].cpu(), rtol=0, atol=1e-6)
+    plan.close()
