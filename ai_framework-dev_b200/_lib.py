@@ -95,7 +95,7 @@ class ParamsConv2D(C.Structure):
 BIAS_SCALAR, BIAS_PER_M, BIAS_PER_N = 0, 1, 2
 ACT = {"none": 0, "relu": 1, "leaky_relu": 2, "leakyrelu": 2, "lrelu": 2, "gelu": 3, "sigmoid": 4, "tanh": 5}
 DT_F32, DT_F16, DT_BF16 = 0, 1, 2
-MATH_FP32, MATH_TENSOR = 0, 1
+MATH_FP32, MATH_TENSOR, MATH_FP32X3 = 0, 1, 2
 NOALLOC_SCRATCH_BYTES = 16 << 20
 
 # every symbol include/ge2_b200.h declares

@@ -83,7 +83,7 @@ extern "C" int ge2_launch_gemm_bias_act_bwd_noalloc(const ge2_uintptr* bufs, int
   DenseBackward b;
   b.M = pb.M; b.N = pb.N; b.K = pb.K;
   b.dtype = dt; b.z_dtype = zdt;
-  b.math = (dt == GE2_DT_F32) ? (pt->math == GE2_MATH_TENSOR ? 1 : 0) : 1;
+  b.math = (dt == GE2_DT_F32) ? (pt->math == GE2_MATH_TENSOR ? 1 : (pt->math == GE2_MATH_FP32X3 ? 2 : 0)) : 1;
   b.A = reinterpret_cast<const void*>(bufs[0]);
   b.B = reinterpret_cast<const void*>(bufs[1]);
   b.C = reinterpret_cast<const void*>(bufs[2]);

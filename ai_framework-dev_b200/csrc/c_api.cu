@@ -108,7 +108,7 @@ int ge2_launch_gemm_bias_act_typed(const ge2_uintptr* bufs, int n, void* stream)
   if (!dtype_ok(pt->dtype) || !dtype_ok(pt->z_dtype)) return kBadArgs;
   DenseForward f;
   f.dtype = pt->dtype; f.z_dtype = pt->z_dtype;
-  f.math = (pt->dtype == GE2_DT_F32) ? (pt->math == GE2_MATH_TENSOR ? 1 : 0) : 1;
+  f.math = (pt->dtype == GE2_DT_F32) ? (pt->math == GE2_MATH_TENSOR ? 1 : (pt->math == GE2_MATH_FP32X3 ? 2 : 0)) : 1;
   f.trans_b = pt->trans_b != 0;
   f.trans_a = pt->trans_a != 0;
   const int rc = forward_from_bufs(bufs, n, pt->base, f);
@@ -157,7 +157,7 @@ int ge2_launch_gemm_bias_act_bwd_typed(const ge2_uintptr* bufs, int n, void* str
   const auto* pt = reinterpret_cast<const ge2_gemm_bwd_typed_params_t*>(bufs[n - 1]);
   if (!pt) return kBadArgs;
   if (!dtype_ok(pt->dtype) || !dtype_ok(pt->z_dtype)) return kBadArgs;
-  const int math = (pt->dtype == GE2_DT_F32) ? (pt->math == GE2_MATH_TENSOR ? 1 : 0) : 1;
+  const int math = (pt->dtype == GE2_DT_F32) ? (pt->math == GE2_MATH_TENSOR ? 1 : (pt->math == GE2_MATH_FP32X3 ? 2 : 0)) : 1;
   return backward_common(bufs, pt->base, pt->dtype, pt->z_dtype, math, reinterpret_cast<void*>(bufs[9]),
                          pt->scratch_bytes, pt->reuse_gz != 0, stream);
 }

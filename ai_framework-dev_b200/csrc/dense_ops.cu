@@ -17,9 +17,39 @@ namespace {
 thread_local int t_last_route = kRouteNone;
 std::atomic<long long> g_launches{0};
 
+// fp32 backward GEMMs (tolerance-checked everywhere; the reference runs them through cuBLAS) default to the
+// error-compensated tensor-core mode; GE2B_FP32_BWD=exact keeps them on the CUDA-core kernel.
+bool fp32_bwd_compensated() {
+  static const bool on = [] { const char* e = std::getenv("GE2B_FP32_BWD"); return !(e && std::strcmp(e, "exact") == 0); }();
+  return on;
+}
+
+bool stream_is_capturing(cudaStream_t s) {
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  return cudaStreamIsCapturing(s, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone;
+}
+
+// Scratch of the compensated mode (big / small copies of the operands), from the stream-ordered allocator; not
+// available while the stream is being captured.
+struct AsyncScratch {
+  cudaStream_t s; void* p = nullptr;
+  AsyncScratch(cudaStream_t st, size_t bytes) : s(st) {
+    if (stream_is_capturing(st)) return;
+    keep_async_pool_cached();
+    if (cudaMallocAsync(&p, bytes, st) != cudaSuccess) { cudaGetLastError(); p = nullptr; }
+  }
+  ~AsyncScratch() { if (p) cudaFreeAsync(p, s); }
+  AsyncScratch(const AsyncScratch&) = delete;
+  AsyncScratch& operator=(const AsyncScratch&) = delete;
+};
+
+size_t up256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
+
+bool aligned_for_tc(const void* p, long long ld) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && (ld * 4) % 16 == 0; }
+
 int run_gemm(const GemmProblem& g, cudaStream_t s) {
   const char* why = nullptr;
-  const bool want_tc = (g.in_dtype != kF32) || g.math == 1;
+  const bool want_tc = (g.in_dtype != kF32) || g.math == 1 || (g.math == 2 && g.A_small && g.B_small);
   cudaError_t e;
   if (want_tc && gemm_tc_supported(g, &why)) {
     e = launch_gemm_tc(g, s);
@@ -36,7 +66,7 @@ int run_gemm(const GemmProblem& g, cudaStream_t s) {
 
 int run_gemm_problem(const GemmProblem& g, cudaStream_t s) {
   if (g.reduce_batch && g.batch > 1) {
-    const bool want_tc = (g.in_dtype != kF32) || g.math == 1;
+    const bool want_tc = (g.in_dtype != kF32) || g.math == 1;      // (the compensated mode has no batch-reducing form)
     if (!want_tc || !gemm_tc_supported(g, nullptr)) return kUnimplemented;
   }
   return run_gemm(g, s);
@@ -73,6 +103,29 @@ int dense_forward(const DenseForward& f, cudaStream_t s) {
   e.act = f.act; e.leaky = f.leaky;
   e.alpha = f.alpha; e.beta = f.beta;
   e.d_dtype = f.dtype; e.z_dtype = f.z_dtype;
+  if (f.dtype == kF32 && f.math == 2) {
+    // error-compensated fp32 on tensor cores: split both operands (big + small), three TF32 products per k-block
+    const size_t a_elems = static_cast<size_t>(f.trans_a ? f.K : f.M) * (f.trans_a ? f.M : f.K);
+    const size_t b_elems = static_cast<size_t>(f.trans_b ? f.N : f.K) * (f.trans_b ? f.K : f.N);
+    const size_t a_b = up256(a_elems * 4), b_b = up256(b_elems * 4);
+    AsyncScratch sc(s, batch == 1 ? 2 * (a_b + b_b) : 0);
+    if (batch == 1 && sc.p) {
+      unsigned char* base = static_cast<unsigned char*>(sc.p);
+      float *Ab = reinterpret_cast<float*>(base), *As = reinterpret_cast<float*>(base + a_b);
+      float *Bb = reinterpret_cast<float*>(base + 2 * a_b), *Bs = reinterpret_cast<float*>(base + 2 * a_b + b_b);
+      const long long a_rows = f.trans_a ? f.K : f.M, a_cols = f.trans_a ? f.M : f.K;
+      const long long b_rows = f.trans_b ? f.N : f.K, b_cols = f.trans_b ? f.K : f.N;
+      if (a_cols % 4 == 0 && b_cols % 4 == 0 &&
+          launch_split_tf32(static_cast<const float*>(f.A), f.lda, Ab, As, a_rows, a_cols, s) == cudaSuccess &&
+          launch_split_tf32(static_cast<const float*>(f.B), f.ldb, Bb, Bs, b_rows, b_cols, s) == cudaSuccess) {
+        g_launches.fetch_add(2, std::memory_order_relaxed);
+        g.A = Ab; g.lda = a_cols; g.A_small = As;
+        g.B = Bb; g.ldb = b_cols; g.B_small = Bs;
+        return run_gemm(g, s);
+      }
+    }
+    g.math = 0;          // no scratch (stream capture, batched call, odd pitch): the exact CUDA-core kernel
+  }
   return run_gemm(g, s);
 }
 
@@ -139,25 +192,52 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
   };
 
   NvtxRange gemms_range("bwd.gemms");
+  // fp32 without a TF32 opt-in: the two GEMMs run in the error-compensated tensor-core mode when their split operands
+  // can be staged (not under stream capture; pitches that TMA can address), else on the exact CUDA-core kernel.
+  const bool want_x3 = b.dtype == kF32 && (b.math == 2 || (b.math == 0 && fp32_bwd_compensated())) && b.N % 4 == 0 &&
+                       b.K % 4 == 0 && (!b.gA || aligned_for_tc(b.gA, b.ldgA)) && (!b.gB || aligned_for_tc(b.gB, b.ldgB));
+  const size_t mn = up256(static_cast<size_t>(b.M) * b.N * 4), kn = up256(static_cast<size_t>(b.K) * b.N * 4),
+               mk = up256(static_cast<size_t>(b.M) * b.K * 4);
+  AsyncScratch x3(s, want_x3 ? 2 * mn + (b.gA ? 2 * kn : 0) + (b.gB ? 2 * mk : 0) : 0);
+  float *gZb = nullptr, *gZs = nullptr, *Wb = nullptr, *Ws = nullptr, *Xb = nullptr, *Xs = nullptr;
+  bool use_x3 = false;
+  if (want_x3 && x3.p) {
+    unsigned char* q = static_cast<unsigned char*>(x3.p);
+    gZb = reinterpret_cast<float*>(q); gZs = reinterpret_cast<float*>(q + mn); q += 2 * mn;
+    use_x3 = launch_split_tf32(static_cast<const float*>(gZ), b.N, gZb, gZs, b.M, b.N, s) == cudaSuccess;
+    if (use_x3 && b.gA) {
+      Wb = reinterpret_cast<float*>(q); Ws = reinterpret_cast<float*>(q + kn); q += 2 * kn;
+      use_x3 = launch_split_tf32(static_cast<const float*>(b.B), b.ldb, Wb, Ws, b.K, b.N, s) == cudaSuccess;
+    }
+    if (use_x3 && b.gB) {
+      Xb = reinterpret_cast<float*>(q); Xs = reinterpret_cast<float*>(q + mk);
+      use_x3 = launch_split_tf32(static_cast<const float*>(b.A), b.lda, Xb, Xs, b.M, b.K, s) == cudaSuccess;
+    }
+    if (use_x3) g_launches.fetch_add(1 + (b.gA ? 1 : 0) + (b.gB ? 1 : 0), std::memory_order_relaxed);
+  }
+  const int gemm_math = use_x3 ? 2 : (b.math == 2 ? 0 : b.math);
+
   GemmProblem ga{}, gb{};
   if (b.gA) {   // gA[M,K] = alpha * gZ[M,N] . B[K,N]^T : reduction over N, contiguous in both operands
     if (b.ldb < b.N || b.ldgA < b.K) return finish(kBadArgs);
     ga.M = b.M; ga.N = b.K; ga.K = b.N; ga.batch = 1;
-    ga.in_dtype = b.dtype; ga.math = b.math;
+    ga.in_dtype = b.dtype; ga.math = gemm_math;
     ga.a_mn = false; ga.A = gZ;  ga.lda = b.N;
     ga.b_mn = false; ga.B = b.B; ga.ldb = b.ldb;
+    if (use_x3) { ga.A = gZb; ga.A_small = gZs; ga.B = Wb; ga.B_small = Ws; ga.ldb = b.N; }
     ga.epi = plain_epilogue(b.gA, b.ldgA);
   }
   if (b.gB) {   // gB[K,N] = alpha * A[M,K]^T . gZ[M,N] : reduction over M, the outer index of both operands
     if (b.lda < b.K || b.ldgB < b.N) return finish(kBadArgs);
     gb.M = b.K; gb.N = b.N; gb.K = b.M; gb.batch = 1;
-    gb.in_dtype = b.dtype; gb.math = b.math;
+    gb.in_dtype = b.dtype; gb.math = gemm_math;
     gb.a_mn = true; gb.A = b.A; gb.lda = b.lda;
     gb.b_mn = true; gb.B = gZ;  gb.ldb = b.N;
+    if (use_x3) { gb.A = Xb; gb.A_small = Xs; gb.lda = b.K; gb.B = gZb; gb.B_small = gZs; }
     gb.epi = plain_epilogue(b.gB, b.ldgB);
   }
   // Both gradients wanted on the tensor-core path: one launch walks the tiles of both (see launch_gemm_tc_dual).
-  if (b.gA && b.gB && ((b.dtype != kF32) || b.math == 1)) {
+  if (b.gA && b.gB && ((b.dtype != kF32) || gemm_math == 1)) {
     const cudaError_t e = launch_gemm_tc_dual(ga, gb, s);
     if (e == cudaSuccess) {
       t_last_route = kRouteTensor;

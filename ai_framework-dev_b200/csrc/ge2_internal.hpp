@@ -67,11 +67,17 @@ struct EpilogueArgs {
 struct GemmProblem {
   int M, N, K, batch;
   int in_dtype;                                   // kBF16 / kF16 / kF32
-  int math;                                       // for kF32: 0 = exact fp32 FMA, 1 = TF32 tensor cores
+  int math;                                       // for kF32: 0 = exact fp32 FMA, 1 = TF32 tensor cores,
+                                                  // 2 = error-compensated TF32 (three products of split operands)
   bool a_mn, b_mn;
   const void* A; long long lda, strideA;
   const void* B; long long ldb, strideB;
   EpilogueArgs epi;
+  // math == 2: A and B hold the TF32-representable "big" parts of the fp32 operands and these the remainders
+  // (operand = big + small exactly), same geometry.  The launch computes big.big + big.small + small.big in one fp32
+  // accumulator: every product is exact in TF32 arithmetic and only small.small (2^-22 relative) is dropped.
+  const void* A_small = nullptr;
+  const void* B_small = nullptr;
   // The batch index joins the reduction: D = act(alpha * sum_b A[b].B[b] + ...), one output matrix.  Tensor-core
   // path only (used by the convolution's weight gradient, which sums over the images of a batch).
   bool reduce_batch = false;
@@ -97,6 +103,10 @@ cudaError_t launch_gemm_tc(const GemmProblem& g, cudaStream_t s);        // TMA 
 // caller then launches the two problems one after the other.
 cudaError_t launch_gemm_tc_dual(const GemmProblem& dx, const GemmProblem& dw, cudaStream_t s);
 cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s);
+// big = src with the 13 low mantissa bits cleared (exactly representable in TF32), small = src - big (exact in fp32);
+// src is rows x cols with pitch ld_src, big and small are written with pitch cols.
+cudaError_t launch_split_tf32(const float* src, long long ld_src, float* big, float* small, long long rows, long long cols,
+                              cudaStream_t s);
 
 // Reads (and optionally clears) the device status word of the current device. Synchronises.
 int  device_status_word(bool clear);

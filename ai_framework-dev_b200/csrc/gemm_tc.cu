@@ -237,6 +237,7 @@ void key_problem(PlanKey& k, const GemmProblem& g) {
   k.add_ptr(g.epi.Z); k.add(g.epi.ldz); k.add(g.epi.strideZ);
   k.add_ptr(g.epi.C); k.add(g.epi.ldc); k.add(g.epi.strideC);
   k.add_ptr(g.epi.bias);
+  k.add_ptr(g.A_small); k.add_ptr(g.B_small);
   k.add_f(g.epi.leaky); k.add_f(g.epi.alpha); k.add_f(g.epi.beta);
 }
 
@@ -326,7 +327,9 @@ void fill_common(const GemmProblem& g, tc::TcParams& p) {
 bool gemm_tc_supported(const GemmProblem& g, const char** why) {
   auto fail = [&](const char* m) { if (why) *why = m; return false; };
   if (g.M < 1 || g.N < 1 || g.K < 1 || g.batch < 1) return fail("empty problem");
-  if (g.in_dtype == kF32 && g.math != 1) return fail("fp32 operands without TF32 opt-in");
+  if (g.in_dtype == kF32 && g.math != 1 && g.math != 2) return fail("fp32 operands without a tensor-core math mode");
+  if (g.in_dtype == kF32 && g.math == 2 && (!g.A_small || !g.B_small || !aligned16(g.A_small) || !aligned16(g.B_small)))
+    return fail("split operands of the compensated mode missing or unaligned");
   const int esz = dtype_bytes(g.in_dtype);
   if (!aligned16(g.A) || !aligned16(g.B)) return fail("operand base not 16-byte aligned");
   if ((g.lda * esz) % 16 || (g.ldb * esz) % 16) return fail("operand row pitch not a multiple of 16 bytes");
@@ -343,6 +346,7 @@ cudaError_t launch_gemm_tc_dual(const GemmProblem& dx, const GemmProblem& dw, cu
   // the pair form: both problems unbatched, same element size, the orders of a dense backward, large enough for
   // CTA pairs, plain epilogues with TMA-storable 16-byte aligned outputs
   if (dx.batch != 1 || dw.batch != 1 || dx.in_dtype != dw.in_dtype) return cudaErrorNotSupported;
+  if (dx.math == 2 || dw.math == 2) return cudaErrorNotSupported;   // the compensated mode uses the second-problem slot
   if (dx.a_mn || dx.b_mn || !dw.a_mn || !dw.b_mn) return cudaErrorNotSupported;
   if (dx.M <= 128 || dw.M <= 128 || dx.N <= 128 || dw.N <= 128) return cudaErrorNotSupported;
   // worth it only when the combined list quantises better than the two lists do separately

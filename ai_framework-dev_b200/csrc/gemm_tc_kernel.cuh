@@ -47,6 +47,9 @@ struct TcParams {
   int a_bcast, b_bcast;     // operand has batch stride 0: always read slice 0
   int kb_per_slice;         // > 0: the reduction runs over every batch slice in turn (k_blocks = slices * this);
                             // one output matrix, `batch` is 1 for the tile schedule
+  int x3_kb;                // > 0: error-compensated fp32 (k_blocks = 3 * this): the reduction is walked three times,
+                            // over (A big, B big), (A big, B small), (A small, B big); the small parts' tensor maps
+                            // travel in the kernel's second-problem slot
   uint32_t idesc;
   EpilogueArgs epi;
   int d_vec, z_vec, c_vec, bias_vec;   // base, pitch and batch stride 16-byte aligned: D / Z leave through TMA stores,
@@ -470,7 +473,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0; bool ok = true;
       // One item (tile or slice of a tile) of problem `pp`, whose operands are stored in the orders AMN / BMN.
       auto produce = [&](auto amn_c, auto bmn_c, const TcParams& pp, const CUtensorMap* mA, const CUtensorMap* mB,
-                         const CUtensorMap* mBh, const WorkItem& w) {
+                         const CUtensorMap* mBh, const WorkItem& w) {   // mA / mB by value: the x3 form re-points them
         constexpr bool AMN = decltype(amn_c)::value, BMN = decltype(bmn_c)::value;
         const int b = w.b;
         const int m0 = w.mb * kTileM + static_cast<int>(cta_rank) * kBlockM;
@@ -491,6 +494,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int sl = kb / pp.kb_per_slice;
             k0 = (kb - sl * pp.kb_per_slice) * Cfg::kBlockK;
             ba = pp.a_bcast ? 0 : sl; bb = pp.b_bcast ? 0 : sl;
+          }
+          if constexpr (!kDual) {
+            if (pp.x3_kb > 0) {                        // three passes over the reduction with the split operands
+              const int pass = kb / pp.x3_kb;
+              k0 = (kb - pass * pp.x3_kb) * Cfg::kBlockK;
+              mA = pass == 2 ? &d2.tmA : &tmA;
+              mB = pass == 1 ? &d2.tmB : &tmB;
+            }
           }
           auto load = [&](uint32_t dst, const void* tm, int c0, int c1, int c2) {
             if constexpr (kCG == 2) ptx::tma_load_3d_pair(dst, tm, fb, c0, c1, c2);
@@ -851,7 +862,7 @@ struct PreparedLaunch {
 };
 cudaError_t run_prepared(const PreparedLaunch& L, cudaStream_t s);
 
-struct ProblemMaps { CUtensorMap tmA, tmB, tmD, tmZ; };
+struct ProblemMaps { CUtensorMap tmA, tmB, tmD, tmZ, tmAs, tmBs; };   // tmAs / tmBs: the small parts of an x3 problem
 
 // Fills the geometry fields of `p` and the tensor maps of one problem for the given tile configuration.
 template <int kElemBytes, bool kAMN, bool kBMN, int kBlockN, int kStages, int kCG>
@@ -866,9 +877,15 @@ bool prepare_problem(const GemmProblem& g, TcParams& p, ProblemMaps& m) {
   // with 32 row-blocks groups of 16 or 32 were not better than 8)
   p.group_m = p.m_blocks <= 16 ? p.m_blocks : kGroupM;
   p.kb_per_slice = 0;
+  p.x3_kb = 0;
   if (g.reduce_batch && g.batch > 1) {
     p.kb_per_slice = p.k_blocks;
     p.k_blocks *= g.batch;
+  }
+  if (g.in_dtype == kF32 && g.math == 2) {
+    if (!g.A_small || !g.B_small || p.kb_per_slice > 0) return false;
+    p.x3_kb = p.k_blocks;
+    p.k_blocks *= 3;
   }
   const int ab_format = g.in_dtype == kF32 ? 2 : (g.in_dtype == kBF16 ? 1 : 0);
   p.idesc = ptx::make_idesc(ab_format, kAMN, kBMN, kTileM, kBlockN);
@@ -882,6 +899,15 @@ bool prepare_problem(const GemmProblem& g, TcParams& p, ProblemMaps& m) {
   if (!kBMN) ok = make_operand_map(&m.tmB, g.in_dtype, g.B, g.K, g.N, g.ldb, g.batch, g.strideB, Cfg::kBlockK, kLocalN, false);
   else       ok = make_operand_map(&m.tmB, g.in_dtype, g.B, g.N, g.K, g.ldb, g.batch, g.strideB, Cfg::kBlockK, Cfg::kBlockK, kWide);
   if (!ok) return false;
+  m.tmAs = m.tmA; m.tmBs = m.tmB;
+  if (p.x3_kb > 0) {
+    if (!kAMN) ok = make_operand_map(&m.tmAs, g.in_dtype, g.A_small, g.K, g.M, g.lda, g.batch, g.strideA, Cfg::kBlockK, kBlockM, false);
+    else       ok = make_operand_map(&m.tmAs, g.in_dtype, g.A_small, g.M, g.K, g.lda, g.batch, g.strideA, Cfg::kBlockK, Cfg::kBlockK, kWide);
+    if (!ok) return false;
+    if (!kBMN) ok = make_operand_map(&m.tmBs, g.in_dtype, g.B_small, g.K, g.N, g.ldb, g.batch, g.strideB, Cfg::kBlockK, kLocalN, false);
+    else       ok = make_operand_map(&m.tmBs, g.in_dtype, g.B_small, g.N, g.K, g.ldb, g.batch, g.strideB, Cfg::kBlockK, Cfg::kBlockK, kWide);
+    if (!ok) return false;
+  }
 
   // Outputs as tensor maps for the epilogue's bulk stores (when base, pitch and batch stride allow).
   m.tmD = m.tmA; m.tmZ = m.tmA;
@@ -920,6 +946,7 @@ cudaError_t prepare_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s, Prepa
   ProblemMaps pm;
   if (!prepare_problem<kElemBytes, kAMN, kBMN, kBlockN, kStages, kCG>(g, p, pm)) return cudaErrorInvalidValue;
   L.tmA = pm.tmA; L.tmB = pm.tmB; L.tmD = pm.tmD; L.tmZ = pm.tmZ;
+  L.d2.tmA = pm.tmAs; L.d2.tmB = pm.tmBs;         // read only when p.x3_kb > 0
 
   const long long tiles = static_cast<long long>(p.batch) * p.m_blocks * p.n_blocks;
   const long long units = sm_budget() / kCG > 0 ? sm_budget() / kCG : 1;   // one CTA (or CTA pair) per SM (pair of SMs)
@@ -961,7 +988,8 @@ cudaError_t prepare_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s, Prepa
   // Narrow tail: several waves whose last one fills at most half of the pairs.
   bool narrow_tail = false;
   static const bool narrow_off = [] { const char* e = getenv("GE2B_NARROW_TAIL"); return e && atoi(e) == 0; }();
-  if (kCG == 2 && kBlockN == 256 && !narrow_off && p.split == 1 && tiles > units && rem > 0 && 2 * rem <= units) {
+  if (kCG == 2 && kBlockN == 256 && !narrow_off && p.x3_kb == 0 && p.split == 1 && tiles > units && rem > 0 &&
+      2 * rem <= units) {
     narrow_tail = true;
     p.main_tiles = static_cast<int>(tiles - rem);
     p.tail_tiles = static_cast<int>(rem);

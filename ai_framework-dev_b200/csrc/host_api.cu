@@ -69,7 +69,7 @@ int ge2b_dense_plan_create(ge2b_dense_plan** out, int M, int K, int N, ge2_dtype
   ge2b_dense_plan* p = new (std::nothrow) ge2b_dense_plan();
   if (!p) return kCudaError;
   p->M = M; p->K = K; p->N = N; p->dtype = dtype; p->act = act; p->has_bias = has_bias; p->leaky = leaky_slope;
-  p->math = (dtype == GE2_DT_F32) ? (math == GE2_MATH_TENSOR ? 1 : 0) : 1;
+  p->math = (dtype == GE2_DT_F32) ? (math == GE2_MATH_TENSOR ? 1 : (math == GE2_MATH_FP32X3 ? 2 : 0)) : 1;
   p->esz = dtype_bytes(dtype);
   const size_t mk = (size_t)M * K * p->esz, kn = (size_t)K * N * p->esz, mn = (size_t)M * N * p->esz;
   bool good = ok(cudaGetDevice(&p->device));

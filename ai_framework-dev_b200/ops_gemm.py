@@ -4,8 +4,9 @@
 `forward_batched` for the strided-batched form.
 
 Differences from the reference glue, all additive: device arrays are torch tensors (CuPy is what the
-reference uses), tensors may be float32, bfloat16 or float16, and fp32 tensors take `math="fp32"` (exact,
-default) or `math="tf32"` (tensor cores).  Bias and bias gradients are always float32.
+reference uses), tensors may be float32, bfloat16 or float16, and fp32 tensors take `math="fp32"` (default: exact
+forward, error-compensated tensor-core backward), `math="tf32"` (TF32 tensor cores) or `math="fp32x3"`
+(error-compensated tensor cores in the forward too).  Bias and bias gradients are always float32.
 """
 from __future__ import annotations
 
@@ -14,7 +15,7 @@ from typing import Dict, Optional, Tuple, Union
 import torch
 
 from . import _lib
-from ._lib import ACT, BIAS_PER_M, BIAS_PER_N, BIAS_SCALAR, DT_BF16, DT_F16, DT_F32, MATH_FP32, MATH_TENSOR
+from ._lib import ACT, BIAS_PER_M, BIAS_PER_N, BIAS_SCALAR, DT_BF16, DT_F16, DT_F32, MATH_FP32, MATH_FP32X3, MATH_TENSOR
 
 _DT = {torch.float32: DT_F32, torch.float16: DT_F16, torch.bfloat16: DT_BF16}
 
@@ -43,9 +44,9 @@ def _act_code(act: Optional[str]) -> int:
 
 
 def _math_code(math: str) -> int:
-    if math not in ("fp32", "tf32"):
-        raise ValueError("math must be 'fp32' or 'tf32'")
-    return MATH_TENSOR if math == "tf32" else MATH_FP32
+    if math not in ("fp32", "tf32", "fp32x3"):
+        raise ValueError("math must be 'fp32', 'tf32' or 'fp32x3'")
+    return {"fp32": MATH_FP32, "tf32": MATH_TENSOR, "fp32x3": MATH_FP32X3}[math]
 
 
 def _stream_ptr(stream, device=None) -> int:

@@ -400,14 +400,6 @@ def run_ours(args):
 
     # burst: exactly --steps steps.  sustained: the step replayed until the region is at least MIN_WINDOW_S long (the
     # count is agreed between the ranks from the burst window), so that the clock settles and is sampled many times.
-    clk_burst = ClockSampler(local)
-    clk = ClockSampler(local, period_s=0.01)
-    burst_ms = timed_window(args.steps, clk_burst)
-    replays = max(args.steps, int(MIN_WINDOW_S * 1e3 / max(burst_ms / args.steps, 1e-3)) + 1)
-    launches0 = lib.ge2b_launches_total()
-    total_ms = timed_window(replays, clk)
-    launches = (launches_per_step * replays) if graph is not None else lib.ge2b_launches_total() - launches0
-
     def graph_of(fn):
         g_ = torch.cuda.CUDAGraph()
         st = torch.cuda.Stream(device=dev)
@@ -432,11 +424,23 @@ def run_ours(args):
         torch.cuda.synchronize()
         return f0.elapsed_time(f1) / reps
 
-    # per-launch duration of the forward kernel for the roofline: the forward launch alone captured into a graph and
-    # replayed back to back (no host in the loop), CUDA events around the run; a short run (burst clocks) and a run of
-    # at least half a second (the clock the power cap settles at)
+    clk_burst = ClockSampler(local)
+    clk = ClockSampler(local, period_s=0.01)
+    burst_ms = timed_window(args.steps, clk_burst)
+    # per-launch duration of the forward kernel for the roofline, burst form: the forward launch alone captured into a
+    # graph and replayed back to back (no host in the loop), CUDA events around a run of a few milliseconds, taken
+    # while the GPU is still at its burst clock (before the long windows below pull it down to the power cap)
     fwd_graph = graph_of(lambda: og.forward_into(X, W, out=Y, bias=b, with_bias=True, act=ACT, save_z=True, z_out=Z))
-    fwd_ms = replay_ms(fwd_graph, max(10, min(args.steps, 50)))
+    torch.cuda.synchronize()
+    time.sleep(0.5)
+    with ClockSampler(local, period_s=0.002) as clk_fwd_burst:
+        fwd_ms = replay_ms(fwd_graph, max(10, min(args.steps, 50)))
+    replays = max(args.steps, int(MIN_WINDOW_S * 1e3 / max(burst_ms / args.steps, 1e-3)) + 1)
+    launches0 = lib.ge2b_launches_total()
+    total_ms = timed_window(replays, clk)
+    launches = (launches_per_step * replays) if graph is not None else lib.ge2b_launches_total() - launches0
+
+    # the same launch replayed for at least half a second (the clock the power cap settles at)
     with ClockSampler(local, period_s=0.01) as clk_fwd:
         fwd_sustained_ms = replay_ms(fwd_graph, int(500.0 / max(fwd_ms, 1e-3)) + 1)
     for _ in range(min(args.steps, 30)):
@@ -641,8 +645,8 @@ def run_ours(args):
                          "frac": achieved / peak, "traffic": traffic,
                          "traffic_source": f"{TRAFFIC_PROFILE} (ncu capture of `bench.py --profile fwd`, not re-measured by this run)",
                          "kernel": "gemm_tc_kernel (forward launch: 2*M*N*K flop; duration = CUDA events around a run of "
-                                   "back-to-back graph replays of that launch, right after the timed region)",
-                         "launch_ms": fwd_ms, "launch_ms_eager_events": fwd_eager_ms,
+                                   "back-to-back graph replays of that launch, between the burst window and the long window)",
+                         "launch_ms": fwd_ms, "launch_ms_eager_events": fwd_eager_ms, "clocks": clk_fwd_burst.summary(),
                          "peak_source": f"MEASURED_PEAKS.json bf16_tflops (burst: the launch is timed alone, a few ms), {peak_kind}",
                          "frac_of_nominal_2250": achieved / NOMINAL_PEAK_TFLOPS,
                          "sustained": {"achieved": achieved_sus, "launch_ms": fwd_sustained_ms, "peak": peak_sus,

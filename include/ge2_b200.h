@@ -33,7 +33,12 @@ typedef enum {
 /* dtype numbering of the reference's DType (backends/cuda/ops/_common/shim/ai_device.hpp:15) */
 typedef enum { GE2_DT_F32 = 0, GE2_DT_F16 = 1, GE2_DT_BF16 = 2 } ge2_dtype_t;
 /* arithmetic for fp32 tensors: exact fp32 FMA (parity with the reference's fp32 path) or TF32 tensor cores */
-typedef enum { GE2_MATH_FP32 = 0, GE2_MATH_TENSOR = 1 } ge2_math_t;
+/* fp32 tensors only.  FP32: exact fp32 FMA chains in the forward (bit-identical pre-activation to the reference
+ * kernel); the backward GEMMs, which the reference hands to cuBLAS, run error-compensated on the tensor cores.
+ * TENSOR: TF32 tensor cores (inputs truncated to 10 mantissa bits).  FP32X3: error-compensated TF32 everywhere (three
+ * TF32 products of operands split into big + small parts, fp32-grade results; needs stream-ordered scratch, so outside
+ * stream capture). */
+typedef enum { GE2_MATH_FP32 = 0, GE2_MATH_TENSOR = 1, GE2_MATH_FP32X3 = 2 } ge2_math_t;
 
 /* ---- replaces dev/backend/graph_executor_v2/include/ge_v2_api.h:12-18 ---- */
 typedef struct {

@@ -517,3 +517,42 @@ def test_bounded_wait_expires_and_reports(pkg, lib):
     torch.cuda.synchronize()
     assert torch.isfinite(y.float()).all() and lib.ge2b_device_status(0) == 0
     assert lib.ge2b_selftest_wait_expiry(0, rep, None) == -1            # budget out of range
+
+
+# --------------------------------------------------------------------------- fp32 on tensor cores, error-compensated
+@pytest.mark.parametrize("shape", [(256, 512, 512), (384, 320, 512), (1024, 1024, 1024), (130, 72, 264), (2304, 2304, 2304)])
+def test_fp32x3_forward_matches_the_fp32_path(pkg, lib, oracle, shape):
+    """math = "fp32x3": operands split into TF32-exact big parts and fp32 remainders, three tensor-core products in one
+    fp32 accumulator.  Contract of the fp32 path: <= 1e-5 relative (floor 1e-5 absolute, as the reference tests'
+    allclose) against the exact fp32 chain; measured against float64 it is as good as that chain itself."""
+    M, K, N = shape
+    X, W, b, _ = oracle.dense_inputs(M, K, N, seed=4)
+    tX, tW, tb = dev(X), dev(W), dev(b)
+    Y, Z = pkg.ops_gemm.forward(tX, tW, tb, act="gelu", return_z=True, math="fp32x3")
+    assert lib.ge2b_last_route() == 2
+    Ye, Ze = pkg.ops_gemm.forward(tX, tW, tb, act="gelu", return_z=True, math="fp32")       # exact chain (CUDA cores)
+    assert lib.ge2b_last_route() == 1
+    torch.cuda.synchronize()
+    for got, want in ((Z, Ze), (Y, Ye)):
+        rel = ((got - want).abs() / want.abs().clamp_min(1.0)).max().item()
+        assert rel <= 1e-5, rel
+    Y64, Z64 = oracle.forward_f64(X, W, b, act="gelu")
+    e3, e1 = oracle.rel_fro(host(Z), Z64), oracle.rel_fro(host(Ze), Z64)
+    assert e3 <= 2e-6 and e3 <= 4 * e1 + 2e-7, (e3, e1)
+
+
+@pytest.mark.parametrize("math", ["fp32", "fp32x3"])
+def test_fp32_backward_runs_compensated_on_tensor_cores(pkg, lib, oracle, math):
+    """fp32 backward GEMMs (the reference hands them to cuBLAS SGEMM) run error-compensated on the tensor cores by
+    default; against float64 the result is fp32-grade."""
+    M, K, N = 512, 384, 640
+    X, W, b, dY = oracle.dense_inputs(M, K, N, seed=6)
+    tX, tW, tdY = dev(X), dev(W), dev(dY)
+    Y, Z = pkg.ops_gemm.forward(tX, tW, dev(b), act="tanh", return_z=True)
+    g = pkg.ops_gemm.backward(tX, tW, tdY, Z, act="tanh", want_gBias=True, math=math)
+    torch.cuda.synchronize()
+    assert lib.ge2b_last_route() == 2
+    g64 = oracle.backward_f64(X, W, dY, host(Z), act="tanh")
+    assert oracle.rel_fro(host(g["gA"]), g64["gA"]) <= 2e-6
+    assert oracle.rel_fro(host(g["gB"]), g64["gB"]) <= 2e-6
+    assert oracle.rel_fro(host(g["gBias"]).ravel(), g64["gBias"]) <= 2e-6
