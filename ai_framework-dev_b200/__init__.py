@@ -9,11 +9,12 @@ There is no CPU fallback: importing works anywhere, computing needs the built li
 from . import _lib  # noqa: F401
 from . import ops_gemm  # noqa: F401
 from . import ops_conv2d  # noqa: F401
+from . import ops_sdpa  # noqa: F401
 from .dense import Dense  # noqa: F401
 from . import train  # noqa: F401
 from . import data_parallel  # noqa: F401
 from .train import DenseStackTrainer, MlpPlan, softmax_ce_fused, sgd_update  # noqa: F401
 from ._lib import load_library, library_path  # noqa: F401
 
-__all__ = ["ops_gemm", "ops_conv2d", "Dense", "train", "data_parallel", "DenseStackTrainer", "MlpPlan", "softmax_ce_fused", "sgd_update", "load_library",
+__all__ = ["ops_gemm", "ops_conv2d", "ops_sdpa", "Dense", "train", "data_parallel", "DenseStackTrainer", "MlpPlan", "softmax_ce_fused", "sgd_update", "load_library",
            "library_path"]

@@ -76,6 +76,11 @@ class MlpConfig(C.Structure):
                 ("nccl_unique_id", C.c_void_p), ("comm_blocks", C.c_int)]
 
 
+class ParamsSdpa(C.Structure):
+    _fields_ = [("B", C.c_int), ("H", C.c_int), ("M", C.c_int), ("N", C.c_int), ("D", C.c_int), ("dtype", C.c_int),
+                ("scale", C.c_float), ("causal", C.c_int), ("mask_kind", C.c_int), ("dropout_p", C.c_float)]
+
+
 class ParamsBwdTyped(C.Structure):
     _fields_ = [("base", ParamsBwd),
                 ("dtype", C.c_int), ("z_dtype", C.c_int), ("math", C.c_int),
@@ -106,7 +111,7 @@ EXPORTS = [
     "ge2b_backward_scratch_bytes", "ge2b_device_status", "ge2b_sm_count", "ge2b_set_sm_limit", "ge2b_version",
     "ge2b_last_route", "ge2b_launches_total", "ge2b_register_gemm_kernels",
     "ge2b_split_unavailable_total", "ge2b_release_scratch", "ge2b_selftest_wait_expiry",
-    "ge2b_allreduce_nvls", "ge2b_allreduce_nvls_pad_bytes",
+    "ge2b_allreduce_nvls", "ge2b_allreduce_nvls_pad_bytes", "ge2b_sdpa_forward",
     "ge2b_mlp_plan_grad_bytes", "ge2b_nccl_unique_id", "ge2b_mlp_plan_create", "ge2b_mlp_plan_destroy",
     "ge2b_mlp_plan_set_params", "ge2b_mlp_plan_get_params", "ge2b_mlp_plan_get_grads", "ge2b_mlp_plan_compile",
     "ge2b_mlp_plan_launch", "ge2b_mlp_plan_step", "ge2b_mlp_plan_sync", "ge2b_mlp_plan_buffer",
@@ -157,6 +162,8 @@ def load_library() -> C.CDLL:
     lib.ge2b_allreduce_nvls.argtypes = [C.POINTER(AllreduceNvls), C.c_void_p]
     lib.ge2b_allreduce_nvls.restype = C.c_int
     lib.ge2b_allreduce_nvls_pad_bytes.restype = C.c_int
+    lib.ge2b_sdpa_forward.argtypes = [C.POINTER(ParamsSdpa)] + [C.c_void_p] * 7
+    lib.ge2b_sdpa_forward.restype = C.c_int
     vp = C.c_void_p
     lib.ge2b_mlp_plan_grad_bytes.argtypes = [C.POINTER(MlpConfig)]
     lib.ge2b_mlp_plan_grad_bytes.restype = C.c_size_t

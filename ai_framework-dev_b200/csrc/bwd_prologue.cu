@@ -5,7 +5,9 @@
 // Replaces the reference's bwd_epilogue_kernel (backends/cuda/ops/gemm/kernels/regemm_backward.cu:92-130),
 // which issues one atomicAdd per element for the bias gradient.  Here each thread owns 8 consecutive
 // columns (one or two 16-byte accesses), a CTA covers 256 columns x 64 rows, sums in registers and shared
-// memory, and issues one fp32 atomic per column (or row) per CTA.  The bias gradient is always formed
+// memory; the per-column bias gradient is then added over the row blocks in a fixed order by the last CTA of each
+// column block (run-to-run identical bits; one fp32 atomic per column per CTA only when no scratch is to be had, and
+// for per-row / scalar bias gradients).  The bias gradient is always formed
 // from the fp32 value of gZ, before gZ is rounded to its storage type.  The buffer gZ is scratch memory
 // that the two backward GEMMs read afterwards.
 #include <cuda_bf16.h>
@@ -80,6 +82,60 @@ __device__ __forceinline__ void store8(void* base, long long off, int dt, bool v
   }
 }
 
+// Per-column bias gradient of one CTA: `s` is this thread's column (c = ty * 32 + tx) summed over the CTA's rows.
+// With a partial buffer the sum over row blocks has a fixed order (run-to-run identical bits): the CTA stores its 256
+// column sums, counts itself into its column block's counter, and the last CTA of the column block adds all row
+// blocks -- thread (ty, tx) takes row blocks ty, ty + 8, ... of columns 8 tx .. 8 tx + 7 (two 16-byte loads per row
+// block, four row blocks in flight), then the eight ty partials are added in order.  Without one: one atomic per column.
+__device__ __forceinline__ void finish_db_per_column(const BwdPrologueArgs& a, float s, float (&red)[kTY][kTileCols + 1]) {
+  const int c = threadIdx.y * kTX + threadIdx.x;
+  const int gc = blockIdx.x * kTileCols + c;
+  if (a.db_partial == nullptr) {
+    if (gc < a.N) atomicAdd(a.gBias + gc, s);
+    return;
+  }
+  __shared__ int is_last;
+  a.db_partial[static_cast<long long>(blockIdx.y) * a.db_pitch + gc] = s;      // the pitch covers the padded columns
+  __threadfence();
+  __syncthreads();
+  if (c == 0) is_last = (atomicAdd(a.db_flags + blockIdx.x, 1) == static_cast<int>(gridDim.y) - 1) ? 1 : 0;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  float acc[kColsPerThread];
+#pragma unroll
+  for (int j = 0; j < kColsPerThread; ++j) acc[j] = 0.f;
+  const float* base = a.db_partial + blockIdx.x * kTileCols + threadIdx.x * kColsPerThread;
+  const int nrb = static_cast<int>(gridDim.y);
+  for (int rb0 = threadIdx.y; rb0 < nrb; rb0 += 4 * kTY) {
+    float4 v[4][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int rb = rb0 + i * kTY;
+      if (rb < nrb) {
+        const float4* p = reinterpret_cast<const float4*>(base + static_cast<long long>(rb) * a.db_pitch);
+        v[i][0] = __ldcg(p); v[i][1] = __ldcg(p + 1);
+      } else {
+        v[i][0] = make_float4(0.f, 0.f, 0.f, 0.f); v[i][1] = v[i][0];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      acc[0] += v[i][0].x; acc[1] += v[i][0].y; acc[2] += v[i][0].z; acc[3] += v[i][0].w;
+      acc[4] += v[i][1].x; acc[5] += v[i][1].y; acc[6] += v[i][1].z; acc[7] += v[i][1].w;
+    }
+  }
+  __syncthreads();                                   // everyone has read `red` for its own column sum
+#pragma unroll
+  for (int j = 0; j < kColsPerThread; ++j) red[threadIdx.y][threadIdx.x * kColsPerThread + j] = acc[j];
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int y = 0; y < kTY; ++y) total += red[y][c];
+  if (gc < a.N) a.gBias[gc] = total;
+  if (c == 0) a.db_flags[blockIdx.x] = 0;            // leave the counter as it was found
+}
+
 // kRowSum: the bias gradient needs sums along rows (per-row or scalar bias); the common per-column case does not.
 template <int ACT, bool kFast, bool kRowSum>
 __global__ void __launch_bounds__(kTX * kTY)
@@ -148,8 +204,7 @@ bwd_prologue_kernel(const ProParams pp) {
     float s = 0.f;
 #pragma unroll
     for (int y = 0; y < kTY; ++y) s += red[y][c];
-    const int gc = blockIdx.x * kTileCols + c;
-    if (gc < a.N) atomicAdd(a.gBias + gc, s);
+    finish_db_per_column(a, s, red);
   } else {  // scalar: everything
     // `total` here is the per-lane partial (rowsum before the per-row shuffle is only taken for PerM)
 #pragma unroll
@@ -241,8 +296,7 @@ bwd_prologue_fast_kernel(const ProParams pp) {
   float s = 0.f;
 #pragma unroll
   for (int y = 0; y < kTY; ++y) s += red[y][c];
-  const int gc = blockIdx.x * kTileCols + c;
-  if (gc < a.N) atomicAdd(a.gBias + gc, s);
+  finish_db_per_column(a, s, red);
 }
 
 bool vec_ok(const void* p, long long ld, int dt) {
@@ -261,6 +315,19 @@ cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s) {
   pp.gz_vec = vec_ok(a.gZ, a.ldgZ, a.gz_dtype);
   pp.gc_vec = vec_ok(a.gC, a.ldgC, a.gc_dtype);
   dim3 block(kTX, kTY), grid((a.N + kTileCols - 1) / kTileCols, (a.M + kTileRows - 1) / kTileRows);
+  // Deterministic per-column bias gradient: partial sums per row block in stream scratch, when there is some.
+  auto want_partials = [&](unsigned row_blocks) {
+    pp.a.db_partial = nullptr; pp.a.db_flags = nullptr; pp.a.db_pitch = 0;
+    if (a.gBias == nullptr || a.bias_kind != kBiasPerN || row_blocks < 2) return cudaSuccess;
+    float* ws = nullptr; int* flags = nullptr; size_t ws_bytes = 0, flag_bytes = 0; bool lent = false;
+    if (!borrow_stream_scratch(s, &ws, &ws_bytes, &flags, &flag_bytes, &lent)) return cudaSuccess;   // atomics instead
+    const long long pitch = static_cast<long long>(grid.x) * kTileCols;
+    if (static_cast<size_t>(row_blocks) * pitch * sizeof(float) > ws_bytes || grid.x * sizeof(int) > flag_bytes)
+      return cudaSuccess;
+    if (lent && cudaMemsetAsync(flags, 0, grid.x * sizeof(int), s) != cudaSuccess) return cudaErrorUnknown;
+    pp.a.db_partial = ws; pp.a.db_pitch = pitch; pp.a.db_flags = flags;
+    return cudaSuccess;
+  };
   // gZ stored in 16 bits: the exp-based derivative forms are accurate enough (see epilogue_math.cuh)
   // the common 16-bit call takes the specialised kernel
   const bool same16 = a.gy_dtype != kF32 && a.gy_dtype == a.z_dtype && a.gy_dtype == a.gz_dtype;
@@ -269,6 +336,7 @@ cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s) {
     if (a.gBias != nullptr && a.bias_kind == kBiasNone) pp.a.gBias = nullptr;
     const bool bf = a.gy_dtype == kBF16;
     const dim3 fgrid((a.N + kTileCols - 1) / kTileCols, (a.M + kFastRows - 1) / kFastRows);
+    if (want_partials(fgrid.y) != cudaSuccess) return cudaErrorUnknown;
 #define GE2B_LAUNCH_FAST(ACT_)                                                                \
     do {                                                                                      \
       if (bf) bwd_prologue_fast_kernel<ACT_, true><<<fgrid, block, 0, s>>>(pp);               \
@@ -285,6 +353,7 @@ cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s) {
 #undef GE2B_LAUNCH_FAST
     return cudaGetLastError();
   }
+  if (want_partials(grid.y) != cudaSuccess) return cudaErrorUnknown;
   const bool fast = a.gz_dtype != kF32;
   const bool rowsum = a.gBias != nullptr && (a.bias_kind == kBiasPerM || a.bias_kind == kBiasScalar);
 #define GE2B_LAUNCH_PRO(ACT_)                                                                   \

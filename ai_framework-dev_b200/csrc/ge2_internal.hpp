@@ -92,6 +92,10 @@ struct BwdPrologueArgs {
   void* gC; long long ldgC; int gc_dtype; float beta;   // optional gC = beta * gZ
   float* gBias; int bias_kind;                    // fp32, zeroed by the launcher before the kernel
   int act; float leaky;
+  // Per-column bias gradient without atomics (filled in by launch_bwd_prologue when stream scratch is to be had):
+  // every CTA leaves the column sums of its rows in db_partial[row block][column], counts itself into
+  // db_flags[column block], and the CTA that arrives last adds the row blocks in a fixed order.  Null: fp32 atomics.
+  float* db_partial = nullptr; long long db_pitch = 0; int* db_flags = nullptr;
 };
 
 // ---- launchers (each returns cudaSuccess or the launch error) ----
@@ -131,6 +135,9 @@ struct ScopedLease {
   ScopedLease(const ScopedLease&) = delete;
   ScopedLease& operator=(const ScopedLease&) = delete;
 };
+// The calling thread's scratch for launches on stream `s` (lent memory first, else the library's per-stream buffer;
+// see split_scratch in gemm_tc.cu).  `flags` are zero and every user leaves them zero, unless `*lent`.
+bool borrow_stream_scratch(cudaStream_t s, float** ws, size_t* ws_bytes, int** flags, size_t* flag_bytes, bool* lent);
 long long split_unavailable_total();   // split-K launches that ran unsplit because no scratch could be had (capture, no_alloc)
 void release_library_scratch();        // synchronises the device and frees every split-K scratch the library created
 std::atomic<unsigned long long>& plan_cache_generation();   // bumping it invalidates every thread's cached launches

@@ -144,6 +144,13 @@ bool driver_has_tensor_maps() { return encode_tiled_fn_impl() != nullptr; }
 
 }  // namespace tc
 
+bool borrow_stream_scratch(cudaStream_t s, float** ws, size_t* ws_bytes, int** flags, size_t* flag_bytes, bool* lent) {
+  tc::SplitScratch sc;
+  if (!tc::split_scratch(s, &sc)) return false;
+  *ws = sc.ws; *ws_bytes = sc.ws_bytes; *flags = sc.flags; *flag_bytes = tc::kSplitFlagBytes; *lent = sc.lent;
+  return true;
+}
+
 long long split_unavailable_total() { return tc::g_split_unavailable.load(std::memory_order_relaxed); }
 
 void release_library_scratch() {

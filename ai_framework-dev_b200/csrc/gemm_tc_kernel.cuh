@@ -48,7 +48,7 @@ struct TcParams {
   int kb_per_slice;         // > 0: the reduction runs over every batch slice in turn (k_blocks = slices * this);
                             // one output matrix, `batch` is 1 for the tile schedule
   int x3_kb;                // > 0: error-compensated fp32 (k_blocks = 3 * this): the reduction is walked three times,
-                            // over (A big, B big), (A big, B small), (A small, B big); the small parts' tensor maps
+                            // over (A big, B small), (A small, B big), (A big, B big); the small parts' tensor maps
                             // travel in the kernel's second-problem slot
   uint32_t idesc;
   EpilogueArgs epi;
@@ -497,10 +497,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           if constexpr (!kDual) {
             if (pp.x3_kb > 0) {                        // three passes over the reduction with the split operands
+              // Order: the two small cross products first, big.big last.  The tensor core adds into its fp32
+              // accumulator with truncation, an error of up to one unit in the last place of the ACCUMULATOR per
+              // MMA; while only cross terms have been added the accumulator is 2^-11 of its final size and those
+              // errors vanish, so only the K/8 additions of the last pass count (measured: big.big first gave
+              // 1.5e-5 relative at K = 512, three times what this order gives).
               const int pass = kb / pp.x3_kb;
               k0 = (kb - pass * pp.x3_kb) * Cfg::kBlockK;
-              mA = pass == 2 ? &d2.tmA : &tmA;
-              mB = pass == 1 ? &d2.tmB : &tmB;
+              mA = pass == 1 ? &d2.tmA : &tmA;
+              mB = pass == 0 ? &d2.tmB : &tmB;
             }
           }
           auto load = [&](uint32_t dst, const void* tm, int c0, int c1, int c2) {
@@ -837,6 +842,7 @@ bool make_operand_map(CUtensorMap* map, int dtype, const void* base, long long i
                       long long batch, long long batch_stride, int box_inner, int box_rows, bool swizzle_32b_units);
 bool make_output_map(CUtensorMap* map, int dtype, const void* base, long long cols, long long rows, long long ld,
                      long long batch, long long batch_stride, bool wide);
+bool driver_has_tensor_maps();
 struct SplitScratch { float* ws = nullptr; int* flags = nullptr; size_t ws_bytes = 0; bool lent = false; };
 constexpr size_t kSplitWsBytes = 64u << 20;
 constexpr int kSplitMaxTail = 256;

@@ -1,0 +1,410 @@
+// Fused scaled-dot-product attention forward for sm_100a:  O = softmax(scale * Q.K^T + mask) . V  per (batch, head),
+// with the scores never leaving the SM.
+//
+// The reference computes this per (b, h) slice as transpose(K) -> GEMM -> scale kernel -> mask kernel -> softmax ->
+// GEMM, with S and P materialised as fp32 [B,H,M,N] tensors (backends/cuda/ops/sdpa/launcher.cu:129-270; scale default
+// 1/sqrt(D): :162; causal: n > m masked, :38-48; additive fp32 mask or 0/1 integer mask [B,1,M,N]: :56-95).  Here one CTA
+// owns 128 query rows of one slice and walks the keys in blocks of 128:
+//   warp 0       TMA producer: Q once, then K_j and V_j into two-deep rings (128-byte-swizzled tiles)
+//   warp 1       MMA issuer:   S_j = Q.K_j^T into TMEM (kind::f16, 128 x 128 x 16), then O += P_j.V_j into TMEM
+//   warps 2..5   softmax:      one query row per thread: tcgen05.ld of the row of S_j, scale / mask, running max and
+//                sum, P_j = exp2(...) written as bf16 into shared memory in the swizzled operand layout, O rescaled in
+//                TMEM by exp2(m_old - m_new) (tcgen05.ld / tcgen05.st), and at the end O / sum -> global memory
+// S_{j+1} = Q.K_{j+1}^T is issued as soon as the softmax warps have pulled S_j into registers, so the tensor pipe
+// works on the next scores while the exponentials of the current block are computed.  Every mbarrier wait is bounded
+// (sm100_ptx.cuh); on expiry the CTA records kErrWaitTimeout in the device status word, frees its TMEM and returns.
+// No TMA load uses cluster multicast.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+
+#include <mutex>
+
+#include "../../include/ge2_b200.h"
+#include "dense_ops.hpp"
+#include "gemm_tc_kernel.cuh"
+#include "sm100_ptx.cuh"
+
+using namespace ge2b;
+
+namespace {
+
+constexpr int kBlockQ = 128;       // query rows per CTA (one TMEM lane each)
+constexpr int kBlockKV = 128;      // keys per step
+constexpr int kSdpaThreads = 192;  // warp 0 TMA, warp 1 MMA, warps 2..5 softmax
+constexpr int kSoftmaxWarps = 4;
+
+struct SdpaParams {
+  int B, H, M, N;                  // batch, heads, queries, keys
+  int causal;
+  float scale_log2;                // scale * log2(e): p = exp2(s * scale_log2 - m)
+  const void* mask; int mask_kind; // 0 none, 1 fp32 additive, 2 int8 (non-zero = masked), 3 int32; [B,1,M,N]
+  void* O; int o_dtype;            // [B,H,M,D]
+  float* lse;                      // optional [B,H,M]: log-sum-exp of the scaled, masked scores (natural log)
+  int* status;
+};
+
+template <int kD>
+struct SdpaCfg {
+  static constexpr int kKB = kD / 64;                    // 64-element (128-byte) blocks along the head dimension
+  static constexpr int kQBytes = kBlockQ * kD * 2;       // kKB tiles of [128 rows x 128 B]
+  static constexpr int kKBytes = kBlockKV * kD * 2;      // kKB tiles of [128 keys x 128 B]   (d contiguous)
+  static constexpr int kVBytes = kBlockKV * kD * 2;      // 2 key halves x kKB boxes of [64 keys x 128 B] (d contiguous)
+  static constexpr int kPBytes = kBlockQ * kBlockKV * 2; // 2 tiles of [128 rows x 128 B]     (keys contiguous)
+  static constexpr int kSmem = kQBytes + 2 * kKBytes + 2 * kVBytes + kPBytes + 256 + 1024;
+  static constexpr int kTmemCols = 256;                  // S: columns [0, 128), O: columns [128, 128 + kD)
+};
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+template <int kD>
+__global__ void __launch_bounds__(kSdpaThreads, 1)
+sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const __grid_constant__ SdpaParams p) {
+  using Cfg = SdpaCfg<kD>;
+  constexpr int kKB = Cfg::kKB;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  const uint32_t base = raw_addr + pad;
+  const uint32_t q_smem = base;
+  const uint32_t k_smem = q_smem + Cfg::kQBytes;                  // 2 stages
+  const uint32_t v_smem = k_smem + 2 * Cfg::kKBytes;              // 2 stages
+  const uint32_t p_smem = v_smem + 2 * Cfg::kVBytes;
+  uint8_t* p_ptr = smem + Cfg::kQBytes + 2 * Cfg::kKBytes + 2 * Cfg::kVBytes;
+  const uint32_t bar0 = p_smem + Cfg::kPBytes;
+  uint8_t* bar_ptr = p_ptr + Cfg::kPBytes;
+  // barriers (8 bytes each)
+  const uint32_t q_full = bar0;
+  auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
+  auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
+  auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
+  const uint32_t s_full = bar0 + 8u * 9, s_empty = bar0 + 8u * 10, p_full = bar0 + 8u * 11, o_done = bar0 + 8u * 12;
+  volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * 13 + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q_blocks = (p.M + kBlockQ - 1) / kBlockQ;
+  const int slice = blockIdx.x / q_blocks;                        // b * H + h
+  const int qb = blockIdx.x - slice * q_blocks;
+  const int q0 = qb * kBlockQ;
+  int n_kv = (p.N + kBlockKV - 1) / kBlockKV;
+  if (p.causal) n_kv = min(n_kv, (min(q0 + kBlockQ, p.M) + kBlockKV - 1) / kBlockKV);   // keys beyond the last row's index
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(k_full(s), 1); ptx::mbar_init(k_empty(s), 1);
+      ptx::mbar_init(v_full(s), 1); ptx::mbar_init(v_empty(s), 1);
+    }
+    ptx::mbar_init(s_full, 1); ptx::mbar_init(s_empty, kSoftmaxWarps);
+    ptx::mbar_init(p_full, kSoftmaxWarps); ptx::mbar_init(o_done, 1);
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+    ptx::prefetch_tensormap(&tmQ); ptx::prefetch_tensormap(&tmK); ptx::prefetch_tensormap(&tmV);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_holder)), Cfg::kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t s_tmem = tmem_base, o_tmem = tmem_base + 128;
+
+  if (warp == 0) {
+    // ===================== TMA producer =====================
+    if (lane == 0) {
+      ptx::mbar_arrive_expect_tx(q_full, Cfg::kQBytes);
+#pragma unroll
+      for (int kb = 0; kb < kKB; ++kb) ptx::tma_load_3d(q_smem + kb * (kBlockQ * 128), &tmQ, q_full, kb * 64, q0, slice);
+      bool ok = true;
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = ((j >> 1) & 1) ^ 1u;
+        if (!ptx::mbar_wait(k_empty(s), ph, abort_flag)) { ok = false; break; }
+        ptx::mbar_arrive_expect_tx(k_full(s), Cfg::kKBytes);
+#pragma unroll
+        for (int kb = 0; kb < kKB; ++kb)
+          ptx::tma_load_3d(k_smem + s * Cfg::kKBytes + kb * (kBlockKV * 128), &tmK, k_full(s), kb * 64, j * kBlockKV, slice);
+        if (!ptx::mbar_wait(v_empty(s), ph, abort_flag)) { ok = false; break; }
+        ptx::mbar_arrive_expect_tx(v_full(s), Cfg::kVBytes);
+        // V block: two halves of 64 keys (the reduction blocks of P.V), each kKB boxes of {64 d, 64 keys}
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int kb = 0; kb < kKB; ++kb)
+            ptx::tma_load_3d(v_smem + s * Cfg::kVBytes + h * (64 * kD * 2) + kb * (64 * 128), &tmV, v_full(s), kb * 64,
+                             j * kBlockKV + h * 64, slice);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ===================== MMA issuer =====================
+    if (lane == 0) {
+      const uint32_t idesc_s = ptx::make_idesc(1, false, false, kBlockQ, kBlockKV);   // bf16, Q and K reduction-contiguous
+      const uint32_t idesc_o = ptx::make_idesc(1, false, true, kBlockQ, kD);          // P reduction-contiguous, V d-contiguous
+      bool ok = ptx::mbar_wait(q_full, 0u, abort_flag);
+      auto issue_s = [&](int j) {
+        const int s = j & 1;
+        if (!ptx::mbar_wait(k_full(s), (j >> 1) & 1, abort_flag)) { ok = false; return; }
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int kb = 0; kb < kKB; ++kb) {
+          const uint64_t a0 = ptx::make_smem_desc_sw128(q_smem + kb * (kBlockQ * 128), 0u, 1024u);
+          const uint64_t b0 = ptx::make_smem_desc_sw128(k_smem + s * Cfg::kKBytes + kb * (kBlockKV * 128), 0u, 1024u);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            ptx::umma<false>(s_tmem, a0 + ks * 2, b0 + ks * 2, idesc_s, (kb | ks) ? 1u : 0u);
+        }
+        ptx::umma_commit(k_empty(s));       // the K slot is free once these MMAs have read it
+        ptx::umma_commit(s_full);           // and the scores are complete
+      };
+      if (ok && n_kv > 0) issue_s(0);
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int s = j & 1;
+        if (j + 1 < n_kv) {
+          // the softmax warps hold S_j in registers: the next scores may overwrite it
+          if (!ptx::mbar_wait(s_empty, j & 1, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          issue_s(j + 1);
+          if (!ok) break;
+        }
+        if (!ptx::mbar_wait(p_full, j & 1, abort_flag)) { ok = false; break; }     // P_j in shared memory, O rescaled
+        if (!ptx::mbar_wait(v_full(s), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint64_t a0 = ptx::make_smem_desc_sw128(p_smem + h * (kBlockQ * 128), 0u, 1024u);
+          const uint64_t b0 = ptx::make_smem_desc_sw128(v_smem + s * Cfg::kVBytes + h * (64 * kD * 2), 64u * 128u, 1024u);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            ptx::umma<false>(o_tmem, a0 + ks * 2, b0 + ks * ((16 * 128) >> 4), idesc_o, (j > 0 || (h | ks)) ? 1u : 0u);
+        }
+        ptx::umma_commit(v_empty(s));
+        ptx::umma_commit(o_done);           // O holds blocks 0..j; P's buffer may be rewritten
+      }
+    }
+    __syncwarp();
+  } else {
+    // ===================== softmax: one query row per thread =====================
+    const int q = warp & 3;                                   // TMEM lane quarter this warp may access
+    const int r_in = q * 32 + lane;
+    const int row = q0 + r_in;
+    const bool row_ok = row < p.M;
+    const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
+    float m_run = -CUDART_INF_F, l_run = 0.f;
+    const long long mask_row = p.mask ? (static_cast<long long>(slice / p.H) * p.M + row) * p.N : 0;
+    bool ok = true;
+    for (int j = 0; ok && j < n_kv; ++j) {
+      // the TMEM accesses below are warp-collective: the warp stays or leaves together
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(s_full, j & 1, abort_flag))) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      float sc[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(s_tmem + lane_sel + c * 32, r);
+        ptx::tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sc[c * 32 + i] = __uint_as_float(r[i]);
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(s_empty);               // S_j is in registers
+      // scale (in log2 units), mask, row maximum
+      const int key0 = j * kBlockKV;
+      float m_blk = -CUDART_INF_F;
+#pragma unroll
+      for (int i = 0; i < 128; ++i) {
+        const int key = key0 + i;
+        float v = sc[i] * p.scale_log2;
+        bool dead = key >= p.N || (p.causal && key > row);
+        if (p.mask_kind == 1) {
+          if (!dead && row_ok) v += static_cast<const float*>(p.mask)[mask_row + key] * 1.4426950408889634f;
+        } else if (p.mask_kind == 2) {
+          if (!dead && row_ok && static_cast<const signed char*>(p.mask)[mask_row + key] != 0) dead = true;
+        } else if (p.mask_kind == 3) {
+          if (!dead && row_ok && static_cast<const int*>(p.mask)[mask_row + key] != 0) dead = true;
+        }
+        v = dead ? -CUDART_INF_F : v;
+        sc[i] = v;
+        m_blk = fmaxf(m_blk, v);
+      }
+      const float m_new = fmaxf(m_run, m_blk);
+      const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;       // a fully masked row so far: keep everything 0
+      const float alpha = ex2(m_run - m_use);                           // exp2(-inf) = 0 on the first block
+      float l_blk = 0.f;
+      // P_j: probabilities (unnormalised) as bf16 pairs; the sum uses the ROUNDED values, which is what the P.V
+      // product will see, so that O / l is a true weighted mean
+      uint32_t pk[64];
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        const float e0 = ex2(sc[2 * i] - m_use), e1 = ex2(sc[2 * i + 1] - m_use);
+        const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+        pk[i] = *reinterpret_cast<const uint32_t*>(&h);
+        const float2 f = __bfloat1622float2(h);
+        l_blk += f.x + f.y;
+      }
+      l_run = l_run * alpha + l_blk;
+      m_run = m_new;
+      // the previous P.V must have finished: it read P's buffer and wrote O
+      if (j > 0) {
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(o_done, (j - 1) & 1, abort_flag))) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {                    // rescale the rows of O by exp2(m_old - m_new)
+#pragma unroll
+          for (int c = 0; c < kD / 32; ++c) {
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(o_tmem + lane_sel + c * 32, r);
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32(o_tmem + lane_sel + c * 32, r);
+          }
+          tmem_wait_st();
+        }
+      }
+      // P row into the operand layout: 2 tiles (64 keys each) of [128 rows x 128 B], 16-byte chunk index XOR (row & 7)
+      {
+        const int swz = r_in & 7;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint8_t* my_row = p_ptr + h * (kBlockQ * 128) + r_in * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(my_row + ((c ^ swz) * 16)) =
+                make_uint4(pk[h * 32 + 4 * c], pk[h * 32 + 4 * c + 1], pk[h * 32 + 4 * c + 2], pk[h * 32 + 4 * c + 3]);
+        }
+      }
+      ptx::fence_proxy_async_smem();                                    // the MMA reads P through the async proxy
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(p_full);
+    }
+    // ---- O / l -> global memory ----
+    if (ok && n_kv > 0) ok = __all_sync(0xffffffffu, ptx::mbar_wait(o_done, (n_kv - 1) & 1, abort_flag));
+    if (ok) {
+      ptx::tc_fence_after_sync();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const long long o_off = (static_cast<long long>(slice) * p.M + row) * kD;
+#pragma unroll
+      for (int c = 0; c < kD / 32; ++c) {
+        uint32_t r[32];
+        if (n_kv > 0) { ptx::tmem_ld_32x32(o_tmem + lane_sel + c * 32, r); ptx::tmem_wait_ld(); }
+        else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (row_ok) {
+          if (p.o_dtype == kF32) {
+            float* dst = static_cast<float*>(p.O) + o_off + c * 32;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              reinterpret_cast<float4*>(dst)[i] = make_float4(__uint_as_float(r[4 * i]) * inv, __uint_as_float(r[4 * i + 1]) * inv,
+                                                               __uint_as_float(r[4 * i + 2]) * inv, __uint_as_float(r[4 * i + 3]) * inv);
+          } else {
+            uint32_t w[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float a = __uint_as_float(r[2 * i]) * inv, b = __uint_as_float(r[2 * i + 1]) * inv;
+              if (p.o_dtype == kBF16) { const __nv_bfloat162 h = __floats2bfloat162_rn(a, b); w[i] = *reinterpret_cast<const uint32_t*>(&h); }
+              else                    { const __half2 h = __floats2half2_rn(a, b);           w[i] = *reinterpret_cast<const uint32_t*>(&h); }
+            }
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<unsigned short*>(p.O) + o_off + c * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+          }
+        }
+      }
+      if (p.lse != nullptr && row_ok)
+        p.lse[static_cast<long long>(slice) * p.M + row] =
+            l_run > 0.f ? (m_run + log2f(l_run)) * 0.6931471805599453f : -CUDART_INF_F;
+    }
+    ptx::tc_fence_before_sync();
+  }
+
+  __syncthreads();
+  if (*abort_flag != 0) {
+    if (threadIdx.x == 0) atomicOr(p.status, kErrWaitTimeout);
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) { __nanosleep(1000); }      // copies in flight land before the memory goes away
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+template <int kD>
+int launch_sdpa(const ge2b_sdpa_params_t& a, const void* Q, const void* K, const void* V, const void* mask, void* O,
+                float* lse, cudaStream_t s) {
+  using Cfg = SdpaCfg<kD>;
+  auto kernel = sdpa_fwd_kernel<kD>;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [&] { attr_err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmem); });
+  if (attr_err != cudaSuccess) return kCudaError;
+  const long long slices = static_cast<long long>(a.B) * a.H;
+  CUtensorMap tmQ, tmK, tmV;
+  // 3-D maps {d, rows of the slice, slice}: a box never crosses into the next slice, rows beyond M / N read as zero
+  if (!tc::make_operand_map(&tmQ, a.dtype, Q, kD, a.M, kD, slices, static_cast<long long>(a.M) * kD, 64, kBlockQ, false) ||
+      !tc::make_operand_map(&tmK, a.dtype, K, kD, a.N, kD, slices, static_cast<long long>(a.N) * kD, 64, kBlockKV, false) ||
+      !tc::make_operand_map(&tmV, a.dtype, V, kD, a.N, kD, slices, static_cast<long long>(a.N) * kD, 64, 64, false))
+    return kCudaError;
+  SdpaParams p{};
+  p.B = a.B; p.H = a.H; p.M = a.M; p.N = a.N;
+  p.causal = a.causal ? 1 : 0;
+  const float scale = a.scale != 0.f ? a.scale : 1.f / sqrtf(static_cast<float>(kD));
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.mask = mask; p.mask_kind = mask ? a.mask_kind : 0;
+  p.O = O; p.o_dtype = a.dtype; p.lse = lse;
+  p.status = device_status_ptr();
+  if (!p.status) return kCudaError;
+  const int q_blocks = (a.M + kBlockQ - 1) / kBlockQ;
+  const long long grid = slices * q_blocks;
+  if (grid > 0x7fffffffll) return kBadArgs;
+  kernel<<<static_cast<unsigned>(grid), kSdpaThreads, Cfg::kSmem, s>>>(tmQ, tmK, tmV, p);
+  return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
+}
+
+}  // namespace
+
+extern "C" int ge2b_sdpa_forward(const ge2b_sdpa_params_t* a, const void* Q, const void* K, const void* V, const void* mask,
+                                 void* O, float* lse, void* stream) {
+  if (!a || !Q || !K || !V || !O || a->B < 1 || a->H < 1 || a->M < 1 || a->N < 1) return kBadArgs;
+  if (a->dtype != GE2_DT_BF16) return kUnimplemented;          // the tile layouts below are the 16-bit ones; f16 would need its own MMA format flag
+  if (a->D != 64 && a->D != 128) return kUnimplemented;
+  if (a->dropout_p != 0.f) return kUnimplemented;               // inference / deterministic training only
+  if (mask && (a->mask_kind < 1 || a->mask_kind > 3)) return kBadArgs;
+  auto aligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+  if (!aligned(Q) || !aligned(K) || !aligned(V) || !aligned(O)) return kBadArgs;
+  if (!tc::driver_has_tensor_maps()) return kCudaError;
+  NvtxRange range("sdpa.fwd");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  return a->D == 128 ? launch_sdpa<128>(*a, Q, K, V, mask, O, lse, s) : launch_sdpa<64>(*a, Q, K, V, mask, O, lse, s);
+}

@@ -255,6 +255,28 @@ int ge2b_conv2d_backward(const ge2b_conv2d_params_t* p, const void* X, const voi
 int ge2b_conv2d_output_size(const ge2b_conv2d_params_t* p, int* Ho, int* Wo);
 
 /* ------------------------------------------------------------------------------------------------
+ * Fused scaled-dot-product attention forward, the caller of the batched GEMM pair S = scale.Q.K^T, O = softmax(S).V
+ * with the scores kept on chip.  Replaces SDPACudaLaunch's per-(batch, head) transpose / GEMM / scale / mask /
+ * softmax / GEMM sequence (backends/cuda/ops/sdpa/api.hpp:18-26, launcher.cu:129-270).
+ * ------------------------------------------------------------------------------------------------ */
+typedef struct {
+  int B, H;                   /* batch, heads */
+  int M, N;                   /* queries, keys per (batch, head) */
+  int D;                      /* head dimension: 64 or 128 */
+  ge2_dtype_t dtype;          /* of Q, K, V and O: GE2_DT_BF16 */
+  float scale;                /* 0: 1/sqrt(D), as SDPAAttrs::scale */
+  int causal;                 /* keys n > m are masked for query m */
+  int mask_kind;              /* of the optional mask [B,1,M,N]: 1 fp32 additive, 2 int8, 3 int32 (non-zero = masked) */
+  float dropout_p;            /* must be 0 (-99 otherwise) */
+} ge2b_sdpa_params_t;
+
+/* Q [B,H,M,D], K, V [B,H,N,D], O [B,H,M,D] contiguous; mask may be null; lse (fp32 [B,H,M], the log-sum-exp of every
+ * row's scaled and masked scores) may be null.  A row with every key masked gives zeros.  Returns 0, -1, -2 or -99
+ * (a dtype, head dimension or dropout this kernel does not cover). */
+int ge2b_sdpa_forward(const ge2b_sdpa_params_t* p, const void* Q, const void* K, const void* V, const void* mask, void* O,
+                      float* lse, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Data-parallel gradient exchange: sum all-reduce over NVLink / NVSwitch in one kernel per rank.
  * No counterpart in the reference (it has no multi-GPU path); this is the "dW / db are combined across the GPUs"
  * step of the sharded dense layer.  Every rank reduces its slice of a symmetric buffer inside the switch

@@ -22,19 +22,19 @@ def test_exports_every_declared_symbol(pkg, lib):
 
 def test_struct_sizes_match_the_header(pkg, tmp_path):
     src = tmp_path / "sz.c"
-    src.write_text('#include <stdio.h>\n#include "ge2_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",'
+    src.write_text('#include <stdio.h>\n#include "ge2_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n",'
                    "sizeof(ge2_gemm_bias_act_params_t),sizeof(ge2_gemm_bias_act_params_ex_t),"
                    "sizeof(ge2_gemm_bias_act_bwd_params_t),sizeof(ge2_gemm_typed_params_t),"
                    "sizeof(ge2_gemm_bwd_typed_params_t),sizeof(ge2b_conv2d_params_t),"
                    "sizeof(ge2_softmax_ce_params_t),sizeof(ge2_sgd_params_t),sizeof(ge2b_allreduce_nvls_t),"
-                   "sizeof(ge2b_mlp_config_t));return 0;}\n")
+                   "sizeof(ge2b_mlp_config_t),sizeof(ge2b_sdpa_params_t));return 0;}\n")
     exe = tmp_path / "sz"
     subprocess.run(["gcc", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
     sizes = list(map(int, subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()))
     L = pkg._lib
     assert sizes == [C.sizeof(L.ParamsLegacy), C.sizeof(L.ParamsEx), C.sizeof(L.ParamsBwd), C.sizeof(L.ParamsTyped),
                      C.sizeof(L.ParamsBwdTyped), C.sizeof(L.ParamsConv2D), C.sizeof(L.ParamsSoftmaxCE), C.sizeof(L.ParamsSGD),
-                     C.sizeof(L.AllreduceNvls), C.sizeof(L.MlpConfig)]
+                     C.sizeof(L.AllreduceNvls), C.sizeof(L.MlpConfig), C.sizeof(L.ParamsSdpa)]
 
 
 def test_argument_errors_use_reference_codes(pkg, lib):
