@@ -525,8 +525,8 @@ def test_fp32x3_forward_matches_the_fp32_path(pkg, lib, oracle, shape):
     """math = "fp32x3": operands split into TF32-exact big parts and fp32 remainders, three tensor-core products in one
     fp32 accumulator.  Every product is exact; what remains is the tensor core's accumulator, which truncates (up to
     one unit in the last place per MMA, K/8 of them at full magnitude), so the bound grows with K: max error
-    <= 2^-23 * K/8 relative to max(|y|, 1) against the exact fp32 chain (7.6e-6 at K = 512, below the fp32 path's 1e-5
-    up to K = 640), relative Frobenius error against float64 <= 1e-8 * K."""
+    <= 3e-6 + 2^-23 * K/8 relative to max(|y|, 1) against the exact fp32 chain (about the fp32 path's 1e-5 at K = 512),
+    relative Frobenius error against float64 <= 1e-8 * K."""
     M, K, N = shape
     X, W, b, _ = oracle.dense_inputs(M, K, N, seed=4)
     tX, tW, tb = dev(X), dev(W), dev(b)
@@ -535,9 +535,10 @@ def test_fp32x3_forward_matches_the_fp32_path(pkg, lib, oracle, shape):
     Ye, Ze = pkg.ops_gemm.forward(tX, tW, tb, act="gelu", return_z=True, math="fp32")       # exact chain (CUDA cores)
     assert lib.ge2b_last_route() == 1
     torch.cuda.synchronize()
-    bound = max(2e-6, 2.0 ** -23 * K / 8)
+    bound = 3e-6 + 2.0 ** -23 * K / 8      # a few units in the last place of the two fp32 results + the accumulator's
     for got, want in ((Z, Ze), (Y, Ye)):
         rel = ((got - want).abs() / want.abs().clamp_min(1.0)).max().item()
+        print(f"fp32x3 vs exact chain, K={K}: max error {rel:.2e} (bound {bound:.2e})")
         assert rel <= bound, (rel, bound)
     Y64, Z64 = oracle.forward_f64(X, W, b, act="gelu")
     e3 = oracle.rel_fro(host(Z), Z64)
