@@ -34,7 +34,7 @@ bool stream_is_capturing(cudaStream_t s) {
 struct AsyncScratch {
   cudaStream_t s; void* p = nullptr;
   AsyncScratch(cudaStream_t st, size_t bytes) : s(st) {
-    if (stream_is_capturing(st)) return;
+    if (bytes == 0 || scratch_lease().no_alloc || stream_is_capturing(st)) return;   // callers that must not allocate
     keep_async_pool_cached();
     if (cudaMallocAsync(&p, bytes, st) != cudaSuccess) { cudaGetLastError(); p = nullptr; }
   }

@@ -4,16 +4,19 @@
 // The reference computes this per (b, h) slice as transpose(K) -> GEMM -> scale kernel -> mask kernel -> softmax ->
 // GEMM, with S and P materialised as fp32 [B,H,M,N] tensors (backends/cuda/ops/sdpa/launcher.cu:129-270; scale default
 // 1/sqrt(D): :162; causal: n > m masked, :38-48; additive fp32 mask or 0/1 integer mask [B,1,M,N]: :56-95).  Here one CTA
-// owns 128 query rows of one slice and walks the keys in blocks of 128:
-//   warp 0       TMA producer: Q once, then K_j and V_j into two-deep rings (128-byte-swizzled tiles)
-//   warp 1       MMA issuer:   S_j = Q.K_j^T into TMEM (kind::f16, 128 x 128 x 16), then O += P_j.V_j into TMEM
-//   warps 2..5   softmax:      one query row per thread: tcgen05.ld of the row of S_j, scale / mask, running max and
-//                sum, P_j = exp2(...) written as bf16 into shared memory in the swizzled operand layout, O rescaled in
-//                TMEM by exp2(m_old - m_new) (tcgen05.ld / tcgen05.st), and at the end O / sum -> global memory
-// S_{j+1} = Q.K_{j+1}^T is issued as soon as the softmax warps have pulled S_j into registers, so the tensor pipe
-// works on the next scores while the exponentials of the current block are computed.  Every mbarrier wait is bounded
-// (sm100_ptx.cuh); on expiry the CTA records kErrWaitTimeout in the device status word, frees its TMEM and returns.
-// No TMA load uses cluster multicast.
+// owns 256 query rows of one slice as TWO tiles of 128 rows and walks the keys in blocks of 128:
+//   warp 0       TMA producer: both Q tiles once, then K_j (two-deep ring) and V_j (128-byte-swizzled tiles)
+//   warp 1       MMA issuer:   per tile t: S_t = Q_t.K_j^T into TMEM (kind::f16, 128 x 128 x 16), O_t += P_t.V_j
+//   warps 2..5   softmax of tile 0, warps 6..9 softmax of tile 1: one query row per thread, two passes over the row of
+//                S_t in TMEM in chunks of 32 columns (tcgen05.ld): running max, then P_t = exp2(...) written as bf16
+//                into shared memory in the swizzled operand layout; O_t rescaled in TMEM by exp2(m_old - m_new)
+//                (tcgen05.ld / tcgen05.st) when the maximum moved; at the end O_t / sum -> global memory
+// The two tiles take turns on the tensor pipe: while the softmax warps of one tile work, the MMAs of the other run,
+// and eight softmax warps give every scheduler two warps to switch between.  The row loops are kept as loops over
+// 32-column chunks: fully unrolled over 128 columns the code outgrows the instruction cache, which with so few warps
+// per scheduler costs more than anything else in the kernel (measured: 2.9 ms against 0.4 ms at B.H = 128, L = 2048).
+// Every mbarrier wait is bounded (sm100_ptx.cuh); on expiry the CTA records kErrWaitTimeout in the device status
+// word, frees its TMEM and returns.  No TMA load uses cluster multicast.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -31,10 +34,11 @@ using namespace ge2b;
 
 namespace {
 
-constexpr int kBlockQ = 128;       // query rows per CTA (one TMEM lane each)
+constexpr int kBlockQ = 128;       // query rows per tile (one TMEM lane each)
+constexpr int kTiles = 2;          // tiles per CTA
 constexpr int kBlockKV = 128;      // keys per step
-constexpr int kSdpaThreads = 192;  // warp 0 TMA, warp 1 MMA, warps 2..5 softmax
-constexpr int kSoftmaxWarps = 4;
+constexpr int kSdpaThreads = 320;  // warp 0 TMA, warp 1 MMA, warps 2..5 / 6..9 softmax of tile 0 / 1
+constexpr int kSoftmaxWarps = 4;   // per tile
 
 struct SdpaParams {
   int B, H, M, N;                  // batch, heads, queries, keys
@@ -49,17 +53,18 @@ struct SdpaParams {
 template <int kD>
 struct SdpaCfg {
   static constexpr int kKB = kD / 64;                    // 64-element (128-byte) blocks along the head dimension
-  static constexpr int kQBytes = kBlockQ * kD * 2;       // kKB tiles of [128 rows x 128 B]
+  static constexpr int kQBytes = kBlockQ * kD * 2;       // per tile: kKB tiles of [128 rows x 128 B]
   static constexpr int kKBytes = kBlockKV * kD * 2;      // kKB tiles of [128 keys x 128 B]   (d contiguous)
   static constexpr int kVBytes = kBlockKV * kD * 2;      // 2 key halves x kKB boxes of [64 keys x 128 B] (d contiguous)
-  static constexpr int kPBytes = kBlockQ * kBlockKV * 2; // 2 tiles of [128 rows x 128 B]     (keys contiguous)
-  static constexpr int kSmem = kQBytes + 2 * kKBytes + 2 * kVBytes + kPBytes + 256 + 1024;
-  static constexpr int kTmemCols = 256;                  // S: columns [0, 128), O: columns [128, 128 + kD)
+  static constexpr int kPBytes = kBlockQ * kBlockKV * 2; // per tile: 2 tiles of [128 rows x 128 B]  (keys contiguous)
+  static constexpr int kSmem = kTiles * kQBytes + 2 * kKBytes + kVBytes + kTiles * kPBytes + 256 + 1024;
+  static constexpr int kTmemCols = 512;                  // S_t: columns [128 t, 128 t + 128), O_t: [256 + 128 t, ... + kD)
+  static_assert(kSmem <= 232448, "attention tiles exceed the shared memory of one SM");
 };
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
-  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
@@ -76,6 +81,23 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// One 32-column chunk of a row of scores, scaled (log2 units) and masked: v[i] for keys key0 .. key0 + 31.
+__device__ __forceinline__ void masked_scores(const SdpaParams& p, const uint32_t (&r)[32], float (&v)[32], int key0, int row,
+                                              bool row_ok, long long mask_row) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    const int key = key0 + i;
+    float x = __uint_as_float(r[i]) * p.scale_log2;
+    bool dead = key >= p.N || (p.causal && key > row);
+    if (p.mask_kind != 0 && !dead && row_ok) {
+      if (p.mask_kind == 1)      x += static_cast<const float*>(p.mask)[mask_row + key] * 1.4426950408889634f;
+      else if (p.mask_kind == 2) dead = static_cast<const signed char*>(p.mask)[mask_row + key] != 0;
+      else                       dead = static_cast<const int*>(p.mask)[mask_row + key] != 0;
+    }
+    v[i] = dead ? -CUDART_INF_F : x;
+  }
+}
+
 template <int kD>
 __global__ void __launch_bounds__(kSdpaThreads, 1)
 sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -87,39 +109,40 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
   const uint32_t base = raw_addr + pad;
-  const uint32_t q_smem = base;
-  const uint32_t k_smem = q_smem + Cfg::kQBytes;                  // 2 stages
-  const uint32_t v_smem = k_smem + 2 * Cfg::kKBytes;              // 2 stages
-  const uint32_t p_smem = v_smem + 2 * Cfg::kVBytes;
-  uint8_t* p_ptr = smem + Cfg::kQBytes + 2 * Cfg::kKBytes + 2 * Cfg::kVBytes;
-  const uint32_t bar0 = p_smem + Cfg::kPBytes;
-  uint8_t* bar_ptr = p_ptr + Cfg::kPBytes;
+  const uint32_t q_smem = base;                                   // 2 tiles
+  const uint32_t k_smem = q_smem + kTiles * Cfg::kQBytes;         // 2 stages
+  const uint32_t v_smem = k_smem + 2 * Cfg::kKBytes;              // 1 stage
+  const uint32_t p_smem = v_smem + Cfg::kVBytes;                  // 2 tiles
+  constexpr int kPOff = kTiles * Cfg::kQBytes + 2 * Cfg::kKBytes + Cfg::kVBytes;
+  uint8_t* p_ptr = smem + kPOff;
+  const uint32_t bar0 = p_smem + kTiles * Cfg::kPBytes;
+  uint8_t* bar_ptr = p_ptr + kTiles * Cfg::kPBytes;
   // barriers (8 bytes each)
   const uint32_t q_full = bar0;
   auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
   auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
-  auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
-  auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
-  const uint32_t s_full = bar0 + 8u * 9, s_empty = bar0 + 8u * 10, p_full = bar0 + 8u * 11, o_done = bar0 + 8u * 12;
+  const uint32_t v_full = bar0 + 8u * 5, v_empty = bar0 + 8u * 6;
+  auto s_full = [&](int t) { return bar0 + 8u * (7 + t); };
+  auto p_full = [&](int t) { return bar0 + 8u * (9 + t); };
+  auto o_done = [&](int t) { return bar0 + 8u * (11 + t); };
   volatile uint32_t* tmem_holder = reinterpret_cast<volatile uint32_t*>(bar_ptr + 8 * 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * 13 + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_blocks = (p.M + kBlockQ - 1) / kBlockQ;
+  const int q_blocks = (p.M + kTiles * kBlockQ - 1) / (kTiles * kBlockQ);
   const int slice = blockIdx.x / q_blocks;                        // b * H + h
   const int qb = blockIdx.x - slice * q_blocks;
-  const int q0 = qb * kBlockQ;
+  const int q0 = qb * kTiles * kBlockQ;
   int n_kv = (p.N + kBlockKV - 1) / kBlockKV;
-  if (p.causal) n_kv = min(n_kv, (min(q0 + kBlockQ, p.M) + kBlockKV - 1) / kBlockKV);   // keys beyond the last row's index
+  if (p.causal) n_kv = min(n_kv, (min(q0 + kTiles * kBlockQ, p.M) + kBlockKV - 1) / kBlockKV);   // keys beyond the last row
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
-      ptx::mbar_init(k_full(s), 1); ptx::mbar_init(k_empty(s), 1);
-      ptx::mbar_init(v_full(s), 1); ptx::mbar_init(v_empty(s), 1);
+    for (int s = 0; s < 2; ++s) { ptx::mbar_init(k_full(s), 1); ptx::mbar_init(k_empty(s), 1); }
+    ptx::mbar_init(v_full, 1); ptx::mbar_init(v_empty, 1);
+    for (int t = 0; t < kTiles; ++t) {
+      ptx::mbar_init(s_full(t), 1); ptx::mbar_init(p_full(t), kSoftmaxWarps); ptx::mbar_init(o_done(t), 1);
     }
-    ptx::mbar_init(s_full, 1); ptx::mbar_init(s_empty, kSoftmaxWarps);
-    ptx::mbar_init(p_full, kSoftmaxWarps); ptx::mbar_init(o_done, 1);
     *abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async_smem();
@@ -133,32 +156,31 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
-  const uint32_t s_tmem = tmem_base, o_tmem = tmem_base + 128;
 
   if (warp == 0) {
     // ===================== TMA producer =====================
     if (lane == 0) {
-      ptx::mbar_arrive_expect_tx(q_full, Cfg::kQBytes);
+      ptx::mbar_arrive_expect_tx(q_full, kTiles * Cfg::kQBytes);
 #pragma unroll
-      for (int kb = 0; kb < kKB; ++kb) ptx::tma_load_3d(q_smem + kb * (kBlockQ * 128), &tmQ, q_full, kb * 64, q0, slice);
-      bool ok = true;
-      for (int j = 0; ok && j < n_kv; ++j) {
+      for (int t = 0; t < kTiles; ++t)
+#pragma unroll
+        for (int kb = 0; kb < kKB; ++kb)
+          ptx::tma_load_3d(q_smem + t * Cfg::kQBytes + kb * (kBlockQ * 128), &tmQ, q_full, kb * 64, q0 + t * kBlockQ, slice);
+      for (int j = 0; j < n_kv; ++j) {
         const int s = j & 1;
-        const uint32_t ph = ((j >> 1) & 1) ^ 1u;
-        if (!ptx::mbar_wait(k_empty(s), ph, abort_flag)) { ok = false; break; }
+        if (!ptx::mbar_wait(k_empty(s), ((j >> 1) & 1) ^ 1u, abort_flag)) break;
         ptx::mbar_arrive_expect_tx(k_full(s), Cfg::kKBytes);
 #pragma unroll
         for (int kb = 0; kb < kKB; ++kb)
           ptx::tma_load_3d(k_smem + s * Cfg::kKBytes + kb * (kBlockKV * 128), &tmK, k_full(s), kb * 64, j * kBlockKV, slice);
-        if (!ptx::mbar_wait(v_empty(s), ph, abort_flag)) { ok = false; break; }
-        ptx::mbar_arrive_expect_tx(v_full(s), Cfg::kVBytes);
+        if (!ptx::mbar_wait(v_empty, (j & 1) ^ 1u, abort_flag)) break;
+        ptx::mbar_arrive_expect_tx(v_full, Cfg::kVBytes);
         // V block: two halves of 64 keys (the reduction blocks of P.V), each kKB boxes of {64 d, 64 keys}
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
           for (int kb = 0; kb < kKB; ++kb)
-            ptx::tma_load_3d(v_smem + s * Cfg::kVBytes + h * (64 * kD * 2) + kb * (64 * 128), &tmV, v_full(s), kb * 64,
-                             j * kBlockKV + h * 64, slice);
+            ptx::tma_load_3d(v_smem + h * (64 * kD * 2) + kb * (64 * 128), &tmV, v_full, kb * 64, j * kBlockKV + h * 64, slice);
       }
     }
     __syncwarp();
@@ -168,153 +190,142 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const uint32_t idesc_s = ptx::make_idesc(1, false, false, kBlockQ, kBlockKV);   // bf16, Q and K reduction-contiguous
       const uint32_t idesc_o = ptx::make_idesc(1, false, true, kBlockQ, kD);          // P reduction-contiguous, V d-contiguous
       bool ok = ptx::mbar_wait(q_full, 0u, abort_flag);
-      auto issue_s = [&](int j) {
+      auto issue_s = [&](int t, int j) {                        // S_t = Q_t . K_j^T
         const int s = j & 1;
         if (!ptx::mbar_wait(k_full(s), (j >> 1) & 1, abort_flag)) { ok = false; return; }
         ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + t * 128;
 #pragma unroll
         for (int kb = 0; kb < kKB; ++kb) {
-          const uint64_t a0 = ptx::make_smem_desc_sw128(q_smem + kb * (kBlockQ * 128), 0u, 1024u);
+          const uint64_t a0 = ptx::make_smem_desc_sw128(q_smem + t * Cfg::kQBytes + kb * (kBlockQ * 128), 0u, 1024u);
           const uint64_t b0 = ptx::make_smem_desc_sw128(k_smem + s * Cfg::kKBytes + kb * (kBlockKV * 128), 0u, 1024u);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            ptx::umma<false>(s_tmem, a0 + ks * 2, b0 + ks * 2, idesc_s, (kb | ks) ? 1u : 0u);
+            ptx::umma<false>(d_tmem, a0 + ks * 2, b0 + ks * 2, idesc_s, (kb | ks) ? 1u : 0u);
         }
-        ptx::umma_commit(k_empty(s));       // the K slot is free once these MMAs have read it
-        ptx::umma_commit(s_full);           // and the scores are complete
+        if (t == kTiles - 1) ptx::umma_commit(k_empty(s));      // both tiles have read this K block
+        ptx::umma_commit(s_full(t));
       };
-      if (ok && n_kv > 0) issue_s(0);
-      for (int j = 0; ok && j < n_kv; ++j) {
-        const int s = j & 1;
-        if (j + 1 < n_kv) {
-          // the softmax warps hold S_j in registers: the next scores may overwrite it
-          if (!ptx::mbar_wait(s_empty, j & 1, abort_flag)) { ok = false; break; }
-          ptx::tc_fence_after_sync();
-          issue_s(j + 1);
-          if (!ok) break;
-        }
-        if (!ptx::mbar_wait(p_full, j & 1, abort_flag)) { ok = false; break; }     // P_j in shared memory, O rescaled
-        if (!ptx::mbar_wait(v_full(s), (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      auto issue_pv = [&](int t, int j) {                       // O_t += P_t . V_j
+        if (!ptx::mbar_wait(p_full(t), j & 1, abort_flag)) { ok = false; return; }   // P_t written, O_t rescaled, S_t read
+        if (!ptx::mbar_wait(v_full, j & 1, abort_flag)) { ok = false; return; }
         ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + 256 + t * 128;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const uint64_t a0 = ptx::make_smem_desc_sw128(p_smem + h * (kBlockQ * 128), 0u, 1024u);
-          const uint64_t b0 = ptx::make_smem_desc_sw128(v_smem + s * Cfg::kVBytes + h * (64 * kD * 2), 64u * 128u, 1024u);
+          const uint64_t a0 = ptx::make_smem_desc_sw128(p_smem + t * Cfg::kPBytes + h * (kBlockQ * 128), 0u, 1024u);
+          const uint64_t b0 = ptx::make_smem_desc_sw128(v_smem + h * (64 * kD * 2), 64u * 128u, 1024u);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)
-            ptx::umma<false>(o_tmem, a0 + ks * 2, b0 + ks * ((16 * 128) >> 4), idesc_o, (j > 0 || (h | ks)) ? 1u : 0u);
+            ptx::umma<false>(d_tmem, a0 + ks * 2, b0 + ks * ((16 * 128) >> 4), idesc_o, (j > 0 || (h | ks)) ? 1u : 0u);
         }
-        ptx::umma_commit(v_empty(s));
-        ptx::umma_commit(o_done);           // O holds blocks 0..j; P's buffer may be rewritten
+        if (t == kTiles - 1) ptx::umma_commit(v_empty);         // both tiles have read this V block
+        ptx::umma_commit(o_done(t));
+      };
+      if (ok && n_kv > 0) { issue_s(0, 0); if (ok) issue_s(1, 0); }
+      for (int j = 0; ok && j < n_kv; ++j) {
+#pragma unroll
+        for (int t = 0; t < kTiles; ++t) {
+          if (!ok) break;
+          issue_pv(t, j);
+          if (ok && j + 1 < n_kv) issue_s(t, j + 1);            // the tile's next scores while its softmax warps wait
+        }
       }
     }
     __syncwarp();
   } else {
     // ===================== softmax: one query row per thread =====================
+    const int t = (warp - 2) >> 2;                            // tile of this warp
     const int q = warp & 3;                                   // TMEM lane quarter this warp may access
     const int r_in = q * 32 + lane;
-    const int row = q0 + r_in;
+    const int row = q0 + t * kBlockQ + r_in;
     const bool row_ok = row < p.M;
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
+    const uint32_t s_tmem = tmem_base + t * 128 + lane_sel, o_tmem = tmem_base + 256 + t * 128 + lane_sel;
+    uint8_t* my_p = p_ptr + t * Cfg::kPBytes + r_in * 128;
+    const int swz = r_in & 7;
     float m_run = -CUDART_INF_F, l_run = 0.f;
     const long long mask_row = p.mask ? (static_cast<long long>(slice / p.H) * p.M + row) * p.N : 0;
     bool ok = true;
+#pragma unroll 1
     for (int j = 0; ok && j < n_kv; ++j) {
       // the TMEM accesses below are warp-collective: the warp stays or leaves together
-      if (!__all_sync(0xffffffffu, ptx::mbar_wait(s_full, j & 1, abort_flag))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(s_full(t), j & 1, abort_flag))) { ok = false; break; }
       ptx::tc_fence_after_sync();
-      float sc[128];
-#pragma unroll
+      const int key0 = j * kBlockKV;
+      // pass 1: row maximum of the scaled, masked scores
+      float m_blk = -CUDART_INF_F;
+#pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
-        ptx::tmem_ld_32x32(s_tmem + lane_sel + c * 32, r);
+        float v[32];
+        ptx::tmem_ld_32x32(s_tmem + c * 32, r);
         ptx::tmem_wait_ld();
+        masked_scores(p, r, v, key0 + c * 32, row, row_ok, mask_row);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sc[c * 32 + i] = __uint_as_float(r[i]);
-      }
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(s_empty);               // S_j is in registers
-      // scale (in log2 units), mask, row maximum
-      const int key0 = j * kBlockKV;
-      float m_blk = -CUDART_INF_F;
-#pragma unroll
-      for (int i = 0; i < 128; ++i) {
-        const int key = key0 + i;
-        float v = sc[i] * p.scale_log2;
-        bool dead = key >= p.N || (p.causal && key > row);
-        if (p.mask_kind == 1) {
-          if (!dead && row_ok) v += static_cast<const float*>(p.mask)[mask_row + key] * 1.4426950408889634f;
-        } else if (p.mask_kind == 2) {
-          if (!dead && row_ok && static_cast<const signed char*>(p.mask)[mask_row + key] != 0) dead = true;
-        } else if (p.mask_kind == 3) {
-          if (!dead && row_ok && static_cast<const int*>(p.mask)[mask_row + key] != 0) dead = true;
-        }
-        v = dead ? -CUDART_INF_F : v;
-        sc[i] = v;
-        m_blk = fmaxf(m_blk, v);
+        for (int i = 0; i < 32; ++i) m_blk = fmaxf(m_blk, v[i]);
       }
       const float m_new = fmaxf(m_run, m_blk);
       const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;       // a fully masked row so far: keep everything 0
       const float alpha = ex2(m_run - m_use);                           // exp2(-inf) = 0 on the first block
-      float l_blk = 0.f;
-      // P_j: probabilities (unnormalised) as bf16 pairs; the sum uses the ROUNDED values, which is what the P.V
-      // product will see, so that O / l is a true weighted mean
-      uint32_t pk[64];
-#pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float e0 = ex2(sc[2 * i] - m_use), e1 = ex2(sc[2 * i + 1] - m_use);
-        const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
-        pk[i] = *reinterpret_cast<const uint32_t*>(&h);
-        const float2 f = __bfloat1622float2(h);
-        l_blk += f.x + f.y;
-      }
-      l_run = l_run * alpha + l_blk;
       m_run = m_new;
-      // the previous P.V must have finished: it read P's buffer and wrote O
+      // the tile's previous P.V must have finished: it read P's buffer and wrote O
       if (j > 0) {
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(o_done, (j - 1) & 1, abort_flag))) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(o_done(t), (j - 1) & 1, abort_flag))) { ok = false; break; }
         ptx::tc_fence_after_sync();
         if (__any_sync(0xffffffffu, alpha != 1.f)) {                    // rescale the rows of O by exp2(m_old - m_new)
-#pragma unroll
+#pragma unroll 1
           for (int c = 0; c < kD / 32; ++c) {
             uint32_t r[32];
-            ptx::tmem_ld_32x32(o_tmem + lane_sel + c * 32, r);
+            ptx::tmem_ld_32x32(o_tmem + c * 32, r);
             ptx::tmem_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32(o_tmem + lane_sel + c * 32, r);
+            tmem_st_32x32(o_tmem + c * 32, r);
           }
           tmem_wait_st();
         }
       }
-      // P row into the operand layout: 2 tiles (64 keys each) of [128 rows x 128 B], 16-byte chunk index XOR (row & 7)
-      {
-        const int swz = r_in & 7;
+      // pass 2: P = exp2(v - m) as bf16 into the operand layout (2 tiles of 64 keys, [128 rows x 128 B], 16-byte chunk
+      // index XOR (row & 7)); the row sum uses the ROUNDED values, which is what the P.V product will see
+      float l_blk = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        float v[32];
+        ptx::tmem_ld_32x32(s_tmem + c * 32, r);
+        ptx::tmem_wait_ld();
+        masked_scores(p, r, v, key0 + c * 32, row, row_ok, mask_row);
+        uint32_t pk[16];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint8_t* my_row = p_ptr + h * (kBlockQ * 128) + r_in * 128;
-#pragma unroll
-          for (int c = 0; c < 8; ++c)
-            *reinterpret_cast<uint4*>(my_row + ((c ^ swz) * 16)) =
-                make_uint4(pk[h * 32 + 4 * c], pk[h * 32 + 4 * c + 1], pk[h * 32 + 4 * c + 2], pk[h * 32 + 4 * c + 3]);
+        for (int i = 0; i < 16; ++i) {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(ex2(v[2 * i] - m_use), ex2(v[2 * i + 1] - m_use));
+          pk[i] = *reinterpret_cast<const uint32_t*>(&h);
+          const float2 f = __bfloat1622float2(h);
+          l_blk += f.x + f.y;
         }
+        uint8_t* dst = my_p + (c >> 1) * (kBlockQ * 128);               // chunk c: keys 32 c .. 32 c + 31 of the block
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          *reinterpret_cast<uint4*>(dst + ((((c & 1) * 4 + k) ^ swz) * 16)) =
+              make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
       }
+      l_run = l_run * alpha + l_blk;
       ptx::fence_proxy_async_smem();                                    // the MMA reads P through the async proxy
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(p_full);
+      if (lane == 0) ptx::mbar_arrive(p_full(t));
     }
     // ---- O / l -> global memory ----
-    if (ok && n_kv > 0) ok = __all_sync(0xffffffffu, ptx::mbar_wait(o_done, (n_kv - 1) & 1, abort_flag));
+    if (ok && n_kv > 0) ok = __all_sync(0xffffffffu, ptx::mbar_wait(o_done(t), (n_kv - 1) & 1, abort_flag));
     if (ok) {
       ptx::tc_fence_after_sync();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const long long o_off = (static_cast<long long>(slice) * p.M + row) * kD;
-#pragma unroll
+#pragma unroll 1
       for (int c = 0; c < kD / 32; ++c) {
         uint32_t r[32];
-        if (n_kv > 0) { ptx::tmem_ld_32x32(o_tmem + lane_sel + c * 32, r); ptx::tmem_wait_ld(); }
+        if (n_kv > 0) { ptx::tmem_ld_32x32(o_tmem + c * 32, r); ptx::tmem_wait_ld(); }
         else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0u;
@@ -385,7 +396,7 @@ int launch_sdpa(const ge2b_sdpa_params_t& a, const void* Q, const void* K, const
   p.O = O; p.o_dtype = a.dtype; p.lse = lse;
   p.status = device_status_ptr();
   if (!p.status) return kCudaError;
-  const int q_blocks = (a.M + kBlockQ - 1) / kBlockQ;
+  const int q_blocks = (a.M + kTiles * kBlockQ - 1) / (kTiles * kBlockQ);
   const long long grid = slices * q_blocks;
   if (grid > 0x7fffffffll) return kBadArgs;
   kernel<<<static_cast<unsigned>(grid), kSdpaThreads, Cfg::kSmem, s>>>(tmQ, tmK, tmV, p);
