@@ -296,7 +296,7 @@ cudaError_t prepare_major(const GemmProblem& g, TcParams& p, TileChoice t, cudaS
 // override.
 TileChoice choose_tile(const GemmProblem& g) {
   TileChoice t{256, 1};
-  static const int force_bn = [] { const char* e = getenv("GE2B_BLOCK_N"); const int v = e ? atoi(e) : 0; return (v == 128 || v == 256) ? v : 0; }();
+  static const int force_bn = [] { const char* e = getenv("GE2B_BLOCK_N"); const int v = e ? atoi(e) : 0; return (v == 64 || v == 128 || v == 256) ? v : 0; }();
   static const int force_cg = [] { const char* e = getenv("GE2B_CTA_GROUP"); const int v = e ? atoi(e) : 0; return (v == 1 || v == 2) ? v : 0; }();
   // A CTA pair (256 rows per tile, half of B per CTA, deeper ring) is the faster form whenever the problem has at
   // least two 128-row blocks; below that the second CTA of a pair would only compute padding.
@@ -311,7 +311,20 @@ TileChoice choose_tile(const GemmProblem& g) {
   };
   // measured on B200: a 128-wide tile reaches about 0.72 of the 256-wide tile's rate (single CTA; the pair form
   // of the narrow tile was slower still and is not built)
-  if (force_bn) { t.block_n = force_bn; if (t.block_n == 128) t.cta_group = 1; return t; }
+  if (force_bn) { t.block_n = force_bn; if (t.block_n <= 128) t.cta_group = 1; return t; }
+  // Skinny M with a long reduction (decode-like: M <= 128, N = K = 8192) streams the weight matrix once and is bound
+  // by HBM.  256-wide tiles give too few CTAs to pull it at full rate unless the reduction is split, and the split
+  // costs 10 us or more; 64-wide tiles give N / 64 CTAs that each stream their own panel of B with nothing to
+  // exchange (eight-deep ring: about 80 KB in flight per SM).
+  static const bool narrow_off = [] { const char* e = getenv("GE2B_SKINNY_64"); return e && atoi(e) == 0; }();
+  if (!narrow_off && g.M <= 128 && !g.reduce_batch && g.K >= 2048) {
+    const long long tiles64 = static_cast<long long>(g.batch) * ((g.N + 63) / 64);
+    const long long tiles256 = static_cast<long long>(g.batch) * ((g.N + 255) / 256);
+    if (tiles256 < static_cast<long long>(sms) && 10 * tiles64 >= 6 * static_cast<long long>(sms)) {
+      t.block_n = 64; t.cta_group = 1;
+      return t;
+    }
+  }
   if (g.N <= 128) { t.block_n = 128; t.cta_group = 1; return t; }
   if (cost(256, t.cta_group, 1.0) > cost(128, 1, 0.72)) { t.block_n = 128; t.cta_group = 1; }
   return t;

@@ -99,7 +99,7 @@ struct TcCfg {
   static constexpr int kBarBytes   = 256;
   static constexpr int kStoreStage = kEpiWarps * kStoreStageWarp;       // per-warp transpose buffers of the epilogue
   static constexpr int kSmemBytes  = kStages * kStageBytes + kBarBytes + kStoreStage + 1024;   // +1024: alignment
-  static_assert(kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
+  static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM allocation must be a power of two");
   static_assert(kSmemBytes <= 232448, "operand ring exceeds the shared memory of one SM");
   static_assert(8 * (2 * kStages + 4) + 16 <= kBarBytes, "barrier block too small");
 };
@@ -917,7 +917,8 @@ bool prepare_problem(const GemmProblem& g, TcParams& p, ProblemMaps& m) {
 
   // Outputs as tensor maps for the epilogue's bulk stores (when base, pitch and batch stride allow).
   m.tmD = m.tmA; m.tmZ = m.tmA;
-  p.store_wide = (p.d_vec && g.epi.Z == nullptr && g.epi.d_dtype != kF32) ? 1 : 0;
+  // (the 64-column store pairs two 32-column chunks of one warp: a warp of the 64-wide tile has only one)
+  p.store_wide = (p.d_vec && g.epi.Z == nullptr && g.epi.d_dtype != kF32 && kBlockN >= 128) ? 1 : 0;
   if (p.d_vec && !make_output_map(&m.tmD, g.epi.d_dtype, g.epi.D, g.N, g.M, g.epi.ldd, p.batch, g.epi.strideD,
                                   p.store_wide != 0)) {
     p.d_vec = 0;
@@ -1060,6 +1061,7 @@ template <int kElemBytes, bool kAMN, bool kBMN>
 cudaError_t prepare_bn(const GemmProblem& g, TcParams& p, TileChoice t, cudaStream_t s, PreparedLaunch& L) {
   if (t.cta_group == 2 && t.block_n == 256) return prepare_cfg<kElemBytes, kAMN, kBMN, 256, 6, 2>(g, p, s, L);
   if (t.block_n == 128) return prepare_cfg<kElemBytes, kAMN, kBMN, 128, 6, 1>(g, p, s, L);
+  if (t.block_n == 64) return prepare_cfg<kElemBytes, kAMN, kBMN, 64, 8, 1>(g, p, s, L);
   return prepare_cfg<kElemBytes, kAMN, kBMN, 256, 4, 1>(g, p, s, L);
 }
 

@@ -338,6 +338,15 @@ def run_ours(args):
         barrier()
         print(json.dumps({"profile": "qk", "status": lib.ge2b_device_status(0)}), flush=True)
         return
+    if args.profile == "sdpa":
+        # the fused attention forward at config 4's shape (B = 8, H = 16, L = 2048, d = 128, bf16), three launches
+        Q, Kt, V = (torch.randn((8, 16, 2048, 128), device=dev).bfloat16() for _ in range(3))
+        O = torch.empty_like(Q)
+        for _ in range(3):
+            pkg.ops_sdpa.forward(Q, Kt, V, out=O)
+        barrier()
+        print(json.dumps({"profile": "sdpa", "status": lib.ge2b_device_status(0)}), flush=True)
+        return
     if args.profile:
         # a short, fixed launch sequence for a profiler capture: 2 warm-up steps, then 2 more
         for _ in range(4):
@@ -806,6 +815,12 @@ def run_sweep(args):
     t_qk = timeit(lambda: og.forward_batched(Q, Kt, out=S, trans_b=True, alpha=1.0 / d ** 0.5), 7)
     t_pv = timeit(lambda: og.forward_batched(P, V, out=O), 7)
     flop = 2.0 * Bn * H * L * L * d
+    t_fa = timeit(lambda: pkg.ops_sdpa.forward(Q, Kt, V, out=O), 7)
+    t_fac = timeit(lambda: pkg.ops_sdpa.forward(Q, Kt, V, out=O, causal=True), 7)
+    print(json.dumps({"sweep": "fused_attention", "B": Bn, "H": H, "L": L, "d": d, "dtype": "bf16",
+                      "fwd_ms": round(t_fa, 4), "fwd_tflops": round(2 * flop / t_fa / 1e9, 1),
+                      "causal_fwd_ms": round(t_fac, 4), "causal_fwd_tflops": round(flop / t_fac / 1e9, 1),
+                      "note": "S = scale.Q.K^T, softmax and P.V in one launch: no S / P traffic"}), flush=True)
     print(json.dumps({"sweep": "batched_attention", "B": Bn, "H": H, "L": L, "d": d, "dtype": "bf16",
                       "qk_ms": round(t_qk, 4), "qk_tflops": round(flop / t_qk / 1e9, 1),
                       "qk_GBs": round((2 * Q.numel() * 2 + S.numel() * 2) / t_qk / 1e6, 1),
@@ -870,7 +885,7 @@ def main():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--profile", default="", choices=["", "fwd", "step", "conv", "qk"],
+    ap.add_argument("--profile", default="", choices=["", "fwd", "step", "conv", "qk", "sdpa"],
                     help="run a short fixed launch sequence (for ncu) instead of the benchmark")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU-oracle leg (profiling runs)")
     ap.add_argument("--skip-mlp", action="store_true", help="omit the MLP training-step leg")
