@@ -315,9 +315,12 @@ TileChoice choose_tile(const GemmProblem& g) {
   // Skinny M with a long reduction (decode-like: M <= 128, N = K = 8192) streams the weight matrix once and is bound
   // by HBM.  256-wide tiles give too few CTAs to pull it at full rate unless the reduction is split, and the split
   // costs 10 us or more; 64-wide tiles give N / 64 CTAs that each stream their own panel of B with nothing to
-  // exchange (eight-deep ring: about 80 KB in flight per SM).
-  static const bool narrow_off = [] { const char* e = getenv("GE2B_SKINNY_64"); return e && atoi(e) == 0; }();
-  if (!narrow_off && g.M <= 128 && !g.reduce_batch && g.K >= 2048) {
+  // exchange (eight-deep ring).
+  // Measured on B200 (M = 16 .. 128, N = K = 8192, graph replay): 40 us, against 32 us for 256-wide tiles with the
+  // reduction split four ways -- eight stages of 10 KB of real data per SM are not enough bytes in flight to pull
+  // HBM at full rate, and the 128-row A box fills most of every stage with zeros.  Off unless GE2B_SKINNY_64=1.
+  static const bool skinny64 = [] { const char* e = getenv("GE2B_SKINNY_64"); return e && atoi(e) == 1; }();
+  if (skinny64 && g.M <= 128 && !g.reduce_batch && g.K >= 2048) {
     const long long tiles64 = static_cast<long long>(g.batch) * ((g.N + 63) / 64);
     const long long tiles256 = static_cast<long long>(g.batch) * ((g.N + 255) / 256);
     if (tiles256 < static_cast<long long>(sms) && 10 * tiles64 >= 6 * static_cast<long long>(sms)) {

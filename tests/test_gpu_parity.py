@@ -418,7 +418,7 @@ def test_host_plan_step_and_pipelined_submit(pkg, lib, oracle):
 
 
 @pytest.mark.parametrize("shape", [(16, 8192, 2048), (64, 4096, 1024), (128, 8192, 8192), (300, 2048, 512),
-                                   (40, 2048, 6000), (16, 8192, 8192)])     # the last three: 64-wide tiles, no split
+                                   (40, 2048, 6000), (16, 8192, 8192)])
 def test_split_reduction_for_small_grids(pkg, lib, oracle, shape):
     """Few output tiles, long reduction: the launch splits the reduction across SMs and adds fp32 partial sums."""
     M, K, N = shape
