@@ -253,17 +253,37 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(s_full(t), j & 1, abort_flag))) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const int key0 = j * kBlockKV;
-      // pass 1: row maximum of the scaled, masked scores
-      float m_blk = -CUDART_INF_F;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        float v[32];
-        ptx::tmem_ld_32x32(s_tmem + c * 32, r);
-        ptx::tmem_wait_ld();
-        masked_scores(p, r, v, key0 + c * 32, row, row_ok, mask_row);
+      // Does any lane of this warp need per-element masking in this key block?  (keys beyond N in the last block, the
+      // diagonal blocks of a causal mask, an explicit mask, a non-positive scale.)  The common block does not, and its
+      // row maximum is the maximum of the raw scores times the scale.
+      const int warp_row0 = row - lane;
+      const bool general = key0 + kBlockKV > p.N || (p.causal && key0 + kBlockKV - 1 > warp_row0) || p.mask_kind != 0 ||
+                           !(p.scale_log2 > 0.f);
+      float m_blk;
+      if (!general) {
+        // pass 1 (fast): four independent running maxima per chunk
+        float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-        for (int i = 0; i < 32; ++i) m_blk = fmaxf(m_blk, v[i]);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(s_tmem + c * 32, r);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(r[i]));
+        }
+        m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+      } else {
+        m_blk = -CUDART_INF_F;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          float v[32];
+          ptx::tmem_ld_32x32(s_tmem + c * 32, r);
+          ptx::tmem_wait_ld();
+          masked_scores(p, r, v, key0 + c * 32, row, row_ok, mask_row);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) m_blk = fmaxf(m_blk, v[i]);
+        }
       }
       const float m_new = fmaxf(m_run, m_blk);
       const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;       // a fully masked row so far: keep everything 0
@@ -287,22 +307,34 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       // pass 2: P = exp2(v - m) as bf16 into the operand layout (2 tiles of 64 keys, [128 rows x 128 B], 16-byte chunk
-      // index XOR (row & 7)); the row sum uses the ROUNDED values, which is what the P.V product will see
-      float l_blk = 0.f;
+      // index XOR (row & 7)) and the row sum (fp32 values, four independent partial sums)
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      const float neg_m = -m_use;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
-        float v[32];
         ptx::tmem_ld_32x32(s_tmem + c * 32, r);
         ptx::tmem_wait_ld();
-        masked_scores(p, r, v, key0 + c * 32, row, row_ok, mask_row);
         uint32_t pk[16];
+        if (!general) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const __nv_bfloat162 h = __floats2bfloat162_rn(ex2(v[2 * i] - m_use), ex2(v[2 * i + 1] - m_use));
-          pk[i] = *reinterpret_cast<const uint32_t*>(&h);
-          const float2 f = __bfloat1622float2(h);
-          l_blk += f.x + f.y;
+          for (int i = 0; i < 16; ++i) {
+            const float e0 = ex2(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, neg_m));
+            const float e1 = ex2(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, neg_m));
+            ls[(2 * i) & 3] += e0; ls[(2 * i + 1) & 3] += e1;
+            const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+            pk[i] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+        } else {
+          float v[32];
+          masked_scores(p, r, v, key0 + c * 32, row, row_ok, mask_row);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float e0 = ex2(v[2 * i] + neg_m), e1 = ex2(v[2 * i + 1] + neg_m);
+            ls[(2 * i) & 3] += e0; ls[(2 * i + 1) & 3] += e1;
+            const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+            pk[i] = *reinterpret_cast<const uint32_t*>(&h);
+          }
         }
         uint8_t* dst = my_p + (c >> 1) * (kBlockQ * 128);               // chunk c: keys 32 c .. 32 c + 31 of the block
 #pragma unroll
@@ -310,6 +342,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           *reinterpret_cast<uint4*>(dst + ((((c & 1) * 4 + k) ^ swz) * 16)) =
               make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
       }
+      const float l_blk = (ls[0] + ls[1]) + (ls[2] + ls[3]);
       l_run = l_run * alpha + l_blk;
       ptx::fence_proxy_async_smem();                                    // the MMA reads P through the async proxy
       ptx::tc_fence_before_sync();
