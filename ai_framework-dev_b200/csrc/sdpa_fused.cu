@@ -133,8 +133,14 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int slice = blockIdx.x / q_blocks;                        // b * H + h
   const int qb = blockIdx.x - slice * q_blocks;
   const int q0 = qb * kTiles * kBlockQ;
-  int n_kv = (p.N + kBlockKV - 1) / kBlockKV;
-  if (p.causal) n_kv = min(n_kv, (min(q0 + kTiles * kBlockQ, p.M) + kBlockKV - 1) / kBlockKV);   // keys beyond the last row
+  // key blocks per tile: under a causal mask a tile needs no keys beyond its own last row, so tile 0 stops one block
+  // before tile 1; n_kv is the CTA's count (tile 1 uses every block that is loaded)
+  const int n_all = (p.N + kBlockKV - 1) / kBlockKV;
+  auto tile_blocks = [&](int t) {
+    return p.causal ? min(n_all, (min(q0 + (t + 1) * kBlockQ, max(p.M, q0 + 1)) + kBlockKV - 1) / kBlockKV) : n_all;
+  };
+  const int n_kv0 = tile_blocks(0);
+  const int n_kv = max(n_kv0, tile_blocks(1));
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(q_full, 1);
@@ -226,9 +232,10 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int j = 0; ok && j < n_kv; ++j) {
 #pragma unroll
         for (int t = 0; t < kTiles; ++t) {
-          if (!ok) break;
+          const int mine = t == 0 ? n_kv0 : n_kv;               // tile 1 walks every block: it frees the K / V slots
+          if (!ok || j >= mine) continue;
           issue_pv(t, j);
-          if (ok && j + 1 < n_kv) issue_s(t, j + 1);            // the tile's next scores while its softmax warps wait
+          if (ok && j + 1 < mine) issue_s(t, j + 1);            // the tile's next scores while its softmax warps wait
         }
       }
     }
@@ -247,31 +254,41 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float m_run = -CUDART_INF_F, l_run = 0.f;
     const long long mask_row = p.mask ? (static_cast<long long>(slice / p.H) * p.M + row) * p.N : 0;
     bool ok = true;
+    const int my_kv = t == 0 ? n_kv0 : n_kv;
 #pragma unroll 1
-    for (int j = 0; ok && j < n_kv; ++j) {
+    for (int j = 0; ok && j < my_kv; ++j) {
       // the TMEM accesses below are warp-collective: the warp stays or leaves together
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(s_full(t), j & 1, abort_flag))) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const int key0 = j * kBlockKV;
-      // Does any lane of this warp need per-element masking in this key block?  (keys beyond N in the last block, the
-      // diagonal blocks of a causal mask, an explicit mask, a non-positive scale.)  The common block does not, and its
-      // row maximum is the maximum of the raw scores times the scale.
+      // Three forms of the per-element work, chosen per key block and warp (warp-uniform):
+      //   0  nothing is masked: the row maximum is the maximum of the raw scores times the (positive) scale;
+      //   1  a column limit: keys beyond N in the last block and / or the diagonal of a causal mask, i.e. column i
+      //      of the block is dead iff i > limit (per row);
+      //   2  explicit masks or a non-positive scale: every element goes through masked_scores().
       const int warp_row0 = row - lane;
-      const bool general = key0 + kBlockKV > p.N || (p.causal && key0 + kBlockKV - 1 > warp_row0) || p.mask_kind != 0 ||
-                           !(p.scale_log2 > 0.f);
+      const int form = (p.mask_kind != 0 || !(p.scale_log2 > 0.f)) ? 2
+                       : (key0 + kBlockKV > p.N || (p.causal && key0 + kBlockKV - 1 > warp_row0)) ? 1 : 0;
+      const int limit = min(p.N - 1 - key0, p.causal ? row - key0 : kBlockKV);      // last live column of this row
       float m_blk;
-      if (!general) {
-        // pass 1 (fast): four independent running maxima per chunk
+      if (form != 2) {
+        // pass 1: four independent running maxima per chunk
         float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
           ptx::tmem_ld_32x32(s_tmem + c * 32, r);
           ptx::tmem_wait_ld();
+          if (form == 0) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(r[i]));
+            for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(r[i]));
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              mx[i & 3] = fmaxf(mx[i & 3], (c * 32 + i <= limit) ? __uint_as_float(r[i]) : -CUDART_INF_F);
+          }
         }
-        m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+        m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;     // (-inf stays -inf)
       } else {
         m_blk = -CUDART_INF_F;
 #pragma unroll 1
@@ -285,9 +302,13 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           for (int i = 0; i < 32; ++i) m_blk = fmaxf(m_blk, v[i]);
         }
       }
-      const float m_new = fmaxf(m_run, m_blk);
+      // The reference point m of the exponentials only has to stay within range, not be the exact maximum: while the
+      // row maximum has grown by less than 8 (a factor 256, harmless for fp32 sums and bf16 P) the old reference is
+      // kept and O needs no rescaling; the final O / l is exact either way.
+      const float m_cand = fmaxf(m_run, m_blk);
+      const float m_new = (m_run != -CUDART_INF_F && m_cand - m_run <= 8.f) ? m_run : m_cand;
       const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;       // a fully masked row so far: keep everything 0
-      const float alpha = ex2(m_run - m_use);                           // exp2(-inf) = 0 on the first block
+      const float alpha = (m_new == m_run) ? 1.f : ex2(m_run - m_use);  // exp2(-inf) = 0 on the first live block
       m_run = m_new;
       // the tile's previous P.V must have finished: it read P's buffer and wrote O
       if (j > 0) {
@@ -316,11 +337,23 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         ptx::tmem_ld_32x32(s_tmem + c * 32, r);
         ptx::tmem_wait_ld();
         uint32_t pk[16];
-        if (!general) {
+        if (form == 0) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const float e0 = ex2(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, neg_m));
             const float e1 = ex2(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, neg_m));
+            ls[(2 * i) & 3] += e0; ls[(2 * i + 1) & 3] += e1;
+            const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
+            pk[i] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+        } else if (form == 1) {
+          const int lim_c = limit - c * 32;                             // last live column within this chunk
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float e0 = ex2(fmaf(__uint_as_float(r[2 * i]), p.scale_log2, neg_m));
+            float e1 = ex2(fmaf(__uint_as_float(r[2 * i + 1]), p.scale_log2, neg_m));
+            e0 = (2 * i <= lim_c) ? e0 : 0.f;
+            e1 = (2 * i + 1 <= lim_c) ? e1 : 0.f;
             ls[(2 * i) & 3] += e0; ls[(2 * i + 1) & 3] += e1;
             const __nv_bfloat162 h = __floats2bfloat162_rn(e0, e1);
             pk[i] = *reinterpret_cast<const uint32_t*>(&h);
@@ -350,7 +383,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (lane == 0) ptx::mbar_arrive(p_full(t));
     }
     // ---- O / l -> global memory ----
-    if (ok && n_kv > 0) ok = __all_sync(0xffffffffu, ptx::mbar_wait(o_done(t), (n_kv - 1) & 1, abort_flag));
+    if (ok && my_kv > 0) ok = __all_sync(0xffffffffu, ptx::mbar_wait(o_done(t), (my_kv - 1) & 1, abort_flag));
     if (ok) {
       ptx::tc_fence_after_sync();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -358,7 +391,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll 1
       for (int c = 0; c < kD / 32; ++c) {
         uint32_t r[32];
-        if (n_kv > 0) { ptx::tmem_ld_32x32(o_tmem + c * 32, r); ptx::tmem_wait_ld(); }
+        if (my_kv > 0) { ptx::tmem_ld_32x32(o_tmem + c * 32, r); ptx::tmem_wait_ld(); }
         else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[i] = 0u;

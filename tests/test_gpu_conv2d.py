@@ -258,3 +258,42 @@ def test_reference_conv2d_binding_runs_on_this_library(pkg, lib, oracle, conv_or
     assert oracle.rel_fro(host(dX), ref["gX"]) <= 1e-5
     assert oracle.rel_fro(host(dW), ref["gW"]) <= 1e-5
     assert oracle.rel_fro(host(dB), ref["gB"]) <= 1e-5
+
+
+def test_conv2d_forward_backward_replay_from_a_cuda_graph(pkg, lib):
+    """The convolution takes its Col / gZ scratch from the stream-ordered allocator, which a stream capture records as
+    graph memory nodes: forward + backward captured once and replayed must give the eager results.  (The reference's
+    `*_into` path gets the same property from caller workspaces sized for ONE image, python/graph_executor_v2/ops/
+    conv2d.py:274-330; the batched kernels here need the whole batch's columns, so those buffers cannot serve.)"""
+    cv = pkg.ops_conv2d
+    g = torch.Generator(device="cuda").manual_seed(2)
+    X = torch.randn((8, 32, 28, 28), device="cuda", generator=g).bfloat16()
+    W = (torch.randn((64, 32, 3, 3), device="cuda", generator=g) / 17).bfloat16()
+    b = torch.randn(64, device="cuda", generator=g)
+    Y = torch.empty((8, 64, 28, 28), device="cuda", dtype=torch.bfloat16)
+    Z, dY = torch.empty_like(Y), torch.randn((8, 64, 28, 28), device="cuda", generator=g).bfloat16()
+    gX, gW, gB = torch.empty_like(X), torch.empty_like(W), torch.empty(64, device="cuda")
+
+    def step():
+        cv.forward_into(X, W, out=Y, B=b, with_bias=True, act="relu", save_z=True, Z_saved=Z, padding=(1, 1))
+        cv.backward_into(X, W, dY, Z, with_bias=True, act="relu", gX_out=gX, gW_out=gW, gB_out=gB, padding=(1, 1))
+
+    step()
+    torch.cuda.synchronize()
+    want = [t.clone() for t in (Y, Z, gX, gW, gB)]
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        step()                                   # the capture stream's own first run
+    st.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=st, capture_error_mode="thread_local"):
+        step()
+    for t in (Y, Z, gX, gW, gB):
+        t.zero_()
+    graph.replay()
+    graph.replay()
+    torch.cuda.synchronize()
+    for a, c in zip(want[:4], (Y, Z, gX, gW)):
+        assert torch.equal(a, c)
+    assert float((want[4] - gB).abs().max()) <= 1e-3
+    assert lib.ge2b_device_status(1) == 0
