@@ -53,7 +53,7 @@ class GradBucket:
         self.impl, self.why = "nccl", "forced" if force_nccl else ""
         self._handle = None
         buf = None
-        if not force_nccl and self.world >= 2:
+        if not force_nccl and self.world >= 2 and self.device.type == "cuda":
             try:
                 import torch.distributed._symmetric_memory as symm_mem
                 buf = symm_mem.empty((total,), dtype=torch.uint8, device=self.device)
@@ -101,6 +101,10 @@ class GradBucket:
         """Sum over the group, in place, asynchronous on `stream` (default: the current stream)."""
         last = len(self.regions) - 1 if last is None else last
         if self._handle is None:
+            if self.device.type != "cuda":                    # host ranks (tests of the bucket logic on CPU process groups)
+                for i in range(first, last + 1):
+                    torch.distributed.all_reduce(self.views[i], group=self.group)
+                return
             s = stream if isinstance(stream, torch.cuda.Stream) else None
             ctx = torch.cuda.stream(s) if s is not None else torch.cuda.stream(torch.cuda.current_stream(self.device))
             with ctx:

@@ -72,3 +72,64 @@ def test_reference_arm_under_torchrun_prints_one_line():
     d = json.loads(lines[0])
     assert d["impl"] == "reference" and d["unit"] == "TFLOP/s" and d["e2e"]["h2d_bytes_per_step"] == 0
     assert d["cpu_baseline"]["kind"] == "port" and d["value"] > 0
+
+
+def _bucket_worker(rank, world, port, out_dir):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, str(ROOT))
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    pkg = importlib.import_module("ai_framework-dev_b200")
+    # the gradient bucket on host ranks: same layout and exchange protocol, collective library instead of the NVLink kernel
+    b = pkg.data_parallel.GradBucket([((5, 7), torch.float32), ((3, 7), torch.float32), ((1, 7), torch.float32)],
+                                     dist.group.WORLD, "cpu")
+    assert b.impl == "nccl" and [o % 256 for o in b.offsets] == [0, 0, 0] and b.offsets[1] >= 5 * 7 * 4
+    for i, v in enumerate(b.views):
+        v.fill_(float((rank + 1) * (i + 1)))
+    b.all_reduce(1, 2)                                    # a sub-range: the first region must stay untouched
+    ok = bool((b.views[0] == rank + 1).all() and (b.views[1] == 2 * 3).all() and (b.views[2] == 3 * 3).all())
+    b.all_reduce()
+    ok = ok and bool((b.views[0] == 3).all() and (b.views[1] == 12).all())
+    (Path(out_dir) / f"bucket{rank}.txt").write_text("ok" if ok else "bad")
+    dist.destroy_process_group()
+
+
+def test_gradient_bucket_layout_and_exchange_on_host_ranks(tmp_path):
+    import torch.multiprocessing as mp
+    port = 29650 + os.getpid() % 300
+    mp.spawn(_bucket_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert all((tmp_path / f"bucket{r}.txt").read_text() == "ok" for r in range(2))
+
+
+def test_gradient_bucket_segments_merge_runs_of_one_dtype(pkg):
+    import torch
+    gb = pkg.data_parallel.GradBucket.__new__(pkg.data_parallel.GradBucket)
+    gb.regions = [((4, 64), torch.bfloat16), ((4, 64), torch.bfloat16), ((1, 64), torch.float32)]
+    gb.offsets, gb.data_bytes = [0, 512, 1024], 1280
+    assert gb._segments(0, 2) == [(0, 1024, pkg._lib.DT_BF16), (1024, 256, pkg._lib.DT_F32)]
+    assert gb._segments(1, 1) == [(512, 512, pkg._lib.DT_BF16)]
+    gb.regions.append(((4, 64), torch.bfloat16))
+    gb.offsets.append(1280)
+    gb.data_bytes = 1792
+    with pytest.raises(ValueError):
+        gb._segments(0, 3)                                # bf16, fp32, bf16: three runs
+
+
+def test_mlp_plan_configuration_is_validated_without_a_gpu(pkg, lib):
+    import ctypes as C
+    L = pkg._lib
+    cfg = L.MlpConfig()
+    plan = C.c_void_p()
+    assert lib.ge2b_mlp_plan_create(C.byref(plan), C.byref(cfg)) == -1           # no layers
+    cfg.n_layers, cfg.batch, cfg.dtype, cfg.lr, cfg.world = 2, 8, L.DT_BF16, 0.1, 1
+    cfg.dims[0], cfg.dims[1], cfg.dims[2] = 16, 32, 8
+    assert lib.ge2b_mlp_plan_grad_bytes(C.byref(cfg)) == (16 * 32 * 2 + 256 + 32 * 8 * 2 + 256) + lib.ge2b_allreduce_nvls_pad_bytes()
+    cfg.world, cfg.exchange = 2, 0
+    assert lib.ge2b_mlp_plan_create(C.byref(plan), C.byref(cfg)) == -1           # replicas without an exchange
+    cfg.exchange = 1
+    assert lib.ge2b_mlp_plan_create(C.byref(plan), C.byref(cfg)) == -1           # ... or without symmetric memory
+    cfg.world, cfg.lr = 1, 0.0
+    assert lib.ge2b_mlp_plan_create(C.byref(plan), C.byref(cfg)) == -1           # learning rate must be positive
+    a = L.AllreduceNvls()
+    assert lib.ge2b_allreduce_nvls(C.byref(a), None) == -1                       # no buffer, no ranks
