@@ -5,9 +5,9 @@
 // Replaces the reference's bwd_epilogue_kernel (backends/cuda/ops/gemm/kernels/regemm_backward.cu:92-130),
 // which issues one atomicAdd per element for the bias gradient.  Here each thread owns 8 consecutive
 // columns (one or two 16-byte accesses), a CTA covers 256 columns x 64 rows, sums in registers and shared
-// memory; the per-column bias gradient is then added over the row blocks in a fixed order by the last CTA of each
-// column block (run-to-run identical bits; one fp32 atomic per column per CTA only when no scratch is to be had, and
-// for per-row / scalar bias gradients).  The bias gradient is always formed
+// memory; the per-column bias gradient is then added over the row blocks in a fixed order (run-to-run identical
+// bits) by the GEMM launch that follows or by a small kernel (DbFinish); one fp32 atomic per column per CTA only when
+// no scratch is to be had, and for per-row / scalar bias gradients.  The bias gradient is always formed
 // from the fp32 value of gZ, before gZ is rounded to its storage type.  The buffer gZ is scratch memory
 // that the two backward GEMMs read afterwards.
 #include <cuda_bf16.h>
@@ -83,10 +83,8 @@ __device__ __forceinline__ void store8(void* base, long long off, int dt, bool v
 }
 
 // Per-column bias gradient of one CTA: `s` is this thread's column (c = ty * 32 + tx) summed over the CTA's rows.
-// With a partial buffer the sum over row blocks has a fixed order (run-to-run identical bits): the CTA stores its 256
-// column sums, counts itself into its column block's counter, and the last CTA of the column block adds all row
-// blocks -- thread (ty, tx) takes row blocks ty, ty + 8, ... of columns 8 tx .. 8 tx + 7 (two 16-byte loads per row
-// block, four row blocks in flight), then the eight ty partials are added in order.  Without one: one atomic per column.
+// With a partial buffer the CTA just stores its 256 column sums; the sum over row blocks is taken afterwards in a
+// fixed order (run-to-run identical bits) by DbFinish.  Without one: one atomic per column.
 __device__ __forceinline__ void finish_db_per_column(const BwdPrologueArgs& a, float s, float (&red)[kTY][kTileCols + 1]) {
   const int c = threadIdx.y * kTX + threadIdx.x;
   const int gc = blockIdx.x * kTileCols + c;
@@ -94,46 +92,25 @@ __device__ __forceinline__ void finish_db_per_column(const BwdPrologueArgs& a, f
     if (gc < a.N) atomicAdd(a.gBias + gc, s);
     return;
   }
-  __shared__ int is_last;
   a.db_partial[static_cast<long long>(blockIdx.y) * a.db_pitch + gc] = s;      // the pitch covers the padded columns
-  __threadfence();
-  __syncthreads();
-  if (c == 0) is_last = (atomicAdd(a.db_flags + blockIdx.x, 1) == static_cast<int>(gridDim.y) - 1) ? 1 : 0;
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  float acc[kColsPerThread];
+}
+
+// out[c] = sum over row blocks, ascending, eight loads in flight per thread
+__global__ void __launch_bounds__(256) db_finish_kernel(const DbFinish f) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= f.n) return;
+  const float* p = f.partial + c;
+  float acc = 0.f;
+  int b = 0;
+  for (; b + 8 <= f.blocks; b += 8) {
+    float v[8];
 #pragma unroll
-  for (int j = 0; j < kColsPerThread; ++j) acc[j] = 0.f;
-  const float* base = a.db_partial + blockIdx.x * kTileCols + threadIdx.x * kColsPerThread;
-  const int nrb = static_cast<int>(gridDim.y);
-  for (int rb0 = threadIdx.y; rb0 < nrb; rb0 += 4 * kTY) {
-    float4 v[4][2];
+    for (int i = 0; i < 8; ++i) v[i] = __ldcg(p + static_cast<long long>(b + i) * f.pitch);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int rb = rb0 + i * kTY;
-      if (rb < nrb) {
-        const float4* p = reinterpret_cast<const float4*>(base + static_cast<long long>(rb) * a.db_pitch);
-        v[i][0] = __ldcg(p); v[i][1] = __ldcg(p + 1);
-      } else {
-        v[i][0] = make_float4(0.f, 0.f, 0.f, 0.f); v[i][1] = v[i][0];
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      acc[0] += v[i][0].x; acc[1] += v[i][0].y; acc[2] += v[i][0].z; acc[3] += v[i][0].w;
-      acc[4] += v[i][1].x; acc[5] += v[i][1].y; acc[6] += v[i][1].z; acc[7] += v[i][1].w;
-    }
+    for (int i = 0; i < 8; ++i) acc += v[i];
   }
-  __syncthreads();                                   // everyone has read `red` for its own column sum
-#pragma unroll
-  for (int j = 0; j < kColsPerThread; ++j) red[threadIdx.y][threadIdx.x * kColsPerThread + j] = acc[j];
-  __syncthreads();
-  float total = 0.f;
-#pragma unroll
-  for (int y = 0; y < kTY; ++y) total += red[y][c];
-  if (gc < a.N) a.gBias[gc] = total;
-  if (c == 0) a.db_flags[blockIdx.x] = 0;            // leave the counter as it was found
+  for (; b < f.blocks; ++b) acc += __ldcg(p + static_cast<long long>(b) * f.pitch);
+  f.out[c] = acc;
 }
 
 // kRowSum: the bias gradient needs sums along rows (per-row or scalar bias); the common per-column case does not.
@@ -306,7 +283,14 @@ bool vec_ok(const void* p, long long ld, int dt) {
 
 }  // namespace
 
-cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s) {
+cudaError_t launch_db_finish(const DbFinish& f, cudaStream_t s) {
+  if (!f.partial || !f.out || f.n < 1 || f.blocks < 1) return cudaSuccess;
+  db_finish_kernel<<<(f.n + 255) / 256, 256, 0, s>>>(f);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s, DbFinish* pending) {
+  if (pending) *pending = DbFinish{};
   if (a.M < 1 || a.N < 1 || !a.gY || !a.Z || !a.gZ) return cudaErrorInvalidValue;
   ProParams pp{};
   pp.a = a;
@@ -316,16 +300,20 @@ cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s) {
   pp.gc_vec = vec_ok(a.gC, a.ldgC, a.gc_dtype);
   dim3 block(kTX, kTY), grid((a.N + kTileCols - 1) / kTileCols, (a.M + kTileRows - 1) / kTileRows);
   // Deterministic per-column bias gradient: partial sums per row block in stream scratch, when there is some.
+  // The partial sums go at the END of the stream scratch: its start belongs to the split-K partial tiles of the GEMM
+  // launch that carries the finish.
   auto want_partials = [&](unsigned row_blocks) {
-    pp.a.db_partial = nullptr; pp.a.db_flags = nullptr; pp.a.db_pitch = 0;
-    if (a.gBias == nullptr || a.bias_kind != kBiasPerN || row_blocks < 2) return cudaSuccess;
+    pp.a.db_partial = nullptr; pp.a.db_pitch = 0;
+    if (pending == nullptr || a.gBias == nullptr || a.bias_kind != kBiasPerN || row_blocks < 2) return cudaSuccess;
     float* ws = nullptr; int* flags = nullptr; size_t ws_bytes = 0, flag_bytes = 0; bool lent = false;
     if (!borrow_stream_scratch(s, &ws, &ws_bytes, &flags, &flag_bytes, &lent)) return cudaSuccess;   // atomics instead
     const long long pitch = static_cast<long long>(grid.x) * kTileCols;
-    if (static_cast<size_t>(row_blocks) * pitch * sizeof(float) > ws_bytes || grid.x * sizeof(int) > flag_bytes)
-      return cudaSuccess;
-    if (lent && cudaMemsetAsync(flags, 0, grid.x * sizeof(int), s) != cudaSuccess) return cudaErrorUnknown;
-    pp.a.db_partial = ws; pp.a.db_pitch = pitch; pp.a.db_flags = flags;
+    const size_t need = static_cast<size_t>(row_blocks) * pitch * sizeof(float);
+    if (need > ws_bytes / 4) return cudaSuccess;           // leave at least three quarters to the GEMMs
+    float* part = ws + (ws_bytes - need) / sizeof(float);
+    pp.a.db_partial = part; pp.a.db_pitch = pitch;
+    pending->partial = part; pending->pitch = pitch; pending->blocks = static_cast<int>(row_blocks);
+    pending->out = a.gBias; pending->n = a.N;
     return cudaSuccess;
   };
   // gZ stored in 16 bits: the exp-based derivative forms are accurate enough (see epilogue_math.cuh)

@@ -138,6 +138,7 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
   const size_t need = static_cast<size_t>(b.M) * static_cast<size_t>(b.N) * esz;
 
   if (b.reuse_gz && !b.scratch) return kBadArgs;
+  DbFinish db_pending;          // second half of a deterministic bias gradient, owed after the prologue
   void* gZ = b.scratch;
   bool owned = false;
   if (gZ) {
@@ -179,7 +180,7 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
   pa.act = b.act; pa.leaky = b.leaky;
   {
     NvtxRange epi_range("bwd.epilogue");
-    if (launch_bwd_prologue(pa, s) != cudaSuccess) return finish(kCudaError);
+    if (launch_bwd_prologue(pa, s, &db_pending) != cudaSuccess) return finish(kCudaError);
   }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   }
@@ -235,6 +236,20 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
     gb.b_mn = true; gb.B = gZ;  gb.ldb = b.N;
     if (use_x3) { gb.A = Xb; gb.A_small = Xs; gb.lda = b.K; gb.B = gZb; gb.B_small = gZs; }
     gb.epi = plain_epilogue(b.gB, b.ldgB);
+  }
+  // The bias gradient's finish rides with the first GEMM launch that goes to the tensor-core kernel; where none does
+  // (exact fp32 kernel, unaligned operands, no GEMM asked for) it runs as its own small kernel.
+  if (db_pending.partial != nullptr) {
+    auto takes_tc = [](const GemmProblem& g) {
+      const bool want = (g.in_dtype != kF32) || g.math == 1 || (g.math == 2 && g.A_small && g.B_small);
+      return want && gemm_tc_supported(g, nullptr);
+    };
+    if (b.gA && takes_tc(ga)) ga.db = db_pending;
+    else if (b.gB && takes_tc(gb)) gb.db = db_pending;
+    else {
+      if (launch_db_finish(db_pending, s) != cudaSuccess) return finish(kCudaError);
+      g_launches.fetch_add(1, std::memory_order_relaxed);
+    }
   }
   // Both gradients wanted on the tensor-core path: one launch walks the tiles of both (see launch_gemm_tc_dual).
   if (b.gA && b.gB && ((b.dtype != kF32) || gemm_math == 1)) {

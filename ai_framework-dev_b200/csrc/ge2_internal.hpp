@@ -44,6 +44,14 @@ enum : int {
 
 __host__ __device__ inline int dtype_bytes(int dt) { return dt == kF32 ? 4 : 2; }
 
+// The second half of a deterministic per-column bias gradient: out[c] = sum over row blocks (ascending) of
+// partial[block * pitch + c].  It rides along with the GEMM launch that follows the prologue (idle lanes of the
+// producer warp do it while the tensor pipe works) or, where no such launch follows, runs as a small kernel.
+struct DbFinish {
+  const float* partial = nullptr; long long pitch = 0; int blocks = 0;
+  float* out = nullptr; int n = 0;
+};
+
 // Everything the fused epilogue needs.  Pointers may be null where stated.
 struct EpilogueArgs {
   void*        D;    long long ldd, strideD;      // output, row-major [M,N] per batch slice
@@ -78,6 +86,7 @@ struct GemmProblem {
   // accumulator: every product is exact in TF32 arithmetic and only small.small (2^-22 relative) is dropped.
   const void* A_small = nullptr;
   const void* B_small = nullptr;
+  DbFinish db;                                    // tensor-core path only: bias-gradient finish carried by this launch
   // The batch index joins the reduction: D = act(alpha * sum_b A[b].B[b] + ...), one output matrix.  Tensor-core
   // path only (used by the convolution's weight gradient, which sums over the images of a batch).
   bool reduce_batch = false;
@@ -93,10 +102,11 @@ struct BwdPrologueArgs {
   float* gBias; int bias_kind;                    // fp32, zeroed by the launcher before the kernel
   int act; float leaky;
   // Per-column bias gradient without atomics (filled in by launch_bwd_prologue when stream scratch is to be had):
-  // every CTA leaves the column sums of its rows in db_partial[row block][column], counts itself into
-  // db_flags[column block], and the CTA that arrives last adds the row blocks in a fixed order.  Null: fp32 atomics.
-  float* db_partial = nullptr; long long db_pitch = 0; int* db_flags = nullptr;
+  // every CTA leaves the column sums of its rows in db_partial[row block][column]; the row blocks are added in a
+  // fixed order afterwards (see DbFinish).  Null: fp32 atomics.
+  float* db_partial = nullptr; long long db_pitch = 0;
 };
+
 
 // ---- launchers (each returns cudaSuccess or the launch error) ----
 cudaError_t launch_gemm_simt(const GemmProblem& g, cudaStream_t s);      // exact fp32-accumulate FMA path (any dtype, any ld)
@@ -106,7 +116,11 @@ cudaError_t launch_gemm_tc(const GemmProblem& g, cudaStream_t s);        // TMA 
 // combined list's last wave is partly filled).  Returns cudaErrorNotSupported when the pair does not qualify; the
 // caller then launches the two problems one after the other.
 cudaError_t launch_gemm_tc_dual(const GemmProblem& dx, const GemmProblem& dw, cudaStream_t s);
-cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s);
+// `pending` (may be null): receives the finish of a deterministic per-column bias gradient that the caller must
+// attach to the next tensor-core GEMM launch on the stream or run with launch_db_finish; without it (or when no
+// scratch is to be had) the kernel adds with atomics and nothing is pending.
+cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s, DbFinish* pending = nullptr);
+cudaError_t launch_db_finish(const DbFinish& f, cudaStream_t s);
 // big = src with the 13 low mantissa bits cleared (exactly representable in TF32), small = src - big (exact in fp32);
 // src is rows x cols with pitch ld_src, big and small are written with pitch cols.
 cudaError_t launch_split_tf32(const float* src, long long ld_src, float* big, float* small, long long rows, long long cols,

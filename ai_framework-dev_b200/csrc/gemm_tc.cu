@@ -216,7 +216,7 @@ using namespace tc;
 // addresses and shapes only, so an entry stays valid even if the buffers behind the pointers are freed and given out
 // again: the key then simply matches a problem with the same geometry at the same addresses.
 struct PlanKey {
-  static constexpr int kWords = 80;
+  static constexpr int kWords = 96;
   unsigned long long w[kWords];
   int n = 0;
   void add(unsigned long long v) { if (n < kWords) w[n++] = v; }
@@ -245,6 +245,8 @@ void key_problem(PlanKey& k, const GemmProblem& g) {
   k.add_ptr(g.epi.C); k.add(g.epi.ldc); k.add(g.epi.strideC);
   k.add_ptr(g.epi.bias);
   k.add_ptr(g.A_small); k.add_ptr(g.B_small);
+  k.add_ptr(g.db.partial); k.add_ptr(g.db.out); k.add(g.db.pitch);
+  k.add((static_cast<unsigned long long>(static_cast<unsigned>(g.db.blocks)) << 32) | static_cast<unsigned>(g.db.n));
   k.add_f(g.epi.leaky); k.add_f(g.epi.alpha); k.add_f(g.epi.beta);
 }
 
@@ -342,6 +344,7 @@ void fill_common(const GemmProblem& g, tc::TcParams& p) {
   p.z_vec = tensor_vec_ok(g.epi.Z, g.epi.ldz, g.epi.strideZ, g.epi.z_dtype);
   p.c_vec = tensor_vec_ok(g.epi.C, g.epi.ldc, g.epi.strideC, g.epi.d_dtype);
   p.bias_vec = g.epi.bias && aligned16(g.epi.bias);
+  p.db = g.db;
   p.status = device_status_ptr();
 }
 

@@ -70,6 +70,7 @@ struct TcParams {
   // into two 128-column halves instead, so that twice as many pairs finish the launch together and nothing is
   // exchanged.  Item main_tiles + i is half (i & 1) of tail tile i / 2; `split` is 2 and `idesc_half` describes the
   // 256 x 128 MMA.
+  DbFinish db;              // bias-gradient finish carried by this launch (partial == null: none)
   int main_tiles, tail_tiles, split;
   uint32_t idesc_half;
   float* ws;
@@ -541,6 +542,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         produce(BoolC<kAMN>{}, BoolC<kBMN>{}, p, &tmA, &tmB, &tmBh, get_work<kSplit, kNarrow>(p, item));
       }
+    } else if (p.db.partial != nullptr) {
+      // The other 31 lanes of the producer warp have nothing to do: they finish the bias gradient the prologue kernel
+      // left as per-row-block column sums (out[c] = sum over row blocks in ascending order: the same bits every run),
+      // while lane 0 feeds the ring and the tensor pipe works.
+      const int stride = static_cast<int>(gridDim.x) * 31;
+      for (int c = static_cast<int>(blockIdx.x) * 31 + lane - 1; c < p.db.n; c += stride) {
+        const float* src = p.db.partial + c;
+        float acc = 0.f;
+        int b = 0;
+        for (; b + 8 <= p.db.blocks; b += 8) {
+          float v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] = __ldcg(src + static_cast<long long>(b + i) * p.db.pitch);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc += v[i];
+        }
+        for (; b < p.db.blocks; ++b) acc += __ldcg(src + static_cast<long long>(b) * p.db.pitch);
+        p.db.out[c] = acc;
+      }
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -975,7 +995,11 @@ cudaError_t prepare_cfg(const GemmProblem& g, TcParams& p, cudaStream_t s, Prepa
     if (sp >= 2) {
       SplitScratch sc;
       if (split_scratch(s, &sc)) {
-        while (sp >= 2 && static_cast<size_t>(sp) * rem * kTileM * kBlockN * sizeof(float) > sc.ws_bytes) --sp;
+        size_t ws_bytes = sc.ws_bytes;              // bias-gradient partials of this launch sit at the end of the scratch
+        const char* dbp = reinterpret_cast<const char*>(g.db.partial);
+        if (dbp >= reinterpret_cast<const char*>(sc.ws) && dbp < reinterpret_cast<const char*>(sc.ws) + sc.ws_bytes)
+          ws_bytes = static_cast<size_t>(dbp - reinterpret_cast<const char*>(sc.ws));
+        while (sp >= 2 && static_cast<size_t>(sp) * rem * kTileM * kBlockN * sizeof(float) > ws_bytes) --sp;
         if (sp >= 2) {
           p.main_tiles = static_cast<int>(tiles - rem);
           p.tail_tiles = static_cast<int>(rem);
