@@ -272,13 +272,9 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int limit = min(p.N - 1 - key0, p.causal ? row - key0 : kBlockKV);      // last live column of this row
       float m_blk;
       if (form != 2) {
-        // pass 1: four independent running maxima per chunk
+        // pass 1: four independent running maxima; two 32-column TMEM loads in flight at a time
         float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(s_tmem + c * 32, r);
-          ptx::tmem_wait_ld();
+        auto max_chunk = [&](int c, const uint32_t (&r)[32]) {
           if (form == 0) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(r[i]));
@@ -287,6 +283,17 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             for (int i = 0; i < 32; ++i)
               mx[i & 3] = fmaxf(mx[i & 3], (c * 32 + i <= limit) ? __uint_as_float(r[i]) : -CUDART_INF_F);
           }
+        };
+        {
+          uint32_t ra[32], rb[32];
+          ptx::tmem_ld_32x32(s_tmem, ra);
+          ptx::tmem_ld_32x32(s_tmem + 32, rb);
+          ptx::tmem_wait_ld();
+          max_chunk(0, ra); max_chunk(1, rb);
+          ptx::tmem_ld_32x32(s_tmem + 64, ra);
+          ptx::tmem_ld_32x32(s_tmem + 96, rb);
+          ptx::tmem_wait_ld();
+          max_chunk(2, ra); max_chunk(3, rb);
         }
         m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;     // (-inf stays -inf)
       } else {
@@ -331,11 +338,7 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // index XOR (row & 7)) and the row sum (fp32 values, four independent partial sums)
       float ls[4] = {0.f, 0.f, 0.f, 0.f};
       const float neg_m = -m_use;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(s_tmem + c * 32, r);
-        ptx::tmem_wait_ld();
+      auto exp_chunk = [&](int c, const uint32_t (&r)[32]) {
         uint32_t pk[16];
         if (form == 0) {
 #pragma unroll
@@ -374,6 +377,22 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int k = 0; k < 4; ++k)
           *reinterpret_cast<uint4*>(dst + ((((c & 1) * 4 + k) ^ swz) * 16)) =
               make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
+      };
+      {
+        // the TMEM load of chunk c + 1 is in flight while chunk c is turned into probabilities
+        uint32_t ra[32], rb[32];
+        ptx::tmem_ld_32x32(s_tmem, ra);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld_32x32(s_tmem + 32, rb);
+        exp_chunk(0, ra);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld_32x32(s_tmem + 64, ra);
+        exp_chunk(1, rb);
+        ptx::tmem_wait_ld();
+        ptx::tmem_ld_32x32(s_tmem + 96, rb);
+        exp_chunk(2, ra);
+        ptx::tmem_wait_ld();
+        exp_chunk(3, rb);
       }
       const float l_blk = (ls[0] + ls[1]) + (ls[2] + ls[3]);
       l_run = l_run * alpha + l_blk;
