@@ -289,7 +289,7 @@ cudaError_t launch_db_finish(const DbFinish& f, cudaStream_t s) {
   return cudaGetLastError();
 }
 
-cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s, DbFinish* pending) {
+cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s, DbFinish* pending, bool zero_gbias) {
   if (pending) *pending = DbFinish{};
   if (a.M < 1 || a.N < 1 || !a.gY || !a.Z || !a.gZ) return cudaErrorInvalidValue;
   ProParams pp{};
@@ -316,6 +316,11 @@ cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s, DbFini
     pending->out = a.gBias; pending->n = a.N;
     return cudaSuccess;
   };
+  auto zero_if_atomic = [&]() {
+    if (!zero_gbias || a.gBias == nullptr || a.bias_kind == kBiasNone || pp.a.db_partial != nullptr) return cudaSuccess;
+    const size_t n = a.bias_kind == kBiasScalar ? 1 : (a.bias_kind == kBiasPerM ? a.M : a.N);
+    return cudaMemsetAsync(a.gBias, 0, n * sizeof(float), s);
+  };
   // gZ stored in 16 bits: the exp-based derivative forms are accurate enough (see epilogue_math.cuh)
   // the common 16-bit call takes the specialised kernel
   const bool same16 = a.gy_dtype != kF32 && a.gy_dtype == a.z_dtype && a.gy_dtype == a.gz_dtype;
@@ -324,7 +329,7 @@ cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s, DbFini
     if (a.gBias != nullptr && a.bias_kind == kBiasNone) pp.a.gBias = nullptr;
     const bool bf = a.gy_dtype == kBF16;
     const dim3 fgrid((a.N + kTileCols - 1) / kTileCols, (a.M + kFastRows - 1) / kFastRows);
-    if (want_partials(fgrid.y) != cudaSuccess) return cudaErrorUnknown;
+    if (want_partials(fgrid.y) != cudaSuccess || zero_if_atomic() != cudaSuccess) return cudaErrorUnknown;
 #define GE2B_LAUNCH_FAST(ACT_)                                                                \
     do {                                                                                      \
       if (bf) bwd_prologue_fast_kernel<ACT_, true><<<fgrid, block, 0, s>>>(pp);               \
@@ -341,7 +346,7 @@ cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s, DbFini
 #undef GE2B_LAUNCH_FAST
     return cudaGetLastError();
   }
-  if (want_partials(grid.y) != cudaSuccess) return cudaErrorUnknown;
+  if (want_partials(grid.y) != cudaSuccess || zero_if_atomic() != cudaSuccess) return cudaErrorUnknown;
   const bool fast = a.gz_dtype != kF32;
   const bool rowsum = a.gBias != nullptr && (a.bias_kind == kBiasPerM || a.bias_kind == kBiasScalar);
 #define GE2B_LAUNCH_PRO(ACT_)                                                                   \

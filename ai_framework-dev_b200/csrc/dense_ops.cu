@@ -164,11 +164,7 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
       return finish(kCudaError);
     }
   }
-  const bool want_bias = b.gBias && b.bias_kind != kBiasNone;
-  if (want_bias) {
-    const size_t n = b.bias_kind == kBiasScalar ? 1 : (b.bias_kind == kBiasPerM ? b.M : b.N);
-    if (cudaMemsetAsync(b.gBias, 0, n * sizeof(float), s) != cudaSuccess) return finish(kCudaError);
-  }
+  const bool want_bias = b.gBias && b.bias_kind != kBiasNone;   // (zeroed by the prologue's launcher where it adds atomically)
 
   BwdPrologueArgs pa{};
   pa.M = b.M; pa.N = b.N;
@@ -180,7 +176,7 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
   pa.act = b.act; pa.leaky = b.leaky;
   {
     NvtxRange epi_range("bwd.epilogue");
-    if (launch_bwd_prologue(pa, s, &db_pending) != cudaSuccess) return finish(kCudaError);
+    if (launch_bwd_prologue(pa, s, &db_pending, true) != cudaSuccess) return finish(kCudaError);
   }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   }
@@ -204,17 +200,20 @@ int dense_backward(const DenseBackward& b, cudaStream_t s) {
   bool use_x3 = false;
   if (want_x3 && x3.p) {
     unsigned char* q = static_cast<unsigned char*>(x3.p);
+    SplitItem items[3];
+    int n_items = 0;
     gZb = reinterpret_cast<float*>(q); gZs = reinterpret_cast<float*>(q + mn); q += 2 * mn;
-    use_x3 = launch_split_tf32(static_cast<const float*>(gZ), b.N, gZb, gZs, b.M, b.N, s) == cudaSuccess;
-    if (use_x3 && b.gA) {
+    items[n_items++] = SplitItem{static_cast<const float*>(gZ), b.N, gZb, gZs, b.M, b.N};
+    if (b.gA) {
       Wb = reinterpret_cast<float*>(q); Ws = reinterpret_cast<float*>(q + kn); q += 2 * kn;
-      use_x3 = launch_split_tf32(static_cast<const float*>(b.B), b.ldb, Wb, Ws, b.K, b.N, s) == cudaSuccess;
+      items[n_items++] = SplitItem{static_cast<const float*>(b.B), b.ldb, Wb, Ws, b.K, b.N};
     }
-    if (use_x3 && b.gB) {
+    if (b.gB) {
       Xb = reinterpret_cast<float*>(q); Xs = reinterpret_cast<float*>(q + mk);
-      use_x3 = launch_split_tf32(static_cast<const float*>(b.A), b.lda, Xb, Xs, b.M, b.K, s) == cudaSuccess;
+      items[n_items++] = SplitItem{static_cast<const float*>(b.A), b.lda, Xb, Xs, b.M, b.K};
     }
-    if (use_x3) g_launches.fetch_add(1 + (b.gA ? 1 : 0) + (b.gB ? 1 : 0), std::memory_order_relaxed);
+    use_x3 = launch_split_tf32_multi(items, n_items, s) == cudaSuccess;      // one launch for all three
+    if (use_x3) g_launches.fetch_add(1, std::memory_order_relaxed);
   }
   const int gemm_math = use_x3 ? 2 : (b.math == 2 ? 0 : b.math);
 

@@ -119,12 +119,18 @@ cudaError_t launch_gemm_tc_dual(const GemmProblem& dx, const GemmProblem& dw, cu
 // `pending` (may be null): receives the finish of a deterministic per-column bias gradient that the caller must
 // attach to the next tensor-core GEMM launch on the stream or run with launch_db_finish; without it (or when no
 // scratch is to be had) the kernel adds with atomics and nothing is pending.
-cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s, DbFinish* pending = nullptr);
+// zero_gbias: the launcher zeroes gBias on the stream first where the kernel adds into it with atomics (it does not
+// when the deterministic form overwrites it).
+cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s, DbFinish* pending = nullptr,
+                                bool zero_gbias = false);
 cudaError_t launch_db_finish(const DbFinish& f, cudaStream_t s);
 // big = src with the 13 low mantissa bits cleared (exactly representable in TF32), small = src - big (exact in fp32);
 // src is rows x cols with pitch ld_src, big and small are written with pitch cols.
 cudaError_t launch_split_tf32(const float* src, long long ld_src, float* big, float* small, long long rows, long long cols,
                               cudaStream_t s);
+// up to three such splits in one launch (a backward splits gZ, W and X)
+struct SplitItem { const float* src; long long ld; float* big; float* small; long long rows, cols; };
+cudaError_t launch_split_tf32_multi(const SplitItem* items, int n, cudaStream_t s);
 
 // Reads (and optionally clears) the device status word of the current device. Synchronises.
 int  device_status_word(bool clear);

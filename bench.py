@@ -793,18 +793,67 @@ def run_sweep(args):
         print(json.dumps(line), flush=True)
 
     quick = args.sweep_quick
-    for n in (1024, 2048, 4096, 8192, 16384):
+    only = args.sweep_only
+
+    def small_points():
+        """small / skinny / MLP-layer shapes from a graph replay: full epilogue, plain epilogue, backward"""
+        for (Mx, Nx, Kx) in [(1024, 1024, 1024), (2048, 2048, 2048), (16, 8192, 8192), (32, 8192, 8192), (128, 8192, 8192),
+                             (1024, 4096, 1024), (1024, 4096, 4096), (1024, 1024, 4096)]:
+            X = torch.randn(Mx, Kx, device="cuda").bfloat16()
+            W = (torch.randn(Kx, Nx, device="cuda") / Kx ** 0.5).bfloat16()
+            b = torch.randn(Nx, device="cuda")
+            Y = torch.empty(Mx, Nx, device="cuda", dtype=torch.bfloat16)
+            Z, dY, work = torch.empty_like(Y), torch.randn(Mx, Nx, device="cuda").bfloat16(), torch.empty_like(Y)
+            dX, dW, db = torch.empty_like(X), torch.empty_like(W), torch.empty(1, Nx, device="cuda")
+            tf = timeit_graph(lambda: og.forward_into(X, W, out=Y, bias=b, with_bias=True, act="gelu", save_z=True, z_out=Z), 7)
+            tp = timeit_graph(lambda: og.forward_into(X, W, out=Y), 7)
+            tb = timeit_graph(lambda: og.backward_into(X, W, dY, Z, act="gelu", with_bias=True, gA_out=dX, gB_out=dW,
+                                                       gBias_out=db, work_dZ=work), 7)
+            print(json.dumps({"sweep": "small", "M": Mx, "N": Nx, "K": Kx, "dtype": "bf16", "fwd_us": round(tf * 1e3, 1),
+                              "fwd_plain_us": round(tp * 1e3, 1), "bwd_us": round(tb * 1e3, 1),
+                              "fwd_tflops": round(2.0 * Mx * Nx * Kx / tf / 1e9, 1)}), flush=True)
+
+    def fp32_mode_points():
+        """fp32 tensors under the three math modes (eager): exact chain, compensated tensor cores, TF32"""
+        for (Mx, Nx, Kx) in [(256, 512, 512), (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096)]:
+            X = torch.randn(Mx, Kx, device="cuda")
+            W = torch.randn(Kx, Nx, device="cuda") / Kx ** 0.5
+            b = torch.randn(Nx, device="cuda")
+            Y = torch.empty(Mx, Nx, device="cuda")
+            Z, dY, work = torch.empty_like(Y), torch.randn(Mx, Nx, device="cuda"), torch.empty_like(Y)
+            dX, dW, db = torch.empty_like(X), torch.empty_like(W), torch.empty(1, Nx, device="cuda")
+            rec = {"sweep": "fp32_modes", "M": Mx, "N": Nx, "K": Kx}
+            for m in ("fp32", "fp32x3", "tf32"):
+                rec["fwd_ms_" + m] = round(timeit(lambda: og.forward_into(X, W, out=Y, bias=b, with_bias=True, act="relu",
+                                                                          save_z=True, z_out=Z, math=m), 5, reps=4), 4)
+                rec["bwd_ms_" + m] = round(timeit(lambda: og.backward_into(X, W, dY, Z, act="relu", with_bias=True, gA_out=dX,
+                                                                           gB_out=dW, gBias_out=db, work_dZ=work, math=m),
+                                                  5, reps=4), 4)
+            print(json.dumps(rec), flush=True)
+
+    if only == "small":
+        small_points()
+        assert lib.ge2b_device_status(0) == 0
+        return
+    if only == "fp32":
+        fp32_mode_points()
+        assert lib.ge2b_device_status(0) == 0
+        return
+    for n in (() if only == "attention" else (1024, 2048, 4096, 8192, 16384)):
         for dtype, math in (("bf16", "fp32"), ("fp32", "tf32")):
             for act in (("gelu",) if quick else ("none", "relu", "gelu", "sigmoid")):
                 dense_point(n, n, n, dtype, math, act, 5 if n <= 8192 else 2)
-    for m in (16, 32, 64, 128):
-        for dtype, math in (("bf16", "fp32"), ("fp32", "tf32")):
-            dense_point(m, 8192, 8192, dtype, math, "gelu", 7)
-    for n in (256, 1024, 2048, 4096):          # the parity path and the reference's own kernels on the same box
-        dense_point(n, n if n > 256 else 512, n if n > 256 else 512, "fp32", "fp32", "relu", 3, with_ref=True)
-    if quick:
-        assert lib.ge2b_device_status(0) == 0
-        return
+    if only != "attention":
+        for m in (16, 32, 64, 128):
+            for dtype, math in (("bf16", "fp32"), ("fp32", "tf32")):
+                dense_point(m, 8192, 8192, dtype, math, "gelu", 7)
+        for n in (256, 1024, 2048, 4096):          # the parity path and the reference's own kernels on the same box
+            dense_point(n, n if n > 256 else 512, n if n > 256 else 512, "fp32", "fp32", "relu", 3, with_ref=True)
+        if quick:
+            assert lib.ge2b_device_status(0) == 0
+            return
+        small_points()
+        fp32_mode_points()
 
     # batched attention GEMMs: B*H = 128 slices, L = 2048, d = 128, bf16, fp32 accumulate
     Bn, H, L, d = 8, 16, 2048, 128
@@ -815,18 +864,39 @@ def run_sweep(args):
     t_qk = timeit(lambda: og.forward_batched(Q, Kt, out=S, trans_b=True, alpha=1.0 / d ** 0.5), 7)
     t_pv = timeit(lambda: og.forward_batched(P, V, out=O), 7)
     flop = 2.0 * Bn * H * L * L * d
-    t_fa = timeit(lambda: pkg.ops_sdpa.forward(Q, Kt, V, out=O), 7)
-    t_fac = timeit(lambda: pkg.ops_sdpa.forward(Q, Kt, V, out=O, causal=True), 7)
-    print(json.dumps({"sweep": "fused_attention", "B": Bn, "H": H, "L": L, "d": d, "dtype": "bf16",
-                      "fwd_ms": round(t_fa, 4), "fwd_tflops": round(2 * flop / t_fa / 1e9, 1),
-                      "causal_fwd_ms": round(t_fac, 4), "causal_fwd_tflops": round(flop / t_fac / 1e9, 1),
-                      "note": "S = scale.Q.K^T, softmax and P.V in one launch: no S / P traffic"}), flush=True)
+    for (b_, h_, l_, d_) in ((Bn, H, L, d), (Bn, H, L, 64), (2, 8, 4096, 128)):
+        q_, k_, v_ = (torch.randn((b_, h_, l_, d_), device="cuda").bfloat16() for _ in range(3))
+        o_ = torch.empty_like(q_)
+        t_fa = timeit(lambda: pkg.ops_sdpa.forward(q_, k_, v_, out=o_), 7)
+        t_fac = timeit(lambda: pkg.ops_sdpa.forward(q_, k_, v_, out=o_, causal=True), 7)
+        fl = 4.0 * b_ * h_ * l_ * l_ * d_
+        rec = {"sweep": "fused_attention", "B": b_, "H": h_, "L": l_, "d": d_, "dtype": "bf16",
+               "fwd_ms": round(t_fa, 4), "fwd_tflops": round(fl / t_fa / 1e9, 1),
+               "causal_fwd_ms": round(t_fac, 4), "causal_fwd_tflops": round(fl / 2 / t_fac / 1e9, 1),
+               "note": "S = scale.Q.K^T, softmax and P.V in one launch: no S / P traffic"}
+        try:       # the vendor's fused attention through torch, for context
+            rec["torch_sdpa_ms"] = round(timeit(lambda: torch.nn.functional.scaled_dot_product_attention(q_, k_, v_), 7), 4)
+        except Exception as e:  # noqa: BLE001
+            rec["torch_sdpa_ms"] = None
+        if (b_, h_, l_, d_) == (Bn, H, L, d):
+            s_ = torch.empty((b_, h_, l_, l_), device="cuda", dtype=torch.bfloat16)
+            p_ = torch.empty_like(s_)
+
+            def unfused():
+                og.forward_batched(q_, k_, out=s_, trans_b=True, alpha=1.0 / d_ ** 0.5)
+                torch.softmax(s_, dim=-1, out=p_)
+                og.forward_batched(p_, v_, out=o_)
+            rec["two_gemms_and_softmax_through_hbm_ms"] = round(timeit(unfused, 3, reps=2), 4)
+            del s_, p_
+        print(json.dumps(rec), flush=True)
     print(json.dumps({"sweep": "batched_attention", "B": Bn, "H": H, "L": L, "d": d, "dtype": "bf16",
                       "qk_ms": round(t_qk, 4), "qk_tflops": round(flop / t_qk / 1e9, 1),
                       "qk_GBs": round((2 * Q.numel() * 2 + S.numel() * 2) / t_qk / 1e6, 1),
                       "pv_ms": round(t_pv, 4), "pv_tflops": round(flop / t_pv / 1e9, 1),
                       "pv_GBs": round((P.numel() * 2 + 2 * V.numel() * 2) / t_pv / 1e6, 1)}), flush=True)
     assert lib.ge2b_device_status(0) == 0
+    if only == "attention":
+        return
     run_conv_points(pkg, lib, timeit)
 
 
@@ -892,6 +962,8 @@ def main():
     ap.add_argument("--skip-target", action="store_true", help="omit the M=N=K=8192 block")
     ap.add_argument("--sweep", action="store_true", help="print the shape sweep (one JSON line per point) and exit")
     ap.add_argument("--sweep-quick", action="store_true", help="with --sweep: GELU only, dense points only")
+    ap.add_argument("--sweep-only", default="", choices=["", "small", "fp32", "attention"],
+                    help="with --sweep: one section (small / skinny shapes from a graph replay; fp32 math modes; attention)")
     args = ap.parse_args()
     if args.sweep:
         run_sweep(args)
