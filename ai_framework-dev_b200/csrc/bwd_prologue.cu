@@ -15,6 +15,7 @@
 
 #include "epilogue_math.cuh"
 #include "ge2_internal.hpp"
+#include "sm100_ptx.cuh"
 
 namespace ge2b {
 namespace {
@@ -117,6 +118,8 @@ __global__ void __launch_bounds__(256) db_finish_kernel(const DbFinish f) {
 template <int ACT, bool kFast, bool kRowSum>
 __global__ void __launch_bounds__(kTX * kTY)
 bwd_prologue_kernel(const ProParams pp) {
+  ptx::griddep_launch();
+  ptx::griddep_wait();          // Z comes from the kernel before this one
   const BwdPrologueArgs& a = pp.a;
   __shared__ float red[kTY][kTileCols + 1];
 
@@ -205,6 +208,8 @@ bwd_prologue_kernel(const ProParams pp) {
 template <int ACT, bool kBf16>
 __global__ void __launch_bounds__(kTX * kTY)
 bwd_prologue_fast_kernel(const ProParams pp) {
+  ptx::griddep_launch();
+  ptx::griddep_wait();          // Z comes from the kernel before this one
   const BwdPrologueArgs& a = pp.a;
   __shared__ float red[kTY][kTileCols + 1];
   const int col0 = blockIdx.x * kTileCols + threadIdx.x * kColsPerThread;
@@ -276,6 +281,19 @@ bwd_prologue_fast_kernel(const ProParams pp) {
   finish_db_per_column(a, s, red);
 }
 
+// Launch that may start while the kernel before it in the stream is finishing (the kernel waits at griddep_wait()).
+template <typename K>
+void launch_early(K kernel, dim3 grid, dim3 block, cudaStream_t s, const ProParams& pp) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = 0; cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = early_start_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, pp);
+}
+
 bool vec_ok(const void* p, long long ld, int dt) {
   if (!p) return false;
   return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && (ld * dtype_bytes(dt)) % 16 == 0;
@@ -332,8 +350,8 @@ cudaError_t launch_bwd_prologue(const BwdPrologueArgs& a, cudaStream_t s, DbFini
     if (want_partials(fgrid.y) != cudaSuccess || zero_if_atomic() != cudaSuccess) return cudaErrorUnknown;
 #define GE2B_LAUNCH_FAST(ACT_)                                                                \
     do {                                                                                      \
-      if (bf) bwd_prologue_fast_kernel<ACT_, true><<<fgrid, block, 0, s>>>(pp);               \
-      else    bwd_prologue_fast_kernel<ACT_, false><<<fgrid, block, 0, s>>>(pp);              \
+      if (bf) launch_early(bwd_prologue_fast_kernel<ACT_, true>, fgrid, block, s, pp);        \
+      else    launch_early(bwd_prologue_fast_kernel<ACT_, false>, fgrid, block, s, pp);       \
     } while (0)
     switch (a.act) {
       case kActReLU:    GE2B_LAUNCH_FAST(kActReLU); break;

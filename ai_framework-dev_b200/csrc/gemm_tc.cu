@@ -169,6 +169,12 @@ void release_library_scratch() {
   plan_cache_generation().fetch_add(1, std::memory_order_relaxed);   // cached launches may point into freed scratch
 }
 
+// GE2B_PDL=0 switches programmatic dependent launch off (every launch then waits for the whole kernel before it).
+bool early_start_enabled() {
+  static const bool on = [] { const char* e = getenv("GE2B_PDL"); return !(e && atoi(e) == 0); }();
+  return on;
+}
+
 ScratchLease& scratch_lease() {
   thread_local ScratchLease lease;
   return lease;
@@ -188,13 +194,18 @@ cudaError_t run_prepared(const PreparedLaunch& L, cudaStream_t s) {
   cfg.blockDim = dim3(kNumThreads, 1, 1);
   cfg.dynamicSmemBytes = static_cast<size_t>(L.smem);
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = static_cast<unsigned>(L.cluster);
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (early_start_enabled() && L.flag_bytes == 0) {     // (a memset before the launch is an ordinary dependency)
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
+  }
   void* args[] = {const_cast<CUtensorMap*>(&L.tmA), const_cast<CUtensorMap*>(&L.tmB), const_cast<CUtensorMap*>(&L.tmBh),
                   const_cast<CUtensorMap*>(&L.tmD), const_cast<CUtensorMap*>(&L.tmZ), const_cast<TcParams*>(&L.p),
                   const_cast<DualParams*>(&L.d2)};

@@ -463,6 +463,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if constexpr (kCG == 2) ptx::cluster_sync_all();   // the peer's barriers exist before anything signals them
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
+  // Everything above touched only this CTA's shared memory and TMEM; from here on global memory is read and written,
+  // so a launch that was allowed to start early waits here for the kernel before it (see sm100_ptx.cuh).
+  ptx::griddep_launch();
+  ptx::griddep_wait();
 
   const long long items1 = static_cast<long long>(p.main_tiles) + static_cast<long long>(p.tail_tiles) * p.split;
   const long long total_items = items1 + (kDual ? static_cast<long long>(d2.p.main_tiles) : 0ll);

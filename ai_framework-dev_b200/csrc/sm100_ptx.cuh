@@ -12,6 +12,14 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// ---------------- programmatic dependent launch ----------------
+// A kernel launched with the programmatic-serialization attribute may start (its CTAs become resident as SMs free
+// up, its set-up runs) while the kernel before it in the stream is still finishing; griddep_wait() is where it stops
+// until that kernel has completed and its writes are visible.  griddep_launch() lets the NEXT kernel in the stream
+// begin that early start.  Both are no-ops for launches without the attribute.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------- mbarrier ----------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
