@@ -58,16 +58,21 @@ def measured_peak(key="bf16_tflops"):
     return (FALLBACK_PEAK_TFLOPS if key == "bf16_tflops" else FALLBACK_SUSTAINED_TFLOPS), "fallback"
 
 
-def fwd_launch_traffic():
-    """dram__bytes_read.sum + dram__bytes_write.sum of one forward launch of this workload, as recorded in the tracked
-    ncu summary (a line `dram_bytes_per_launch = <bytes>`); None when the summary has no such line."""
+def launch_traffic(key="dram_bytes_per_launch"):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, as recorded in the tracked ncu
+    summary (a line `<key> = <bytes>`: `dram_bytes_per_launch` for the forward launch, `dram_bytes_per_launch_dual` for
+    the dX + dW launch); None when the summary has no such line."""
     try:
         for line in (ROOT / TRAFFIC_PROFILE).read_text().splitlines():
-            if line.strip().startswith("dram_bytes_per_launch"):
+            if line.split("=")[0].strip() == key:
                 return float(line.split("=")[1].split()[0])
     except Exception:
         pass
     return None
+
+
+def fwd_launch_traffic():
+    return launch_traffic("dram_bytes_per_launch")
 
 
 class ClockSampler:
@@ -444,6 +449,16 @@ def run_ours(args):
     time.sleep(0.5)
     with ClockSampler(local, period_s=0.002) as clk_fwd_burst:
         fwd_ms = replay_ms(fwd_graph, max(10, min(args.steps, 50)))
+    # the same for the launch that computes dX and dW together (the larger share of the step): gZ is taken as already
+    # in `work` (reuse_dZ), so the graph holds that one launch
+    og.backward_into(X, W, dY, Z, act=ACT, with_bias=True, gA_out=dX, gB_out=dW, gBias_out=db, work_dZ=work)
+    l_b0 = lib.ge2b_launches_total()
+    bwd_graph = graph_of(lambda: og.backward_into(X, W, dY, Z, act=ACT, gA_out=dX, gB_out=dW, work_dZ=work, reuse_dZ=True))
+    bwd_gemm_launches = (lib.ge2b_launches_total() - l_b0) // 2          # graph_of runs the call twice
+    torch.cuda.synchronize()
+    time.sleep(0.3)
+    with ClockSampler(local, period_s=0.002) as clk_bwd_burst:
+        bwd_ms = replay_ms(bwd_graph, max(10, min(args.steps, 50)))
     replays = max(args.steps, int(MIN_WINDOW_S * 1e3 / max(burst_ms / args.steps, 1e-3)) + 1)
     launches0 = lib.ge2b_launches_total()
     total_ms = timed_window(replays, clk)
@@ -452,6 +467,8 @@ def run_ours(args):
     # the same launch replayed for at least half a second (the clock the power cap settles at)
     with ClockSampler(local, period_s=0.01) as clk_fwd:
         fwd_sustained_ms = replay_ms(fwd_graph, int(500.0 / max(fwd_ms, 1e-3)) + 1)
+    with ClockSampler(local, period_s=0.01) as clk_bwd:
+        bwd_sustained_ms = replay_ms(bwd_graph, int(500.0 / max(bwd_ms, 1e-3)) + 1)
     for _ in range(min(args.steps, 30)):
         step(True)
     barrier()
@@ -624,10 +641,35 @@ def run_ours(args):
     if rank == 0:
         peak, peak_kind = measured_peak("bf16_tflops")
         peak_sus, _ = measured_peak("bf16_tflops_sustained")
-        achieved = FLOP_FWD_LAUNCH / (fwd_ms * 1e-3) / 1e12
-        achieved_sus = FLOP_FWD_LAUNCH / (fwd_sustained_ms * 1e-3) / 1e12
-        traffic = fwd_launch_traffic()
         cs = clk.summary()
+
+        def roof_block(name, flop, ms, ms_sus, ck, ck_sus, traffic, what):
+            a_, a_s = flop / (ms * 1e-3) / 1e12, flop / (ms_sus * 1e-3) / 1e12
+            return {"bound": "tensor", "achieved": a_, "peak": peak, "unit": "TFLOP/s", "frac": a_ / peak,
+                    "traffic": traffic,
+                    "traffic_source": f"{TRAFFIC_PROFILE} (ncu capture of `bench.py --profile fwd` / `--profile step`, "
+                                      "not re-measured by this run)",
+                    "kernel": f"gemm_tc_kernel, {name}: {what}; duration = CUDA events around a run of back-to-back graph "
+                              "replays of that launch, between the burst window and the long window",
+                    "launch_ms": ms, "share_of_step": ms / (burst_ms / args.steps), "clocks": ck.summary(),
+                    "peak_source": f"MEASURED_PEAKS.json bf16_tflops (burst: the launch is timed alone, a few ms), {peak_kind}",
+                    "frac_of_nominal_2250": a_ / NOMINAL_PEAK_TFLOPS,
+                    "sustained": {"achieved": a_s, "launch_ms": ms_sus, "peak": peak_sus, "frac": a_s / peak_sus,
+                                  "clocks": ck_sus.summary(),
+                                  "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (the same launch replayed for "
+                                                 "half a second)"}}
+
+        roof_fwd = roof_block("forward launch", FLOP_FWD_LAUNCH, fwd_ms, fwd_sustained_ms, clk_fwd_burst, clk_fwd,
+                              launch_traffic("dram_bytes_per_launch"), "Y, Z = GELU(X.W + b), 2*M*N*K flop")
+        roof_fwd["launch_ms_eager_events"] = fwd_eager_ms
+        roof_bwd = roof_block("dX + dW launch", 2 * FLOP_FWD_LAUNCH, bwd_ms, bwd_sustained_ms, clk_bwd_burst, clk_bwd,
+                              launch_traffic("dram_bytes_per_launch_dual") if bwd_gemm_launches == 1 else None,
+                              "dX = gZ.W^T and dW = X^T.gZ as one tile list, 4*M*N*K flop")
+        # the dominant kernel of the step is the one with the larger measured share; the other sits beside it
+        if bwd_gemm_launches == 1 and bwd_ms >= fwd_ms:
+            roofline = dict(roof_bwd, other_kernel=roof_fwd)
+        else:
+            roofline = dict(roof_fwd, other_kernel=roof_bwd if bwd_gemm_launches == 1 else None)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(3, args.warmup), "ms_per_step": total_ms / replays, "higher_is_better": True,
@@ -650,18 +692,7 @@ def run_ours(args):
                     "api": "ge2b_dense_plan_submit / _wait (C ABI, pinned host buffers, two steps in flight)", "clocks": clk2.summary()},
             "gpu_launches": int(launches), "launch_mode": "cuda graph replay" if graph is not None else "eager",
             "split_k_unavailable_in_capture": int(lib.ge2b_split_unavailable_total() - split_unavailable0),
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": traffic,
-                         "traffic_source": f"{TRAFFIC_PROFILE} (ncu capture of `bench.py --profile fwd`, not re-measured by this run)",
-                         "kernel": "gemm_tc_kernel (forward launch: 2*M*N*K flop; duration = CUDA events around a run of "
-                                   "back-to-back graph replays of that launch, between the burst window and the long window)",
-                         "launch_ms": fwd_ms, "launch_ms_eager_events": fwd_eager_ms, "clocks": clk_fwd_burst.summary(),
-                         "peak_source": f"MEASURED_PEAKS.json bf16_tflops (burst: the launch is timed alone, a few ms), {peak_kind}",
-                         "frac_of_nominal_2250": achieved / NOMINAL_PEAK_TFLOPS,
-                         "sustained": {"achieved": achieved_sus, "launch_ms": fwd_sustained_ms, "peak": peak_sus,
-                                       "frac": achieved_sus / peak_sus, "clocks": clk_fwd.summary(),
-                                       "peak_source": "MEASURED_PEAKS.json bf16_tflops_sustained (the same launch replayed "
-                                                      "for half a second)"}},
+            "roofline": roofline,
         }
         if target is not None:
             line["target_8192"] = target
