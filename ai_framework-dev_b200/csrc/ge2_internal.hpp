@@ -162,7 +162,7 @@ long long split_unavailable_total();   // split-K launches that ran unsplit beca
 void release_library_scratch();        // synchronises the device and frees every split-K scratch the library created
 std::atomic<unsigned long long>& plan_cache_generation();   // bumping it invalidates every thread's cached launches
 
-bool early_start_enabled(); // programmatic dependent launch for the GEMM and prologue kernels (GE2B_PDL=0: off)
+bool early_start_enabled(); // programmatic dependent launch for the GEMM and prologue kernels (GE2B_PDL=1: on)
 int  sm_count();            // cached multiprocessor count of the current device
 int  sm_budget();           // SMs the persistent GEMM may occupy: sm_count() unless lowered by set_sm_limit()
 void keep_async_pool_cached();   // call before cudaMallocAsync: the default pool then keeps freed scratch for reuse
