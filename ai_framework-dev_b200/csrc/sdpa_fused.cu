@@ -270,22 +270,23 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int form = (p.mask_kind != 0 || !(p.scale_log2 > 0.f)) ? 2
                        : (key0 + kBlockKV > p.N || (p.causal && key0 + kBlockKV - 1 > warp_row0)) ? 1 : 0;
       const int limit = min(p.N - 1 - key0, p.causal ? row - key0 : kBlockKV);      // last live column of this row
-      float m_blk;
-      if (form != 2) {
-        // pass 1: four independent running maxima; two 32-column TMEM loads in flight at a time
-        float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-        auto max_chunk = [&](int c, const uint32_t (&r)[32]) {
-          if (form == 0) {
+      float mx[4], ls[4], neg_m = 0.f;
+      // raw (unscaled) maxima of one chunk, live columns only
+      auto max_chunk = [&](int c, const uint32_t (&r)[32]) {
+        if (form == 0) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(r[i]));
-          } else {
+          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(r[i]));
+        } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              mx[i & 3] = fmaxf(mx[i & 3], (c * 32 + i <= limit) ? __uint_as_float(r[i]) : -CUDART_INF_F);
-          }
-        };
-        {
-          uint32_t ra[32], rb[32];
+          for (int i = 0; i < 32; ++i)
+            mx[i & 3] = fmaxf(mx[i & 3], (c * 32 + i <= limit) ? __uint_as_float(r[i]) : -CUDART_INF_F);
+        }
+      };
+      // pass 1: row maximum of the scaled, masked scores of this block
+      auto block_max = [&]() -> float {
+        if (form != 2) {
+          mx[0] = mx[1] = mx[2] = mx[3] = -CUDART_INF_F;
+          uint32_t ra[32], rb[32];                                      // two 32-column TMEM loads in flight at a time
           ptx::tmem_ld_32x32(s_tmem, ra);
           ptx::tmem_ld_32x32(s_tmem + 32, rb);
           ptx::tmem_wait_ld();
@@ -294,10 +295,9 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           ptx::tmem_ld_32x32(s_tmem + 96, rb);
           ptx::tmem_wait_ld();
           max_chunk(2, ra); max_chunk(3, rb);
+          return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;     // (-inf stays -inf)
         }
-        m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;     // (-inf stays -inf)
-      } else {
-        m_blk = -CUDART_INF_F;
+        float m = -CUDART_INF_F;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
@@ -306,38 +306,25 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           ptx::tmem_wait_ld();
           masked_scores(p, r, v, key0 + c * 32, row, row_ok, mask_row);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) m_blk = fmaxf(m_blk, v[i]);
+          for (int i = 0; i < 32; ++i) m = fmaxf(m, v[i]);
         }
-      }
-      // The reference point m of the exponentials only has to stay within range, not be the exact maximum: while the
-      // row maximum has grown by less than 8 (a factor 256, harmless for fp32 sums and bf16 P) the old reference is
-      // kept and O needs no rescaling; the final O / l is exact either way.
-      const float m_cand = fmaxf(m_run, m_blk);
-      const float m_new = (m_run != -CUDART_INF_F && m_cand - m_run <= 8.f) ? m_run : m_cand;
-      const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;       // a fully masked row so far: keep everything 0
-      const float alpha = (m_new == m_run) ? 1.f : ex2(m_run - m_use);  // exp2(-inf) = 0 on the first live block
-      m_run = m_new;
-      // the tile's previous P.V must have finished: it read P's buffer and wrote O
-      if (j > 0) {
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(o_done(t), (j - 1) & 1, abort_flag))) { ok = false; break; }
-        ptx::tc_fence_after_sync();
-        if (__any_sync(0xffffffffu, alpha != 1.f)) {                    // rescale the rows of O by exp2(m_old - m_new)
+        return m;
+      };
+      // rows of O times alpha (warp-collective TMEM traffic: every lane takes part, with its own alpha)
+      auto rescale_o = [&](float alpha) {
 #pragma unroll 1
-          for (int c = 0; c < kD / 32; ++c) {
-            uint32_t r[32];
-            ptx::tmem_ld_32x32(o_tmem + c * 32, r);
-            ptx::tmem_wait_ld();
+        for (int c = 0; c < kD / 32; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(o_tmem + c * 32, r);
+          ptx::tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32(o_tmem + c * 32, r);
-          }
-          tmem_wait_st();
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st_32x32(o_tmem + c * 32, r);
         }
-      }
-      // pass 2: P = exp2(v - m) as bf16 into the operand layout (2 tiles of 64 keys, [128 rows x 128 B], 16-byte chunk
-      // index XOR (row & 7)) and the row sum (fp32 values, four independent partial sums)
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};
-      const float neg_m = -m_use;
+        tmem_wait_st();
+      };
+      // one chunk: P = exp2(v - m) as bf16 into the operand layout (2 tiles of 64 keys, [128 rows x 128 B], 16-byte
+      // chunk index XOR (row & 7)) and the row sum (fp32 values, four independent partial sums)
       auto exp_chunk = [&](int c, const uint32_t (&r)[32]) {
         uint32_t pk[16];
         if (form == 0) {
@@ -378,21 +365,68 @@ sdpa_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           *reinterpret_cast<uint4*>(dst + ((((c & 1) * 4 + k) ^ swz) * 16)) =
               make_uint4(pk[4 * k], pk[4 * k + 1], pk[4 * k + 2], pk[4 * k + 3]);
       };
-      {
-        // the TMEM load of chunk c + 1 is in flight while chunk c is turned into probabilities
+      // pass 2: the whole block with reference -neg_m; the TMEM load of chunk c + 1 is in flight while chunk c is
+      // turned into probabilities.  kTrack: also collect the block's raw maxima on the way (forms 0 and 1).
+      auto exp_block = [&](bool track) {
+        ls[0] = ls[1] = ls[2] = ls[3] = 0.f;
+        if (track) mx[0] = mx[1] = mx[2] = mx[3] = -CUDART_INF_F;
         uint32_t ra[32], rb[32];
         ptx::tmem_ld_32x32(s_tmem, ra);
         ptx::tmem_wait_ld();
         ptx::tmem_ld_32x32(s_tmem + 32, rb);
+        if (track) max_chunk(0, ra);
         exp_chunk(0, ra);
         ptx::tmem_wait_ld();
         ptx::tmem_ld_32x32(s_tmem + 64, ra);
+        if (track) max_chunk(1, rb);
         exp_chunk(1, rb);
         ptx::tmem_wait_ld();
         ptx::tmem_ld_32x32(s_tmem + 96, rb);
+        if (track) max_chunk(2, ra);
         exp_chunk(2, ra);
         ptx::tmem_wait_ld();
+        if (track) max_chunk(3, rb);
         exp_chunk(3, rb);
+      };
+
+      // The reference point m of the exponentials only has to stay within range, not be the exact maximum: while the
+      // row maximum has grown by less than 8 (a factor 256, harmless for fp32 sums and bf16 P) the old reference is
+      // kept and O needs no rescaling; the final O / l is exact either way.
+      float alpha = 1.f;
+      const bool two_pass = form == 2 || __any_sync(0xffffffffu, m_run == -CUDART_INF_F);
+      if (two_pass) {
+        // first live block of a row, or explicit masks: maximum first, then the probabilities
+        const float m_blk = block_max();
+        const float m_cand = fmaxf(m_run, m_blk);
+        const float m_new = (m_run != -CUDART_INF_F && m_cand - m_run <= 8.f) ? m_run : m_cand;
+        const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;     // a fully masked row so far: keep everything 0
+        alpha = (m_new == m_run) ? 1.f : ex2(m_run - m_use);            // exp2(-inf) = 0 on the first live block
+        m_run = m_new;
+        if (j > 0) {      // the tile's previous P.V must have finished: it read P's buffer and wrote O
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(o_done(t), (j - 1) & 1, abort_flag))) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          if (__any_sync(0xffffffffu, alpha != 1.f)) rescale_o(alpha);
+        }
+        neg_m = -m_use;
+        exp_block(false);
+      } else {
+        // the usual block: ONE pass with the reference as it stands, collecting the block's maximum on the way; only
+        // if that maximum turns out to exceed the reference by more than 8 (rare after the first blocks) is the
+        // reference moved, O rescaled and the block redone
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(o_done(t), (j - 1) & 1, abort_flag))) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        neg_m = -m_run;
+        exp_block(true);
+        const float m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+        const bool grew = m_blk - m_run > 8.f;
+        if (__any_sync(0xffffffffu, grew)) {
+          const float m_new = grew ? m_blk : m_run;
+          alpha = grew ? ex2(m_run - m_new) : 1.f;
+          m_run = m_new;
+          rescale_o(alpha);
+          neg_m = -m_new;
+          exp_block(false);
+        }
       }
       const float l_blk = (ls[0] + ls[1]) + (ls[2] + ls[3]);
       l_run = l_run * alpha + l_blk;
