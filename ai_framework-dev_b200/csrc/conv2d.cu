@@ -21,8 +21,12 @@
 
 #include "../../include/ge2_b200.h"
 #include "../../include/ge2_conv2d_api.hpp"
+#include "conv2d_implicit.hpp"
 #include "dense_ops.hpp"
 #include "epilogue_math.cuh"
+
+#include <cstdlib>
+#include <cstring>
 
 namespace ge2b {
 namespace {
@@ -222,6 +226,18 @@ const void* aligned_weight(AsyncBuf& buf, const void* W, const ConvGeom& g, int 
   return buf.p;
 }
 
+// GE2B_CONV in the environment: "explicit" keeps the column-matrix route, "general" takes the implicit kernel with
+// its element-wise gather only; anything else: the implicit kernel wherever it applies.  Read on every call so that
+// one process can compare the routes.
+enum : int { kConvImplicit = 0, kConvExplicit = 1, kConvImplicitGeneral = 2 };
+int conv_route() {
+  const char* e = std::getenv("GE2B_CONV");
+  if (!e) return kConvImplicit;
+  if (std::strcmp(e, "explicit") == 0) return kConvExplicit;
+  if (std::strcmp(e, "general") == 0) return kConvImplicitGeneral;
+  return kConvImplicit;
+}
+
 }  // namespace
 
 int conv2d_forward(const ge2b_conv2d_params_t& p, const void* X, const void* W, const float* bias, void* Y, void* Z,
@@ -233,6 +249,37 @@ int conv2d_forward(const ge2b_conv2d_params_t& p, const void* X, const void* W, 
   if (Z && !(zdt == p.dtype || zdt == kF32)) return kBadArgs;
   const int esz = dtype_bytes(p.dtype);
 
+  AsyncBuf wpad(s);
+  long long ldw = g.K;
+  bool failed = false;
+  const void* Wm = aligned_weight(wpad, W, g, p.dtype, p.math, ldw, s, failed);
+  if (failed) return kCudaError;
+
+  const int route = conv_route();
+  if (route != kConvExplicit && p.dtype != kF32 && !pointwise(g, esz) && g.Kh * g.Kw <= kConvMaxTaps) {
+    // implicit GEMM: the column matrix exists only as operand tiles in shared memory
+    ImplicitConv d;
+    d.dtype = p.dtype;
+    d.X = X; d.img_pitch = static_cast<long long>(g.Cin) * g.H * g.W; d.plane_pitch = static_cast<long long>(g.H) * g.W;
+    d.row_pitch = g.W; d.H = g.H; d.W = g.W;
+    d.Ho = g.Ho; d.Wo = g.Wo; d.P = static_cast<long long>(g.N) * g.HWo;
+    d.out_img_pitch = static_cast<long long>(g.Cout) * g.HWo;
+    d.sh = g.sh; d.sw = g.sw;
+    d.taps = g.Kh * g.Kw;
+    for (int kh = 0; kh < g.Kh; ++kh)
+      for (int kw = 0; kw < g.Kw; ++kw) {
+        d.tap_row[kh * g.Kw + kw] = kh * g.dh - g.ph;
+        d.tap_col[kh * g.Kw + kw] = kw * g.dw - g.pw;
+      }
+    d.Wm = Wm; d.ldw = ldw; d.K = g.K; d.Cout = g.Cout;
+    d.bias = (bias && p.with_bias) ? bias : nullptr;
+    d.act = p.act_kind; d.leaky = p.leaky_slope;
+    d.Y = Y; d.Z = Z; d.z_dtype = zdt;
+    d.force_general = route == kConvImplicitGeneral;
+    const int rc = conv_implicit_launch(d, s);
+    if (rc != kUnimplemented) return rc;
+  }
+
   AsyncBuf col(s);
   const void* B = X;
   long long ldb = static_cast<long long>(g.H) * g.W, strideB = static_cast<long long>(g.Cin) * g.H * g.W;
@@ -241,11 +288,6 @@ int conv2d_forward(const ge2b_conv2d_params_t& p, const void* X, const void* W, 
     if (launch_im2col(X, col.p, g, p.dtype, s) != cudaSuccess) return kCudaError;
     B = col.p; ldb = static_cast<long long>(g.N) * g.HWp; strideB = g.HWp;
   }
-  AsyncBuf wpad(s);
-  long long ldw = g.K;
-  bool failed = false;
-  const void* Wm = aligned_weight(wpad, W, g, p.dtype, p.math, ldw, s, failed);
-  if (failed) return kCudaError;
   DenseForward f;
   f.M = g.Cout; f.N = g.HWo; f.K = g.K; f.batch = g.N;
   f.dtype = p.dtype; f.z_dtype = zdt; f.math = p.math;
@@ -295,12 +337,47 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
   const long long gz_stride = static_cast<long long>(g.Cout) * g.HWp;
   const void* B = X;
   long long ldb = static_cast<long long>(g.H) * g.W, strideB = static_cast<long long>(g.Cin) * g.H * g.W;
-  if (!pw) {
-    if (!col.alloc(static_cast<size_t>(g.K) * g.N * g.HWp * esz)) return kCudaError;
+  // the column matrix of the batch (also the home of dCol), taken when a step first needs it
+  auto need_col = [&]() {
+    if (pw || col.p) return true;
+    if (!col.alloc(static_cast<size_t>(g.K) * g.N * g.HWp * esz)) return false;
     B = col.p; ldb = static_cast<long long>(g.N) * g.HWp; strideB = g.HWp;
+    return true;
+  };
+
+  const int route = conv_route();
+  bool dw_done = false;
+  if (dW && !pw && route != kConvExplicit && p.dtype != kF32 && g.Kh * g.Kw <= kConvMaxTaps) {
+    // weight gradient with the column tiles gathered inside the kernel (no Col), slices summed in fixed order
+    ImplicitWgrad w;
+    ImplicitConv& d = w.in;
+    d.dtype = p.dtype;
+    d.X = X; d.img_pitch = static_cast<long long>(g.Cin) * g.H * g.W; d.plane_pitch = static_cast<long long>(g.H) * g.W;
+    d.row_pitch = g.W; d.H = g.H; d.W = g.W;
+    d.Ho = g.Ho; d.Wo = g.Wo;
+    d.sh = g.sh; d.sw = g.sw;
+    d.taps = g.Kh * g.Kw;
+    for (int kh = 0; kh < g.Kh; ++kh)
+      for (int kw = 0; kw < g.Kw; ++kw) {
+        d.tap_row[kh * g.Kw + kw] = kh * g.dh - g.ph;
+        d.tap_col[kh * g.Kw + kw] = kw * g.dw - g.pw;
+      }
+    d.K = g.K; d.Cout = g.Cout;
+    d.force_general = route == kConvImplicitGeneral;
+    w.imgs = g.N; w.G = gz.p; w.g_plane_pitch = g.HWp; w.g_img_pitch = gz_stride;
+    w.dW = dW;
+    int split = 0; size_t bytes = 0;
+    AsyncBuf part(s);
+    if (conv_wgrad_plan(w, &split, &bytes) && part.alloc(bytes)) {
+      w.part = static_cast<float*>(part.p); w.part_bytes = bytes;
+      const int rc = conv_wgrad_launch(w, s);
+      if (rc == kOk) dw_done = true;
+      else if (rc != kUnimplemented) return rc;
+    }
   }
 
-  if (dW) {
+  if (dW && !dw_done) {
+    if (!need_col()) return kCudaError;
     if (!pw && launch_im2col(X, col.p, g, p.dtype, s) != cudaSuccess) return kCudaError;
     // dW (Cout x K) = sum_n gZ[n] (Cout x HWo) . Col[n]^T (HWo x K)
     GemmProblem q{};
@@ -361,8 +438,39 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
     }
   }
 
-  if (dX) {
+  bool dx_done = false;
+  if (dX && !pw && route != kConvExplicit && p.dtype != kF32 && g.sh == 1 && g.sw == 1 && g.Kh * g.Kw <= kConvMaxTaps) {
+    // Input gradient of a unit-stride convolution = convolution of gZ with mirrored taps and the weight read as
+    // [Cin][Cout * Kh * Kw]: the implicit kernel again, no dCol and no col2im.
+    const int taps = g.Kh * g.Kw;
+    const long long kt = static_cast<long long>(g.Cout) * taps, ldt = (kt + 7) / 8 * 8;
+    AsyncBuf wt(s);
+    if (kt <= (1 << 24) && wt.alloc(static_cast<size_t>(g.Cin) * ldt * esz) &&
+        launch_transpose_weight(W, wt.p, g.Cout, g.Cin, taps, ldt, s) == cudaSuccess) {
+      ImplicitConv d;
+      d.dtype = p.dtype;
+      d.X = gz.p; d.img_pitch = gz_stride; d.plane_pitch = g.HWp; d.row_pitch = g.Wo; d.H = g.Ho; d.W = g.Wo;
+      d.Ho = g.H; d.Wo = g.W; d.P = static_cast<long long>(g.N) * g.H * g.W;
+      d.out_img_pitch = static_cast<long long>(g.Cin) * g.H * g.W;
+      d.sh = 1; d.sw = 1;
+      d.taps = taps;
+      for (int kh = 0; kh < g.Kh; ++kh)
+        for (int kw = 0; kw < g.Kw; ++kw) {
+          d.tap_row[kh * g.Kw + kw] = g.ph - kh * g.dh;
+          d.tap_col[kh * g.Kw + kw] = g.pw - kw * g.dw;
+        }
+      d.Wm = wt.p; d.ldw = ldt; d.K = static_cast<int>(kt); d.Cout = g.Cin;
+      d.Y = dX;
+      d.force_general = route == kConvImplicitGeneral;
+      const int rc = conv_implicit_launch(d, s);
+      if (rc == kOk) dx_done = true;
+      else if (rc != kUnimplemented) return rc;
+    }
+  }
+
+  if (dX && !dx_done) {
     // dCol[n] (K x HWo) = W^T (K x Cout) . gZ[n] (Cout x HWo); for a pointwise convolution dCol[n] is dX[n]
+    if (!need_col()) return kCudaError;
     DenseForward f;
     f.M = g.K; f.N = g.HWo; f.K = g.Cout; f.batch = g.N;
     f.dtype = p.dtype; f.z_dtype = p.dtype; f.math = p.math;

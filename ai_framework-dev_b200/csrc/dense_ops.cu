@@ -73,6 +73,10 @@ int run_gemm_problem(const GemmProblem& g, cudaStream_t s) {
 }
 
 int last_route() { return t_last_route; }
+void note_tensor_launch(int kernels) {
+  t_last_route = kRouteTensor;
+  g_launches.fetch_add(kernels, std::memory_order_relaxed);
+}
 long long launches_total() { return g_launches.load(std::memory_order_relaxed); }
 
 int default_fp32_math() {

@@ -48,6 +48,7 @@ enum : int { kOk = 0, kBadArgs = -1, kCudaError = -2, kUnimplemented = -99 };
 enum : int { kRouteNone = 0, kRouteSimt = 1, kRouteTensor = 2 };
 int last_route();                 // thread-local: route of the most recent GEMM launch of this thread
 long long launches_total();       // process-wide count of kernels launched by this library
+void note_tensor_launch(int kernels);   // a tensor-core kernel outside run_gemm (the implicit convolution) was launched
 
 int dense_forward(const DenseForward& f, cudaStream_t s);
 // Routes a fully described problem (used by the convolution, which needs the batch-reducing form).  A problem with

@@ -164,6 +164,81 @@ def test_bf16_layer_sized_case(pkg, lib, oracle, conv_oracle):
     assert oracle.rel_fro(host(out["gB"]), gz.sum(dim=(0, 2, 3)).numpy()) <= FRO_TOL
 
 
+# --------------------------------------------------------------------------- implicit GEMM against the other routes
+IMPLICIT_GEOMS = {
+    # rows that are multiples of 8 wide take the aligned 16-byte gather, the others the element-wise one
+    "3x3_w16":          (2, 8, 16, 16, 16, 3, 3, (1, 1), (1, 1), (1, 1)),
+    "5x5_w24_pad2":     (2, 6, 24, 24, 10, 5, 5, (1, 1), (2, 2), (1, 1)),
+    "3x3_w16_dil2":     (2, 4, 16, 16, 8, 3, 3, (1, 1), (2, 2), (2, 2)),
+    "3x3_w32_valid":    (1, 5, 12, 32, 9, 3, 3, (1, 1), (0, 0), (1, 1)),      # Wo = 30: general gather on aligned input
+    "4x2_w8_even_taps": (3, 3, 9, 8, 4, 4, 2, (1, 1), (2, 1), (1, 1)),
+    "3x3_cout_300":     (1, 16, 16, 16, 300, 3, 3, (1, 1), (1, 1), (1, 1)),   # two channel tiles, ragged second one
+    "3x3_cout_100":     (2, 12, 10, 16, 100, 3, 3, (1, 1), (1, 1), (1, 1)),   # 128-wide channel tile
+    "3x3_stride2":      GEOMS["3x3_stride2"],
+    "5x3_dilated":      GEOMS["5x3_dilated"],
+    "7x7_stem":         GEOMS["7x7_stem"],
+    "wide":             GEOMS["wide"],
+}
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("name", sorted(IMPLICIT_GEOMS))
+def test_implicit_gemm_routes(pkg, lib, oracle, conv_oracle, monkeypatch, name, dtype):
+    """Forward (Y, Z) and the input gradient through the implicit-GEMM kernel with its aligned gather where it
+    applies, with the element-wise gather everywhere, and through the column-matrix route: the two gathers feed the
+    same arithmetic (bit-identical results), the column-matrix route sums in another order (close), and all three
+    stay inside the bf16 / f16 bound against float64."""
+    g = IMPLICIT_GEOMS[name]
+    X, Wt, b, dY = conv_oracle.conv_inputs(*g[:7], seed=11, **_kw(g))
+    if dtype == torch.bfloat16:
+        X, Wt, dY = (oracle.bf16_round(a) for a in (X, Wt, dY))
+    else:
+        X, Wt, dY = (a.astype(np.float16).astype(np.float32) for a in (X, Wt, dY))
+    tX, tW, tdY = dev(X, dtype), dev(Wt, dtype), dev(dY, dtype)
+    Y64, Z64 = conv_oracle.forward_f64(X, Wt, b, act="tanh", **_kw(g))
+    got = {}
+    for route in ("implicit", "general", "explicit"):
+        monkeypatch.setenv("GE2B_CONV", route)
+        Y, Z = pkg.ops_conv2d.forward(tX, tW, dev(b), with_bias=True, act="tanh", save_z=True, z_dtype=torch.float32,
+                                      **_kw(g))
+        out = pkg.ops_conv2d.backward(tX, tW, tdY, Z, with_bias=True, act="tanh", want_gB=True, **_kw(g))
+        torch.cuda.synchronize()
+        assert lib.ge2b_device_status(1) == 0
+        got[route] = (Y, Z, out["gX"], out["gW"])
+        ref = conv_oracle.backward_f64(X, Wt, dY, host(Z), act="tanh", **_kw(g))
+        errs = {"Y": oracle.rel_fro(host(Y), Y64), "Z": oracle.rel_fro(host(Z), Z64),
+                "gX": oracle.rel_fro(host(out["gX"]), ref["gX"]), "gW": oracle.rel_fro(host(out["gW"]), ref["gW"])}
+        assert all(e <= FRO_TOL for e in errs.values()), (route, errs)
+        # element-wise: fp32 accumulation of K products of 16-bit operands, then one rounding of Y
+        K = g[1] * g[5] * g[6]
+        eps = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -9     # 16-bit epilogues use tanh.approx
+        assert float(np.abs(host(Z) - Z64).max()) <= 1e-5 * K + 1e-6, route
+        assert float(np.abs(host(Y) - Y64).max()) <= eps + 1e-5 * K, route
+    for a, c in zip(got["implicit"], got["general"]):
+        assert torch.equal(a, c)
+    for a, c in zip(got["implicit"][:3], got["explicit"][:3]):
+        assert float((a.float() - c.float()).abs().max()) <= 2e-2 * max(1.0, float(c.float().abs().max()))
+
+
+def test_implicit_gemm_is_the_default_route_and_moves_no_column_matrix(pkg, lib, monkeypatch):
+    """On a ResNet-sized layer the default forward is ONE launch (the column-matrix route takes two and allocates
+    K x N x HWo elements)."""
+    monkeypatch.delenv("GE2B_CONV", raising=False)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    X = torch.randn((4, 64, 56, 56), device="cuda", generator=g).bfloat16()
+    W = (torch.randn((64, 64, 3, 3), device="cuda", generator=g) / 24).bfloat16()
+    b = torch.randn(64, device="cuda", generator=g)
+    pkg.ops_conv2d.forward(X, W, b, with_bias=True, act="relu", padding=(1, 1))
+    torch.cuda.synchronize()
+    before = lib.ge2b_launches_total()
+    Y = pkg.ops_conv2d.forward(X, W, b, with_bias=True, act="relu", padding=(1, 1))
+    torch.cuda.synchronize()
+    assert lib.ge2b_launches_total() - before == 1
+    assert lib.ge2b_last_route() == 2
+    want = torch.nn.functional.conv2d(X.float(), W.float(), b, padding=1).relu()
+    assert float((Y.float() - want).abs().max()) <= 2.0 ** -7 * float(want.abs().max())
+
+
 # --------------------------------------------------------------------------- against the reference's own GPU op
 def _ref_conv():
     path = ROOT / "oracle" / "_ref" / "libref_conv.so"
