@@ -17,7 +17,7 @@ OBJ_DIR = PKG / "build"
 LIB = LIB_DIR / "libge2_b200.so"
 
 SOURCES = ["runtime.cu", "gemm_simt.cu", "gemm_tc.cu", "bwd_prologue.cu", "dense_ops.cu", "c_api.cu", "op_api.cu",
-           "host_api.cu", "bwd_noalloc.cu", "train_step.cu", "dispatch.cu", "conv2d.cu", "conv2d_implicit.cu", "selftest.cu", "allreduce_nvls.cu", "mlp_plan.cu", "fp32x3.cu", "sdpa_fused.cu"] + \
+           "host_api.cu", "bwd_noalloc.cu", "train_step.cu", "dispatch.cu", "conv2d.cu", "conv2d_implicit.cu", "conv2d_patch.cu", "selftest.cu", "allreduce_nvls.cu", "mlp_plan.cu", "fp32x3.cu", "sdpa_fused.cu"] + \
           [f"gemm_tc_inst_{t}_{o}.cu" for t in ("16bit", "tf32") for o in ("kk", "km", "mk", "mm")]
 
 NVCC_FLAGS = [

@@ -226,16 +226,27 @@ const void* aligned_weight(AsyncBuf& buf, const void* W, const ConvGeom& g, int 
   return buf.p;
 }
 
-// GE2B_CONV in the environment: "explicit" keeps the column-matrix route, "general" takes the implicit kernel with
-// its element-wise gather only; anything else: the implicit kernel wherever it applies.  Read on every call so that
-// one process can compare the routes.
-enum : int { kConvImplicit = 0, kConvExplicit = 1, kConvImplicitGeneral = 2 };
+// GE2B_CONV in the environment picks the route of 16-bit convolutions (read on every call so that one process can
+// compare them): "explicit" = column matrix in memory; "gather" = the kernels that gather column tiles from global
+// memory, wherever they apply; "general" = the same with their element-wise gather only; unset = by shape: the
+// shared-memory patch kernel for unit-stride forward / input-gradient passes, the gathering kernel for the weight
+// gradient where its aligned gather applies, the column matrix for the rest.
+enum : int { kConvAuto = 0, kConvExplicit = 1, kConvGather = 2, kConvGatherGeneral = 3 };
 int conv_route() {
   const char* e = std::getenv("GE2B_CONV");
-  if (!e) return kConvImplicit;
+  if (!e) return kConvAuto;
   if (std::strcmp(e, "explicit") == 0) return kConvExplicit;
-  if (std::strcmp(e, "general") == 0) return kConvImplicitGeneral;
-  return kConvImplicit;
+  if (std::strcmp(e, "gather") == 0) return kConvGather;
+  if (std::strcmp(e, "general") == 0) return kConvGatherGeneral;
+  return kConvAuto;
+}
+
+// The patch kernel pads the channels of a block to 64 and copies 128 + (Kh-1)*dil_h*Wp + (Kw-1)*dil_w pixels per
+// 128 output positions: taken when the padding costs at most twice the arithmetic and the halo at most twice the tile
+// (on wide images, e.g. 3 x 3 at 224 x 224, the gathering kernel measured faster).
+bool patch_worthwhile(int channels, int kh, int kw, int dh, int dw, int padded_width) {
+  const long long halo = static_cast<long long>(kh - 1) * dh * padded_width + static_cast<long long>(kw - 1) * dw;
+  return (channels + 63) / 64 * 64 <= 2 * channels && halo <= 256;
 }
 
 }  // namespace
@@ -256,8 +267,32 @@ int conv2d_forward(const ge2b_conv2d_params_t& p, const void* X, const void* W, 
   if (failed) return kCudaError;
 
   const int route = conv_route();
-  if (route != kConvExplicit && p.dtype != kF32 && !pointwise(g, esz) && g.Kh * g.Kw <= kConvMaxTaps) {
-    // implicit GEMM: the column matrix exists only as operand tiles in shared memory
+  const bool sixteen = p.dtype != kF32 && !pointwise(g, esz) && g.Kh * g.Kw <= kConvMaxTaps;
+  if (route == kConvAuto && sixteen && g.sh == 1 && g.sw == 1 &&
+      patch_worthwhile(g.Cin, g.Kh, g.Kw, g.dh, g.dw, g.W + 2 * g.pw)) {
+    // unit stride: operand tiles are windows of one input patch in shared memory
+    PatchConv d;
+    d.dtype = p.dtype;
+    d.X = X; d.img_pitch = static_cast<long long>(g.Cin) * g.H * g.W; d.plane_pitch = static_cast<long long>(g.H) * g.W;
+    d.row_pitch = g.W; d.imgs = g.N; d.Cin = g.Cin; d.H = g.H; d.W = g.W;
+    d.ph = g.ph; d.pw = g.pw; d.Kh = g.Kh; d.Kw = g.Kw; d.dh = g.dh; d.dw = g.dw;
+    d.W_ = W; d.w_row_stride = g.K; d.w_chan_stride = static_cast<long long>(g.Kh) * g.Kw;
+    d.Cout = g.Cout;
+    d.bias = (bias && p.with_bias) ? bias : nullptr;
+    d.act = p.act_kind; d.leaky = p.leaky_slope;
+    d.Y = Y; d.Z = Z; d.z_dtype = zdt;
+    d.out_img_pitch = static_cast<long long>(g.Cout) * g.HWo;
+    AsyncBuf wr(s);
+    if (conv_patch_supported(d) && wr.alloc(conv_patch_weight_bytes(d))) {
+      d.Wr = wr.p;
+      const int rc = conv_patch_launch(d, s);
+      if (rc != kUnimplemented) return rc;
+    }
+  }
+  const bool gather_aligned = g.sw == 1 && g.W % 8 == 0 && g.Wo % 8 == 0;
+  if (sixteen && (route == kConvGather || route == kConvGatherGeneral || (route == kConvAuto && gather_aligned))) {
+    // column tiles gathered from global memory inside the kernel (by shape only where its aligned gather applies:
+    // the other shapes measured faster through the column matrix)
     ImplicitConv d;
     d.dtype = p.dtype;
     d.X = X; d.img_pitch = static_cast<long long>(g.Cin) * g.H * g.W; d.plane_pitch = static_cast<long long>(g.H) * g.W;
@@ -275,7 +310,7 @@ int conv2d_forward(const ge2b_conv2d_params_t& p, const void* X, const void* W, 
     d.bias = (bias && p.with_bias) ? bias : nullptr;
     d.act = p.act_kind; d.leaky = p.leaky_slope;
     d.Y = Y; d.Z = Z; d.z_dtype = zdt;
-    d.force_general = route == kConvImplicitGeneral;
+    d.force_general = route == kConvGatherGeneral;
     const int rc = conv_implicit_launch(d, s);
     if (rc != kUnimplemented) return rc;
   }
@@ -347,7 +382,10 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
 
   const int route = conv_route();
   bool dw_done = false;
-  if (dW && !pw && route != kConvExplicit && p.dtype != kF32 && g.Kh * g.Kw <= kConvMaxTaps) {
+  const bool sixteen = p.dtype != kF32 && !pw && g.Kh * g.Kw <= kConvMaxTaps;
+  // (by shape: where the aligned 16-byte gather applies; other shapes measured faster through the column matrix)
+  const bool wgrad_aligned = g.sw == 1 && g.W % 8 == 0 && g.Wo % 8 == 0;
+  if (dW && sixteen && (route == kConvGather || route == kConvGatherGeneral || (route == kConvAuto && wgrad_aligned))) {
     // weight gradient with the column tiles gathered inside the kernel (no Col), slices summed in fixed order
     ImplicitWgrad w;
     ImplicitConv& d = w.in;
@@ -363,7 +401,7 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
         d.tap_col[kh * g.Kw + kw] = kw * g.dw - g.pw;
       }
     d.K = g.K; d.Cout = g.Cout;
-    d.force_general = route == kConvImplicitGeneral;
+    d.force_general = route == kConvGatherGeneral;
     w.imgs = g.N; w.G = gz.p; w.g_plane_pitch = g.HWp; w.g_img_pitch = gz_stride;
     w.dW = dW;
     int split = 0; size_t bytes = 0;
@@ -439,9 +477,33 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
   }
 
   bool dx_done = false;
-  if (dX && !pw && route != kConvExplicit && p.dtype != kF32 && g.sh == 1 && g.sw == 1 && g.Kh * g.Kw <= kConvMaxTaps) {
-    // Input gradient of a unit-stride convolution = convolution of gZ with mirrored taps and the weight read as
-    // [Cin][Cout * Kh * Kw]: the implicit kernel again, no dCol and no col2im.
+  if (dX && sixteen && route == kConvAuto && g.sh == 1 && g.sw == 1 &&
+      g.ph <= (g.Kh - 1) * g.dh && g.pw <= (g.Kw - 1) * g.dw &&
+      patch_worthwhile(g.Cout, g.Kh, g.Kw, g.dh, g.dw, g.Wo + 2 * ((g.Kw - 1) * g.dw - g.pw))) {
+    // Input gradient of a unit-stride convolution = convolution of gZ (border dil*(K-1) - pad) with the taps mirrored
+    // and the weight read as [Cin][tap][Cout]: the patch kernel again, no dCol and no col2im.
+    PatchConv d;
+    d.dtype = p.dtype;
+    d.X = gz.p; d.img_pitch = gz_stride; d.plane_pitch = g.HWp; d.row_pitch = g.Wo;
+    d.imgs = g.N; d.Cin = g.Cout; d.H = g.Ho; d.W = g.Wo;
+    d.ph = (g.Kh - 1) * g.dh - g.ph; d.pw = (g.Kw - 1) * g.dw - g.pw;
+    d.Kh = g.Kh; d.Kw = g.Kw; d.dh = g.dh; d.dw = g.dw;
+    d.W_ = W; d.w_row_stride = static_cast<long long>(g.Kh) * g.Kw; d.w_chan_stride = g.K; d.flip_taps = true;
+    d.Cout = g.Cin;
+    d.Y = dX;
+    d.out_img_pitch = static_cast<long long>(g.Cin) * g.H * g.W;
+    AsyncBuf wr(s);
+    if (conv_patch_supported(d) && wr.alloc(conv_patch_weight_bytes(d))) {
+      d.Wr = wr.p;
+      const int rc = conv_patch_launch(d, s);
+      if (rc == kOk) dx_done = true;
+      else if (rc != kUnimplemented) return rc;
+    }
+  }
+  // (gZ rows are Wo wide and dX rows W wide: the aligned gather needs both to be multiples of 8)
+  if (dX && !dx_done && sixteen && g.sh == 1 && g.sw == 1 &&
+      (route == kConvGather || route == kConvGatherGeneral || (route == kConvAuto && wgrad_aligned))) {
+    // the same through the gathering kernel
     const int taps = g.Kh * g.Kw;
     const long long kt = static_cast<long long>(g.Cout) * taps, ldt = (kt + 7) / 8 * 8;
     AsyncBuf wt(s);
@@ -461,7 +523,7 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
         }
       d.Wm = wt.p; d.ldw = ldt; d.K = static_cast<int>(kt); d.Cout = g.Cin;
       d.Y = dX;
-      d.force_general = route == kConvImplicitGeneral;
+      d.force_general = route == kConvGatherGeneral;
       const int rc = conv_implicit_launch(d, s);
       if (rc == kOk) dx_done = true;
       else if (rc != kUnimplemented) return rc;

@@ -85,71 +85,60 @@ __device__ __forceinline__ Pos decode_pos(const ConvParams& p, long long pos) {
   return r;
 }
 
-// The 16-byte chunk of eight consecutive output positions starting at (ho, wo) of one (image, channel) plane, read
-// through the tap offset `off`; positions from `valid` on are zeros.
-__device__ __forceinline__ uint4 gather_core(const ConvParams& p, const unsigned short* plane, short2 off, int ho, int wo,
-                                             int valid) {
-  uint4 out = make_uint4(0u, 0u, 0u, 0u);
-  if (p.fast) {
-    // all eight positions share the image and the output row; unit column stride; 16-byte aligned rows
-    const int hi = ho * p.sh + off.x;
-    if (static_cast<unsigned>(hi) >= static_cast<unsigned>(p.H)) return out;
-    const unsigned short* row = plane + static_cast<long long>(hi) * p.row_pitch;
-    const int wi0 = wo + off.y;
-    const int e = wi0 & 7, a = wi0 - e;                  // aligned chunk [a, a+8) and the element offset inside it
-    uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi4 = lo;
-    if (static_cast<unsigned>(a) < static_cast<unsigned>(p.W)) lo = ldg16(row + a);
-    if (e != 0 && static_cast<unsigned>(a + 8) < static_cast<unsigned>(p.W)) hi4 = ldg16(row + a + 8);
-    if (e == 0) return lo;
-    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi4.x, hi4.y, hi4.z, hi4.w};
-    uint32_t a0, a1, a2, a3, a4;
-    switch (e >> 1) {
-      case 0:  a0 = w[0]; a1 = w[1]; a2 = w[2]; a3 = w[3]; a4 = w[4]; break;
-      case 1:  a0 = w[1]; a1 = w[2]; a2 = w[3]; a3 = w[4]; a4 = w[5]; break;
-      case 2:  a0 = w[2]; a1 = w[3]; a2 = w[4]; a3 = w[5]; a4 = w[6]; break;
-      default: a0 = w[3]; a1 = w[4]; a2 = w[5]; a3 = w[6]; a4 = w[7]; break;
-    }
-    const uint32_t sft = (e & 1) * 16;
-    out.x = __funnelshift_r(a0, a1, sft);
-    out.y = __funnelshift_r(a1, a2, sft);
-    out.z = __funnelshift_r(a2, a3, sft);
-    out.w = __funnelshift_r(a3, a4, sft);
-    return out;
-  }
-  // general form: one 2-byte load per position, walking (column, row, image) as the positions advance
+// Aligned form of the gather, in two halves so that a thread can have the loads of several chunks in flight before it
+// uses the first: the chunk of eight consecutive positions starting at column wo of output row ho, read through the
+// tap offset `off`, lies inside two aligned 16-byte pieces of one input row (all eight positions share the image and
+// the output row; unit column stride; rows start on 16-byte boundaries).
+struct RawChunk { uint4 lo, hi; int e; };
+__device__ __forceinline__ RawChunk gather_issue(const ConvParams& p, const unsigned short* plane, short2 off, int ho,
+                                                 int wo, bool on) {
+  RawChunk r;
+  const int hi_row = ho * p.sh + off.x;
+  on = on && static_cast<unsigned>(hi_row) < static_cast<unsigned>(p.H);
+  const unsigned short* row = plane + static_cast<long long>(hi_row) * p.row_pitch;
+  const int wi0 = wo + off.y;
+  r.e = wi0 & 7;
+  const int a = wi0 - r.e;                               // aligned piece [a, a+8), element offset e inside it
+  const bool on_lo = on && static_cast<unsigned>(a) < static_cast<unsigned>(p.W);
+  const bool on_hi = on && r.e != 0 && static_cast<unsigned>(a + 8) < static_cast<unsigned>(p.W);
+  r.lo = on_lo ? ldg16(row + a) : make_uint4(0u, 0u, 0u, 0u);
+  r.hi = on_hi ? ldg16(row + a + 8) : make_uint4(0u, 0u, 0u, 0u);
+  return r;
+}
+// Elements e .. e+7 of the 16 elements (lo, hi): a 256-bit value shifted right by 16 e bits, without branches.
+__device__ __forceinline__ uint4 gather_finish(const RawChunk& r) {
+  const bool two = (r.e & 4) != 0, one = (r.e & 2) != 0;
+  const uint32_t t0 = two ? r.lo.z : r.lo.x, t1 = two ? r.lo.w : r.lo.y, t2 = two ? r.hi.x : r.lo.z,
+                 t3 = two ? r.hi.y : r.lo.w, t4 = two ? r.hi.z : r.hi.x, t5 = two ? r.hi.w : r.hi.y;
+  const uint32_t u0 = one ? t1 : t0, u1 = one ? t2 : t1, u2 = one ? t3 : t2, u3 = one ? t4 : t3, u4 = one ? t5 : t4;
+  const uint32_t sft = (r.e & 1) * 16;
+  return make_uint4(__funnelshift_r(u0, u1, sft), __funnelshift_r(u1, u2, sft), __funnelshift_r(u2, u3, sft),
+                    __funnelshift_r(u3, u4, sft));
+}
+
+// General form of the gather: one 2-byte load per position, walking (column, row, image) as the positions advance;
+// positions from `valid` on are zeros.
+__device__ __forceinline__ uint4 gather_general(const ConvParams& p, const unsigned short* plane, short2 off, int ho, int wo,
+                                                int valid) {
   const int Ho = p.HWo / p.Wo;
   uint32_t v[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int hi = ho * p.sh + off.x, wi = wo * p.sw + off.y;
-    unsigned short x = 0;
-    if (j < valid && static_cast<unsigned>(hi) < static_cast<unsigned>(p.H) &&
-        static_cast<unsigned>(wi) < static_cast<unsigned>(p.W))
-      x = __ldg(plane + static_cast<long long>(hi) * p.row_pitch + wi);
-    v[j] = x;
+    const bool on = j < valid && static_cast<unsigned>(hi) < static_cast<unsigned>(p.H) &&
+                    static_cast<unsigned>(wi) < static_cast<unsigned>(p.W);
+    v[j] = on ? __ldg(plane + static_cast<long long>(hi) * p.row_pitch + wi) : static_cast<unsigned short>(0);
     if (++wo == p.Wo) {
       wo = 0;
       if (++ho == Ho) { ho = 0; plane += p.img_pitch; }
     }
   }
-  out.x = v[0] | (v[1] << 16); out.y = v[2] | (v[3] << 16);
-  out.z = v[4] | (v[5] << 16); out.w = v[6] | (v[7] << 16);
-  return out;
+  return make_uint4(v[0] | (v[1] << 16), v[2] | (v[3] << 16), v[4] | (v[5] << 16), v[6] | (v[7] << 16));
 }
 
 // Reduction index k -> channel and tap.
 __device__ __forceinline__ int channel_of(const ConvParams& p, int k) {
   return p.taps == 1 ? k : static_cast<int>(__umulhi(static_cast<unsigned>(k), p.tap_magic));
-}
-
-// The 16-byte chunk Col[p0 .. p0+7][k]: eight consecutive output positions (of the whole batch) of reduction index k.
-__device__ __forceinline__ uint4 gather_chunk(const ConvParams& p, const short2* tap_s, long long p0, const Pos& q,
-                                              int k) {
-  if (k >= p.K || p0 >= p.P) return make_uint4(0u, 0u, 0u, 0u);
-  const int c = channel_of(p, k);
-  const long long left = p.P - p0;
-  return gather_core(p, p.X + q.n * p.img_pitch + c * p.plane_pitch, tap_s[k - c * p.taps], q.ho, q.wo,
-                     left < 8 ? static_cast<int>(left) : 8);
 }
 
 template <int ACT>
@@ -180,6 +169,13 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_const
   constexpr int kBStageBytes = kBN * 128;
   constexpr int kStageBytes = kAStageBytes + kBStageBytes;
   constexpr int kTmemCols = 2 * kBN;
+  // Stage fills are dealt round-robin to kSpan groups of gather warps.  A group's next fill is kSpan fills after its
+  // last one; kSpan <= kStages keeps it less than two laps of the ring ahead of the consumer, which is what the
+  // one-bit phase of the empty barriers can tell apart.
+  constexpr int kSpan = kStages >= kGatherWarps ? kGatherWarps : 4;
+  constexpr int kWarpsPerStage = kGatherWarps / kSpan;
+  constexpr int kStepsPerWarp = 32 / kWarpsPerStage;     // of the 32 row steps of one stage
+  static_assert(kSpan <= kStages && kGatherWarps % kSpan == 0, "gather groups and ring depth do not fit");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -199,7 +195,7 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_const
   const long long tiles = static_cast<long long>(p.pos_tiles) * p.n_tiles;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1 + kGatherWarps); ptx::mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1 + kWarpsPerStage); ptx::mbar_init(empty_bar(s), 1); }
     for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), kEpiWarpsConv); }
     *abort_flag = 0;
     ptx::fence_barrier_init();
@@ -305,33 +301,65 @@ conv_implicit_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_const
     ptx::tc_fence_before_sync();
   } else {
     // ===================== gather of the Col tile =====================
-    // A stage holds 16 position chunks x 64 k rows.  A half-warp covers the 16 chunks of one k row (256 bytes of
-    // positions, contiguous in the input at unit stride), a warp two rows, the eight warps 16 rows per pass.
+    // Every gather warp produces whole stages (the stage's running index modulo the number of gather warps picks the
+    // warp), so that as many stages are being fetched at once as the ring has slots: one stage is one round trip to
+    // L2 per batch of loads, and only several in flight hide it.  A stage holds 16 position chunks x 64 k rows; a
+    // half-warp covers the 16 chunks of one k row (256 bytes of positions, contiguous in the input at unit stride).
     const int g = warp - kGatherWarp0;
-    const int chunk = lane & 15;
-    const int r_sub = g * 2 + (lane >> 4);
+    const int chunk = lane & 15, r_half = lane >> 4;
+    const int t_first = (g / kSpan) * kStepsPerWarp;    // this warp's share of the stage's row steps
     const uint32_t chunk_off = static_cast<uint32_t>(chunk >> 3) * (kBK * 128);
-    int stage = 0; uint32_t phase = 0; bool ok = true;
+    constexpr int kBatch = 8;                           // chunks whose loads a thread issues before it uses the first
+    long long idx = 0;                                  // running index of the stage fills of this CTA
+    bool ok = true;
     for (long long t = blockIdx.x; ok && t < tiles; t += gridDim.x) {
       const long long pt = t / p.n_tiles;
       const long long p0 = pt * kBM + chunk * 8;
-      const Pos q = decode_pos(p, p0 < p.P ? p0 : 0);
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
+      const bool pos_on = p0 < p.P;
+      const Pos q = decode_pos(p, pos_on ? p0 : 0);
+      const unsigned short* img = p.X + q.n * p.img_pitch;
+      const long long left = p.P - p0;
+      const int valid = left < 8 ? static_cast<int>(left) : 8;
+      for (int kb = 0; kb < p.k_blocks; ++kb, ++idx) {
+        if (static_cast<int>(idx % kSpan) != g % kSpan) continue;
+        const int stage = static_cast<int>(idx % kStages);
+        const uint32_t phase = static_cast<uint32_t>(idx / kStages) & 1u;
         ok = __all_sync(0xffffffffu, ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag));
         if (!ok) break;
-        uint8_t* a_stage = smem + stage * kStageBytes;
-        uint4 v[4];
+        uint8_t* a_stage = smem + stage * kStageBytes + chunk_off;
+        if (p.fast) {
+#pragma unroll 1
+          for (int t0 = t_first; t0 < t_first + kStepsPerWarp; t0 += kBatch) {
+            RawChunk raw[kBatch];
 #pragma unroll
-        for (int it = 0; it < 4; ++it) v[it] = gather_chunk(p, tap_s, p0, q, kb * kBK + it * 16 + r_sub);
+            for (int u = 0; u < kBatch; ++u) {
+              const int k = kb * kBK + 2 * (t0 + u) + r_half;
+              const bool on = pos_on && k < p.K;
+              const int c = on ? channel_of(p, k) : 0;
+              raw[u] = gather_issue(p, img + c * p.plane_pitch, tap_s[on ? k - c * p.taps : 0], q.ho, q.wo, on);
+            }
 #pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const int r = it * 16 + r_sub;
-          *reinterpret_cast<uint4*>(a_stage + chunk_off + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = v[it];
+            for (int u = 0; u < kBatch; ++u) {
+              const int r = 2 * (t0 + u) + r_half;
+              *reinterpret_cast<uint4*>(a_stage + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = gather_finish(raw[u]);
+            }
+          }
+        } else {
+#pragma unroll 2
+          for (int t0 = t_first; t0 < t_first + kStepsPerWarp; ++t0) {
+            const int r = 2 * t0 + r_half;
+            const int k = kb * kBK + r;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (pos_on && k < p.K) {
+              const int c = channel_of(p, k);
+              v = gather_general(p, img + c * p.plane_pitch, tap_s[k - c * p.taps], q.ho, q.wo, valid);
+            }
+            *reinterpret_cast<uint4*>(a_stage + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = v;
+          }
         }
         ptx::fence_proxy_async_smem();                 // the MMA reads the stage through the async proxy
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(full_bar(stage));
-        if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
     }
   }
@@ -381,6 +409,13 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap tmG, const __grid_constant
   constexpr int kBStageBytes = kBN * 128;
   constexpr int kStageBytes = kAStageBytes + kBStageBytes;
   constexpr int kTmemCols = 2 * kBN;
+  // Stage fills are dealt round-robin to kSpan groups of gather warps.  A group's next fill is kSpan fills after its
+  // last one; kSpan <= kStages keeps it less than two laps of the ring ahead of the consumer, which is what the
+  // one-bit phase of the empty barriers can tell apart.
+  constexpr int kSpan = kStages >= kGatherWarps ? kGatherWarps : 4;
+  constexpr int kWarpsPerStage = kGatherWarps / kSpan;
+  constexpr int kStepsPerWarp = 32 / kWarpsPerStage;     // of the 32 row steps of one stage
+  static_assert(kSpan <= kStages && kGatherWarps % kSpan == 0, "gather groups and ring depth do not fit");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
@@ -412,7 +447,7 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap tmG, const __grid_constant
   };
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1 + kGatherWarps); ptx::mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1 + kWarpsPerStage); ptx::mbar_init(empty_bar(s), 1); }
     for (int a = 0; a < 2; ++a) { ptx::mbar_init(tfull_bar(a), 1); ptx::mbar_init(tempty_bar(a), kEpiWarpsConv); }
     *abort_flag = 0;
     ptx::fence_barrier_init();
@@ -508,25 +543,20 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap tmG, const __grid_constant
     ptx::tc_fence_before_sync();
   } else {
     // ===================== gather of the Col tile (128 k rows x 8 position chunks per stage) =====================
-    // Eight lanes cover the 8 chunks of one k row (128 bytes of positions), a warp four rows, the eight warps 32 rows
-    // per pass.
+    // As in the forward kernel every gather warp produces whole stages.  Eight lanes cover the 8 chunks of one k row
+    // (128 bytes of positions), a warp four rows per step.
     const int g = warp - kGatherWarp0;
-    const int chunk = lane & 7;
-    const int r_sub = g * 4 + (lane >> 3);
-    int stage = 0; uint32_t phase = 0; bool ok = true;
+    const int chunk = lane & 7, r_quarter = lane >> 3;
+    const int t_first = (g / kSpan) * kStepsPerWarp;
+    constexpr int kBatch = 8;
+    long long idx = 0;
+    bool ok = true;
     for (long long u = blockIdx.x; ok && u < units; u += gridDim.x) {
       const Unit w = decode_unit(u);
-      // this thread's four k rows: channel plane offset and tap offsets, fixed for the unit
-      long long plane_off[4]; short2 off[4]; bool k_ok[4];
-#pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        const int k = w.mt * kBM + it * 32 + r_sub;
-        k_ok[it] = k < p.K;
-        const int c = k_ok[it] ? channel_of(p, k) : 0;
-        plane_off[it] = c * p.plane_pitch;
-        off[it] = k_ok[it] ? tap_s[k - c * p.taps] : make_short2(0, 0);
-      }
-      for (int b = w.b0; b < w.b1; ++b) {
+      for (int b = w.b0; b < w.b1; ++b, ++idx) {
+        if (static_cast<int>(idx % kSpan) != g % kSpan) continue;
+        const int stage = static_cast<int>(idx % kStages);
+        const uint32_t phase = static_cast<uint32_t>(idx / kStages) & 1u;
         const int n = b / p.bpi, j = b - n * p.bpi;
         const int hw0 = j * 64 + chunk * 8;
         const int valid = min(8, p.HWo - hw0);          // <= 0: the chunk lies past the end of the image
@@ -535,20 +565,39 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap tmG, const __grid_constant
         ok = __all_sync(0xffffffffu, ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag));
         if (!ok) break;
         uint8_t* a_stage = smem + stage * kStageBytes;
-        uint4 v[4];
+        if (p.fast) {
+#pragma unroll 1
+          for (int t0 = t_first; t0 < t_first + kStepsPerWarp; t0 += kBatch) {
+            RawChunk raw[kBatch];
 #pragma unroll
-        for (int it = 0; it < 4; ++it)
-          v[it] = (k_ok[it] && valid > 0) ? gather_core(p, img + plane_off[it], off[it], ho, wo, valid)
-                                          : make_uint4(0u, 0u, 0u, 0u);
+            for (int v = 0; v < kBatch; ++v) {
+              const int k = w.mt * kBM + 4 * (t0 + v) + r_quarter;
+              const bool on = valid > 0 && k < p.K;
+              const int c = on ? channel_of(p, k) : 0;
+              raw[v] = gather_issue(p, img + c * p.plane_pitch, tap_s[on ? k - c * p.taps : 0], ho, wo, on);
+            }
 #pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const int r = it * 32 + r_sub;
-          *reinterpret_cast<uint4*>(a_stage + r * 128 + ((chunk ^ (r & 7)) << 4)) = v[it];
+            for (int v = 0; v < kBatch; ++v) {
+              const int r = 4 * (t0 + v) + r_quarter;
+              *reinterpret_cast<uint4*>(a_stage + r * 128 + ((chunk ^ (r & 7)) << 4)) = gather_finish(raw[v]);
+            }
+          }
+        } else {
+#pragma unroll 2
+          for (int t0 = t_first; t0 < t_first + kStepsPerWarp; ++t0) {
+            const int r = 4 * t0 + r_quarter;
+            const int k = w.mt * kBM + r;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (valid > 0 && k < p.K) {
+              const int c = channel_of(p, k);
+              v = gather_general(p, img + c * p.plane_pitch, tap_s[k - c * p.taps], ho, wo, valid);
+            }
+            *reinterpret_cast<uint4*>(a_stage + r * 128 + ((chunk ^ (r & 7)) << 4)) = v;
+          }
         }
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(full_bar(stage));
-        if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
     }
   }
@@ -663,8 +712,8 @@ int conv_implicit_launch(const ImplicitConv& d, cudaStream_t s) {
   CUtensorMap tmW;
   if (!tc::make_operand_map(&tmW, d.dtype, d.Wm, d.K, d.Cout, d.ldw, 1, 0, kBK, bn, false)) return kCudaError;
   switch (bn) {
-    case 64:  return launch_cfg<64, 6>(tmW, p, s);
-    case 128: return launch_cfg<128, 6>(tmW, p, s);
+    case 64:  return launch_cfg<64, 9>(tmW, p, s);
+    case 128: return launch_cfg<128, 7>(tmW, p, s);
     default:  return launch_cfg<256, 4>(tmW, p, s);
   }
 }
@@ -711,8 +760,8 @@ int conv_wgrad_launch(const ImplicitWgrad& w, cudaStream_t s) {
     return kCudaError;
   int lrc;
   switch (bn) {
-    case 64:  lrc = launch_wgrad_cfg<64, 6>(tmG, p, s); break;
-    case 128: lrc = launch_wgrad_cfg<128, 6>(tmG, p, s); break;
+    case 64:  lrc = launch_wgrad_cfg<64, 9>(tmG, p, s); break;
+    case 128: lrc = launch_wgrad_cfg<128, 7>(tmG, p, s); break;
     default:  lrc = launch_wgrad_cfg<256, 4>(tmG, p, s); break;
   }
   if (lrc != kOk) return lrc;

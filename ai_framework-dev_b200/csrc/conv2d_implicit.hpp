@@ -52,4 +52,29 @@ int conv_implicit_launch(const ImplicitConv& d, cudaStream_t s);
 // Wt[ci][co * taps + t] = W[co][ci][t]: the weight as the input-gradient convolution reads it (pitch ldt elements).
 cudaError_t launch_transpose_weight(const void* W, void* Wt, int Cout, int Cin, int taps, long long ldt, cudaStream_t s);
 
+// ---- unit-stride convolution from a position-major input patch in shared memory (conv2d_patch.cu) ----
+// Y[n][co][ho][wo] = act(bias[co] + sum over c, kh, kw of X[n][c][ho + kh*dh - ph][wo + kw*dw - pw] . Wt(co, c, kh, kw))
+// with Wt(co, c, tap) = W[co * w_row_stride + c * w_chan_stride + tap'] and tap' = tap, or the mirrored tap when
+// flip_taps is set (the input-gradient form).
+struct PatchConv {
+  int dtype = kBF16;
+  const void* X = nullptr;
+  long long img_pitch = 0, plane_pitch = 0; int row_pitch = 0;
+  int imgs = 0, Cin = 0, H = 0, W = 0;
+  int ph = 0, pw = 0, Kh = 1, Kw = 1, dh = 1, dw = 1;
+  const void* W_ = nullptr;              // weight elements as described above
+  long long w_row_stride = 0, w_chan_stride = 0;
+  bool flip_taps = false;
+  void* Wr = nullptr;                    // scratch of conv_patch_weight_bytes(): the weight as the kernel reads it
+  int Cout = 0;
+  const float* bias = nullptr;
+  int act = kActNone; float leaky = 0.01f;
+  void* Y = nullptr;                     // dense planes of Ho x Wo
+  void* Z = nullptr; int z_dtype = kBF16;
+  long long out_img_pitch = 0;
+};
+size_t conv_patch_weight_bytes(const PatchConv& d);
+bool conv_patch_supported(const PatchConv& d);
+int conv_patch_launch(const PatchConv& d, cudaStream_t s);
+
 }  // namespace ge2b

@@ -928,18 +928,20 @@ def run_sweep(args):
     assert lib.ge2b_device_status(0) == 0
     if only == "attention":
         return
-    run_conv_points(pkg, lib, timeit)
+    run_conv_points(pkg, lib, timeit, timeit_graph)
 
 
 CONV_POINTS = [  # name, N, Cin, H, W, Cout, k, stride, pad  (ResNet-50-like layer shapes, batch 32)
-    ("3x3 64->64 56x56", 32, 64, 56, 56, 64, 3, 1, 1), ("3x3 128->128 28x28 s2", 32, 128, 56, 56, 128, 3, 2, 1),
+    ("3x3 64->64 56x56", 32, 64, 56, 56, 64, 3, 1, 1), ("3x3 128->128 28x28", 32, 128, 28, 28, 128, 3, 1, 1),
+    ("3x3 128->128 28x28 s2", 32, 128, 56, 56, 128, 3, 2, 1),
     ("3x3 256->256 14x14", 32, 256, 14, 14, 256, 3, 1, 1), ("1x1 256->1024 14x14", 32, 256, 14, 14, 1024, 1, 1, 0),
     ("7x7 3->64 224x224 s2", 32, 3, 224, 224, 64, 7, 2, 3)]
 
 
-def run_conv_points(pkg, lib, timeit):
-    """conv2d (+bias+ReLU, pre-activation saved) forward and backward on the GEMM kernels, and the reference's own
-    conv2d op (fp32, per-image loop) where its library was built.  One JSON line per point."""
+def run_conv_points(pkg, lib, timeit, timeit_graph):
+    """conv2d (+bias+ReLU, pre-activation saved) forward and backward through this library (replayed from a CUDA graph:
+    no host launch cost in the timed region), the reference's own conv2d op (fp32, per-image loop) where its library
+    was built, and torch's convolution of the same bf16 layer for context.  One JSON line per point."""
     import ctypes as C
     import torch
     cv = pkg.ops_conv2d
@@ -964,7 +966,7 @@ def run_conv_points(pkg, lib, timeit):
                                           math=math, **kw)
             bwd = lambda: cv.backward_into(X, Wt, dY, Z, with_bias=True, act="relu", gX_out=gX, gW_out=gW,  # noqa: E731
                                            gB_out=gB, math=math, **kw)
-            t_f, t_b = timeit(fwd, 5), timeit(bwd, 5)
+            t_f, t_b = timeit_graph(fwd, 5), timeit_graph(bwd, 5)
             rec = {"sweep": "conv2d", "layer": name, "N": N, "dtype": str(dt)[6:], "math": math,
                    "fwd_ms": round(t_f, 4), "fwd_tflops": round(flop / t_f / 1e9, 1),
                    "bwd_ms": round(t_b, 4), "bwd_tflops": round(2 * flop / t_b / 1e9, 1)}
@@ -976,6 +978,13 @@ def run_conv_points(pkg, lib, timeit):
                                                    gB.data_ptr(), gX.data_ptr(), *geom, 1, 0.01, None)
                 rec["reference_fwd_ms"] = round(timeit(rf, 1, reps=3), 3)
                 rec["reference_bwd_ms"] = round(timeit(rb, 1, reps=3), 3)
+            if dt == torch.bfloat16:
+                bt = b.to(dt)
+                try:
+                    rec["torch_fwd_ms"] = round(timeit_graph(
+                        lambda: torch.relu(torch.nn.functional.conv2d(X, Wt, bt, **kw)), 5), 4)
+                except Exception:
+                    rec["torch_fwd_ms"] = None
             print(json.dumps(rec), flush=True)
     assert lib.ge2b_device_status(0) == 0
 

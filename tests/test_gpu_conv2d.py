@@ -174,6 +174,15 @@ IMPLICIT_GEOMS = {
     "4x2_w8_even_taps": (3, 3, 9, 8, 4, 4, 2, (1, 1), (2, 1), (1, 1)),
     "3x3_cout_300":     (1, 16, 16, 16, 300, 3, 3, (1, 1), (1, 1), (1, 1)),   # two channel tiles, ragged second one
     "3x3_cout_100":     (2, 12, 10, 16, 100, 3, 3, (1, 1), (1, 1), (1, 1)),   # 128-wide channel tile
+    # reductions longer than the operand ring of the 256- and 128-channel tiles (4 and 7 stages): the ring wraps
+    "3x3_deep_cout_300": (2, 64, 8, 16, 300, 3, 3, (1, 1), (1, 1), (1, 1)),
+    "3x3_deep_cout_100": (4, 64, 16, 16, 100, 3, 3, (1, 1), (1, 1), (1, 1)),
+    "3x3_deep_w12":      (3, 72, 10, 12, 130, 3, 3, (1, 1), (1, 1), (1, 1)),   # the same with the element-wise gather
+    # several 64-channel blocks per tile (the patch is refilled per block), odd widths for the narrower fill loads
+    "3x3_cin_160_w28":   (2, 160, 9, 28, 48, 3, 3, (1, 1), (1, 1), (1, 1)),
+    "3x3_cin_128_w14":   (3, 128, 14, 14, 64, 3, 3, (1, 1), (1, 1), (1, 1)),
+    "3x3_cin_64_w7":     (5, 64, 7, 7, 96, 3, 3, (1, 1), (1, 1), (1, 1)),
+    "5x5_cin_96_pad1":   (2, 96, 13, 20, 40, 5, 5, (1, 1), (1, 1), (1, 1)),
     "3x3_stride2":      GEOMS["3x3_stride2"],
     "5x3_dilated":      GEOMS["5x3_dilated"],
     "7x7_stem":         GEOMS["7x7_stem"],
@@ -184,10 +193,11 @@ IMPLICIT_GEOMS = {
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("name", sorted(IMPLICIT_GEOMS))
 def test_implicit_gemm_routes(pkg, lib, oracle, conv_oracle, monkeypatch, name, dtype):
-    """Forward (Y, Z) and the input gradient through the implicit-GEMM kernel with its aligned gather where it
-    applies, with the element-wise gather everywhere, and through the column-matrix route: the two gathers feed the
-    same arithmetic (bit-identical results), the column-matrix route sums in another order (close), and all three
-    stay inside the bf16 / f16 bound against float64."""
+    """Forward (Y, Z), input gradient and weight gradient through every route: chosen by shape (the shared-memory
+    patch kernel for unit-stride passes), the gathering kernels with their aligned gather where it applies, the same
+    with the element-wise gather everywhere, and the column matrix in memory.  The two gathers feed the same
+    arithmetic (bit-identical results), the other routes sum in another order (close), and all of them stay inside the
+    bf16 / f16 bound against float64."""
     g = IMPLICIT_GEOMS[name]
     X, Wt, b, dY = conv_oracle.conv_inputs(*g[:7], seed=11, **_kw(g))
     if dtype == torch.bfloat16:
@@ -197,8 +207,11 @@ def test_implicit_gemm_routes(pkg, lib, oracle, conv_oracle, monkeypatch, name, 
     tX, tW, tdY = dev(X, dtype), dev(Wt, dtype), dev(dY, dtype)
     Y64, Z64 = conv_oracle.forward_f64(X, Wt, b, act="tanh", **_kw(g))
     got = {}
-    for route in ("implicit", "general", "explicit"):
-        monkeypatch.setenv("GE2B_CONV", route)
+    for route in ("auto", "gather", "general", "explicit"):
+        if route == "auto":
+            monkeypatch.delenv("GE2B_CONV", raising=False)
+        else:
+            monkeypatch.setenv("GE2B_CONV", route)
         Y, Z = pkg.ops_conv2d.forward(tX, tW, dev(b), with_bias=True, act="tanh", save_z=True, z_dtype=torch.float32,
                                       **_kw(g))
         out = pkg.ops_conv2d.backward(tX, tW, tdY, Z, with_bias=True, act="tanh", want_gB=True, **_kw(g))
@@ -214,15 +227,16 @@ def test_implicit_gemm_routes(pkg, lib, oracle, conv_oracle, monkeypatch, name, 
         eps = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -9     # 16-bit epilogues use tanh.approx
         assert float(np.abs(host(Z) - Z64).max()) <= 1e-5 * K + 1e-6, route
         assert float(np.abs(host(Y) - Y64).max()) <= eps + 1e-5 * K, route
-    for a, c in zip(got["implicit"], got["general"]):
+    for a, c in zip(got["gather"], got["general"]):
         assert torch.equal(a, c)
-    for a, c in zip(got["implicit"][:3], got["explicit"][:3]):
-        assert float((a.float() - c.float()).abs().max()) <= 2e-2 * max(1.0, float(c.float().abs().max()))
+    for other in ("auto", "gather"):
+        for a, c in zip(got[other], got["explicit"]):
+            assert float((a.float() - c.float()).abs().max()) <= 2e-2 * max(1.0, float(c.float().abs().max()))
 
 
 def test_implicit_gemm_is_the_default_route_and_moves_no_column_matrix(pkg, lib, monkeypatch):
-    """On a ResNet-sized layer the default forward is ONE launch (the column-matrix route takes two and allocates
-    K x N x HWo elements)."""
+    """On a ResNet-sized layer the default forward is the weight re-layout plus ONE convolution launch (the
+    column-matrix route allocates and fills K x N x HWo elements first)."""
     monkeypatch.delenv("GE2B_CONV", raising=False)
     g = torch.Generator(device="cuda").manual_seed(5)
     X = torch.randn((4, 64, 56, 56), device="cuda", generator=g).bfloat16()
@@ -233,7 +247,7 @@ def test_implicit_gemm_is_the_default_route_and_moves_no_column_matrix(pkg, lib,
     before = lib.ge2b_launches_total()
     Y = pkg.ops_conv2d.forward(X, W, b, with_bias=True, act="relu", padding=(1, 1))
     torch.cuda.synchronize()
-    assert lib.ge2b_launches_total() - before == 1
+    assert lib.ge2b_launches_total() - before == 2
     assert lib.ge2b_last_route() == 2
     want = torch.nn.functional.conv2d(X.float(), W.float(), b, padding=1).relu()
     assert float((Y.float() - want).abs().max()) <= 2.0 ** -7 * float(want.abs().max())
