@@ -234,6 +234,43 @@ def test_implicit_gemm_routes(pkg, lib, oracle, conv_oracle, monkeypatch, name, 
             assert float((a.float() - c.float()).abs().max()) <= 2e-2 * max(1.0, float(c.float().abs().max()))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("name", ["3x3_w16", "3x3_cin_160_w28", "3x3_cin_128_w14", "3x3_cin_64_w7", "5x5_cin_96_pad1",
+                                  "3x3_deep_cout_300", "3x3_w32_valid"])
+def test_patch_kernel_with_16bit_preactivation(pkg, lib, oracle, conv_oracle, monkeypatch, name, dtype):
+    """Z saved in the tensors' own 16-bit type: on even widths the patch kernel's epilogue writes two positions per
+    32-bit store (neighbouring lanes swap one value per channel pair), on odd widths one element per store.  Y and Z
+    against float64 and, element for element, against the column-matrix route."""
+    g = IMPLICIT_GEOMS[name]
+    X, Wt, b, dY = conv_oracle.conv_inputs(*g[:7], seed=23, **_kw(g))
+    rnd = oracle.bf16_round if dtype == torch.bfloat16 else (lambda a: a.astype(np.float16).astype(np.float32))
+    X, Wt = rnd(X), rnd(Wt)
+    tX, tW = dev(X, dtype), dev(Wt, dtype)
+    Y64, Z64 = conv_oracle.forward_f64(X, Wt, b, act="leaky_relu", **_kw(g))
+    eps = 2.0 ** -8 if dtype == torch.bfloat16 else 2.0 ** -11
+    got = {}
+    for route in ("auto", "explicit"):
+        if route == "auto":
+            monkeypatch.delenv("GE2B_CONV", raising=False)
+        else:
+            monkeypatch.setenv("GE2B_CONV", route)
+        for with_bias in (True, False):
+            Y, Z = pkg.ops_conv2d.forward(tX, tW, dev(b) if with_bias else None, with_bias=with_bias, act="leaky_relu",
+                                          save_z=True, **_kw(g))
+            torch.cuda.synchronize()
+            assert Z.dtype == dtype
+            if with_bias:
+                got[route] = (Y, Z)
+                scale = float(np.abs(Z64).max())
+                assert float(np.abs(host(Z) - Z64).max()) <= eps * scale + 1e-5 * g[1] * g[5] * g[6], route
+                assert float(np.abs(host(Y) - Y64).max()) <= eps * scale + 1e-5 * g[1] * g[5] * g[6], route
+            else:
+                Y0, Z0 = conv_oracle.forward_f64(X, Wt, np.zeros_like(b), act="leaky_relu", **_kw(g))
+                assert oracle.rel_fro(host(Z), Z0) <= FRO_TOL and oracle.rel_fro(host(Y), Y0) <= FRO_TOL
+    for a, c in zip(got["auto"], got["explicit"]):
+        assert float((a.float() - c.float()).abs().max()) <= 2 * eps * max(1.0, float(c.float().abs().max()))
+
+
 def test_implicit_gemm_is_the_default_route_and_moves_no_column_matrix(pkg, lib, monkeypatch):
     """On a ResNet-sized layer the default forward is the weight re-layout plus ONE convolution launch (the
     column-matrix route allocates and fills K x N x HWo elements first)."""
