@@ -500,7 +500,13 @@ bool patch_geometry(const PatchConv& d, PatchParams& p) {
   return tc::driver_has_tensor_maps();
 }
 
-int patch_tile_n(int Cout) { return Cout <= 64 ? 64 : (Cout <= 128 ? 128 : 256); }
+// Output channels per tile: the widest tile that still gives every SM a tile (a wide tile copies each patch for more
+// channels at once, but a 14 x 14 or 7 x 7 layer has too few position tiles to fill the GPU with wide ones).
+int patch_tile_n(int Cout, long long position_tiles) {
+  int bn = Cout <= 64 ? 64 : (Cout <= 128 ? 128 : 256);
+  while (bn > 64 && position_tiles * ((Cout + bn - 1) / bn) < sm_budget()) bn >>= 1;
+  return bn;
+}
 
 template <typename F>
 int for_patch_cfg(int bn, const PatchParams& p, F&& f) {
@@ -530,7 +536,7 @@ size_t conv_patch_weight_bytes(const PatchConv& d) {
 bool conv_patch_supported(const PatchConv& d) {
   PatchParams p{};
   if (!patch_geometry(d, p)) return false;
-  const int bn = patch_tile_n(d.Cout);
+  const int bn = patch_tile_n(d.Cout, static_cast<long long>(d.imgs) * p.tiles_per_img);
   CUtensorMap dummy{};
   return for_patch_cfg(bn, p, [&](auto bn_c, auto st_c) {
            return launch_patch_cfg<decltype(bn_c)::value, decltype(st_c)::value>(dummy, p, nullptr, true);
@@ -541,7 +547,7 @@ int conv_patch_launch(const PatchConv& d, cudaStream_t s) {
   PatchParams p{};
   if (!patch_geometry(d, p)) return kUnimplemented;
   if (!d.Wr || !d.W_ || !d.Y) return kBadArgs;
-  const int bn = patch_tile_n(d.Cout);
+  const int bn = patch_tile_n(d.Cout, static_cast<long long>(d.imgs) * p.tiles_per_img);
   p.n_tiles = (d.Cout + bn - 1) / bn;
   p.tiles = static_cast<long long>(d.imgs) * p.tiles_per_img * p.n_tiles;
   p.Cout = d.Cout;
