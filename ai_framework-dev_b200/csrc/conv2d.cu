@@ -477,7 +477,8 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
   }
 
   bool dx_done = false;
-  if (dX && sixteen && route == kConvAuto && g.sh == 1 && g.sw == 1 &&
+  // (1 x 1 layers measured faster through the batched GEMM: their dCol is dX itself or one small copy)
+  if (dX && sixteen && route == kConvAuto && g.sh == 1 && g.sw == 1 && g.Kh * g.Kw > 1 &&
       g.ph <= (g.Kh - 1) * g.dh && g.pw <= (g.Kw - 1) * g.dw &&
       patch_worthwhile(g.Cout, g.Kh, g.Kw, g.dh, g.dw, g.Wo + 2 * ((g.Kw - 1) * g.dw - g.pw))) {
     // Input gradient of a unit-stride convolution = convolution of gZ (border dil*(K-1) - pad) with the taps mirrored
