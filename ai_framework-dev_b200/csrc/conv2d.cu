@@ -27,6 +27,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <vector>
 
 namespace ge2b {
 namespace {
@@ -478,7 +479,7 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
 
   bool dx_done = false;
   // (1 x 1 layers measured faster through the batched GEMM: their dCol is dX itself or one small copy)
-  if (dX && sixteen && route == kConvAuto && g.sh == 1 && g.sw == 1 && g.Kh * g.Kw > 1 &&
+  if (dX && sixteen && route == kConvAuto && g.sh == 1 && g.sw == 1 && g.Kh * g.Kw > 1 && g.Cin >= 16 &&
       g.ph <= (g.Kh - 1) * g.dh && g.pw <= (g.Kw - 1) * g.dw &&
       patch_worthwhile(g.Cout, g.Kh, g.Kw, g.dh, g.dw, g.Wo + 2 * ((g.Kw - 1) * g.dw - g.pw))) {
     // Input gradient of a unit-stride convolution = convolution of gZ (border dil*(K-1) - pad) with the taps mirrored
@@ -501,6 +502,81 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
       else if (rc != kUnimplemented) return rc;
     }
   }
+  // (not for layers with a handful of input channels, e.g. an RGB stem: the kernel's narrowest output tile is 64 wide)
+  if (dX && !dx_done && sixteen && route == kConvAuto && (g.sh > 1 || g.sw > 1) && g.sh <= 4 && g.sw <= 4 &&
+      (g.Cout + 63) / 64 * 64 <= 2 * g.Cout && g.Cin >= 16) {
+    // Strided convolution: the input pixels (h, w) with h % sh == a and w % sw == b receive only the taps with
+    // (a + ph - kh*dh) % sh == 0 and (b + pw - kw*dw) % sw == 0, and for those dX[a + sh*i][b + sw*j] is a UNIT-stride
+    // correlation of gZ: sum of gZ[i + (a + ph - kh*dh)/sh][j + (b + pw - kw*dw)/sw] . W[.., kh, kw].  One patch-kernel
+    // launch per phase (a, b), each writing its own pixels of dX; no dCol, no col2im.
+    struct Phase { PatchConv d; bool empty; };
+    std::vector<Phase> phases;
+    bool all_ok = true, any_empty = false;
+    for (int a = 0; a < g.sh && all_ok; ++a)
+      for (int b = 0; b < g.sw && all_ok; ++b) {
+        Phase ph{};
+        PatchConv& d = ph.d;
+        const int Hph = (g.H - a + g.sh - 1) / g.sh, Wph = (g.W - b + g.sw - 1) / g.sw;
+        if (Hph <= 0 || Wph <= 0) continue;
+        int qh[kConvMaxTaps], qw[kConvMaxTaps], kh_of[kConvMaxTaps], kw_of[kConvMaxTaps], nh = 0, nw = 0;
+        for (int kh = 0; kh < g.Kh; ++kh) {
+          const int num = a + g.ph - kh * g.dh;
+          if (((num % g.sh) + g.sh) % g.sh == 0) { qh[nh] = (num - (((num % g.sh) + g.sh) % g.sh)) / g.sh; kh_of[nh++] = kh; }
+        }
+        for (int kw = 0; kw < g.Kw; ++kw) {
+          const int num = b + g.pw - kw * g.dw;
+          if (((num % g.sw) + g.sw) % g.sw == 0) { qw[nw] = (num - (((num % g.sw) + g.sw) % g.sw)) / g.sw; kw_of[nw++] = kw; }
+        }
+        ph.empty = nh == 0 || nw == 0;
+        any_empty = any_empty || ph.empty;
+        if (!ph.empty) {
+          int top = 0, left = 0;                       // zero border so that every tap offset is >= 0
+          for (int i = 0; i < nh; ++i) top = std::max(top, -qh[i]);
+          for (int i = 0; i < nw; ++i) left = std::max(left, -qw[i]);
+          int max_tc = 0;
+          d.n_taps = nh * nw;
+          for (int i = 0; i < nh; ++i)
+            for (int j = 0; j < nw; ++j) {
+              const int t = i * nw + j;
+              d.tap_r[t] = qh[i] + top; d.tap_c[t] = qw[j] + left;
+              d.tap_src[t] = kh_of[i] * g.Kw + kw_of[j];
+              max_tc = std::max(max_tc, d.tap_c[t]);
+            }
+          d.dtype = p.dtype;
+          d.X = gz.p; d.img_pitch = gz_stride; d.plane_pitch = g.HWp; d.row_pitch = g.Wo;
+          d.imgs = g.N; d.Cin = g.Cout; d.H = g.Ho; d.W = g.Wo;
+          d.ph = top; d.pw = left;
+          d.Wp = std::max(g.Wo + left, Wph + max_tc);
+          d.out_H = Hph; d.out_W = Wph;
+          d.W_ = W; d.w_row_stride = static_cast<long long>(g.Kh) * g.Kw; d.w_chan_stride = g.K;
+          d.Cout = g.Cin;
+          d.Y = dX;
+          d.out_img_pitch = static_cast<long long>(g.Cin) * g.H * g.W;
+          d.out_plane = static_cast<long long>(g.H) * g.W; d.out_row_pitch = g.W;
+          d.osh = g.sh; d.osw = g.sw; d.out_off = a * g.W + b;
+          all_ok = conv_patch_supported(d);
+        }
+        phases.push_back(ph);
+      }
+    if (all_ok && !phases.empty()) {
+      size_t wbytes = 0;
+      for (const Phase& ph : phases) if (!ph.empty) wbytes = std::max(wbytes, conv_patch_weight_bytes(ph.d));
+      AsyncBuf wr(s);
+      if (wr.alloc(wbytes)) {
+        // pixels of a phase without taps (kernel smaller than the stride) get no contribution at all
+        if (any_empty && cudaMemsetAsync(dX, 0, static_cast<size_t>(g.N) * g.Cin * g.H * g.W * esz, s) != cudaSuccess)
+          return kCudaError;
+        dx_done = true;
+        for (Phase& ph : phases) {
+          if (ph.empty) continue;
+          ph.d.Wr = wr.p;
+          const int rc = conv_patch_launch(ph.d, s);
+          if (rc != kOk) return rc == kUnimplemented ? kCudaError : rc;
+        }
+      }
+    }
+  }
+
   // (gZ rows are Wo wide and dX rows W wide: the aligned gather needs both to be multiples of 8)
   if (dX && !dx_done && sixteen && g.sh == 1 && g.sw == 1 &&
       (route == kConvGather || route == kConvGatherGeneral || (route == kConvAuto && wgrad_aligned))) {

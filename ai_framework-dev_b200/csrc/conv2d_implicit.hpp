@@ -72,6 +72,16 @@ struct PatchConv {
   void* Y = nullptr;                     // dense planes of Ho x Wo
   void* Z = nullptr; int z_dtype = kBF16;
   long long out_img_pitch = 0;
+  // Optional generalisations (zero: the plain convolution described above).
+  // A list of taps instead of the Kh x Kw grid: tap i reads the padded pixel (ho + tap_r[i], wq + tap_c[i]) and uses
+  // the weight's tap tap_src[i]; Kh, Kw, dh, dw and flip_taps are then unused.
+  int n_taps = 0;
+  int tap_r[kConvMaxTaps] = {}, tap_c[kConvMaxTaps] = {}, tap_src[kConvMaxTaps] = {};
+  int Wp = 0;                            // padded row width (>= W + pw and >= out_W + largest tap_c)
+  int out_H = 0, out_W = 0;              // output extent
+  // Output position (ho, wq) of channel co is written to Y[n*out_img_pitch + co*out_plane + ho*osh*out_row_pitch +
+  // wq*osw + out_off] (defaults: dense planes of out_H x out_W).
+  long long out_plane = 0; int out_row_pitch = 0, osh = 0, osw = 0, out_off = 0;
 };
 size_t conv_patch_weight_bytes(const PatchConv& d);
 bool conv_patch_supported(const PatchConv& d);

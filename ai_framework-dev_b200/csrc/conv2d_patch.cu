@@ -25,6 +25,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <mutex>
 #include <type_traits>
 
@@ -55,7 +56,9 @@ struct PatchParams {
   int V;                                  // elements per fill load: 8, 4, 2 or 1
   int Cout;
   void* Y; void* Z; const float* bias;
-  long long out_img_pitch;                // elements from image to image in Y / Z (planes of Ho * Wo)
+  long long out_img_pitch;                // elements from image to image in Y / Z
+  int out_plane, out_row_pitch;           // elements from channel plane to plane / row to row of the output
+  int osh, osw, out_off;                  // output pixel of position (ho, wq): row ho*osh, column wq*osw, plus out_off
   int y_dtype, z_dtype, act;
   float leaky;
   uint32_t idesc;
@@ -316,10 +319,11 @@ conv_patch_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   } else if (warp < kFillWarp0) {
     // ===================== epilogue =====================
     const int q = warp & 3;                            // hardware rule: a warp reads TMEM lanes 32*(warp%4)..+31
-    const int plane = p.Ho * p.Wo;
+    const int plane = p.out_plane;
     const int zkind = p.Z == nullptr ? 0 : (p.z_dtype == kF32 ? 2 : 1);
     // two positions per store where pairs of lanes map to pairs of pixels of one row on 4-byte boundaries
-    const bool pairs = !(p.Wo & 1) && !(p.Wp & 1) && !(p.out_img_pitch & 1) && (p.Z == nullptr || p.z_dtype != kF32) &&
+    const bool pairs = p.osw == 1 && !(p.Wo & 1) && !(p.Wp & 1) && !(p.out_img_pitch & 1) && !(p.out_plane & 1) &&
+                       !(p.out_row_pitch & 1) && !(p.out_off & 1) && (p.Z == nullptr || p.z_dtype != kF32) &&
                        !((reinterpret_cast<uintptr_t>(p.Y) | reinterpret_cast<uintptr_t>(p.Z)) & 3);
     float* bias_s = bias_all + (warp - 2) * kBN;
     int bias_nt = -1;
@@ -338,7 +342,7 @@ conv_patch_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const int u = w.j * kPM + q * 32 + lane;         // padded position of this lane
       const int ho = u / p.Wp, wq = u - ho * p.Wp;
       const bool pos_ok = ho < p.Ho && wq < p.Wo;
-      const long long off0 = w.n * p.out_img_pitch + (pos_ok ? ho * p.Wo + wq : 0);
+      const long long off0 = w.n * p.out_img_pitch + (pos_ok ? ho * p.osh * p.out_row_pitch + wq * p.osw + p.out_off : 0);
       ok = __all_sync(0xffffffffu, ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag));
       if (!ok) break;
       ptx::tc_fence_after_sync();
@@ -432,17 +436,17 @@ conv_patch_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   }
 }
 
-// Wr[o][tap' * Cp + c] = W[o * so + c * sc + tap]  (tap = flip ? taps - 1 - tap' : tap'), zero for c >= C.
+// Wr[o][t * Cp + c] = W[o * so + c * sc + map.src[t]] for the taps t the convolution uses, zero for c >= C.
+struct TapMap { int src[kConvMaxTaps]; };
 __global__ void relayout_weight_kernel(const unsigned short* __restrict__ W, unsigned short* __restrict__ Wr, int rows,
-                                       int C, int Cp, int taps, long long so, long long sc, int flip) {
+                                       int C, int Cp, int taps, long long so, long long sc, const TapMap map) {
   const long long total = static_cast<long long>(rows) * taps * Cp;
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += gridDim.x * 256ll) {
     const int c = static_cast<int>(i % Cp);
     const long long r = i / Cp;
-    const int tp = static_cast<int>(r % taps);
+    const int t = static_cast<int>(r % taps);
     const long long o = r / taps;
-    const int tap = flip ? taps - 1 - tp : tp;
-    Wr[i] = c < C ? W[o * so + c * sc + tap] : static_cast<unsigned short>(0);
+    Wr[i] = c < C ? W[o * so + c * sc + map.src[t]] : static_cast<unsigned short>(0);
   }
 }
 
@@ -468,16 +472,44 @@ int launch_patch_cfg(const CUtensorMap& tmW, PatchParams& p, cudaStream_t s, boo
   return kOk;
 }
 
+// The taps of a call: the full Kh x Kw grid (mirrored for the input-gradient form) or the caller's list.
+struct TapList { int n; int r[kConvMaxTaps], c[kConvMaxTaps], src[kConvMaxTaps]; };
+bool make_taps(const PatchConv& d, TapList& t) {
+  if (d.n_taps > 0) {
+    if (d.n_taps > kConvMaxTaps) return false;
+    t.n = d.n_taps;
+    for (int i = 0; i < t.n; ++i) {
+      if (d.tap_r[i] < 0 || d.tap_c[i] < 0 || d.tap_src[i] < 0) return false;
+      t.r[i] = d.tap_r[i]; t.c[i] = d.tap_c[i]; t.src[i] = d.tap_src[i];
+    }
+    return true;
+  }
+  if (d.Kh < 1 || d.Kw < 1 || d.Kh * d.Kw > kConvMaxTaps || d.dh < 1 || d.dw < 1) return false;
+  t.n = d.Kh * d.Kw;
+  for (int kh = 0; kh < d.Kh; ++kh)
+    for (int kw = 0; kw < d.Kw; ++kw) {
+      const int i = kh * d.Kw + kw;
+      t.r[i] = kh * d.dh; t.c[i] = kw * d.dw;
+      t.src[i] = d.flip_taps ? t.n - 1 - i : i;
+    }
+  return true;
+}
+
 // Fills the geometry part of the parameters; false when the shape is outside what the kernel takes.
-bool patch_geometry(const PatchConv& d, PatchParams& p) {
+bool patch_geometry(const PatchConv& d, PatchParams& p, TapList& taps) {
   if (!(d.dtype == kBF16 || d.dtype == kF16)) return false;
-  if (d.Kh < 1 || d.Kw < 1 || d.Kh * d.Kw > kConvMaxTaps || d.ph < 0 || d.pw < 0 || d.dh < 1 || d.dw < 1) return false;
+  if (d.ph < 0 || d.pw < 0 || !make_taps(d, taps)) return false;
   if (d.imgs < 1 || d.Cin < 1 || d.Cout < 1 || d.H < 1 || d.W < 1) return false;
-  const int max_tr = (d.Kh - 1) * d.dh, max_tc = (d.Kw - 1) * d.dw;
+  int max_tr = 0, max_tc = 0;
+  for (int i = 0; i < taps.n; ++i) { max_tr = std::max(max_tr, taps.r[i]); max_tc = std::max(max_tc, taps.c[i]); }
   p.Cin = d.Cin; p.H = d.H; p.W = d.W; p.ph = d.ph; p.pw = d.pw;
-  p.Wp = d.W + 2 * d.pw; p.Hp = d.H + 2 * d.ph;
-  p.Ho = p.Hp - max_tr; p.Wo = p.Wp - max_tc;
+  p.Wp = d.Wp > 0 ? d.Wp : d.W + 2 * d.pw;
+  p.Hp = d.H + d.ph;                       // rows from here on hold no pixels (they read as zero)
+  p.Ho = d.out_H > 0 ? d.out_H : d.H + 2 * d.ph - max_tr;
+  p.Wo = d.out_W > 0 ? d.out_W : p.Wp - max_tc;
   if (p.Ho < 1 || p.Wo < 1) return false;
+  // a row of the padded plane must hold the pixels and everything a valid output reads
+  if (p.Wp < d.W + d.pw || p.Wp < p.Wo + max_tc) return false;
   const long long upos = static_cast<long long>(p.Ho) * p.Wp;           // padded output positions per image
   const long long max_shift = static_cast<long long>(max_tr) * p.Wp + max_tc;
   if (upos > (1 << 28) || max_shift > 1400) return false;
@@ -486,9 +518,13 @@ bool patch_geometry(const PatchConv& d, PatchParams& p) {
   p.tiles_per_img = static_cast<int>((upos + kPM - 1) / kPM);
   p.cblocks = (d.Cin + 63) / 64;
   p.Cp = p.cblocks * 64;
-  p.taps = d.Kh * d.Kw;
-  for (int kh = 0; kh < d.Kh; ++kh)
-    for (int kw = 0; kw < d.Kw; ++kw) p.shift[kh * d.Kw + kw] = kh * d.dh * p.Wp + kw * d.dw;
+  p.taps = taps.n;
+  for (int i = 0; i < taps.n; ++i) p.shift[i] = taps.r[i] * p.Wp + taps.c[i];
+  // output addressing: dense planes unless the caller spreads the positions out
+  p.out_row_pitch = d.out_row_pitch > 0 ? d.out_row_pitch : p.Wo;
+  p.out_plane = d.out_plane > 0 ? static_cast<int>(d.out_plane) : p.Ho * p.Wo;
+  p.osh = d.osh > 0 ? d.osh : 1; p.osw = d.osw > 0 ? d.osw : 1; p.out_off = d.out_off;
+  if (d.out_plane > 0x7fffffffll) return false;
   // channel offsets stay inside 32-bit arithmetic in the fill
   if (d.img_pitch > 0x7fffffffll || d.plane_pitch * d.Cin > 0x7fffffffll) return false;
   p.X = static_cast<const unsigned short*>(d.X);
@@ -530,12 +566,14 @@ int for_patch_cfg(int bn, const PatchParams& p, F&& f) {
 }  // namespace
 
 size_t conv_patch_weight_bytes(const PatchConv& d) {
-  return static_cast<size_t>(d.Cout) * d.Kh * d.Kw * ((d.Cin + 63) / 64 * 64) * 2;
+  const int taps = d.n_taps > 0 ? d.n_taps : d.Kh * d.Kw;
+  return static_cast<size_t>(d.Cout) * taps * ((d.Cin + 63) / 64 * 64) * 2;
 }
 
 bool conv_patch_supported(const PatchConv& d) {
   PatchParams p{};
-  if (!patch_geometry(d, p)) return false;
+  TapList taps{};
+  if (!patch_geometry(d, p, taps)) return false;
   const int bn = patch_tile_n(d.Cout, static_cast<long long>(d.imgs) * p.tiles_per_img);
   CUtensorMap dummy{};
   return for_patch_cfg(bn, p, [&](auto bn_c, auto st_c) {
@@ -545,7 +583,8 @@ bool conv_patch_supported(const PatchConv& d) {
 
 int conv_patch_launch(const PatchConv& d, cudaStream_t s) {
   PatchParams p{};
-  if (!patch_geometry(d, p)) return kUnimplemented;
+  TapList taps{};
+  if (!patch_geometry(d, p, taps)) return kUnimplemented;
   if (!d.Wr || !d.W_ || !d.Y) return kBadArgs;
   const int bn = patch_tile_n(d.Cout, static_cast<long long>(d.imgs) * p.tiles_per_img);
   p.n_tiles = (d.Cout + bn - 1) / bn;
@@ -557,6 +596,8 @@ int conv_patch_launch(const PatchConv& d, cudaStream_t s) {
   p.status = device_status_ptr();
   if (!p.status) return kCudaError;
   // weight -> Wr[Cout][tap][Cp]
+  TapMap map{};
+  for (int i = 0; i < taps.n; ++i) map.src[i] = taps.src[i];
   const long long ldr = static_cast<long long>(p.taps) * p.Cp;
   {
     const long long total = static_cast<long long>(d.Cout) * ldr;
@@ -564,7 +605,7 @@ int conv_patch_launch(const PatchConv& d, cudaStream_t s) {
     if (blocks > 4096) blocks = 4096;
     relayout_weight_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(
         static_cast<const unsigned short*>(d.W_), static_cast<unsigned short*>(d.Wr), d.Cout, d.Cin, p.Cp, p.taps, d.w_row_stride,
-        d.w_chan_stride, d.flip_taps ? 1 : 0);
+        d.w_chan_stride, map);
     if (cudaGetLastError() != cudaSuccess) return kCudaError;
     note_tensor_launch(1);
   }

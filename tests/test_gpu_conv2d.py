@@ -183,6 +183,13 @@ IMPLICIT_GEOMS = {
     "3x3_cin_128_w14":   (3, 128, 14, 14, 64, 3, 3, (1, 1), (1, 1), (1, 1)),
     "3x3_cin_64_w7":     (5, 64, 7, 7, 96, 3, 3, (1, 1), (1, 1), (1, 1)),
     "5x5_cin_96_pad1":   (2, 96, 13, 20, 40, 5, 5, (1, 1), (1, 1), (1, 1)),
+    # strided layers with enough output channels for the per-phase input-gradient launches (one unit-stride
+    # correlation per residue of the input pixel modulo the stride); 1x1 / stride 2 leaves three of four phases empty
+    "3x3_s2_cout_64":    (2, 24, 18, 20, 64, 3, 3, (2, 2), (1, 1), (1, 1)),
+    "3x3_s2_odd_hw":     (2, 16, 17, 15, 40, 3, 3, (2, 2), (1, 1), (1, 1)),
+    "5x5_s3x2_dil":      (1, 16, 23, 26, 64, 5, 5, (3, 2), (2, 2), (1, 2)),
+    "1x1_s2":            (2, 32, 12, 12, 64, 1, 1, (2, 2), (0, 0), (1, 1)),
+    "2x2_s2_tiles":      (2, 16, 12, 16, 32, 2, 2, (2, 2), (0, 0), (1, 1)),
     "3x3_stride2":      GEOMS["3x3_stride2"],
     "5x3_dilated":      GEOMS["5x3_dilated"],
     "7x7_stem":         GEOMS["7x7_stem"],
