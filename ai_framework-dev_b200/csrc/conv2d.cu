@@ -386,7 +386,9 @@ int conv2d_backward(const ge2b_conv2d_params_t& p, const void* X, const void* W,
   const bool sixteen = p.dtype != kF32 && !pw && g.Kh * g.Kw <= kConvMaxTaps;
   // (by shape: where the aligned 16-byte gather applies; other shapes measured faster through the column matrix)
   const bool wgrad_aligned = g.sw == 1 && g.W % 8 == 0 && g.Wo % 8 == 0;
-  if (dW && sixteen && (route == kConvGather || route == kConvGatherGeneral || (route == kConvAuto && wgrad_aligned))) {
+  // (small planes, 14 x 14 and below, also measured faster gathered than through a column matrix of short rows)
+  const bool wgrad_gather = wgrad_aligned || g.HWo <= 256;
+  if (dW && sixteen && (route == kConvGather || route == kConvGatherGeneral || (route == kConvAuto && wgrad_gather))) {
     // weight gradient with the column tiles gathered inside the kernel (no Col), slices summed in fixed order
     ImplicitWgrad w;
     ImplicitConv& d = w.in;
