@@ -278,6 +278,51 @@ def test_patch_kernel_with_16bit_preactivation(pkg, lib, oracle, conv_oracle, mo
         assert float((a.float() - c.float()).abs().max()) <= 2 * eps * max(1.0, float(c.float().abs().max()))
 
 
+def test_conv_routes_on_random_geometries(pkg, lib, monkeypatch):
+    """Seeded random layers (channels 16..130 -> 8..300, planes 5..36 x 5..40, kernels up to 5 x 5, strides up to 3,
+    padding up to 2, dilation up to 2, bf16 / f16, Z in 16 or 32 bits): the route chosen by shape against the
+    column-matrix route on Y, Z, gX, gW and gB, and Z against torch's fp32 convolution of the same 16-bit inputs."""
+    import random
+    rng = random.Random(7)
+    done = 0
+    for trial in range(60):
+        N = rng.randint(1, 3)
+        Cin = rng.choice([16, 17, 24, 32, 48, 64, 70, 128, 130])
+        Cout = rng.choice([8, 16, 33, 64, 65, 100, 128, 200, 300])
+        H, W = rng.randint(5, 36), rng.choice([5, 7, 8, 9, 12, 14, 16, 20, 24, 28, 31, 32, 40])
+        Kh, Kw = rng.randint(1, 5), rng.randint(1, 5)
+        st = (rng.randint(1, 3), rng.randint(1, 3)) if rng.random() < 0.4 else (1, 1)
+        kw = dict(stride=st, padding=(rng.randint(0, 2), rng.randint(0, 2)), dilation=(rng.randint(1, 2), rng.randint(1, 2)))
+        Ho, Wo = pkg.ops_conv2d.out_hw(H, W, Kh, Kw, **kw)
+        if Ho < 1 or Wo < 1:
+            continue
+        dt = rng.choice([torch.bfloat16, torch.float16])
+        act, zdt = rng.choice(["none", "relu", "tanh"]), rng.choice([dt, torch.float32])
+        g = torch.Generator(device="cuda").manual_seed(trial)
+        X = torch.randn((N, Cin, H, W), device="cuda", generator=g).to(dt)
+        Wt = (torch.randn((Cout, Cin, Kh, Kw), device="cuda", generator=g) / (Cin * Kh * Kw) ** 0.5).to(dt)
+        b = torch.randn(Cout, device="cuda", generator=g)
+        dY = torch.randn((N, Cout, Ho, Wo), device="cuda", generator=g).to(dt)
+        res = {}
+        for route in ("auto", "explicit"):
+            if route == "auto":
+                monkeypatch.delenv("GE2B_CONV", raising=False)
+            else:
+                monkeypatch.setenv("GE2B_CONV", route)
+            Y, Z = pkg.ops_conv2d.forward(X, Wt, b, with_bias=True, act=act, save_z=True, z_dtype=zdt, **kw)
+            out = pkg.ops_conv2d.backward(X, Wt, dY, Z, with_bias=True, act=act, want_gB=True, **kw)
+            torch.cuda.synchronize()
+            res[route] = [t.float() for t in (Y, Z, out["gX"], out["gW"], out["gB"])]
+        geom = (trial, N, Cin, H, W, Cout, Kh, Kw, kw, str(dt), act, str(zdt))
+        for name, a, c in zip(("Y", "Z", "gX", "gW", "gB"), res["auto"], res["explicit"]):
+            assert float((a - c).abs().max()) <= 3e-2 * max(1.0, float(c.abs().max())), (name, geom)
+        ref = torch.nn.functional.conv2d(X.float(), Wt.float(), b, **kw)
+        assert float((res["auto"][1] - ref).abs().max()) <= 2e-2 * max(1.0, float(ref.abs().max())), geom
+        done += 1
+    assert done >= 40
+    assert lib.ge2b_device_status(1) == 0
+
+
 def test_implicit_gemm_is_the_default_route_and_moves_no_column_matrix(pkg, lib, monkeypatch):
     """On a ResNet-sized layer the default forward is the weight re-layout plus ONE convolution launch (the
     column-matrix route allocates and fills K x N x HWo elements first)."""
